@@ -1,0 +1,110 @@
+// Embedding gather, RMSNorm and SwiGLU.
+//
+// Formulas (reference, computerex/dlgo):
+//   embedding  x = E[token, :]                                models/llm/forward.go:132
+//   RMSNorm    ss = sum x^2 (fp32); s = 1/sqrt(ss/n + eps) with the square root and
+//              the reciprocal in double, cast to fp32; out = x*s*w   ops/norm.go:10-32
+//   SwiGLU     out = g / (1 + exp(-g)) * u                    ops/activation.go:8-38
+// The residual stream is fp32 in both precisions; T is the element type of the
+// activations handed to the next contraction (float or bfloat16).
+#include "common.cuh"
+
+namespace dlgo {
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int d, int vocab) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const TW* row = table + (size_t)(ok ? tok : 0) * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  `rows` (optional) picks the input row of each
+// output row, so the final norm runs on the wanted positions only.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float mean = ss / (float)d + eps;
+  const float s = (float)(1.0 / sqrt((double)mean));
+  TO* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(xr[i] * s * w[i]);
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// in: [T, 2F] with the gate in columns [0, F) and the up projection in [F, 2F).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int F, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  size_t t = i / F;
+  int c = (int)(i - t * F);
+  float g = to_float(in[t * 2 * F + c]);
+  float u = to_float(in[t * 2 * F + F + c]);
+  float h = g / (1.0f + expf(-g)) * u;
+  out[i] = from_float<T>(h);
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+// tokens[T] int32, table[vocab, d] (f32 or bf16), out[T, d] f32
+DLGO_EXPORT int dlgo_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int d,
+                           int vocab, cudaStream_t stream) {
+  if (T <= 0) return DLGO_OK;
+  if (d <= 0 || vocab <= 0) return DLGO_ERR_SIZE;
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == DLGO_F32)
+    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab);
+  else if (table_dtype == DLGO_BF16)
+    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, d, vocab);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}
+
+// x[*, d] f32, w[d] f32, out[R, d] (f32 or bf16); rows[R] int32 or null (then row r of x)
+DLGO_EXPORT int dlgo_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int R,
+                             int d, float eps, cudaStream_t stream) {
+  if (R <= 0) return DLGO_OK;
+  if (d <= 0) return DLGO_ERR_SIZE;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  if (out_dtype == DLGO_F32)
+    rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, w, (float*)out, rows, d, eps);
+  else if (out_dtype == DLGO_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, d, eps);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}
+
+// in[T, 2F], out[T, F], same element type
+DLGO_EXPORT int dlgo_swiglu(const void* in, void* out, int dtype, int T, int F, cudaStream_t stream) {
+  if (T <= 0) return DLGO_OK;
+  if (F <= 0) return DLGO_ERR_SIZE;
+  const size_t total = (size_t)T * F;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  if (dtype == DLGO_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)in, (float*)out, F, total);
+  else if (dtype == DLGO_BF16)
+    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, F,
+                                                                 total);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}

@@ -1,0 +1,243 @@
+"""Python face of the CUDA entry points: tensors in, checked, launched on the
+current stream.  Nothing here computes; a missing or failing library raises."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_STATUS = {
+    -1: "a size this kernel does not take",
+    -2: "a pointer or stride that breaks an alignment rule",
+    -3: "an element type this kernel does not take",
+    -4: "a CUDA driver entry point could not be found",
+    -5: "the kernel gave up a bounded wait on the device",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: refused ({_STATUS.get(status, status)})")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, dt: Optional[torch.dtype], name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on the GPU (there is no CPU path)")
+    if dt is not None and t.dtype != dt:
+        raise KernelError(f"{name} must be {dt}, is {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    return build.load_library(name)
+
+
+_i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = table[tokens[t], :] as fp32."""
+    _need(tokens, torch.int32, "tokens")
+    _need(table, None, "table")
+    T, (V, d) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+    _need(out, torch.float32, "out")
+    st = _lib("elementwise").dlgo_embed(_ptr(tokens), _ptr(table), _i(dtype_code(table.dtype)), _ptr(out), _i(T), _i(d),
+                                        _i(V), _stream())
+    _check(st, "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-wise RMSNorm of fp32 ``x``; with ``rows`` only those rows, in that order."""
+    _need(x, torch.float32, "x")
+    _need(w, torch.float32, "w")
+    d = x.shape[-1]
+    if w.numel() != d:
+        raise KernelError(f"rmsnorm: weight has {w.numel()} elements, rows have {d}")
+    R = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if out is None:
+        out = torch.empty((R, d), dtype=out_dtype, device=x.device)
+    _need(out, out_dtype, "out")
+    st = _lib("elementwise").dlgo_rmsnorm(_ptr(x), _ptr(w), _ptr(out), _i(dtype_code(out_dtype)), _ptr(rows), _i(R),
+                                          _i(d), _f(eps), _stream())
+    _check(st, "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, 2F] (gate | up) -> [T, F]."""
+    _need(gate_up, None, "gate_up")
+    T, F2 = gate_up.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty((T, F), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, gate_up.dtype, "out")
+    st = _lib("elementwise").dlgo_swiglu(_ptr(gate_up), _ptr(out), _i(dtype_code(gate_up.dtype)), _i(T), _i(F),
+                                         _stream())
+    _check(st, "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------------ GEMM
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32 = 0, 1, 2
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[M, K] . w[N, K]^T on the fp32 pipes; epilogue stores (x's type or fp32) or adds into fp32 ``out``."""
+    _need(w, x.dtype, "w")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("gemm: x must be 2-D with unit inner stride")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm: x has K={K}, w has K={K2}")
+    if out is None:
+        if epilogue == EPI_ADD_F32:
+            raise KernelError("gemm: the add epilogue needs the tensor to add into")
+        out = torch.empty((M, N), dtype=x.dtype if epilogue == EPI_STORE else torch.float32, device=x.device)
+    if out.dim() != 2 or out.stride(1) != 1 or out.shape != (M, N):
+        raise KernelError(f"gemm: out must be [{M}, {N}] with unit inner stride")
+    want = x.dtype if epilogue == EPI_STORE else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm: out must be {want}")
+    st = _lib("gemm_simt").dlgo_gemm_simt(_ptr(x), _ptr(w), _ptr(out), _i(dtype_code(x.dtype)), _i(M), _i(N), _i(K),
+                                          _i(x.stride(0)), _i(w.stride(0)), _i(out.stride(0)), _i(epilogue), _stream())
+    _check(st, "gemm_simt")
+    return out
+
+
+# --------------------------------------------------------------- rope + append
+def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos: torch.Tensor,
+                token_seq: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
+                kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                rotary_dim: int, interleaved: bool, write_cache: bool = True) -> None:
+    """Rotate q (in place) and k, and store k and v at their positions' pages."""
+    _need(qkv, None, "qkv")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    _need(kpages, qkv.dtype, "kpages")
+    _need(vpages, qkv.dtype, "vpages")
+    T = qkv.shape[0]
+    page_size = kpages.shape[-2]
+    st = _lib("rope_append").dlgo_rope_append(
+        _ptr(qkv), _i(dtype_code(qkv.dtype)), _i(T), _i(qkv.stride(0)), _ptr(cos), _ptr(sin), _ptr(token_pos),
+        _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages), _ptr(vpages),
+        _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim), _i(page_size), _i(1 if interleaved else 0),
+        _i(1 if write_cache else 0), _stream())
+    _check(st, "rope_append")
+
+
+# ------------------------------------------------------------------- attention
+ATT_ROW_ELEMS = 128 * 32  # rows of a block times head_dim may not exceed this
+
+
+def attention_tile_shape(head_dim: int, group: int, decode: bool) -> tuple[int, int]:
+    """(tokens per tile, query heads of a kv head per block) that the kernel takes."""
+    rows = max(1, ATT_ROW_ELEMS // head_dim)
+    rows = min(rows, 32)
+    gchunk = min(group, rows)
+    qt = 1 if decode else max(1, min(8, rows // gchunk))
+    return qt, gchunk
+
+
+def attention_scratch_floats(T: int, num_heads: int, head_dim: int, n_splits: int) -> int:
+    return 0 if n_splits <= 1 else T * num_heads * n_splits * (head_dim + 2)
+
+
+def attention(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor, vpages: torch.Tensor,
+              page_table: torch.Tensor, tiles: torch.Tensor, tile_tokens_max: int, seq_slot: torch.Tensor,
+              token_pos: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+              scale: float, window: int = 0, n_splits: int = 1, gchunk: int = 1,
+              scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal grouped-query attention of T packed tokens over the paged cache."""
+    _need(out, q.dtype, "out")
+    _need(kpages, q.dtype, "kpages")
+    _need(vpages, q.dtype, "vpages")
+    for n, t in (("page_table", page_table), ("tiles", tiles), ("seq_slot", seq_slot), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    if n_splits > 1:
+        need = attention_scratch_floats(T, num_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention: {n_splits} slices need {need} floats of scratch")
+    st = _lib("attention").dlgo_attention(
+        _ptr(q), _i(dtype_code(q.dtype)), _i(T), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table),
+        _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _i(tile_tokens_max), _ptr(seq_slot),
+        _ptr(token_pos), _ptr(out), _i(out.stride(0)), _ptr(scratch), _i(num_heads), _i(num_kv_heads), _i(head_dim),
+        _i(kpages.shape[-2]), _i(n_splits), _i(gchunk), _i(window), _f(scale), _stream())
+    _check(st, "attention")
+    return out
+
+
+# -------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, torch.float32, "logits")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _need(out, torch.int32, "out")
+    st = _lib("sampling").dlgo_argmax(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(out), _stream())
+    _check(st, "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tensor, draw: torch.Tensor, seed: int,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, torch.float32, "logits")
+    _need(temperature, torch.float32, "temperature")
+    _need(request, torch.int32, "request")
+    _need(draw, torch.int32, "draw")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    st = _lib("sampling").dlgo_sample(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(temperature),
+                                      _ptr(request), _ptr(draw), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(out),
+                                      _stream())
+    _check(st, "sample")
+    return out
+
+
+def uniform(seed: int, draw: torch.Tensor, request: torch.Tensor) -> torch.Tensor:
+    _need(draw, torch.int32, "draw")
+    _need(request, torch.int32, "request")
+    out = torch.empty((draw.numel(),), dtype=torch.float32, device=draw.device)
+    st = _lib("sampling").dlgo_uniform(ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(draw), _ptr(request), _ptr(out),
+                                       _i(draw.numel()), _stream())
+    _check(st, "uniform")
+    return out

@@ -1,0 +1,99 @@
+// Rotary position encoding of the query and key heads and the append of this
+// step's keys and values to the paged cache, in one pass over the fused
+// projection output.
+//
+// Reference: rotation of every Q and K head at the token's absolute position
+// from precomputed cos/sin tables (models/llm/forward.go:246-252,
+// models/llm/workers.go:182-215; pairings ops/rope.go:21-31), then
+// `Store(pos, k, v)` (models/llm/forward.go:257, memory/kvcache.go:30-36).
+// Only the first `rot` dims of a head are rotated, the rest pass through
+// (workers.go:151-159).  The rotation is computed in fp32.
+//
+// qkv[T, ld]: q heads, then k heads, then v heads, `hd` elements each.  q is
+// rotated in place; k (rotated) and v go to the page of their position:
+// pages[page_table[slot][pos / PS]][kv_head][pos % PS][:].
+#include "common.cuh"
+
+namespace dlgo {
+
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                                   const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
+                                   T* __restrict__ vpages, int Hq, int Hkv, int hd, int rot, int page_size,
+                                   int interleaved, int write_cache) {
+  const int t = blockIdx.x;
+  const int half = hd / 2, rhalf = rot / 2;
+  const int items = (Hq + 2 * Hkv) * half;
+  const int pos = token_pos[t];
+  T* row = qkv + (size_t)t * ld;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (write_cache) {
+    const int slot = seq_slot[token_seq[t]];
+    const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+    const size_t base = ((size_t)page * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+    kdst = kpages + base;
+    vdst = vpages + base;
+  }
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    const int head = it / half, i = it - head * half;
+    T* h = row + (size_t)head * hd;
+    int i0, i1;
+    bool rotate = i < rhalf;
+    if (rotate) {
+      if (interleaved) { i0 = 2 * i; i1 = 2 * i + 1; }
+      else { i0 = i; i1 = i + rhalf; }
+    } else {
+      i0 = rot + 2 * (i - rhalf);
+      i1 = i0 + 1;
+    }
+    float x0 = to_float(h[i0]), x1 = to_float(h[i1]);
+    if (head < Hq + Hkv && rotate) {
+      const float c = cos_t[(size_t)pos * rhalf + i], s = sin_t[(size_t)pos * rhalf + i];
+      const float y0 = x0 * c - x1 * s;
+      const float y1 = x0 * s + x1 * c;
+      x0 = y0;
+      x1 = y1;
+    }
+    if (head < Hq) {
+      h[i0] = from_float<T>(x0);
+      h[i1] = from_float<T>(x1);
+    } else if (write_cache) {
+      const bool is_k = head < Hq + Hkv;
+      const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+      T* dst = (is_k ? kdst : vdst) + (size_t)kvh * page_size * hd;
+      dst[i0] = from_float<T>(x0);
+      dst[i1] = from_float<T>(x1);
+    }
+  }
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const float* cos_t, const float* sin_t,
+                                 const int* token_pos, const int* token_seq, const int* seq_slot,
+                                 const int* page_table, int max_pages, void* kpages, void* vpages, int Hq, int Hkv,
+                                 int hd, int rot, int page_size, int interleaved, int write_cache,
+                                 cudaStream_t stream) {
+  if (T <= 0) return DLGO_OK;
+  if (hd <= 0 || hd % 2 || rot < 0 || rot > hd || rot % 2 || Hq <= 0 || Hkv <= 0 || page_size <= 0 ||
+      ld < (Hq + 2 * Hkv) * hd)
+    return DLGO_ERR_SIZE;
+  const int items = (Hq + 2 * Hkv) * (hd / 2);
+  const int threads = items >= 1024 ? 256 : 128;
+  if (dtype == DLGO_F32)
+    rope_append_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot,
+                                                         page_table, max_pages, (float*)kpages, (float*)vpages, Hq,
+                                                         Hkv, hd, rot, page_size, interleaved, write_cache);
+  else if (dtype == DLGO_BF16)
+    rope_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+        (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved, write_cache);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}

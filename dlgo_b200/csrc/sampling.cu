@@ -1,0 +1,167 @@
+// Greedy and temperature sampling on the device: only token ids go to the host.
+//
+// Reference (ops/sampling.go, ops/ops.go):
+//   greedy       first index of the maximum, strict '>'            ops/ops.go:272-285
+//   temperature  logits * (1/T), softmax, then the first index whose running
+//                sum of probabilities reaches a uniform draw r in [0, 1);
+//                the last index if none does           ops/sampling.go:72-80,167-181
+// Filters that set logits to -inf beforehand (top-k, top-p, min-p) are honoured:
+// a -inf logit has probability 0.
+//
+// The reference draws r from one generator per request, seeded by the caller
+// (models/llm/generate.go:92-95).  Here r = philox4x32-10(key = seed,
+// counter = (draw index, request index)), so a request's draws do not depend on
+// which other requests share its batch.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dlgo {
+
+__device__ __forceinline__ void philox_round(uint32_t& c0, uint32_t& c1, uint32_t& c2, uint32_t& c3, uint32_t k0,
+                                             uint32_t k1) {
+  const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+  const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+  const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+  c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+}
+
+// uniform in [0, 1) with 24 bits
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t draw, uint32_t request) {
+  uint32_t c0 = draw, c1 = request, c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    philox_round(c0, c1, c2, c3, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return (float)(c0 >> 8) * (1.0f / 16777216.0f);
+}
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    // a strided scan visits indices in rising order, so strict '>' keeps the first maximum
+    if (v > best || besti == 0x7fffffff) { best = v; besti = i; }
+  }
+  // reduce (value, index): larger value wins, ties go to the smaller index
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { bv[warp] = best; bi[warp] = besti; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < nw; ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < besti)) { best = bv[w]; besti = bi[w]; }
+    out[blockIdx.x] = besti == 0x7fffffff ? 0 : besti;
+  }
+}
+
+// One block per row.  Each thread owns a contiguous chunk of the vocabulary, so
+// "first index whose running sum reaches r" keeps its meaning.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ request, const int* __restrict__ draw, uint64_t seed, int* __restrict__ out) {
+  __shared__ float scratch[32];
+  __shared__ float csum[SAMPLE_THREADS];
+  __shared__ int chosen;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const float inv_t = 1.0f / temperature[r];
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int b = threadIdx.x * chunk, e = min(V, b + chunk);
+  float mx = -INFINITY;
+  for (int i = b; i < e; ++i) mx = fmaxf(mx, row[i] * inv_t);
+  mx = block_max(mx, scratch);
+  float s = 0.f;
+  for (int i = b; i < e; ++i) {
+    const float v = row[i] * inv_t;
+    s += (v == -INFINITY) ? 0.f : expf(v - mx);
+  }
+  csum[threadIdx.x] = s;
+  if (threadIdx.x == 0) chosen = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int i = 0; i < (int)blockDim.x; ++i) total += csum[i];
+    const float u = philox_uniform(seed, (uint32_t)draw[r], (uint32_t)request[r]);
+    const float target = u * total;
+    float run = 0.f;
+    int owner = -1;
+    for (int i = 0; i < (int)blockDim.x; ++i) {
+      if (run + csum[i] >= target && csum[i] > 0.f) { owner = i; break; }
+      run += csum[i];
+    }
+    if (owner < 0) {
+      // rounding left the target above the total: the last index with weight
+      for (int i = (int)blockDim.x - 1; i >= 0; --i)
+        if (csum[i] > 0.f) { owner = i; break; }
+      scratch[0] = -1.f;  // sentinel: take the chunk's last weighted index
+    } else {
+      scratch[0] = target - run;
+    }
+    chosen = owner;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x == chosen) {
+    const float rest = scratch[0];
+    float run = 0.f;
+    int pick = -1, last = b;
+    for (int i = b; i < e; ++i) {
+      const float v = row[i] * inv_t;
+      const float pr = (v == -INFINITY) ? 0.f : expf(v - mx);
+      if (pr > 0.f) last = i;
+      run += pr;
+      if (rest >= 0.f && pr > 0.f && run >= rest) { pick = i; break; }
+    }
+    out[r] = pick >= 0 ? pick : last;
+  }
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+// logits[R, V] f32 (row stride ld) -> out[R] int32
+DLGO_EXPORT int dlgo_argmax(const float* logits, int R, int ld, int V, int* out, cudaStream_t stream) {
+  if (R <= 0) return DLGO_OK;
+  if (V <= 0 || ld < V) return DLGO_ERR_SIZE;
+  const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
+  argmax_kernel<<<R, threads, 0, stream>>>(logits, ld, V, out);
+  return launch_status();
+}
+
+// temperature[R] f32 (> 0), request[R] and draw[R] int32 key the uniform of each row
+DLGO_EXPORT int dlgo_sample(const float* logits, int R, int ld, int V, const float* temperature, const int* request,
+                            const int* draw, unsigned long long seed, int* out, cudaStream_t stream) {
+  if (R <= 0) return DLGO_OK;
+  if (V <= 0 || ld < V) return DLGO_ERR_SIZE;
+  const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
+  sample_kernel<<<R, threads, 0, stream>>>(logits, ld, V, temperature, request, draw, (uint64_t)seed, out);
+  return launch_status();
+}
+
+// the uniform a (seed, draw, request) triple yields, for tests and host-side twins
+__global__ void uniform_kernel(uint64_t seed, const int* draw, const int* request, float* out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = philox_uniform(seed, (uint32_t)draw[i], (uint32_t)request[i]);
+}
+DLGO_EXPORT int dlgo_uniform(unsigned long long seed, const int* draw, const int* request, float* out, int n,
+                             cudaStream_t stream) {
+  if (n <= 0) return DLGO_OK;
+  uniform_kernel<<<(n + 255) / 256, 256, 0, stream>>>((uint64_t)seed, draw, request, out, n);
+  return launch_status();
+}

@@ -1,0 +1,155 @@
+"""The engine: one model, one cache, one step function.
+
+``step`` is the only way tokens reach the model.  It takes a batch of
+sequences, each with its next tokens (a whole prompt, or one token, or anything
+between), runs exactly those tokens as one packed batch against the cache, and
+returns fp32 logits at the wanted places.  The reference has two functions for
+its single sequence, ``Forward(token, pos)`` (models/llm/forward.go:123) and
+``ForwardBatch(tokens, startPos)`` (models/llm/forward_batch.go:78); both are
+this step with a batch of one.
+
+Nothing is padded: sequences of unequal length are packed one after another, so
+there is no padding that could change a result.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.kv_cache import KVCache, PAGE_SIZE
+from ..config.registry import load_config
+from ..weights.loader import WeightSource
+from .model import CausalLM
+from .runtime import Runtime, StepContext, build_context
+
+
+class StepError(ValueError):
+    """A step the engine refuses (bad token id, unknown slot, sequence too long)."""
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
+                 max_seq_len: Optional[int] = None, cuda_graphs: bool = True, default_batch: int = 1):
+        """``max_tokens``: positions live sequences may hold in total (each sequence's count
+        rounded up to a multiple of 64); it sizes the cache.  ``max_seq_len``: longest single
+        sequence, clamped to the model's context like the reference's ``maxSeqLen``
+        (models/llm/generate.go:56-58)."""
+        self.runtime = Runtime(device, dtype)
+        self.config = load_config(model_dir)
+        self.spec = self.config.architecture_spec()
+        self.model = CausalLM(self.spec)
+        with torch.cuda.device(self.runtime.device):
+            source = WeightSource(model_dir, self.runtime.device)
+            self.model.load_weights(source, self.runtime)
+            source.release()
+        context = self.spec.max_positions
+        if max_seq_len is None or max_seq_len <= 0 or max_seq_len > context:
+            max_seq_len = context
+        needs, borrows, states = self.model.cache_needs()
+        if max_tokens is None or max_tokens <= 0:
+            # room for `default_batch` sequences of full length, within half of the free memory
+            per_position = sum(2 * n.num_kv_heads * n.head_dim for n, b in zip(needs, borrows)
+                               if n is not None and b is None) * (2 if self.runtime.dtype == torch.bfloat16 else 4)
+            free, _ = torch.cuda.mem_get_info(self.runtime.device)
+            fits = max(PAGE_SIZE, int(free * 0.5) // max(per_position, 1))
+            max_tokens = max(min(max_seq_len * max(default_batch, 1), fits), min(max_seq_len, fits))
+        self.cache = KVCache(needs, borrows, states, max_tokens, max_seq_len, self.runtime.dtype, self.runtime.device,
+                             PAGE_SIZE)
+        self.max_seq_len = self.cache.max_seq_len
+        self.vocab_size = self.spec.vocab_size
+        self.cuda_graphs = cuda_graphs
+        self._graphs: Dict[int, "object"] = {}
+        self.launches_last_step = 0
+
+    # -------------------------------------------------------------------- slots
+    def take_slot(self) -> int:
+        return self.cache.take_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # --------------------------------------------------------------------- step
+    def _validate(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+                  want: Optional[Sequence[Sequence[int]]]) -> None:
+        if len(slots) != len(tokens):
+            raise StepError(f"{len(slots)} slots for {len(tokens)} token lists")
+        if len(set(slots)) != len(slots):
+            raise StepError("a slot appears twice in one step")
+        if want is not None and len(want) != len(tokens):
+            raise StepError(f"{len(want)} want lists for {len(tokens)} sequences")
+        V = self.vocab_size
+        for i, (s, tk) in enumerate(zip(slots, tokens)):
+            if len(tk) == 0:
+                raise StepError(f"sequence {i} (slot {s}) brings no token")
+            bad = [t for t in tk if not 0 <= int(t) < V]
+            if bad:
+                raise StepError(f"sequence {i} (slot {s}): token id {bad[0]} is outside the vocabulary [0, {V})")
+            cur = self.cache.length(s)
+            if cur + len(tk) > self.max_seq_len:
+                raise StepError(
+                    f"sequence {i} (slot {s}) would reach {cur + len(tk)} positions; the limit is {self.max_seq_len}")
+            if want is not None:
+                for w in want[i]:
+                    if not 0 <= int(w) < len(tk):
+                        raise StepError(f"sequence {i}: wanted place {w} is outside its {len(tk)} tokens")
+
+    @torch.no_grad()
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Run ``tokens[i]`` as the next tokens of the sequence in ``slots[i]``.
+
+        ``want[i]`` lists the places among ``tokens[i]`` whose logits are asked for
+        (default: the last).  Returns ``[wanted, vocab]`` fp32 on the device, in the
+        order of the sequences and of ``want``; ``None`` if nothing is wanted.
+        """
+        slots = [int(s) for s in slots]
+        self._validate(slots, tokens, want)
+        ntok = [len(t) for t in tokens]
+        starts = [self.cache.length(s) for s in slots]
+        rows: List[int] = []
+        off = 0
+        for i, n in enumerate(ntok):
+            rows.extend(off + int(w) for w in (want[i] if want is not None else [n - 1]))
+            off += n
+        with torch.cuda.device(self.runtime.device):
+            self.cache.reserve(slots, ntok)
+            decode = all(n == 1 for n in ntok)
+            if decode and self.cuda_graphs and want is None:
+                from .graphs import decode_with_graph
+                logits = decode_with_graph(self, slots, [int(t[0]) for t in tokens], starts)
+            else:
+                ctx = build_context(self.runtime, tokens, slots, starts, self.max_seq_len)
+                want_rows = (torch.tensor(rows, dtype=torch.int32).to(self.runtime.device, non_blocking=True)
+                             if rows else None)
+                logits = self.model.forward(ctx, self.cache, want_rows)
+            self.cache.commit(slots, ntok)
+        return logits
+
+    # ------------------------------------------------------------------ summary
+    def weight_bytes(self) -> int:
+        """Bytes of weights a decode step reads once (embedding table excluded unless it is the head)."""
+        seen = set()
+        total = 0
+
+        def add(t: Optional[torch.Tensor]) -> None:
+            nonlocal total
+            if t is None or t.data_ptr() in seen:
+                return
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
+
+        for blk in self.model.blocks:
+            for part in (blk.mixer, blk.ffn, blk.mixer_norm, blk.ffn_norm):
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor):
+                        add(v)
+                    elif hasattr(v, "weight") and isinstance(getattr(v, "weight"), torch.Tensor):
+                        add(v.weight)
+        add(getattr(self.model.final_norm, "weight", None))
+        proj = getattr(self.model.head, "proj", None)
+        add(getattr(proj, "weight", None))
+        return total

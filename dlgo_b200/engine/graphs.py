@@ -1,0 +1,81 @@
+"""CUDA graphs for decode steps.
+
+A decode step is a hundred-odd small launches; at one token per sequence the
+GPU work of each is a few microseconds, so the launches themselves bound the
+step.  One graph per batch size replays the whole step from persistent input
+buffers (token ids, positions, slots).  Nothing inside the graph may depend on
+the sequences' lengths through the host: grids are sized from the cache's
+capacity and every kernel reads lengths and pages from device memory.
+"""
+from __future__ import annotations
+
+from typing import Any, List, Sequence
+
+import torch
+
+from .runtime import StepContext
+
+
+class DecodeGraph:
+    def __init__(self, engine: Any, batch: int):
+        rt = engine.runtime
+        dev = rt.device
+        self.batch = batch
+        self.meta = torch.zeros((3, batch), dtype=torch.int32, device=dev)   # ids, positions, slots
+        self.host = torch.zeros((3, batch), dtype=torch.int32).pin_memory()
+        self.token_seq = torch.arange(batch, dtype=torch.int32, device=dev)
+        self.want_rows = torch.arange(batch, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            runtime=rt, n_tokens=batch, n_seqs=batch, token_ids=self.meta[0], token_pos=self.meta[1],
+            token_seq=self.token_seq, seq_slot=self.meta[2], seq_slots_host=[0] * batch, seq_start_host=[0] * batch,
+            seq_ntok_host=[1] * batch, decode=True, max_len=engine.max_seq_len, captured=True,
+            capacity=engine.max_seq_len)
+        self.ctx.tiles(1)  # built before capture: a capture may not copy from pageable host memory
+        self.graph = torch.cuda.CUDAGraph()
+        self.logits = None
+        self.engine = engine
+        self._copied = torch.cuda.Event()
+
+    def capture(self) -> None:
+        eng = self.engine
+        # Warm-up runs on a side stream (lazy initialisations must not land in the capture).
+        s = torch.cuda.Stream(device=eng.runtime.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            eng.model.forward(self.ctx, eng.cache, self.want_rows)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(self.graph):
+            self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+
+    def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
+        h = self.host
+        self._copied.synchronize()  # the previous step's copy out of the pinned buffer has finished
+        h[0] = torch.tensor(token_ids, dtype=torch.int32)
+        h[1] = torch.tensor(starts, dtype=torch.int32)
+        h[2] = torch.tensor(slots, dtype=torch.int32)
+        self.meta.copy_(h, non_blocking=True)
+        self._copied.record()
+        self.graph.replay()
+        return self.logits
+
+
+def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
+    """Logits [batch, vocab] of one decode step, through the graph of this batch size.
+
+    The returned tensor is the graph's output buffer: it is overwritten by the next
+    decode step of the same batch size.
+    """
+    b = len(slots)
+    g = engine._graphs.get(b)
+    if g is None:
+        g = DecodeGraph(engine, b)
+        # the warm-up and the capture run the step for real, on whatever the buffers
+        # hold: give them this step's inputs so they write where this step writes anyway
+        g.host[0] = torch.tensor(token_ids, dtype=torch.int32)
+        g.host[1] = torch.tensor(starts, dtype=torch.int32)
+        g.host[2] = torch.tensor(slots, dtype=torch.int32)
+        g.meta.copy_(g.host)
+        g.capture()
+        engine._graphs[b] = g
+    return g.run(slots, token_ids, starts)

@@ -1,0 +1,106 @@
+"""Grouped-query attention over the cache, with rotary positions.
+
+Reference (models/llm/forward.go:207-290): q, k, v projections in one dispatch
+(:224), rotation of every q and k head at the token's position (:246-252),
+append to the cache (:257), per head ``softmax(q.k * scale)`` over positions
+``0..pos`` and the weighted sum of values with kv head ``h / (Hq/Hkv)``
+(:258-278), output projection (:286); the caller adds the result to the
+residual (:163).  Prompts run the same steps over all their positions and read
+keys and values back from the cache (models/llm/forward_batch.go:135-210).
+
+Every constant is a parameter: head counts, head size, score scale, an optional
+window (keys t > pos - window only), the name of the position encoding to use,
+and the cache group the layer's keys and values belong to.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Mapping, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
+from .linear import ADD_F32, STORE, Linear
+from .registry import MIXERS
+
+_TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention
+
+
+class GQAAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 window: Optional[int] = None, position_encoding: Optional[str] = "rope",
+                 cache_group: str = "full"):
+        super().__init__(hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                         scale=scale, window=window, position_encoding=position_encoding, cache_group=cache_group)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads ({num_heads}) must be a multiple of num_kv_heads ({num_kv_heads})")
+        if head_dim % 16:
+            raise ValueError(f"head_dim must be a multiple of 16, got {head_dim}")
+        if window is not None and window <= 0:
+            raise ValueError(f"window must be positive or None, got {window}")
+        self.hidden_size = int(hidden_size)
+        self.num_heads = int(num_heads)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.scale = float(scale)
+        self.window = None if window is None else int(window)
+        self.position_encoding = position_encoding
+        self.cache_group = cache_group
+        self.q_dim = self.num_heads * self.head_dim
+        self.kv_dim = self.num_kv_heads * self.head_dim
+        self.wqkv: Optional[Linear] = None
+        self.wo: Optional[Linear] = None
+        self._no_rotation: Optional[torch.Tensor] = None
+
+    # --------------------------------------------------------------- declarations
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {
+            "q_proj.weight": ParamSpec((self.q_dim, self.hidden_size)),
+            "k_proj.weight": ParamSpec((self.kv_dim, self.hidden_size)),
+            "v_proj.weight": ParamSpec((self.kv_dim, self.hidden_size)),
+            "o_proj.weight": ParamSpec((self.hidden_size, self.q_dim)),
+        }
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.cache_group, self.num_kv_heads, self.head_dim, self.window)
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        # one fused projection: rows q | k | v (the reference splits a fused tensor
+        # the other way round, models/llm/loader.go:267-279)
+        parts = [runtime.compute_copy(get(n)) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        self.wqkv = Linear(torch.cat(parts, dim=0), runtime)
+        self.wo = Linear(get("o_proj.weight"), runtime)
+        self._no_rotation = torch.zeros((1, 1), dtype=torch.float32, device=runtime.device)
+
+    # -------------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+        T = ctx.n_tokens
+        qkv = self.wqkv(x, STORE)
+        if self.position_encoding is not None:
+            pe = positions[self.position_encoding]
+            cos, sin, rot, inter = pe.cos, pe.sin, pe.rotary_dim, pe.interleaved
+        else:
+            cos = sin = self._no_rotation
+            rot, inter = 0, False
+        K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                      cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes)
+        group = self.num_heads // self.num_kv_heads
+        qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
+        tiles, n_tiles, tile_max = ctx.tiles(qt)
+        n_gchunks = (group + gchunk - 1) // gchunk
+        longest = ctx.capacity if ctx.captured else ctx.max_len
+        pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
+        base_blocks = n_tiles * self.num_kv_heads * n_gchunks
+        n_splits = max(1, min(pages, -(-_TARGET_BLOCKS // base_blocks))) if ctx.decode else 1
+        scratch = None
+        if n_splits > 1:
+            scratch = ctx.scratch("attention", K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+        out = torch.empty((T, self.q_dim), dtype=qkv.dtype, device=qkv.device)
+        K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max, ctx.seq_slot,
+                    ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                    self.window or 0, n_splits, gchunk, scratch)
+        self.wo(out, ADD_F32, residual)
+
+
+MIXERS.register("gqa_attention", GQAAttention)

@@ -1,0 +1,47 @@
+"""SwiGLU feed-forward: ``y = Wd . (silu(Wg . x) * (Wu . x))``.
+
+Reference (models/llm/forward.go:293-298): gate and up projections in one
+dispatch, ``h = g / (1 + exp(-g)) * u`` (ops/activation.go:8-38), down
+projection; the caller adds the result to the residual (:169).  Dense: no
+experts, no routing.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import FeedForward, ParamSpec
+from .linear import ADD_F32, STORE, Linear
+from .registry import FEED_FORWARDS
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size)
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.w_gate_up: Optional[Linear] = None
+        self.w_down: Optional[Linear] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {
+            "gate_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
+            "up_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
+            "down_proj.weight": ParamSpec((self.hidden_size, self.intermediate_size)),
+        }
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        gate = runtime.compute_copy(get("gate_proj.weight"))
+        up = runtime.compute_copy(get("up_proj.weight"))
+        self.w_gate_up = Linear(torch.cat([gate, up], dim=0), runtime)
+        self.w_down = Linear(get("down_proj.weight"), runtime)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
+        gate_up = self.w_gate_up(x, STORE)
+        h = K.swiglu(gate_up)
+        self.w_down(h, ADD_F32, residual)
+
+
+FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -1,0 +1,33 @@
+"""A weight matrix ``[out, in]`` and its contraction ``y = x . W^T``.
+
+The reference keeps matrices row-major ``[out x in]`` and computes one dot
+product per output row (models/llm/model.go:64-80, blas/blas.go:152-196).  In
+float32 the contraction runs on the fp32 pipes; in bfloat16 on the tensor cores
+where the kernel takes the sizes, on the fp32 pipes (bfloat16 operands, fp32
+sums) where it does not.
+"""
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+
+from ..csrc import kernels as K
+
+STORE, STORE_F32, ADD_F32 = K.EPI_STORE, K.EPI_STORE_F32, K.EPI_ADD_F32
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, runtime: Any):
+        self.weight = runtime.compute_copy(weight).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        self.runtime = runtime
+        self._tc = None
+        if self.weight.dtype == torch.bfloat16:
+            from . import tensor_core
+            self._tc = tensor_core.plan_for(self.weight)
+
+    def __call__(self, x: torch.Tensor, epilogue: int = STORE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._tc is not None:
+            return self._tc(x, epilogue, out)
+        return K.gemm_simt(x, self.weight, epilogue, out)

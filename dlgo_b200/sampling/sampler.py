@@ -1,0 +1,127 @@
+"""Choosing the next token.
+
+The reference's pipeline (ops/sampling.go:32-48): greedy if the temperature is
+<= 0, else repetition penalty over the recent tokens (:53-69), temperature
+(:72-80), top-k (:83-95), top-p (:99-138), min-p (:143-165), softmax and an
+inverse-CDF draw (:167-181).  Defaults 0.7 / 40 / 0.9 / 0 / 1.1 (:19-27).
+
+Greedy and the temperature draw are CUDA kernels of this package
+(csrc/sampling.cu) and only token ids leave the device.  The filters, when
+switched on, are applied to the logits on the device beforehand; they set
+logits to -inf, which the draw treats as probability zero.
+
+The uniform number of a draw is a counter-based function of (seed, request
+index, index of the draw within the request), so what a request samples does
+not depend on which other requests share its batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..csrc import kernels as K
+
+
+@dataclass(frozen=True)
+class SamplerConfig:
+    temperature: float = 0.7
+    top_k: int = 40
+    top_p: float = 0.9
+    min_p: float = 0.0
+    repetition_penalty: float = 1.1
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0
+
+    @property
+    def filtered(self) -> bool:
+        return self.top_k > 0 or self.top_p < 1.0 or self.min_p > 0 or self.repetition_penalty > 1.0
+
+    @staticmethod
+    def greedy_config() -> "SamplerConfig":
+        return SamplerConfig(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repetition_penalty=1.0)
+
+    @staticmethod
+    def plain_temperature(t: float) -> "SamplerConfig":
+        return SamplerConfig(temperature=t, top_k=0, top_p=1.0, min_p=0.0, repetition_penalty=1.0)
+
+
+RECENT_WINDOW = 64  # tokens the repetition penalty looks back over (models/llm/generate.go:143)
+
+
+def apply_repetition_penalty(logits: torch.Tensor, recent: Sequence[Sequence[int]], penalty: float) -> None:
+    """In place: positive logits of recent tokens are divided by the penalty, negative ones multiplied."""
+    if penalty <= 1.0:
+        return
+    V = logits.shape[1]
+    for r, toks in enumerate(recent):
+        ids = sorted({int(t) for t in toks if 0 <= int(t) < V})
+        if not ids:
+            continue
+        idx = torch.tensor(ids, dtype=torch.int64, device=logits.device)
+        v = logits[r, idx]
+        logits[r, idx] = torch.where(v > 0, v / penalty, v * penalty)
+
+
+def apply_top_k(logits: torch.Tensor, k: int) -> None:
+    """In place: everything below the k-th largest value becomes -inf (ties at the cutoff stay)."""
+    if k <= 0 or k >= logits.shape[1]:
+        return
+    kth = torch.topk(logits, k, dim=1).values[:, -1:]
+    logits.masked_fill_(logits < kth, float("-inf"))
+
+
+def apply_top_p(logits: torch.Tensor, p: float) -> None:
+    """In place: keep the shortest prefix of the descending-probability order whose sum reaches p."""
+    if p >= 1.0:
+        return
+    probs = torch.softmax(logits, dim=1)
+    sp, order = torch.sort(probs, dim=1, descending=True, stable=True)
+    cum = torch.cumsum(sp, dim=1)
+    # position i is kept if the sum BEFORE it is still below p
+    keep_sorted = (cum - sp) < p
+    keep_sorted[:, 0] = True
+    keep = torch.zeros_like(keep_sorted)
+    keep.scatter_(1, order, keep_sorted)
+    logits.masked_fill_(~keep, float("-inf"))
+
+
+def apply_min_p(logits: torch.Tensor, min_p: float) -> None:
+    """In place: drop tokens whose probability is below min_p times the largest."""
+    if min_p <= 0:
+        return
+    probs = torch.softmax(logits, dim=1)
+    thr = probs.max(dim=1, keepdim=True).values * min_p
+    logits.masked_fill_(probs < thr, float("-inf"))
+
+
+class DeviceSampler:
+    """Samples one token per row of a logits tensor, on the device."""
+
+    def __init__(self, seed: int = 0):
+        self.seed = int(seed)
+
+    def sample(self, logits: torch.Tensor, cfg: SamplerConfig, requests: Sequence[int], draws: Sequence[int],
+               recent: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """``logits`` [rows, vocab] fp32 on the device -> int32 [rows] on the device."""
+        if cfg.greedy:
+            return K.argmax(logits)
+        dev = logits.device
+        rows = logits.shape[0]
+        meta = torch.tensor([list(requests), list(draws)], dtype=torch.int32).to(dev, non_blocking=True)
+        if cfg.filtered:
+            work = logits * (1.0 / cfg.temperature) if cfg.temperature != 1.0 else logits.clone()
+            # the reference applies the penalty before the temperature; both orders give
+            # the same result because the penalty is a scaling of each logit
+            if recent is not None:
+                apply_repetition_penalty(work, recent, cfg.repetition_penalty)
+            apply_top_k(work, cfg.top_k)
+            apply_top_p(work, cfg.top_p)
+            apply_min_p(work, cfg.min_p)
+            temp = torch.ones((rows,), dtype=torch.float32, device=dev)
+            return K.sample(work, temp, meta[0], meta[1], self.seed)
+        temp = torch.full((rows,), float(cfg.temperature), dtype=torch.float32, device=dev)
+        return K.sample(logits, temp, meta[0], meta[1], self.seed)
