@@ -14,6 +14,7 @@ the start of a request (models/llm/generate.go:97-100).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -98,6 +99,9 @@ class KVCache:
                 self._entry_place[e] = (name, j)
         self._borrows = list(borrows)
         self.state = StateArea(state_needs, self.n_slots, device)
+        self.poison_freed = bool(os.environ.get("DLGO_CACHE_POISON"))  # debug switch: unwritten cache reads as NaN
+        if self.poison_freed:
+            self.poison()
 
     # ------------------------------------------------------------------ views
     def view(self, entry: int) -> Optional[CacheView]:
@@ -119,9 +123,13 @@ class KVCache:
         return slot
 
     def free_slot(self, slot: int) -> None:
-        self.book.free_slot(slot)
+        released = self.book.free_slot(slot)
         for pt in self.page_tables.values():
             pt[slot].fill_(-1)
+        if self.poison_freed:
+            for g, pages in released.items():
+                if pages:
+                    self.storage[g][:, :, torch.tensor(pages, device=self.device)] = float("nan")
 
     def length(self, slot: int) -> int:
         return self.book.length(slot)
@@ -146,6 +154,7 @@ class KVCache:
 
     def poison(self, value: float = float("nan")) -> None:
         """Fill every page with ``value`` (tests: nothing unwritten may reach a result)."""
+        self.poison_freed = True
         for st in self.storage.values():
             st.fill_(value)
 

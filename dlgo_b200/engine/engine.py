@@ -13,13 +13,13 @@ there is no padding that could change a result.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..cache.kv_cache import KVCache, PAGE_SIZE
 from ..config.registry import load_config
-from ..weights.loader import WeightSource
+from ..weights.loader import DictSource, WeightSource
 from .model import CausalLM
 from .runtime import Runtime, StepContext, build_context
 
@@ -29,18 +29,31 @@ class StepError(ValueError):
 
 
 class Engine:
-    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
-                 max_seq_len: Optional[int] = None, cuda_graphs: bool = True, default_batch: int = 1):
+    def __init__(self, model_dir: Optional[str] = None, dtype="bfloat16", device="cuda:0",
+                 max_tokens: Optional[int] = None, max_seq_len: Optional[int] = None, cuda_graphs: bool = True,
+                 default_batch: int = 1, spec: Any = None, tensors: Optional[Dict[str, torch.Tensor]] = None):
         """``max_tokens``: positions live sequences may hold in total (each sequence's count
         rounded up to a multiple of 64); it sizes the cache.  ``max_seq_len``: longest single
         sequence, clamped to the model's context like the reference's ``maxSeqLen``
-        (models/llm/generate.go:56-58)."""
+        (models/llm/generate.go:56-58).
+
+        A model comes from ``model_dir`` (config.json chooses the architecture), or from an
+        :class:`ArchitectureSpec` and its tensors given in memory (``spec``, ``tensors``)."""
         self.runtime = Runtime(device, dtype)
-        self.config = load_config(model_dir)
-        self.spec = self.config.architecture_spec()
+        if spec is None:
+            if model_dir is None:
+                raise ValueError("give a model folder, or a spec with its tensors")
+            self.config = load_config(model_dir)
+            self.spec = self.config.architecture_spec()
+        else:
+            self.config = None
+            self.spec = spec
         self.model = CausalLM(self.spec)
         with torch.cuda.device(self.runtime.device):
-            source = WeightSource(model_dir, self.runtime.device)
+            if tensors is not None:
+                source = DictSource(tensors, self.runtime.device)
+            else:
+                source = WeightSource(model_dir, self.runtime.device)
             self.model.load_weights(source, self.runtime)
             source.release()
         context = self.spec.max_positions
@@ -118,7 +131,8 @@ class Engine:
         with torch.cuda.device(self.runtime.device):
             self.cache.reserve(slots, ntok)
             decode = all(n == 1 for n in ntok)
-            if decode and self.cuda_graphs and want is None:
+            last_only = want is None or all(list(w) == [0] for w in want)
+            if decode and self.cuda_graphs and last_only:
                 from .graphs import decode_with_graph
                 logits = decode_with_graph(self, slots, [int(t[0]) for t in tokens], starts)
             else:

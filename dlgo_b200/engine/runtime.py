@@ -39,19 +39,21 @@ class Runtime:
                 f"the engine runs on a CUDA device only (asked for {self.device}); there is no CPU path")
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device is available; the engine has no CPU path")
-        self._compute_copies: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
+        self._compute_copies: Dict[Tuple[int, torch.dtype], Tuple[torch.Tensor, torch.Tensor]] = {}
 
     def compute_copy(self, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``t`` in the compute precision; tensors that share storage (tied weights) share the copy."""
         dtype = dtype or self.dtype
         if t.dtype == dtype:
             return t
+        # the source is kept alive beside its copy, so its address cannot be handed to another
+        # tensor while the entry exists
         key = (t.data_ptr(), dtype)
-        c = self._compute_copies.get(key)
-        if c is None or c.shape != t.shape:
-            c = t.to(dtype)
-            self._compute_copies[key] = c
-        return c
+        hit = self._compute_copies.get(key)
+        if hit is None or hit[0].shape != t.shape:
+            hit = (t, t.to(dtype))
+            self._compute_copies[key] = hit
+        return hit[1]
 
     def forget_copies(self) -> None:
         self._compute_copies.clear()

@@ -94,3 +94,24 @@ class WeightSource:
         """Drop the by-name references (parts keep what they use)."""
         self._cache.clear()
         self.checkpoint.close()
+
+
+class DictSource:
+    """Tensors given in memory (name -> tensor), with the interface of :class:`WeightSource`."""
+
+    def __init__(self, tensors: Mapping[str, torch.Tensor], device: torch.device):
+        self.tensors = dict(tensors)
+        self.device = device
+        self._cache: Dict[str, torch.Tensor] = {}
+
+    def found(self) -> Dict[str, Tuple[Tuple[int, ...], torch.dtype]]:
+        return {n: (tuple(t.shape), t.dtype) for n, t in self.tensors.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        t = self._cache.get(name)
+        if t is None:
+            t = self._cache[name] = stored_precision(self.tensors[name].to(self.device))
+        return t
+
+    def release(self) -> None:
+        self._cache.clear()

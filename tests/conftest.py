@@ -23,4 +23,8 @@ def model_dirs(tmp_path_factory):
     """Model folders of the tiny configurations, written once per session into a temporary folder."""
     from tiny_configs import TINY, write_tiny
     root = tmp_path_factory.mktemp("models")
-    return {name: write_tiny(name, str(root / name)) for name in TINY}
+    dirs = {name: write_tiny(name, str(root / name)) for name in TINY}
+    # queries and keys x8: scores spread over several units instead of hundredths, so attention is far
+    # from uniform and a wrong or missing key moves the logits
+    dirs["Bsharp"] = write_tiny("B", str(root / "Bsharp"), sharpen=8.0)
+    return dirs

@@ -84,14 +84,13 @@ def rope(vec: torch.Tensor, pos: int, freqs: List[float]) -> torch.Tensor:
     cast to the working precision (models/llm/workers.go:160-169); pairs (i, i + half) -> (x0 c - x1 s,
     x0 s + x1 c) (ops/rope.go:21-25, models/llm/workers.go:196-204)."""
     half = len(freqs)
+    ang = torch.tensor([float(pos) * f for f in freqs], dtype=torch.float64)
+    c = torch.cos(ang).to(torch.float32).to(vec.dtype)
+    s = torch.sin(ang).to(torch.float32).to(vec.dtype)
+    x0, x1 = vec[:half], vec[half:2 * half]
     out = vec.clone()
-    for i in range(half):
-        ang = float(pos) * freqs[i]
-        c = torch.tensor(math.cos(ang), dtype=torch.float32).to(vec.dtype)
-        s = torch.tensor(math.sin(ang), dtype=torch.float32).to(vec.dtype)
-        x0, x1 = vec[i], vec[i + half]
-        out[i] = x0 * c - x1 * s
-        out[i + half] = x0 * s + x1 * c
+    out[:half] = x0 * c - x1 * s
+    out[half:2 * half] = x0 * s + x1 * c
     return out
 
 

@@ -1,0 +1,202 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every way of
+cutting the work: whole requests, last tokens one by one, unequal batches with slot reuse, long
+decoding, first tokens, and generation through the entry point.  Needs a GPU."""
+import os
+
+import pytest
+import torch
+
+import plain_llama as P
+import traces as T
+from tiny_configs import TINY, assert_close, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+# request lengths: page edges (64, 65, 128, 129), a single token, lengths across original_max_position (64)
+LENGTHS = {"A": [5, 17, 32, 64, 100], "B": [1, 9, 70, 130, 200], "C": [3, 65, 129, 300, 64], "Bsharp": [2, 40, 128, 250]}
+_engines = {}
+
+
+def vocab_of(name):
+    return TINY[name.replace("sharp", "")]["cfg"]["vocab_size"]
+
+
+def requests_of(name):
+    return {f"{name}{i}": random_tokens(n, vocab_of(name), 100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+def engine_for(model_dirs, name, dtype, graphs=True, max_tokens=1536):
+    from dlgo_b200.engine.engine import Engine
+    key = (name, dtype, graphs, max_tokens)
+    if key not in _engines:
+        e = Engine(model_dirs[name], dtype=dtype, max_tokens=max_tokens, cuda_graphs=graphs)
+        e.cache.poison()      # whatever was never written, or was given back, reads as NaN
+        _engines[key] = e
+    return _engines[key]
+
+
+def check(name, model_dirs, dtype, steps, outs, reqs, what):
+    got = T.collect(steps, outs, reqs)
+    for rid, toks in reqs.items():
+        assert_close(got[rid], plain_logits(model_dirs[name], toks), dtype, f"{what} {rid} ({len(toks)} tokens, {dtype})")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C", "Bsharp"])
+def test_each_request_alone_and_whole(model_dirs, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    reqs = requests_of(name)
+    steps = T.whole(reqs)
+    check(name, model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, "whole")
+    eng.cache.book.check()
+    assert eng.cache.book.live_slots() == []
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C", "Bsharp"])
+def test_last_32_tokens_one_by_one(model_dirs, name, dtype, graphs):
+    eng = engine_for(model_dirs, name, dtype, graphs)
+    reqs = requests_of(name)
+    steps = T.tail_one_by_one(reqs, 32)
+    check(name, model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, "tail")
+    assert eng.cache.book.live_slots() == []
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C", "Bsharp"])
+def test_unequal_batches_one_after_another(model_dirs, name, dtype, graphs):
+    # a cache just large enough for one batch at a time: the second batch runs in the first one's pages
+    reqs = requests_of(name)
+    lens = sorted((len(t) for t in reqs.values()), reverse=True)
+    need = sum((n + 63) // 64 * 64 for n in lens[:3])
+    eng = engine_for(model_dirs, name, dtype, graphs, max_tokens=max(need, 64 * ((max(lens) + 63) // 64)) + 64)
+    for rep, decode in enumerate([(32, 5, 17, 1, 40), (3, 33, 0, 12, 7)]):
+        steps = T.batched(reqs, 3, decode)
+        check(name, model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, f"batched#{rep}")
+        eng.cache.book.check()
+        assert eng.cache.book.live_slots() == []
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_composition_changes_nothing_in_float32_beyond_rounding(model_dirs, dtype):
+    # the same request alone and inside two different batches
+    eng = engine_for(model_dirs, "B", dtype)
+    reqs = requests_of("B")
+    alone = T.collect(T.whole(reqs), T.run_in_process(eng, T.whole(reqs)), reqs)
+    st = T.batched(reqs, 5, (1, 1, 1, 1, 1))
+    together = T.collect(st, T.run_in_process(eng, st), reqs)
+    tol = 2e-6 if dtype == "float32" else 2e-2
+    for rid in reqs:
+        scale = float(alone[rid].abs().max())
+        assert float((alone[rid] - together[rid]).abs().max()) <= tol * scale, rid
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_dirs, dtype):
+    # 4 prompt tokens, then 500 tokens one by one, across seven page edges, through the graph
+    eng = engine_for(model_dirs, "C", dtype)
+    reqs = {"long": random_tokens(504, vocab_of("C"), 9)}
+    steps = T.tail_one_by_one(reqs, 500)
+    check("C", model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, "long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    # every token from the very first one by one: position 0, the first decoded token, the second
+    eng = engine_for(model_dirs, name, dtype)
+    reqs = {"f1": random_tokens(1, vocab_of(name), 1), "f2": random_tokens(2, vocab_of(name), 2),
+            "f6": random_tokens(6, vocab_of(name), 3)}
+    steps = T.tail_one_by_one(reqs, 1000)
+    check(name, model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, "first tokens")
+    st2 = T.batched(reqs, 3, (5, 1, 0))
+    check(name, model_dirs, dtype, st2, T.run_in_process(eng, st2), reqs, "first tokens batched")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(model_dirs, dtype, tmp_path):
+    # the program a user runs, line by line on its standard input, with a poisoned cache
+    reqs = requests_of("B")
+    steps = T.batched(reqs, 2, (32, 3, 10))
+    outs = T.run_program(model_dirs["B"], dtype, steps, str(tmp_path / "out"), 512, vocab_of("B"),
+                         env={"DLGO_CACHE_POISON": "1"})
+    check("B", model_dirs, dtype, steps, outs, reqs, "trace_run")
+    same = T.run_in_process(engine_for(model_dirs, "B", dtype, True, 512), steps)
+    for k in outs:
+        assert torch.equal(outs[k], same[k]), f"step {k}: the program and the library disagree"
+
+
+def test_step_refuses_what_it_cannot_run(model_dirs):
+    from dlgo_b200.cache import CacheError
+    from dlgo_b200.engine.engine import StepError
+    eng = engine_for(model_dirs, "A", "float32")
+    s = eng.take_slot()
+    with pytest.raises(StepError, match="vocabulary"):
+        eng.step([s], [[1, 256]])
+    with pytest.raises(StepError, match="no token"):
+        eng.step([s], [[]])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([s, s], [[1], [2]])
+    with pytest.raises(StepError, match="limit"):
+        eng.step([s], [[1] * 129])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([s], [[1, 2]], [[2]])
+    with pytest.raises(CacheError):
+        eng.step([s + 1], [[1]])
+    assert eng.step([s], [[1, 2, 3]], [[]]) is None and eng.length(s) == 3
+    eng.free_slot(s)
+    eng.cache.book.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    import dlgo_b200
+    llm = dlgo_b200.load_llm(model_dirs[name], dtype=dtype, max_tokens=1024)
+    cfg, w = P.read_model(model_dirs[name])
+    lens = [5, 17, 32] if name == "A" else [1, 9, 70]
+    prompts = [random_tokens(n, vocab_of(name), 40 + n) for n in lens]
+    n_new = 16 if name == "A" else 24
+    got = llm.generate(prompts, max_tokens=n_new, greedy=True, ignore_eos=True)
+    for p, g in zip(prompts, got):
+        assert len(g) == n_new
+        want = P.greedy_generate(cfg, w, p, n_new)
+        if g != want:
+            # a different token is admissible only at a near tie of the plain logits
+            k = next(i for i in range(n_new) if g[i] != want[i])
+            lg = P.forward(cfg, w, p + want[:k])[-1]
+            gap = float(lg[want[k]] - lg[g[k]])
+            assert dtype == "bfloat16" and gap < 2e-2 * float(lg.abs().max()), (
+                f"{name} {dtype}: token {k} is {g[k]}, plain says {want[k]} (gap {gap:.3e})")
+    # one prompt alone gives what it gave inside the batch
+    assert llm.generate(prompts[1], max_tokens=n_new, greedy=True, ignore_eos=True) == got[1]
+    info = llm.model_info()
+    assert info.layers == cfg["num_hidden_layers"] and info.vocab_size == cfg["vocab_size"]
+
+
+def test_temperature_generation_is_seeded_and_independent_of_the_batch(model_dirs):
+    import dlgo_b200
+    llm = dlgo_b200.load_llm(model_dirs["B"], dtype="float32", max_tokens=1024)
+    prompts = [random_tokens(n, 384, 60 + n) for n in (1, 9, 70, 130)]
+    opts = dict(max_tokens=24, temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=7, ignore_eos=True)
+    a = llm.generate(prompts, **opts)
+    assert a == llm.generate(prompts, **opts)
+    assert a != llm.generate(prompts, **{**opts, "seed": 8})
+    seen = []
+    llm.generate_stream(prompts[:2], lambda r, t: seen.append((r, t)), **opts)
+    assert [t for r, t in seen if r == 1] == a[1]
+    # the plain sampler, fed the plain logits and the same counter-based uniforms, picks the same tokens
+    cfg, w = P.read_model(model_dirs["B"])
+    seq = list(prompts[1])
+    for d in range(6):
+        lg = P.forward(cfg, w, seq)[-1]
+        tok = P.sample_temperature(lg, 0.8, P.philox_uniform(7, d, 1))
+        assert tok == a[1][d], f"draw {d}"
+        seq.append(tok)
+    filt = llm.generate(prompts, max_tokens=8, temperature=0.7, top_k=40, top_p=0.9, seed=3, ignore_eos=True)
+    assert filt == llm.generate(prompts, max_tokens=8, temperature=0.7, top_k=40, top_p=0.9, seed=3, ignore_eos=True)
+    res = llm.benchmark(prompts, max_tokens=4, greedy=True, ignore_eos=True)
+    assert res.output_tokens == 16 and res.tokens_per_sec > 0 and "tok/s" in str(res)

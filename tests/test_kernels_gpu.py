@@ -1,0 +1,331 @@
+"""Each kernel alone against a plain fp32 reference written here, at sizes other than the engine's.
+Needs a GPU."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def K():
+    from dlgo_b200.csrc import kernels
+    return kernels
+
+
+def tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == "float32" else dict(atol=1e-2, rtol=1.6e-2)
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    table = torch.randn(37, 50, device=DEV).to(DT[dtype])
+    toks = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = K().embed(toks, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table.float()[toks.long()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,eps", [(1, 1e-5), (50, 1e-6), (200, 3e-6), (2048, 1e-5), (5000, 1e-2)])
+def test_rmsnorm(dtype, d, eps):
+    x = torch.randn(7, d, device=DEV) * 3
+    w = 1 + 0.1 * torch.randn(d, device=DEV)
+    ref = P.rmsnorm(x.cpu(), w.cpu(), eps)
+    out = K().rmsnorm(x, w, eps, DT[dtype])
+    assert out.dtype == DT[dtype]
+    torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    torch.testing.assert_close(K().rmsnorm(x, w, eps, DT[dtype], rows).float().cpu(), ref[[6, 0, 3]], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    gu = (torch.randn(5, 2 * 77, device=DEV) * 4).to(DT[dtype])
+    ref = P.swiglu(gu.float().cpu()[:, :77], gu.float().cpu()[:, 77:])
+    torch.testing.assert_close(K().swiglu(gu).float().cpu(), ref, **tol(dtype))
+
+
+# ------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K_", [(1, 1, 1), (3, 65, 17), (70, 130, 96), (129, 50, 200), (64, 64, 64), (5, 1000, 33)])
+def test_gemm_simt(dtype, M, N, K_):
+    k = K()
+    x = torch.randn(M, K_, device=DEV).to(DT[dtype])
+    w = torch.randn(N, K_, device=DEV).to(DT[dtype])
+    ref = (x.double() @ w.double().t()).float()
+    t = dict(atol=1e-5 * math.sqrt(K_), rtol=1e-5) if dtype == "float32" else dict(atol=3e-2 * math.sqrt(K_), rtol=1.6e-2)
+    torch.testing.assert_close(k.gemm_simt(x, w, k.EPI_STORE).float(), ref, **t)
+    f32 = k.gemm_simt(x, w, k.EPI_STORE_F32)
+    assert f32.dtype == torch.float32
+    torch.testing.assert_close(f32, ref, atol=1e-5 * math.sqrt(K_), rtol=1e-5)
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    k.gemm_simt(x, w, k.EPI_ADD_F32, acc)
+    torch.testing.assert_close(acc, res + ref, atol=1e-5 * math.sqrt(K_), rtol=1e-5)
+    # a strided input (a column block of a wider tensor) is taken by its row stride
+    wide = torch.randn(M, K_ + 24, device=DEV).to(DT[dtype])
+    torch.testing.assert_close(k.gemm_simt(wide[:, 8:8 + K_], w, k.EPI_STORE_F32),
+                               (wide[:, 8:8 + K_].double() @ w.double().t()).float(), atol=1e-5 * math.sqrt(K_), rtol=1e-5)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    k = K()
+    x = torch.randn(90, 200, device=DEV)
+    w = torch.randn(77, 200, device=DEV)
+    full = k.gemm_simt(x, w, k.EPI_STORE_F32)
+    assert torch.equal(k.gemm_simt(x[17:18].contiguous(), w, k.EPI_STORE_F32), full[17:18])
+
+
+# --------------------------------------------------------------- rope + append
+def _paged(n_pages, hkv, hd, dtype, fill=float("nan")):
+    return (torch.full((n_pages, hkv, 64, hd), fill, device=DEV, dtype=DT[dtype]),
+            torch.full((n_pages, hkv, 64, hd), fill, device=DEV, dtype=DT[dtype]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,hd,rot,inter", [(4, 2, 16, 16, False), (3, 1, 32, 32, True), (5, 5, 48, 24, False),
+                                                 (2, 1, 80, 32, True)])
+def test_rope_append(dtype, hq, hkv, hd, rot, inter):
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    pe = RotaryEmbedding(hd, rot, 10000.0, 300, pairing="interleaved" if inter else "split_half")
+    cos, sin = pe.tables()
+    # two sequences: slot 3 brings positions 62..66 (crosses a page edge), slot 1 brings position 130
+    pos = [62, 63, 64, 65, 66, 130]
+    seq = [0, 0, 0, 0, 0, 1]
+    slots = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    pt = torch.full((4, 5), -1, dtype=torch.int32, device=DEV)
+    pt[3, 0], pt[3, 1], pt[1, 2] = 5, 2, 7
+    kp, vp = _paged(8, hkv, hd, dtype)
+    ld = (hq + 2 * hkv) * hd
+    qkv = torch.randn(6, ld, device=DEV).to(DT[dtype])
+    orig = qkv.float().cpu().clone()
+    K().rope_append(qkv, cos.to(DEV), sin.to(DEV), torch.tensor(pos, dtype=torch.int32, device=DEV),
+                    torch.tensor(seq, dtype=torch.int32, device=DEV), slots, pt, kp, vp, hq, hkv, hd, rot, inter)
+
+    def rotate(vec, p):
+        out = vec.clone()
+        for i in range(rot // 2):
+            i0, i1 = (2 * i, 2 * i + 1) if inter else (i, i + rot // 2)
+            c, s = cos[p, i], sin[p, i]
+            out[i0] = vec[i0] * c - vec[i1] * s
+            out[i1] = vec[i0] * s + vec[i1] * c
+        return out
+
+    t = tol(dtype)
+    pages = {62: (5, 62), 63: (5, 63), 64: (2, 0), 65: (2, 1), 66: (2, 2), 130: (7, 2)}
+    for r, p in enumerate(pos):
+        for h in range(hq):
+            torch.testing.assert_close(qkv[r, h * hd:(h + 1) * hd].float().cpu(), rotate(orig[r, h * hd:(h + 1) * hd], p), **t)
+        pg, off = pages[p]
+        for h in range(hkv):
+            ko = orig[r, (hq + h) * hd:(hq + h + 1) * hd]
+            vo = orig[r, (hq + hkv + h) * hd:(hq + hkv + h + 1) * hd]
+            torch.testing.assert_close(kp[pg, h, off].float().cpu(), rotate(ko, p), **t)
+            assert torch.equal(vp[pg, h, off].float().cpu(), vo)
+    written = (~torch.isnan(kp.float())).sum().item()
+    assert written == 6 * hkv * hd, "the append wrote outside its positions"
+    # an entry that borrows another's cache rotates its queries and writes nothing
+    kp2, vp2 = _paged(8, hkv, hd, dtype)
+    q2 = orig.to(DEV).to(DT[dtype]).clone()
+    K().rope_append(q2, cos.to(DEV), sin.to(DEV), torch.tensor(pos, dtype=torch.int32, device=DEV),
+                    torch.tensor(seq, dtype=torch.int32, device=DEV), slots, pt, kp2, vp2, hq, hkv, hd, rot, inter, False)
+    assert torch.isnan(kp2.float()).all() and torch.equal(q2[:, :hq * hd], qkv[:, :hq * hd])
+
+
+# ------------------------------------------------------------------- attention
+def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False, special=None, dead_pages=False):
+    """seqs: list of (kv length before the step, new tokens).  Builds pages in a scrambled order,
+    runs the kernel, returns (out, reference)."""
+    k = K()
+    torch.manual_seed(hq * 1000 + hd + len(seqs))
+    B = len(seqs)
+    total = [s + n for s, n in seqs]
+    max_pages = max((t + 63) // 64 for t in total) + 1
+    n_pages = sum((t + 63) // 64 for t in total) + 3
+    perm = torch.randperm(n_pages).tolist()
+    kp, vp = _paged(n_pages, hkv, hd, dtype)
+    pt = torch.full((B + 2, max_pages), -1, dtype=torch.int32)
+    slots = [B + 1 - i for i in range(B)]                       # slots in falling order, not 0..B-1
+    Ks, Vs, qs, pos, seq_of = [], [], [], [], []
+    for i, (s, n) in enumerate(seqs):
+        Kf = torch.randn(total[i], hkv, hd)
+        Vf = torch.randn(total[i], hkv, hd)
+        if special:
+            special(i, Kf, Vf)
+        Kf, Vf = Kf.to(DT[dtype]).float(), Vf.to(DT[dtype]).float()
+        Ks.append(Kf); Vs.append(Vf)
+        first_live = max(0, s - window + 1) // 64 if (window and dead_pages) else 0
+        for pg in range((total[i] + 63) // 64):
+            if pg < first_live:
+                continue                                         # given back: the kernel may not touch it
+            page = perm.pop()
+            pt[slots[i], pg] = page
+            lo, hi = pg * 64, min(total[i], pg * 64 + 64)
+            kp[page, :, :hi - lo] = Kf[lo:hi].transpose(0, 1).to(DEV).to(DT[dtype])
+            vp[page, :, :hi - lo] = Vf[lo:hi].transpose(0, 1).to(DEV).to(DT[dtype])
+        for j in range(n):
+            q = torch.randn(hq, hd)
+            if special:
+                special(i, None, None, q, s + j)
+            qs.append(q.to(DT[dtype]).float()); pos.append(s + j); seq_of.append(i)
+    T_ = len(qs)
+    ld = hq * hd + 16                                            # a row stride wider than the heads
+    qbuf = torch.zeros(T_, ld, dtype=DT[dtype], device=DEV)
+    qbuf[:, :hq * hd] = torch.stack(qs).reshape(T_, hq * hd).to(DEV).to(DT[dtype])
+    qt, gchunk = k.attention_tile_shape(hd, hq // hkv, decode)
+    tiles, off = [], 0
+    for i, (s, n) in enumerate(seqs):
+        for b in range(0, n, qt):
+            tiles.append((i, off + b, min(qt, n - b)))
+        off += n
+    out = torch.full((T_, hq * hd), float("nan"), dtype=DT[dtype], device=DEV)
+    scratch = torch.full((max(1, k.attention_scratch_floats(T_, hq, hd, n_splits)),), float("nan"), device=DEV)
+    k.attention(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                max(t[2] for t in tiles), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd), window,
+                n_splits, gchunk, scratch)
+    ref = torch.zeros(T_, hq * hd)
+    G = hq // hkv
+    for r in range(T_):
+        i, p = seq_of[r], pos[r]
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(hq):
+            sc = (Ks[i][lo:p + 1, h // G] @ qs[r][h]) * (1.0 / math.sqrt(hd))
+            ref[r, h * hd:(h + 1) * hd] = P.softmax(sc) @ Vs[i][lo:p + 1, h // G]
+    return out.float().cpu(), ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (8, 2, 64), (6, 3, 128), (2, 1, 256),
+                                       (40, 1, 128)])
+def test_attention_prompts_chunks_and_single_tokens_in_one_batch(dtype, hq, hkv, hd):
+    out, ref = _attention_case(dtype, hq, hkv, hd, [(0, 70), (129, 1), (60, 9), (0, 1)])
+    torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_splits", [1, 2, 3, 7, 16])
+def test_attention_decode_in_slices(dtype, n_splits):
+    out, ref = _attention_case(dtype, 8, 2, 64, [(299, 1), (0, 1), (64, 1), (63, 1), (127, 1)], n_splits=n_splits,
+                               decode=True)
+    torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 3, 63, 64, 448, 698, 699])
+def test_attention_finds_one_far_key_among_hundreds(dtype, far):
+    # one key lines up with the query and outweighs the other 699: the output is that key's value
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[far, :, 0] = 12.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    for n_splits in (1, 5):
+        out, ref = _attention_case(dtype, 4, 2, 64, [(699, 1)], n_splits=n_splits, decode=True, special=special)
+        torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
+        assert float((out - ref).abs().max()) < 0.05 and float(ref.abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("where", ["first_inside", "last_outside"])
+def test_attention_window_edge(dtype, where):
+    # window 100 at position 300 keeps keys 201..300; a dominant key sits on either side of the edge
+    edge = 201 if where == "first_inside" else 200
+
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[edge, :, 0] = 12.0
+            Vf[edge] = 7.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    for n_splits, dead in ((1, False), (3, True)):
+        out, ref = _attention_case(dtype, 4, 2, 32, [(300, 1)], window=100, n_splits=n_splits, decode=True,
+                                   special=special, dead_pages=dead)
+        torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=3e-2, rtol=2e-2)))
+        if where == "first_inside":
+            assert float((out - 7.0).abs().max()) < 0.1
+        else:
+            assert float(out.abs().max()) < 6.0
+    # and for a prompt chunk whose queries straddle the window differently
+    out, ref = _attention_case(dtype, 4, 2, 32, [(250, 60)], window=100, special=special, dead_pages=True)
+    torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=3e-2, rtol=2e-2)))
+
+
+def test_attention_refuses_sizes_it_does_not_take():
+    k = K()
+    z = torch.zeros(1, 8, device=DEV)
+    i = torch.zeros(1, 3, dtype=torch.int32, device=DEV)
+    pages = torch.zeros(1, 1, 64, 6, device=DEV)
+    with pytest.raises(k.KernelError, match="size"):
+        k.attention(z, 8, 1, pages, pages, i, i, 1, i[0], i[0], torch.zeros(1, 6, device=DEV), 1, 1, 6, 1.0)
+    pages = torch.zeros(1, 1, 64, 512, device=DEV)
+    with pytest.raises(k.KernelError, match="size"):
+        k.attention(torch.zeros(1, 512, device=DEV), 512, 1, pages, pages, i, i, 1, i[0], i[0],
+                    torch.zeros(1, 512, device=DEV), 1, 1, 512, 1.0)
+
+
+# -------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("V", [5, 384, 1000, 128256])
+def test_argmax_first_maximum_wins(V):
+    lg = torch.randn(6, V, device=DEV)
+    lg[1, V // 2] = 50.0
+    lg[2, [0, V - 1]] = 60.0                    # a tie: the smaller index
+    lg[3, V - 1] = 70.0
+    lg[4] = -float("inf")
+    lg[5] = 3.0
+    got = K().argmax(lg).cpu().tolist()
+    want = [P.argmax(lg[r].cpu()) if V <= 1000 else int(lg[r].argmax()) for r in range(6)]
+    want[2], want[4], want[5] = 0, 0, 0
+    assert got == want
+
+
+def test_uniform_matches_the_plain_philox():
+    draws = torch.tensor([0, 1, 2, 500, 0], dtype=torch.int32, device=DEV)
+    reqs = torch.tensor([0, 0, 7, 3, 65000], dtype=torch.int32, device=DEV)
+    for seed in (0, 7, 2 ** 40 + 5):
+        got = K().uniform(seed, draws, reqs).cpu().tolist()
+        want = [P.philox_uniform(seed, int(d), int(r)) for d, r in zip(draws.tolist(), reqs.tolist())]
+        assert got == want
+
+
+@pytest.mark.parametrize("V", [7, 384, 5000, 128256])
+def test_sample_is_the_inverse_cdf_of_the_softmax(V):
+    torch.manual_seed(V)
+    R = 64
+    lg = torch.randn(R, V, device=DEV) * 3
+    lg[:, V // 3] = -float("inf")                                # a filtered token can never be drawn
+    temps = torch.full((R,), 0.8, device=DEV)
+    reqs = torch.arange(R, dtype=torch.int32, device=DEV)
+    draws = torch.full((R,), 5, dtype=torch.int32, device=DEV)
+    got = K().sample(lg, temps, reqs, draws, 11).cpu().tolist()
+    assert got == K().sample(lg, temps, reqs, draws, 11).cpu().tolist()
+    p = torch.softmax(lg.double().cpu() / 0.8, dim=1)
+    c = torch.cumsum(p, dim=1)
+    for r in range(R):
+        u = P.philox_uniform(11, 5, r)
+        t = got[r]
+        assert t != V // 3 and p[r, t] > 0
+        lo = float(c[r, t - 1]) if t > 0 else 0.0
+        assert lo - 1e-5 <= u <= float(c[r, t]) + 1e-5, f"row {r}: u={u} outside [{lo}, {float(c[r, t])}]"
+    one = torch.full((2, V), -float("inf"), device=DEV)
+    one[:, V - 1] = 0.0
+    assert K().sample(one, temps[:2], reqs[:2], draws[:2], 3).cpu().tolist() == [V - 1, V - 1]
+
+
+def test_sample_frequencies_follow_the_probabilities():
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.125])
+    n = 4000
+    lg = torch.log(probs).to(DEV).repeat(n, 1)
+    got = K().sample(lg, torch.ones(n, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                     torch.arange(n, dtype=torch.int32, device=DEV), 1)
+    freq = torch.bincount(got.cpu().long(), minlength=4).float() / n
+    assert float((freq - probs).abs().max()) < 0.03

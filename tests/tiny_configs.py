@@ -29,11 +29,22 @@ TINY: Dict[str, dict] = {
 }
 
 
-def write_tiny(name: str, out_dir: str, std: float = 0.02) -> str:
+def write_tiny(name: str, out_dir: str, std: float = 0.02, sharpen: float = 1.0) -> str:
+    """The model folder of a tiny configuration.  `sharpen` > 1 scales the query and key projections,
+    so that attention is far from uniform and a wrong or missing key changes the logits visibly."""
     from dlgo_b200.config import config_from_dict
-    from dlgo_b200.weights import write_random_model
+    from dlgo_b200.weights import Checkpoint, save_tensors, write_random_model
     cfg = config_from_dict(TINY[name]["cfg"])
-    return write_random_model(cfg, TINY[name]["seed"], out_dir, std=std)
+    write_random_model(cfg, TINY[name]["seed"], out_dir, std=std)
+    if sharpen != 1.0:
+        ck = Checkpoint(out_dir)
+        tensors = {n: ck.read(n).clone() for n in ck.names()}
+        ck.close()
+        for n in tensors:
+            if n.endswith("q_proj.weight") or n.endswith("k_proj.weight"):
+                tensors[n] = (tensors[n].float() * sharpen).to(tensors[n].dtype)
+        save_tensors(os.path.join(out_dir, "model.safetensors"), tensors)
+    return out_dir
 
 
 def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
