@@ -1,0 +1,254 @@
+"""Benchmark: decode tok/s at batch 8 (also 1 and 64) and prefill tok/s at 2,048 tokens, Llama 3.2 1B
+shape, bfloat16, random weights, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Prints ONE JSON line.  The weights a step reads
+(2.47 GB) are far larger than the L2 cache, which is stated in `config` as the timing hygiene rule asks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# the benchmark model: Llama 3.2 1B shape (random weights, seed 2)
+MODEL = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_layers=16, intermediate_size=8192,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", "0", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6 or not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def make_model_dir(tmp):
+    import torch
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.weights import write_random_model
+    cfg = config_from_dict(MODEL)
+    t0 = time.time()
+    write_random_model(cfg, 2, tmp, device="cuda" if torch.cuda.is_available() else "cpu")
+    print(f"[bench] wrote random 1B model in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    return tmp
+
+
+def prompts_for(batch, seed=3):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(128, 1025, (batch,), generator=g).tolist()
+    return [torch.randint(0, MODEL["vocab_size"], (n,), generator=g).tolist() for n in lens]
+
+
+def decode_run(llm, batch, steps, warmup, sample_clocks=False):
+    """Device-timed decode: prompts in, `warmup` untimed steps, then exactly `steps` timed steps."""
+    import torch
+    from dlgo_b200.csrc import kernels
+    eng = llm.engine
+    prompts = prompts_for(batch)
+    slots = [eng.take_slot() for _ in prompts]
+    logits = eng.step(slots, prompts)
+    nxt = kernels.argmax(logits).cpu().tolist()
+    for _ in range(warmup):
+        logits = eng.step(slots, [[t] for t in nxt])
+        nxt = kernels.argmax(logits).cpu().tolist()
+    sampler = ClockSampler() if sample_clocks else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    launches0 = kernels.LAUNCHES
+    t0 = time.time()
+    start.record()
+    feed = [[t] for t in nxt]
+    for _ in range(steps):
+        # device-timed: the step and the argmax are queued without waiting for their result (the
+        # ids fed are fixed; the end-to-end number below feeds back what was sampled)
+        logits = eng.step(slots, feed)
+        kernels.argmax(logits)
+    end.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    lens = [eng.length(s) for s in slots]
+    for s in slots:
+        eng.free_slot(s)
+    return dict(ms_per_step=ms / steps, tok_s=batch * steps / (ms / 1e3), launches=kernels.LAUNCHES - launches0,
+                clocks=clocks, mean_context=sum(lens) / len(lens) - steps / 2)
+
+
+def prefill_run(llm, n_tokens, reps=5):
+    import torch
+    eng = llm.engine
+    g = torch.Generator().manual_seed(11)
+    times = []
+    for r in range(reps + 2):
+        toks = torch.randint(0, MODEL["vocab_size"], (n_tokens,), generator=g).tolist()
+        s = eng.take_slot()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        eng.step([s], [toks])
+        end.record()
+        torch.cuda.synchronize()
+        eng.free_slot(s)
+        if r >= 2:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def prefill_flops(n_tokens):
+    m = MODEL
+    d, f, hq, hkv, hd, L = (m["hidden_size"], m["intermediate_size"], m["num_attention_heads"],
+                            m["num_key_value_heads"], m["head_dim"], m["num_hidden_layers"])
+    per_token = 2 * d * (hq * hd + 2 * hkv * hd) + 2 * hq * hd * d + 2 * d * 2 * f + 2 * f * d
+    gemm = n_tokens * per_token * L + 2 * d * m["vocab_size"]      # the head runs for the last row only
+    attn = L * hq * hd * 2 * 2 * (n_tokens * (n_tokens + 1) // 2)  # causal QK^T and PV
+    return gemm + attn
+
+
+def e2e_run(llm, batch, steps):
+    """The same metric through the public entry point: host token ids in, host token ids out."""
+    prompts = prompts_for(batch)
+    llm.generate(prompts, max_tokens=4, greedy=True, ignore_eos=True)          # warm-up (graphs, pages)
+    res = llm.generate_detailed(prompts, max_tokens=steps + 1, greedy=True, ignore_eos=True)
+    return batch * steps / (res.generate_ms / 1e3)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "computerex/dlgo is a Go module (no setup.py/pyproject.toml: pip cannot install it), no Go "
+                          "toolchain is in the image, and its GPU path is Vulkan, which is unavailable on this box"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    import torch
+    import dlgo_b200
+    warmup = max(a.warmup, 3)
+    pk = peaks()
+    MODEL["num_hidden_layers"] = a.layers
+    tmp = tempfile.mkdtemp(prefix="dlgo_b200_bench_")
+    try:
+        make_model_dir(tmp)
+        llm = dlgo_b200.load_llm(tmp, CONTEXT, dtype="bfloat16", max_batch=64)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    eng = llm.engine
+    main_run = decode_run(llm, a.batch, a.steps, warmup, sample_clocks=True)
+    points = {}
+    for b in (1, 64):
+        points[f"decode_b{b}"] = round(decode_run(llm, b, min(a.steps, 64), warmup)["tok_s"], 1)
+    e2e = e2e_run(llm, a.batch, a.steps)
+    pre_ms = prefill_run(llm, PREFILL_TOKENS)
+    weight_bytes = eng.weight_bytes()
+    kv_per_pos = sum(2 * n.num_kv_heads * n.head_dim for n in eng.model.cache_needs()[0] if n is not None) * 2
+    step_bytes = weight_bytes + a.batch * main_run["mean_context"] * kv_per_pos
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    flops = prefill_flops(PREFILL_TOKENS)
+    out = {
+        "metric": "decode tok/s @ batch 8 (Llama-3.2-1B shape, bf16); points: batch 1/64; prefill tok/s @ 2,048",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights seed 2)",
+        "impl": "ours",
+        "config": {
+            "model": "llama-3.2-1b-shape", "layers": a.layers, "layers_of_config": 16, "hidden": 2048, "heads": 32,
+            "kv_heads": 8, "head_dim": 64, "ffn": 8192, "vocab": 128256, "tied": True, "global_batch": a.batch,
+            "seq_len": CONTEXT, "prompt_len": "uniform[128,1024] seed 3", "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (weights read per step: %.2f GB)" % (weight_bytes / 1e9),
+            "cuda_graph": True, "peaks": pk["source"]},
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 3 * 4 * a.batch,
+                "d2h_bytes_per_step": 4 * a.batch},
+        "gpu_launches": main_run["launches"],
+        "clocks": main_run["clocks"],
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -31,8 +31,13 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
 
 
-def _check(status: int, what: str) -> None:
+LAUNCHES = 0  # kernels of this package launched (or captured into a graph) so far
+
+
+def _check(status: int, what: str, launches: int = 1) -> None:
+    global LAUNCHES
     if status == 0:
+        LAUNCHES += launches
         return
     if status < 0:
         raise KernelError(f"{what}: refused ({_STATUS.get(status, status)})")
@@ -201,7 +206,7 @@ def attention(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor, vpages: t
         _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _i(tile_tokens_max), _ptr(seq_slot),
         _ptr(token_pos), _ptr(out), _i(out.stride(0)), _ptr(scratch), _i(num_heads), _i(num_kv_heads), _i(head_dim),
         _i(kpages.shape[-2]), _i(n_splits), _i(gchunk), _i(window), _f(scale), _stream())
-    _check(st, "attention")
+    _check(st, "attention", 2 if n_splits > 1 else 1)
     return out
 
 

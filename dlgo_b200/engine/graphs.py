@@ -45,8 +45,11 @@ class DecodeGraph:
             eng.model.forward(self.ctx, eng.cache, self.want_rows)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        from ..csrc import kernels
+        before = kernels.LAUNCHES
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+        self.kernels_per_replay = kernels.LAUNCHES - before
 
     def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
         h = self.host
@@ -57,6 +60,8 @@ class DecodeGraph:
         self.meta.copy_(h, non_blocking=True)
         self._copied.record()
         self.graph.replay()
+        from ..csrc import kernels
+        kernels.LAUNCHES += self.kernels_per_replay
         return self.logits
 
 
