@@ -296,3 +296,56 @@ DLGO_EXPORT int dlgo_attention(const void* q, int dtype, int T, int ldq, const v
   if (dtype == DLGO_BF16) return launch_attention<__nv_bfloat16>(p, n_tiles, T, stream);
   return DLGO_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see attention_noalloc.h for who needs it and its rules).
+#include "attention_noalloc.h"
+
+// The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress, never a
+// device address: a kernel must be given the looked-up pointer.
+static __device__ __align__(256) float g_attention_scratch[DLGO_ATTENTION_NOALLOC_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch on the current device; looked up once per device.
+int scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return DLGO_ERR_SIZE;
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_attention_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return DLGO_ERR_DRIVER;
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return DLGO_OK;
+}
+}  // namespace
+
+DLGO_EXPORT long long dlgo_attention_noalloc_needs(int T, int Hq, int hd, int n_splits) {
+  return dlgo_attention_scratch_floats(T, Hq, hd, n_splits);
+}
+
+DLGO_EXPORT int dlgo_attention_noalloc(const void* q, int dtype, int T, int ldq, const void* kpages,
+                                       const void* vpages, const int* page_table, int max_pages, const int* tiles,
+                                       int n_tiles, int tile_tokens_max, const int* seq_slot, const int* token_pos,
+                                       void* out, int ldo, int Hq, int Hkv, int hd, int page_size, int n_splits,
+                                       int gchunk, int window, float scale, cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return DLGO_OK;
+  if (Hq <= 0 || hd <= 0 || n_splits <= 0) return DLGO_ERR_SIZE;
+  const long long need = dlgo_attention_scratch_floats(T, Hq, hd, n_splits);
+  if (need > (long long)DLGO_ATTENTION_NOALLOC_FLOATS) return DLGO_ERR_SIZE;  // beyond the stated maximum
+  float* scratch = nullptr;
+  if (need > 0) {
+    const int st = scratch_address(&scratch);
+    if (st != DLGO_OK) return st;
+  }
+  return dlgo_attention(q, dtype, T, ldq, kpages, vpages, page_table, max_pages, tiles, n_tiles, tile_tokens_max,
+                        seq_slot, token_pos, out, ldo, scratch, Hq, Hkv, hd, page_size, n_splits, gchunk, window,
+                        scale, stream);
+}

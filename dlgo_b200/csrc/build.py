@@ -33,7 +33,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
 }
-_HEADERS = ["common.cuh"]
+_HEADERS = ["common.cuh", "attention_noalloc.h"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
