@@ -32,8 +32,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "rope_append": ["rope_append.cu"],
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
 }
-_HEADERS = ["common.cuh", "attention_noalloc.h"]
+_HEADERS = ["common.cuh", "attention_noalloc.h", "tcgen05.cuh"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

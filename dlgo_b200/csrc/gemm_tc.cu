@@ -1,0 +1,406 @@
+// bfloat16 contraction on the Blackwell tensor cores: D[Ra, Rb] = A[Ra, K] . B[Rb, K]^T with fp32
+// accumulation in tensor memory.
+//
+// Both operands are K-major ([rows, K] row-major), which is how the reference keeps weights
+// ([out x in], models/llm/model.go:64-80) and how activations are packed.  One CTA computes a
+// 128 x BN tile (optionally one K-slice of it):
+//   warp 0    one thread issues TMA tile loads (128-byte swizzle) into a ring of shared-memory stages
+//   warp 1    allocates tensor memory; one thread issues tcgen05.mma (128 x BN x 16 per instruction) and
+//             commits each stage back to the loader and the finished accumulator to the epilogue
+//   warps 2-5 read the accumulator from tensor memory (each warp its own 32 lanes) and run the epilogue
+// Rows and columns beyond the matrices are zero-filled by TMA on the way in and masked on the way out,
+// so any Ra, Rb and any K that is a multiple of 8 are taken.
+//
+// Which operand is the weight is the caller's choice.  For many tokens A is the activations and the
+// output is written row-major (`transposed` = 0).  For few tokens (decode) A is the WEIGHT, so its
+// 128 rows fill the tensor core's M while the tokens sit in N = 16..64, and the tile is written
+// transposed: out[col * ldo + row].
+//
+// Epilogues: store bf16, store fp32 (logits), add into an fp32 residual in place
+// (models/llm/forward.go:163,169), or SwiGLU (ops/activation.go:8-38) over a weight whose rows come
+// in blocks of 16 gate rows followed by their 16 up rows, writing h = silu(g) * u.
+//
+// Split-K (decode): `splits` CTAs share an output tile.  Each writes its fp32 partial to a
+// workspace; the CTA that arrives last adds the partials in slice order (so the sum does not
+// depend on which one was last) and runs the epilogue.
+#include <math.h>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace dlgo {
+
+using namespace sm100;
+
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3 };
+
+constexpr int TILE_M = 128;
+constexpr int TILE_K = 64;  // 128 bytes of bf16: one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int TC_THREADS = 192;
+
+__device__ int g_gemm_tc_error = 0;  // set when a bounded wait ran out
+
+struct TcParams {
+  int Ra, Rb, K;      // rows of A, rows of B, contraction length
+  void* out;
+  int ldo;
+  int transposed;     // 0: out[row * ldo + col]; 1: out[col * ldo + row]
+  int epilogue;
+  int splits;
+  float* workspace;   // [splits][tiles][BN][128] fp32, when splits > 1
+  int* counters;      // [tiles], zero before the first launch; left zero
+};
+
+template <int BN> struct TcConfig {
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int A_BYTES = TILE_M * TILE_K * 2;
+  static constexpr int B_BYTES = BN * TILE_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// One row's 32 consecutive columns (or 16 when NV == 16) -> memory, per epilogue.
+template <int NV>
+__device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v, int row, int col0, int lane) {
+  if (p.epilogue == TC_SWIGLU) {
+    if (!p.transposed) {
+      // columns are weight rows: [16 gate | 16 up] per 32 columns -> 16 outputs at column col0 / 2
+      static_assert(NV == 32 || NV == 16, "");
+      if (NV == 32 && row < p.Ra) {
+        __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + col0 / 2;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (col0 + 16 + j < p.Rb) {
+            const float g = v[j], u = v[16 + j];
+            o[j] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+          }
+        }
+      }
+    } else {
+      // rows are weight rows: lanes 0-15 hold gate rows, lanes 16-31 their up rows
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        const int col = col0 + j;
+        if (lane < 16 && row + 16 < p.Ra && col < p.Rb) {
+          const float g = v[j];
+          const int feature = (row >> 5) * 16 + (row & 15);
+          ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
+        }
+      }
+    }
+    return;
+  }
+  if (!p.transposed) {
+    if (row >= p.Ra) return;
+    const size_t base = (size_t)row * p.ldo + col0;
+    if (col0 + NV <= p.Rb && (p.ldo & 7) == 0) {
+      // whole, aligned run of columns: 16-byte accesses
+      if (p.epilogue == TC_STORE) {
+        uint4* o = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + base);
+#pragma unroll
+        for (int j = 0; j < NV / 8; ++j) {
+          __nv_bfloat162 h[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+          o[j] = *reinterpret_cast<uint4*>(h);
+        }
+      } else {
+        float4* o = reinterpret_cast<float4*>((float*)p.out + base);
+#pragma unroll
+        for (int j = 0; j < NV / 4; ++j) {
+          float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          if (p.epilogue == TC_ADD_F32) {
+            const float4 y = o[j];
+            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+          }
+          o[j] = x;
+        }
+      }
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (col0 + j < p.Rb) {
+        if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[base + j] = __float2bfloat16_rn(v[j]);
+        else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[base + j] = v[j];
+        else ((float*)p.out)[base + j] += v[j];
+      }
+    }
+  } else {
+    if (row >= p.Ra) return;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int col = col0 + j;
+      if (col < p.Rb) {
+        const size_t o = (size_t)col * p.ldo + row;
+        if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
+        else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[o] = v[j];
+        else ((float*)p.out)[o] += v[j];
+      }
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+  using C = TcConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // tiles want 1024-byte alignment for the 128-byte swizzle
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* accum = empty + C::STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* last_flag = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int kblocks_total = (p.K + TILE_K - 1) / TILE_K;
+  const int per = (kblocks_total + p.splits - 1) / p.splits;
+  const int kb0 = split * per;
+  const int kb1 = min(kblocks_total, kb0 + per);
+  const int nkb = max(0, kb1 - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (i / C::STAGES) & 1;
+        if (i >= C::STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + C::A_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * TILE_K, tile_a * TILE_M);
+        tma_load_2d(b_dst, &map_b, &full[s], (kb0 + i) * TILE_K, tile_b * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN < 16 ? 16 : BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (i / C::STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t db = umma_desc_k_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+          // inside a 128-byte swizzle row, the next K = 16 slice starts 32 bytes on (2 in 16-byte units)
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+        }
+        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(accum);        // the accumulator is complete
+    }
+  } else {
+    // epilogue warps: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    const int row = tile_a * TILE_M + quarter * 32 + lane;
+    bool ok = true;
+    if (nkb > 0) ok = mbar_wait(accum, 0, abort_flag);
+    tc_fence_after_sync();
+    constexpr int NV = BN >= 32 ? 32 : 16;
+    const int ntiles = gridDim.x * gridDim.y;
+    const int tile_lin = tile_b * gridDim.x + tile_a;
+    if (p.splits == 1) {
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += NV) {
+          float v[NV];
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+          tmem_ld_wait();
+          epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+        }
+      }
+    } else {
+      // partial tile -> workspace [split][tile][col][128 rows] (rows innermost: coalesced)
+      float* ws = p.workspace + ((size_t)split * ntiles + tile_lin) * (size_t)(BN * TILE_M);
+      const int r_in = quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += NV) {
+        float v[NV];
+        if (ok && nkb > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) ws[(size_t)(c0 + j) * TILE_M + r_in] = v[j];
+      }
+      __threadfence();
+      // the 128 epilogue threads meet, one of them takes a ticket
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const int ticket = atomicAdd(&p.counters[tile_lin], 1);
+        *last_flag = (ticket == p.splits - 1);
+        if (ticket == p.splits - 1) p.counters[tile_lin] = 0;  // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag && ok) {
+        __threadfence();
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += NV) {
+          float v[NV];
+#pragma unroll
+          for (int j = 0; j < NV; ++j) v[j] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float* src = p.workspace + ((size_t)s * ntiles + tile_lin) * (size_t)(BN * TILE_M);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) v[j] += __ldcg(&src[(size_t)(c0 + j) * TILE_M + r_in]);
+          }
+          epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_gemm_tc_error, 1);
+    // give tile loads that may still be in flight time to land before shared memory is handed on
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// [rows, K] bf16, row stride ld elements; box = 64 columns x box_rows rows, 128-byte swizzle, zero fill
+int make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return DLGO_ERR_DRIVER;
+  if (((uintptr_t)base & 15) != 0 || (ld % 8) != 0) return DLGO_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
+}
+
+template <int BN>
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
+  using C = TcConfig<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.Ra + TILE_M - 1) / TILE_M, (p.Rb + BN - 1) / BN, p.splits);
+  if (grid.y > 65535 || grid.z > 65535) return DLGO_ERR_SIZE;
+  gemm_tc_kernel<BN><<<grid, TC_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// Floats of workspace and ints of counters a call with `splits` > 1 needs.
+DLGO_EXPORT long long dlgo_gemm_tc_workspace_floats(int Ra, int Rb, int bn, int splits) {
+  if (splits <= 1) return 0;
+  const long long tiles = (long long)((Ra + TILE_M - 1) / TILE_M) * ((Rb + bn - 1) / bn);
+  return tiles * splits * bn * TILE_M;
+}
+DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
+  return ((Ra + TILE_M - 1) / TILE_M) * ((Rb + bn - 1) / bn);
+}
+
+// A[Ra, K] (row stride lda) and B[Rb, K] (row stride ldb) in bf16; out per `transposed` and `epilogue`
+// (0 store bf16, 1 store f32, 2 add into f32, 3 SwiGLU to bf16); bn in {16, 32, 64, 128, 256}.
+DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
+                             int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
+                             int* counters, cudaStream_t stream) {
+  if (Ra <= 0 || Rb <= 0) return DLGO_OK;
+  if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
+  if (epilogue < 0 || epilogue > 3) return DLGO_ERR_SIZE;
+  if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
+  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return DLGO_ERR_SIZE;
+  if (epilogue == TC_SWIGLU) {
+    const int weight_rows = transposed ? Ra : Rb;
+    if (weight_rows % 32 || (!transposed && bn < 32)) return DLGO_ERR_SIZE;
+  }
+  CUtensorMap ma, mb;
+  int st = make_map(&ma, A, Ra, K, lda, TILE_M);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mb, B, Rb, K, ldb, bn);
+  if (st != DLGO_OK) return st;
+  TcParams p;
+  p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
+  p.splits = splits; p.workspace = workspace; p.counters = counters;
+  switch (bn) {
+    case 16: return launch_tc<16>(ma, mb, p, stream);
+    case 32: return launch_tc<32>(ma, mb, p, stream);
+    case 64: return launch_tc<64>(ma, mb, p, stream);
+    case 128: return launch_tc<128>(ma, mb, p, stream);
+    case 256: return launch_tc<256>(ma, mb, p, stream);
+    default: return DLGO_ERR_SIZE;
+  }
+}
+
+// 1 if a kernel of this library gave up a bounded wait since the last call (clears the flag).
+DLGO_EXPORT int dlgo_gemm_tc_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof(int));
+  return v;
+}

@@ -246,3 +246,51 @@ def uniform(seed: int, draw: torch.Tensor, request: torch.Tensor) -> torch.Tenso
                                        _i(draw.numel()), _stream())
     _check(st, "uniform")
     return out
+
+
+# ------------------------------------------------------- tensor-core contraction
+TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU = 0, 1, 2, 3
+TC_TILE_M, TC_TILE_K = 128, 64
+
+
+def gemm_tc_workspace_floats(ra: int, rb: int, bn: int, splits: int) -> int:
+    if splits <= 1:
+        return 0
+    return ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn) * splits * bn * TC_TILE_M
+
+
+def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, epilogue: int, bn: int,
+            splits: int = 1, workspace: Optional[torch.Tensor] = None,
+            counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """D[Ra, Rb] = a[Ra, K] . b[Rb, K]^T on the tensor cores (bf16 in, fp32 accumulate).
+
+    ``out`` receives D (``transposed``: D^T) through ``epilogue``; with ``splits`` > 1 the K range is
+    shared by that many CTAs per tile, which needs ``workspace`` (fp32) and zeroed ``counters`` (int32).
+    """
+    for n, t in (("a", a), ("b", b)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_tc: {n} must be a 2-D bfloat16 GPU tensor with unit inner stride")
+    ra, k = a.shape
+    rb, k2 = b.shape
+    if k != k2:
+        raise KernelError(f"gemm_tc: a has K={k}, b has K={k2}")
+    if out.stride(-1) != 1:
+        raise KernelError("gemm_tc: out must have unit inner stride")
+    if splits > 1:
+        need = gemm_tc_workspace_floats(ra, rb, bn, splits)
+        tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
+        if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
+            raise KernelError(f"gemm_tc: {splits} K-slices need {need} floats of workspace and {tiles} counters")
+    st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
+                                      _ptr(out), _i(out.stride(0)), _i(1 if transposed else 0), _i(epilogue), _i(bn),
+                                      _i(splits), _ptr(workspace), _ptr(counters), _stream())
+    _check(st, "gemm_tc")
+    return out
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel gave up a bounded wait on the device since the last check (synchronises)."""
+    if "gemm_tc" in build._loaded:
+        v = build._loaded["gemm_tc"].dlgo_gemm_tc_error()
+        if v != 0:
+            raise KernelError("a tensor-core kernel gave up a bounded wait on the device; its results are invalid")

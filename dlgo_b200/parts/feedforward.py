@@ -35,12 +35,23 @@ class SwiGLU(FeedForward):
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
         gate = runtime.compute_copy(get("gate_proj.weight"))
         up = runtime.compute_copy(get("up_proj.weight"))
-        self.w_gate_up = Linear(torch.cat([gate, up], dim=0), runtime)
+        f, d = self.intermediate_size, self.hidden_size
+        self.fused = False
+        if runtime.dtype == torch.bfloat16 and f % 16 == 0 and d % 8 == 0:
+            # blocks of 16 gate rows followed by their 16 up rows: the contraction's epilogue then
+            # holds a gate value and its up value side by side and writes silu(g) * u directly
+            inter = torch.stack([gate.view(f // 16, 16, d), up.view(f // 16, 16, d)], dim=1).reshape(2 * f, d)
+            self.w_gate_up = Linear(inter.contiguous(), runtime, fused_swiglu=True)
+            self.fused = True
+        else:
+            self.w_gate_up = Linear(torch.cat([gate, up], dim=0), runtime)
         self.w_down = Linear(get("down_proj.weight"), runtime)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
-        gate_up = self.w_gate_up(x, STORE)
-        h = K.swiglu(gate_up)
+        if self.fused:
+            h = self.w_gate_up(x)
+        else:
+            h = K.swiglu(self.w_gate_up(x, STORE))
         self.w_down(h, ADD_F32, residual)
 
 

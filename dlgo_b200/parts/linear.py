@@ -18,14 +18,21 @@ STORE, STORE_F32, ADD_F32 = K.EPI_STORE, K.EPI_STORE_F32, K.EPI_ADD_F32
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, runtime: Any):
+    """``fused_swiglu``: the weight holds gate and up rows in blocks of 16 + 16 and the contraction's
+    epilogue writes ``silu(gate) * up`` ([T, out/2]); only the tensor-core kernel offers it
+    (:attr:`fuses_swiglu` says whether this weight got it)."""
+
+    def __init__(self, weight: torch.Tensor, runtime: Any, fused_swiglu: bool = False):
         self.weight = runtime.compute_copy(weight).contiguous()
         self.out_features, self.in_features = self.weight.shape
         self.runtime = runtime
         self._tc = None
         if self.weight.dtype == torch.bfloat16:
             from . import tensor_core
-            self._tc = tensor_core.plan_for(self.weight)
+            self._tc = tensor_core.plan_for(self.weight, swiglu=fused_swiglu)
+        self.fuses_swiglu = fused_swiglu and self._tc is not None
+        if fused_swiglu and not self.fuses_swiglu:
+            raise ValueError("this weight cannot take the fused SwiGLU epilogue")
 
     def __call__(self, x: torch.Tensor, epilogue: int = STORE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self._tc is not None:

@@ -1,15 +1,91 @@
 """Choice of the tensor-core contraction for a bfloat16 weight.
 
-``plan_for(weight)`` returns a callable ``(x, epilogue, out) -> out`` that runs
-the tcgen05 kernel, or ``None`` when the kernel does not take the weight's sizes
-(the caller then uses the fp32-pipe kernel, never a wrong result).
+``plan_for(weight)`` returns a callable ``(x, epilogue, out) -> out`` that runs the tcgen05
+kernel, or ``None`` when the kernel does not take the weight's sizes (the caller then uses the
+fp32-pipe kernel, never a wrong result).
+
+Few tokens (decode): the WEIGHT is the tensor core's M operand (128 rows per tile) and the tokens
+are its N (16 / 32 / 64); tiles are written transposed, and the K range is shared by several CTAs
+per tile so that every SM streams its part of the weight.  Many tokens: the activations are M, the
+weight is N (tiles of 128 x 256), written row-major.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Callable, Dict, List, Optional
 
 import torch
 
+from ..csrc import kernels as K
 
-def plan_for(weight: torch.Tensor) -> Optional[Callable]:
-    return None
+SKINNY_MAX = 64          # tokens up to which the weight is the M operand
+TARGET_CTAS = 148        # one CTA per SM streams the weight
+MIN_KBLOCKS_PER_SPLIT = 4
+
+_workspaces: Dict[int, List[torch.Tensor]] = {}
+_counters: Dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, floats: int) -> torch.Tensor:
+    """One workspace per device, shared by all contractions (they run one after another on a stream).
+    Buffers that were outgrown stay alive: a captured graph may still point at them."""
+    lst = _workspaces.setdefault(device.index or 0, [])
+    if not lst or lst[-1].numel() < floats:
+        lst.append(torch.empty((max(floats, 1 << 20),), dtype=torch.float32, device=device))
+    return lst[-1]
+
+
+def _counter_buffer(device: torch.device) -> torch.Tensor:
+    c = _counters.get(device.index or 0)
+    if c is None:
+        c = _counters[device.index or 0] = torch.zeros((1 << 16,), dtype=torch.int32, device=device)
+    return c
+
+
+def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
+    """(bn, splits) for ``tokens`` <= SKINNY_MAX against a weight [n, k]."""
+    bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
+    tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
+    kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
+    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, -(-TARGET_CTAS // tiles))) if tiles < TARGET_CTAS else 1
+    return bn, max(1, min(splits, kblocks))
+
+
+class TensorCorePlan:
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+        self.weight = weight
+        self.n, self.k = weight.shape
+        self.swiglu = swiglu
+
+    def __call__(self, x: torch.Tensor, epilogue: int, out: Optional[torch.Tensor]) -> torch.Tensor:
+        t = x.shape[0]
+        if self.swiglu:
+            epi = K.TC_SWIGLU
+            if out is None:
+                out = torch.empty((t, self.n // 2), dtype=torch.bfloat16, device=x.device)
+        else:
+            epi = {K.EPI_STORE: K.TC_STORE, K.EPI_STORE_F32: K.TC_STORE_F32, K.EPI_ADD_F32: K.TC_ADD_F32}[epilogue]
+            if out is None:
+                if epilogue == K.EPI_ADD_F32:
+                    raise K.KernelError("the add epilogue needs the tensor to add into")
+                out = torch.empty((t, self.n), dtype=torch.bfloat16 if epilogue == K.EPI_STORE else torch.float32,
+                                  device=x.device)
+        if t <= SKINNY_MAX:
+            bn, splits = skinny_shape(t, self.n, self.k)
+            ws = cnt = None
+            if splits > 1:
+                ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
+                cnt = _counter_buffer(x.device)
+            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt)
+        bn = 256 if self.n > 128 else 128
+        return K.gemm_tc(x, self.weight, out, False, epi, bn)
+
+
+def plan_for(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:
+    n, k = weight.shape
+    if weight.dtype != torch.bfloat16 or k % 8 or weight.stride(1) != 1 or weight.stride(0) % 8:
+        return None
+    if weight.data_ptr() % 16:
+        return None
+    if swiglu and n % 32:
+        return None
+    return TensorCorePlan(weight, swiglu)

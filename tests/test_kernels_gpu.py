@@ -329,3 +329,95 @@ def test_sample_frequencies_follow_the_probabilities():
                      torch.arange(n, dtype=torch.int32, device=DEV), 1)
     freq = torch.bincount(got.cpu().long(), minlength=4).float() / n
     assert float((freq - probs).abs().max()) < 0.03
+
+
+# ------------------------------------------------------- tensor-core contraction
+def _tc_ref(a, b):
+    return a.double() @ b.double().t()
+
+
+@pytest.mark.parametrize("Ra,Rb,K_,bn", [(128, 16, 64, 16), (128, 256, 64, 256), (300, 7, 200, 16), (77, 40, 96, 64),
+                                         (256, 130, 2048, 128), (1000, 33, 264, 64), (130, 600, 328, 256)])
+def test_gemm_tc_all_epilogues_both_orientations(Ra, Rb, K_, bn):
+    k = K()
+    torch.manual_seed(Ra + Rb)
+    a = torch.randn(Ra, K_, device=DEV).to(torch.bfloat16)
+    b = torch.randn(Rb, K_, device=DEV).to(torch.bfloat16)
+    ref = _tc_ref(a, b).float()
+    t = dict(atol=2e-3 * math.sqrt(K_), rtol=1e-2)
+    for transposed in (False, True):
+        want = ref.t() if transposed else ref
+        shape = (Rb, Ra) if transposed else (Ra, Rb)
+        o = torch.full(shape, float("nan"), device=DEV)
+        k.gemm_tc(a, b, o, transposed, k.TC_STORE_F32, bn)
+        torch.testing.assert_close(o, want, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+        ob = torch.full(shape, float("nan"), device=DEV, dtype=torch.bfloat16)
+        k.gemm_tc(a, b, ob, transposed, k.TC_STORE, bn)
+        torch.testing.assert_close(ob.float(), want, **t)
+        res = torch.randn(shape, device=DEV)
+        acc = res.clone()
+        k.gemm_tc(a, b, acc, transposed, k.TC_ADD_F32, bn)
+        torch.testing.assert_close(acc, res + want, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
+@pytest.mark.parametrize("N,T_,K_,splits", [(256, 5, 512, 2), (384, 16, 2048, 8), (130, 33, 200, 4), (2048, 64, 8192, 9),
+                                            (128, 1, 640, 10)])
+def test_gemm_tc_split_k_is_exact_and_repeatable(N, T_, K_, splits):
+    k = K()
+    torch.manual_seed(N + T_)
+    w = torch.randn(N, K_, device=DEV).to(torch.bfloat16)
+    x = torch.randn(T_, K_, device=DEV).to(torch.bfloat16)
+    bn = 16 if T_ <= 16 else (32 if T_ <= 32 else 64)
+    ws = torch.full((k.gemm_tc_workspace_floats(N, T_, bn, splits),), float("nan"), device=DEV)
+    cnt = torch.zeros(64, dtype=torch.int32, device=DEV)
+    ref = _tc_ref(x, w).float()
+    outs = []
+    for _ in range(3):
+        o = torch.full((T_, N), float("nan"), device=DEV)
+        k.gemm_tc(w, x, o, True, k.TC_STORE_F32, bn, splits, ws, cnt)
+        outs.append(o)
+    torch.testing.assert_close(outs[0], ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    assert int(cnt.abs().sum()) == 0
+    res = torch.randn(T_, N, device=DEV)
+    acc = res.clone()
+    k.gemm_tc(w, x, acc, True, k.TC_ADD_F32, bn, splits, ws, cnt)
+    torch.testing.assert_close(acc, res + ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
+@pytest.mark.parametrize("T_", [3, 40, 200])
+def test_gemm_tc_swiglu_epilogue(T_):
+    k = K()
+    F_, d = 112, 72
+    torch.manual_seed(T_)
+    gate = torch.randn(F_, d, device=DEV).to(torch.bfloat16)
+    up = torch.randn(F_, d, device=DEV).to(torch.bfloat16)
+    x = (torch.randn(T_, d, device=DEV) * 0.3).to(torch.bfloat16)
+    inter = torch.stack([gate.view(F_ // 16, 16, d), up.view(F_ // 16, 16, d)], dim=1).reshape(2 * F_, d).contiguous()
+    ref = P.swiglu((x.double() @ gate.double().t()).float().cpu(), (x.double() @ up.double().t()).float().cpu())
+    h = torch.full((T_, F_), float("nan"), device=DEV, dtype=torch.bfloat16)
+    if T_ <= 64:
+        bn = 16 if T_ <= 16 else 64
+        k.gemm_tc(inter, x, h, True, k.TC_SWIGLU, bn)
+    else:
+        k.gemm_tc(x, inter, h, False, k.TC_SWIGLU, 256)
+    torch.testing.assert_close(h.float().cpu(), ref, atol=3e-2, rtol=2e-2)
+    k.check_device_errors()
+
+
+def test_gemm_tc_refuses_what_it_cannot_take():
+    k = K()
+    a = torch.zeros(128, 60, device=DEV, dtype=torch.bfloat16)     # K not a multiple of 8
+    o = torch.zeros(128, 128, device=DEV)
+    with pytest.raises(k.KernelError, match="size"):
+        k.gemm_tc(a, a, o, False, k.TC_STORE_F32, 128)
+    b = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError, match="size"):
+        k.gemm_tc(b, b, o, False, k.TC_STORE_F32, 48)               # not a tile width
+    ws, cnt = torch.zeros(1 << 16, device=DEV), torch.zeros(4, dtype=torch.int32, device=DEV)
+    with pytest.raises(k.KernelError, match="size"):
+        k.gemm_tc(b, b, o, False, k.TC_STORE_F32, 128, 2, ws, cnt)  # more K-slices than K blocks
+    with pytest.raises(k.KernelError, match="workspace"):
+        k.gemm_tc(b, b, o, False, k.TC_STORE_F32, 128, 2)           # K-slices without their workspace
