@@ -192,6 +192,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
+    ap.add_argument("--only", choices=["decode", "prefill"], help="run one small workload (for profiling) and stop")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -209,10 +211,19 @@ def main() -> int:
     tmp = tempfile.mkdtemp(prefix="dlgo_b200_bench_")
     try:
         make_model_dir(tmp)
-        llm = dlgo_b200.load_llm(tmp, CONTEXT, dtype="bfloat16", max_batch=64)
+        llm = dlgo_b200.load_llm(tmp, CONTEXT, dtype="bfloat16", max_batch=64, cuda_graphs=not a.no_graphs)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
     eng = llm.engine
+    if a.only == "decode":
+        r = decode_run(llm, a.batch, a.steps, warmup)
+        print(json.dumps({"only": "decode", "batch": a.batch, "ms_per_step": round(r["ms_per_step"], 4),
+                          "tok_s": round(r["tok_s"], 1), "launches": r["launches"]}))
+        return 0
+    if a.only == "prefill":
+        ms = prefill_run(llm, PREFILL_TOKENS, reps=max(1, a.steps))
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(ms, 3)}))
+        return 0
     main_run = decode_run(llm, a.batch, a.steps, warmup, sample_clocks=True)
     points = {}
     for b in (1, 64):

@@ -17,6 +17,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "attention_combine.cuh"
 
 namespace dlgo {
 
@@ -207,29 +208,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(AttnParams p) {
         }
       }
     }
-  }
-}
-
-// out[token, head, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp(m_s - max m)
-template <typename T>
-__global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                         T* __restrict__ out, int ldo, int Hq, int hd, int n_splits) {
-  const int token = blockIdx.x, head = blockIdx.y;
-  const size_t o = ((size_t)token * Hq + head) * n_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(o + s) * 2]);
-  float denom = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part_ml[(o + s) * 2];
-    if (ms != -INFINITY) denom += expf(ms - m) * part_ml[(o + s) * 2 + 1];
-  }
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[(o + s) * 2];
-      if (ms != -INFINITY) a = fmaf(expf(ms - m), part_acc[(o + s) * hd + d], a);
-    }
-    out[(size_t)token * ldo + (size_t)head * hd + d] = from_float<T>(a / denom);
   }
 }
 

@@ -1,0 +1,294 @@
+// Attention for decode steps: one new token per sequence against its cached keys and values.
+//
+// Same formulas as attention.cu (models/llm/forward.go:258-278): scores q.k * scale over the keys
+// t <= pos (t > pos - window if windowed), softmax, weighted sum of the values, all in fp32.  Decode
+// reads every cached key and value once and does a handful of flops per byte, so the kernel is
+// shaped for memory latency, not arithmetic:
+//   * a block takes one sequence, one kv head (up to 4 of its query heads) and a slice of the pages;
+//   * a warp takes tiles of keys; LPK lanes share a key, each loading 16 bytes of it straight from
+//     global memory (coalesced rows of the page), so nothing is staged in shared memory;
+//   * scores of a tile are kept in registers, the running maximum is made uniform across the warp,
+//     and the values of the same tile are then streamed with the probabilities as weights;
+//   * lanes, then warps, merge their partial sums; with several slices the partial (max, sum,
+//     output) go to scratch and attention_combine_kernel finishes.
+#include <math.h>
+
+#include "attention_combine.cuh"
+#include "common.cuh"
+
+namespace dlgo {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr int DEC_GMAX = 4;   // query heads of a kv head per block
+constexpr int DEC_ITER = 4;   // keys per lane group and tile
+
+struct DecParams {
+  const void* q;
+  int ldq;
+  const void* kpages;
+  const void* vpages;
+  const int* page_table;
+  int max_pages;
+  const int* seq_slot;   // [B]
+  const int* token_pos;  // [B] position of the new token (its key is already in the cache)
+  void* out;
+  int ldo;
+  float* part_acc;
+  float* part_ml;
+  int Hq, Hkv, page_size, n_splits, n_gchunks, window;
+  float scale;
+};
+
+template <typename T> struct Ld16;
+template <> struct Ld16<float> {
+  static constexpr int VEC = 4;
+  __device__ static void load(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct Ld16<__nv_bfloat16> {
+  static constexpr int VEC = 8;
+  __device__ static void load(const __nv_bfloat16* p, float* o) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      o[2 * i] = f.x;
+      o[2 * i + 1] = f.y;
+    }
+  }
+};
+
+// LPK lanes per key; head_dim = LPK * VEC.
+template <typename T, int LPK>
+__global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams p) {
+  constexpr int VEC = Ld16<T>::VEC;
+  constexpr int HD = LPK * VEC;
+  constexpr int KPW = 32 / LPK;            // keys a warp covers per iteration
+  constexpr int TILE = KPW * DEC_ITER;     // keys per tile (divides the page size)
+  __shared__ float sm_acc[DEC_WARPS][DEC_GMAX][HD];
+  __shared__ float sm_ml[DEC_WARPS][DEC_GMAX][2];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPK;              // which 16 bytes of the key
+  const int grp = lane / LPK;              // which key of the iteration
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y / p.n_gchunks, gc = blockIdx.y - kvh * p.n_gchunks;
+  const int split = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int g0 = gc * DEC_GMAX;
+  const int GC = min(DEC_GMAX, G - g0);
+  const int PS = p.page_size;
+  const int slot = p.seq_slot[b];
+  const int pos = p.token_pos[b];
+  const int t_end = pos + 1;
+  const int t_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int pg_first = t_begin / PS, pg_last = pos / PS;
+  const int per = (pg_last - pg_first + 1 + p.n_splits - 1) / p.n_splits;
+  const int pg_b = pg_first + split * per;
+  const int pg_e = min(pg_last + 1, pg_b + per);
+
+  float q[DEC_GMAX][VEC], acc[DEC_GMAX][VEC], m[DEC_GMAX], l[DEC_GMAX];
+  const T* qrow = (const T*)p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0) * HD + sub * VEC;
+#pragma unroll
+  for (int g = 0; g < DEC_GMAX; ++g) {
+    if (g < GC) Ld16<T>::load(qrow + (size_t)g * HD, q[g]);
+    else
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[g][e] = 0.f;
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+  }
+
+  const int tiles_per_page = PS / TILE;
+  const int n_tiles = max(0, pg_e - pg_b) * tiles_per_page;
+  for (int tile = warp; tile < n_tiles; tile += DEC_WARPS) {
+    const int pg = pg_b + tile / tiles_per_page;
+    const int key0 = (tile % tiles_per_page) * TILE;
+    if (pg * PS + key0 >= t_end) continue;                       // wholly beyond the sequence (warp-uniform)
+    const int page = p.page_table[(size_t)slot * p.max_pages + pg];
+    const size_t base = ((size_t)page * p.Hkv + kvh) * PS * HD;
+    const T* kp = (const T*)p.kpages + base;
+    const T* vp = (const T*)p.vpages + base;
+    float s[DEC_GMAX][DEC_ITER];
+    bool live[DEC_ITER];
+    float tmax[DEC_GMAX];
+#pragma unroll
+    for (int g = 0; g < DEC_GMAX; ++g) tmax[g] = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < DEC_ITER; ++it) {
+      const int key = key0 + it * KPW + grp;
+      const int t = pg * PS + key;
+      live[it] = t < t_end && t >= t_begin;
+      float kf[VEC];
+      if (live[it]) Ld16<T>::load(kp + (size_t)key * HD + sub * VEC, kf);
+      else
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) kf[e] = 0.f;
+#pragma unroll
+      for (int g = 0; g < DEC_GMAX; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) d = fmaf(q[g][e], kf[e], d);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        s[g][it] = live[it] ? d * p.scale : -INFINITY;
+        tmax[g] = fmaxf(tmax[g], s[g][it]);
+      }
+    }
+    // one running maximum per head for the whole warp, so partial sums of its lane groups add up
+#pragma unroll
+    for (int g = 0; g < DEC_GMAX; ++g) {
+#pragma unroll
+      for (int o = 16; o >= LPK; o >>= 1) tmax[g] = fmaxf(tmax[g], __shfl_xor_sync(0xffffffffu, tmax[g], o));
+      const float m_new = fmaxf(m[g], tmax[g]);
+      const float c = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
+      m[g] = m_new;
+      l[g] *= c;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[g][e] *= c;
+#pragma unroll
+      for (int it = 0; it < DEC_ITER; ++it) {
+        const float pr = (s[g][it] == -INFINITY) ? 0.f : expf(s[g][it] - m_new);
+        s[g][it] = pr;
+        l[g] += pr;
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < DEC_ITER; ++it) {
+      if (!live[it]) continue;
+      const int key = key0 + it * KPW + grp;
+      float vf[VEC];
+      Ld16<T>::load(vp + (size_t)key * HD + sub * VEC, vf);
+#pragma unroll
+      for (int g = 0; g < DEC_GMAX; ++g)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[g][e] = fmaf(s[g][it], vf[e], acc[g][e]);
+    }
+  }
+
+  // lane groups of a warp share their maximum: sums add up.  l was counted once per lane of a
+  // group, so only lanes with sub == 0 contribute it.
+#pragma unroll
+  for (int g = 0; g < DEC_GMAX; ++g) {
+    float lg = (sub == 0) ? l[g] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
+    l[g] = lg;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float a = acc[g][e];
+#pragma unroll
+      for (int o = 16; o >= LPK; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      acc[g][e] = a;
+    }
+    if (grp == 0) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sm_acc[warp][g][sub * VEC + e] = acc[g][e];
+      if (sub == 0) {
+        sm_ml[warp][g][0] = m[g];
+        sm_ml[warp][g][1] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps: thread -> (head g, dim d)
+  for (int idx = threadIdx.x; idx < GC * HD; idx += DEC_THREADS) {
+    const int g = idx / HD, d = idx - g * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, sm_ml[w][g][0]);
+    float a = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float mw = sm_ml[w][g][0];
+      if (mw != -INFINITY) {
+        const float c = expf(mw - mm);
+        a = fmaf(c, sm_acc[w][g][d], a);
+        ll = fmaf(c, sm_ml[w][g][1], ll);
+      }
+    }
+    const int head = kvh * G + g0 + g;
+    if (p.n_splits == 1) {
+      ((T*)p.out)[(size_t)b * p.ldo + (size_t)head * HD + d] = from_float<T>(a / ll);
+    } else {
+      const size_t o = ((size_t)b * p.Hq + head) * p.n_splits + split;
+      p.part_acc[o * HD + d] = a;
+      if (d == 0) {
+        p.part_ml[o * 2] = mm;
+        p.part_ml[o * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+template <typename T, int LPK>
+int launch_decode(const DecParams& p, int B, cudaStream_t stream) {
+  constexpr int HD = LPK * Ld16<T>::VEC;
+  dim3 grid(B, p.Hkv * p.n_gchunks, p.n_splits);
+  attention_decode_kernel<T, LPK><<<grid, DEC_THREADS, 0, stream>>>(p);
+  int st = launch_status();
+  if (st != DLGO_OK || p.n_splits == 1) return st;
+  dim3 cgrid(B, p.Hq);
+  const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
+  attention_combine_kernel<T><<<cgrid, threads, 0, stream>>>(p.part_acc, p.part_ml, (T*)p.out, p.ldo, p.Hq, HD,
+                                                             p.n_splits);
+  return launch_status();
+}
+
+template <typename T>
+int dispatch_decode(const DecParams& p, int B, int hd, cudaStream_t stream) {
+  switch (hd / Ld16<T>::VEC) {
+    case 2: return launch_decode<T, 2>(p, B, stream);
+    case 4: return launch_decode<T, 4>(p, B, stream);
+    case 8: return launch_decode<T, 8>(p, B, stream);
+    case 16: return launch_decode<T, 16>(p, B, stream);
+    case 32: return launch_decode<T, 32>(p, B, stream);
+    default: return DLGO_ERR_SIZE;
+  }
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+// 1 if the kernel takes this head size for this element type (16 bytes per lane, 2..32 lanes per key)
+DLGO_EXPORT int dlgo_attention_decode_takes(int dtype, int hd, int page_size) {
+  const int vec = dtype == DLGO_BF16 ? 8 : 4;
+  if (hd % vec) return 0;
+  const int lpk = hd / vec;
+  if (!(lpk == 2 || lpk == 4 || lpk == 8 || lpk == 16 || lpk == 32)) return 0;
+  const int tile = (32 / lpk) * DEC_ITER;
+  return page_size % tile == 0;
+}
+
+// q[B, .] (row stride ldq, head h at column h*hd), one token per sequence at position token_pos[b];
+// scratch: B * Hq * n_splits * (hd + 2) floats when n_splits > 1.
+DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, const void* kpages,
+                                      const void* vpages, const int* page_table, int max_pages,
+                                      const int* seq_slot, const int* token_pos, void* out, int ldo, float* scratch,
+                                      int Hq, int Hkv, int hd, int page_size, int n_splits, int window, float scale,
+                                      cudaStream_t stream) {
+  if (B <= 0) return DLGO_OK;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_splits <= 0 || n_splits > 65535) return DLGO_ERR_SIZE;
+  if (dtype != DLGO_F32 && dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
+  if (!dlgo_attention_decode_takes(dtype, hd, page_size)) return DLGO_ERR_SIZE;
+  if (n_splits > 1 && scratch == nullptr) return DLGO_ERR_SIZE;
+  const int G = Hq / Hkv;
+  DecParams p;
+  p.q = q; p.ldq = ldq; p.kpages = kpages; p.vpages = vpages; p.page_table = page_table; p.max_pages = max_pages;
+  p.seq_slot = seq_slot; p.token_pos = token_pos; p.out = out; p.ldo = ldo;
+  p.part_acc = scratch;
+  p.part_ml = scratch ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
+  p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
+  p.n_gchunks = (G + DEC_GMAX - 1) / DEC_GMAX;
+  p.window = window; p.scale = scale;
+  if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;
+  if (dtype == DLGO_F32) return dispatch_decode<float>(p, B, hd, stream);
+  return dispatch_decode<__nv_bfloat16>(p, B, hd, stream);
+}

@@ -33,8 +33,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "attention_decode": ["attention_decode.cu"],
 }
-_HEADERS = ["common.cuh", "attention_noalloc.h", "tcgen05.cuh"]
+_HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "tcgen05.cuh"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

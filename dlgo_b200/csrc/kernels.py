@@ -212,13 +212,20 @@ def attention(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor, vpages: t
 
 # -------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First index of each row's maximum (int32 on the device)."""
     _need(logits, torch.float32, "logits")
     R, V = logits.shape
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     _need(out, torch.int32, "out")
-    st = _lib("sampling").dlgo_argmax(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(out), _stream())
-    _check(st, "argmax")
+    lib = _lib("sampling")
+    chunks = lib.dlgo_argmax_chunks(_i(R), _i(V))
+    pv = pi = None
+    if chunks > 1:
+        pv = torch.empty((R * chunks,), dtype=torch.float32, device=logits.device)
+        pi = torch.empty((R * chunks,), dtype=torch.int32, device=logits.device)
+    st = lib.dlgo_argmax(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(out), _ptr(pv), _ptr(pi), _stream())
+    _check(st, "argmax", 2 if chunks > 1 else 1)
     return out
 
 
@@ -294,3 +301,31 @@ def check_device_errors() -> None:
         v = build._loaded["gemm_tc"].dlgo_gemm_tc_error()
         if v != 0:
             raise KernelError("a tensor-core kernel gave up a bounded wait on the device; its results are invalid")
+
+
+# ------------------------------------------------------------ decode attention
+def attention_decode_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return bool(_lib("attention_decode").dlgo_attention_decode_takes(_i(dtype_code(dtype)), _i(head_dim), _i(page_size)))
+
+
+def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
+                     page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor, out: torch.Tensor,
+                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                     n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys and values."""
+    _need(out, q.dtype, "out")
+    _need(kpages, q.dtype, "kpages")
+    _need(vpages, q.dtype, "vpages")
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    if n_splits > 1:
+        need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_decode: {n_splits} slices need {need} floats of scratch")
+    st = _lib("attention_decode").dlgo_attention_decode(
+        _ptr(q), _i(dtype_code(q.dtype)), _i(B), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table),
+        _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _ptr(scratch),
+        _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]), _i(n_splits), _i(window), _f(scale),
+        _stream())
+    _check(st, "attention_decode", 2 if n_splits > 1 else 1)
+    return out

@@ -41,19 +41,19 @@ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t draw, ui
 
 constexpr int SAMPLE_THREADS = 1024;
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+// (value, index) of the first maximum among row[begin, end): larger value wins, ties go to the
+// smaller index.  Called by every thread of the block; the result is valid in thread 0.
+__device__ __forceinline__ void block_argmax(const float* __restrict__ row, int begin, int end, float& best,
+                                             int& besti) {
   __shared__ float bv[32];
   __shared__ int bi[32];
-  const float* row = logits + (size_t)blockIdx.x * ld;
-  float best = -INFINITY;
-  int besti = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  best = -INFINITY;
+  besti = 0x7fffffff;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
     const float v = row[i];
     // a strided scan visits indices in rising order, so strict '>' keeps the first maximum
     if (v > best || besti == 0x7fffffff) { best = v; besti = i; }
   }
-  // reduce (value, index): larger value wins, ties go to the smaller index
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
@@ -66,8 +66,46 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
     const int nw = (blockDim.x + 31) >> 5;
     for (int w = 1; w < nw; ++w)
       if (bv[w] > best || (bv[w] == best && bi[w] < besti)) { best = bv[w]; besti = bi[w]; }
-    out[blockIdx.x] = besti == 0x7fffffff ? 0 : besti;
   }
+}
+
+// grid (rows, nblk): block (r, c) scans its chunk of the vocabulary.  With nblk == 1 it writes the
+// answer; otherwise its (value, index) go to scratch for argmax_finish_kernel.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out, float* __restrict__ part_v,
+              int* __restrict__ part_i) {
+  const int nblk = gridDim.y;
+  const int chunk = (V + nblk - 1) / nblk;
+  const int begin = blockIdx.y * chunk, end = min(V, begin + chunk);
+  float best;
+  int besti;
+  block_argmax(logits + (size_t)blockIdx.x * ld, begin, end, best, besti);
+  if (threadIdx.x == 0) {
+    if (nblk == 1) out[blockIdx.x] = besti == 0x7fffffff ? 0 : besti;
+    else {
+      part_v[blockIdx.x * nblk + blockIdx.y] = best;
+      part_i[blockIdx.x * nblk + blockIdx.y] = besti;
+    }
+  }
+}
+
+__global__ void argmax_finish_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nblk,
+                                     int* __restrict__ out) {
+  // one warp per row; chunks are in rising index order
+  const int r = blockIdx.x;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int c = threadIdx.x; c < nblk; c += 32) {
+    const float v = part_v[r * nblk + c];
+    const int i = part_i[r * nblk + c];
+    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+  }
+  if (threadIdx.x == 0) out[r] = besti == 0x7fffffff ? 0 : besti;
 }
 
 // One block per row.  Each thread owns a contiguous chunk of the vocabulary, so
@@ -135,12 +173,27 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 
 using namespace dlgo;
 
-// logits[R, V] f32 (row stride ld) -> out[R] int32
-DLGO_EXPORT int dlgo_argmax(const float* logits, int R, int ld, int V, int* out, cudaStream_t stream) {
+// Chunks the vocabulary is cut into for `R` rows (1: one kernel, no scratch).
+DLGO_EXPORT int dlgo_argmax_chunks(int R, int V) {
+  if (V < 16384) return 1;
+  int c = (V + 8191) / 8192;
+  const int want = (2 * 148 + R - 1) / R;   // enough blocks for every SM
+  if (c > want) c = want;
+  return c < 1 ? 1 : (c > 64 ? 64 : c);
+}
+
+// logits[R, V] f32 (row stride ld) -> out[R] int32; scratch: R * chunks floats and as many ints
+DLGO_EXPORT int dlgo_argmax(const float* logits, int R, int ld, int V, int* out, float* part_v, int* part_i,
+                            cudaStream_t stream) {
   if (R <= 0) return DLGO_OK;
   if (V <= 0 || ld < V) return DLGO_ERR_SIZE;
-  const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-  argmax_kernel<<<R, threads, 0, stream>>>(logits, ld, V, out);
+  int nblk = dlgo_argmax_chunks(R, V);
+  if (part_v == nullptr || part_i == nullptr) nblk = 1;
+  const int threads = V / nblk >= 8192 ? 1024 : (V / nblk >= 1024 ? 256 : 64);
+  argmax_kernel<<<dim3(R, nblk), threads, 0, stream>>>(logits, ld, V, out, part_v, part_i);
+  int st = launch_status();
+  if (st != DLGO_OK || nblk == 1) return st;
+  argmax_finish_kernel<<<R, 32, 0, stream>>>(part_v, part_i, nblk, out);
   return launch_status();
 }
 

@@ -23,7 +23,8 @@ from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
 from .linear import ADD_F32, STORE, Linear
 from .registry import MIXERS
 
-_TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention
+_TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (general kernel)
+_DECODE_BLOCKS = 4 * 148  # and for the decode kernel, whose blocks are small
 
 
 class GQAAttention(Mixer):
@@ -86,20 +87,33 @@ class GQAAttention(Mixer):
         K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                       cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes)
         group = self.num_heads // self.num_kv_heads
-        qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
-        tiles, n_tiles, tile_max = ctx.tiles(qt)
-        n_gchunks = (group + gchunk - 1) // gchunk
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
-        base_blocks = n_tiles * self.num_kv_heads * n_gchunks
-        n_splits = max(1, min(pages, -(-_TARGET_BLOCKS // base_blocks))) if ctx.decode else 1
-        scratch = None
-        if n_splits > 1:
-            scratch = ctx.scratch("attention", K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
         out = torch.empty((T, self.q_dim), dtype=qkv.dtype, device=qkv.device)
-        K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max, ctx.seq_slot,
-                    ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                    self.window or 0, n_splits, gchunk, scratch)
+        if ctx.decode and K.attention_decode_takes(qkv.dtype, self.head_dim, cache.page_size):
+            # one token per sequence: the latency-shaped kernel, sliced so that every SM has several blocks
+            base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
+            n_splits = max(1, min(pages, -(-_DECODE_BLOCKS // base_blocks)))
+            scratch = None
+            if n_splits > 1:
+                scratch = ctx.scratch("attention",
+                                      K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+            K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                               ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                               self.window or 0, n_splits, scratch)
+        else:
+            qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
+            tiles, n_tiles, tile_max = ctx.tiles(qt)
+            n_gchunks = (group + gchunk - 1) // gchunk
+            base_blocks = n_tiles * self.num_kv_heads * n_gchunks
+            n_splits = max(1, min(pages, -(-_TARGET_BLOCKS // base_blocks))) if ctx.decode else 1
+            scratch = None
+            if n_splits > 1:
+                scratch = ctx.scratch("attention",
+                                      K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+            K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
+                        ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                        self.scale, self.window or 0, n_splits, gchunk, scratch)
         self.wo(out, ADD_F32, residual)
 
 

@@ -138,7 +138,8 @@ def test_rope_append(dtype, hq, hkv, hd, rot, inter):
 
 
 # ------------------------------------------------------------------- attention
-def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False, special=None, dead_pages=False):
+def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False, special=None, dead_pages=False,
+                    kernel="general"):
     """seqs: list of (kv length before the step, new tokens).  Builds pages in a scrambled order,
     runs the kernel, returns (out, reference)."""
     k = K()
@@ -185,10 +186,16 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
         off += n
     out = torch.full((T_, hq * hd), float("nan"), dtype=DT[dtype], device=DEV)
     scratch = torch.full((max(1, k.attention_scratch_floats(T_, hq, hd, n_splits)),), float("nan"), device=DEV)
-    k.attention(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
-                max(t[2] for t in tiles), torch.tensor(slots, dtype=torch.int32, device=DEV),
-                torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd), window,
-                n_splits, gchunk, scratch)
+    if kernel == "decode":
+        assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
+        k.attention_decode(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                           torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
+                           window, n_splits, scratch)
+    else:
+        k.attention(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                    max(t[2] for t in tiles), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                    torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd), window,
+                    n_splits, gchunk, scratch)
     ref = torch.zeros(T_, hq * hd)
     G = hq // hkv
     for r in range(T_):
@@ -209,16 +216,18 @@ def test_attention_prompts_chunks_and_single_tokens_in_one_batch(dtype, hq, hkv,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["general", "decode"])
 @pytest.mark.parametrize("n_splits", [1, 2, 3, 7, 16])
-def test_attention_decode_in_slices(dtype, n_splits):
+def test_attention_decode_in_slices(dtype, n_splits, kernel):
     out, ref = _attention_case(dtype, 8, 2, 64, [(299, 1), (0, 1), (64, 1), (63, 1), (127, 1)], n_splits=n_splits,
-                               decode=True)
+                               decode=True, kernel=kernel)
     torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["general", "decode"])
 @pytest.mark.parametrize("far", [0, 3, 63, 64, 448, 698, 699])
-def test_attention_finds_one_far_key_among_hundreds(dtype, far):
+def test_attention_finds_one_far_key_among_hundreds(dtype, far, kernel):
     # one key lines up with the query and outweighs the other 699: the output is that key's value
     def special(i, Kf, Vf, q=None, p=None):
         if Kf is not None:
@@ -228,14 +237,16 @@ def test_attention_finds_one_far_key_among_hundreds(dtype, far):
             q.mul_(0.05)
             q[:, 0] = 12.0
     for n_splits in (1, 5):
-        out, ref = _attention_case(dtype, 4, 2, 64, [(699, 1)], n_splits=n_splits, decode=True, special=special)
+        out, ref = _attention_case(dtype, 4, 2, 64, [(699, 1)], n_splits=n_splits, decode=True, special=special,
+                                   kernel=kernel)
         torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
         assert float((out - ref).abs().max()) < 0.05 and float(ref.abs().max()) > 0.5
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["general", "decode"])
 @pytest.mark.parametrize("where", ["first_inside", "last_outside"])
-def test_attention_window_edge(dtype, where):
+def test_attention_window_edge(dtype, where, kernel):
     # window 100 at position 300 keeps keys 201..300; a dominant key sits on either side of the edge
     edge = 201 if where == "first_inside" else 200
 
@@ -249,7 +260,7 @@ def test_attention_window_edge(dtype, where):
             q[:, 0] = 12.0
     for n_splits, dead in ((1, False), (3, True)):
         out, ref = _attention_case(dtype, 4, 2, 32, [(300, 1)], window=100, n_splits=n_splits, decode=True,
-                                   special=special, dead_pages=dead)
+                                   special=special, dead_pages=dead, kernel=kernel)
         torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=3e-2, rtol=2e-2)))
         if where == "first_inside":
             assert float((out - 7.0).abs().max()) < 0.1
@@ -258,6 +269,20 @@ def test_attention_window_edge(dtype, where):
     # and for a prompt chunk whose queries straddle the window differently
     out, ref = _attention_case(dtype, 4, 2, 32, [(250, 60)], window=100, special=special, dead_pages=True)
     torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=3e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 16), (3, 1, 32), (8, 2, 64), (6, 3, 128), (2, 1, 256), (40, 2, 64),
+                                       (5, 5, 48)])
+def test_attention_decode_kernel_sizes(dtype, hq, hkv, hd):
+    k = K()
+    if not k.attention_decode_takes(DT[dtype], hd, 64):
+        assert (hd, dtype) in ((48, "bfloat16"), (48, "float32"), (256, "float32"))
+        return
+    for n_splits in (1, 4):
+        out, ref = _attention_case(dtype, hq, hkv, hd, [(500, 1), (0, 1), (65, 1)], n_splits=n_splits, decode=True,
+                                   kernel="decode")
+        torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
 
 
 def test_attention_refuses_sizes_it_does_not_take():
