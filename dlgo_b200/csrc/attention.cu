@@ -66,6 +66,8 @@ template <> struct Vec<__nv_bfloat16> {
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hd = p.hd, PS = p.page_size, kstride = hd + 1;
@@ -222,12 +224,12 @@ int launch_attention(const AttnParams& p, int n_tiles, int T_tokens, cudaStream_
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_tiles, p.Hkv * p.n_gchunks, p.n_splits);
-  attention_kernel<T><<<grid, ATT_THREADS, smem, stream>>>(p);
+  launch_kernel(attention_kernel<T>, dim3(grid), dim3(ATT_THREADS), smem, stream, p);
   int st = launch_status();
   if (st != DLGO_OK || p.n_splits == 1) return st;
   dim3 cgrid(T_tokens, p.Hq);
   const int threads = p.hd >= 128 ? 128 : (p.hd >= 64 ? 64 : 32);
-  attention_combine_kernel<T><<<cgrid, threads, 0, stream>>>(p.part_acc, p.part_ml, (T*)p.out, p.ldo, p.Hq, p.hd,
+  launch_kernel(attention_combine_kernel<T>, dim3(cgrid), dim3(threads), 0, stream, p.part_acc, p.part_ml, (T*)p.out, p.ldo, p.Hq, p.hd,
                                                              p.n_splits);
   return launch_status();
 }

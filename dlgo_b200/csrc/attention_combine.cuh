@@ -10,6 +10,8 @@ namespace dlgo {
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int ldo, int Hq, int hd, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int token = blockIdx.x, head = blockIdx.y;
   const size_t o = ((size_t)token * Hq + head) * n_splits;
   float m = -INFINITY;

@@ -36,6 +36,7 @@ struct DecParams {
   int ldo;
   float* part_acc;
   float* part_ml;
+  int* counters;         // [B * Hkv * n_gchunks] zero before the first launch and left zero, or null
   int Hq, Hkv, page_size, n_splits, n_gchunks, window;
   float scale;
 };
@@ -62,15 +63,32 @@ template <> struct Ld16<__nv_bfloat16> {
   }
 };
 
+template <typename T> __device__ __forceinline__ void cvt16(const uint4& raw, float* o);
+template <> __device__ __forceinline__ void cvt16<float>(const uint4& raw, float* o) {
+  o[0] = __uint_as_float(raw.x); o[1] = __uint_as_float(raw.y); o[2] = __uint_as_float(raw.z); o[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void cvt16<__nv_bfloat16>(const uint4& raw, float* o) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+
 // LPK lanes per key; head_dim = LPK * VEC.
 template <typename T, int LPK>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int VEC = Ld16<T>::VEC;
   constexpr int HD = LPK * VEC;
   constexpr int KPW = 32 / LPK;            // keys a warp covers per iteration
   constexpr int TILE = KPW * DEC_ITER;     // keys per tile (divides the page size)
   __shared__ float sm_acc[DEC_WARPS][DEC_GMAX][HD];
   __shared__ float sm_ml[DEC_WARPS][DEC_GMAX][2];
+  __shared__ int sm_last;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK;              // which 16 bytes of the key
@@ -118,18 +136,26 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
     float s[DEC_GMAX][DEC_ITER];
     bool live[DEC_ITER];
     float tmax[DEC_GMAX];
-#pragma unroll
-    for (int g = 0; g < DEC_GMAX; ++g) tmax[g] = -INFINITY;
+    // all of the tile's keys AND values are requested before any arithmetic: one memory round trip
+    uint4 kraw[DEC_ITER], vraw[DEC_ITER];
 #pragma unroll
     for (int it = 0; it < DEC_ITER; ++it) {
       const int key = key0 + it * KPW + grp;
       const int t = pg * PS + key;
       live[it] = t < t_end && t >= t_begin;
-      float kf[VEC];
-      if (live[it]) Ld16<T>::load(kp + (size_t)key * HD + sub * VEC, kf);
-      else
+      kraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      vraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (live[it]) {
+        kraw[it] = *reinterpret_cast<const uint4*>(kp + (size_t)key * HD + sub * VEC);
+        vraw[it] = *reinterpret_cast<const uint4*>(vp + (size_t)key * HD + sub * VEC);
+      }
+    }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) kf[e] = 0.f;
+    for (int g = 0; g < DEC_GMAX; ++g) tmax[g] = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < DEC_ITER; ++it) {
+      float kf[VEC];
+      cvt16<T>(kraw[it], kf);
 #pragma unroll
       for (int g = 0; g < DEC_GMAX; ++g) {
         float d = 0.f;
@@ -161,10 +187,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
     }
 #pragma unroll
     for (int it = 0; it < DEC_ITER; ++it) {
-      if (!live[it]) continue;
-      const int key = key0 + it * KPW + grp;
       float vf[VEC];
-      Ld16<T>::load(vp + (size_t)key * HD + sub * VEC, vf);
+      cvt16<T>(vraw[it], vf);   // zeros where the key is not live; its probability is zero as well
 #pragma unroll
       for (int g = 0; g < DEC_GMAX; ++g)
 #pragma unroll
@@ -225,18 +249,48 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
       }
     }
   }
+  if (p.n_splits == 1 || p.counters == nullptr) return;
+  // the block that finishes last among the slices of this (sequence, kv head, head chunk) combines them
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = p.counters + (size_t)b * gridDim.y + blockIdx.y;
+    const int ticket = atomicAdd(c, 1);
+    sm_last = ticket == p.n_splits - 1;
+    if (sm_last) *c = 0;
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < GC * HD; idx += DEC_THREADS) {
+    const int g = idx / HD, d = idx - g * HD;
+    const int head = kvh * G + g0 + g;
+    const size_t o = ((size_t)b * p.Hq + head) * p.n_splits;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < p.n_splits; ++sp) mm = fmaxf(mm, __ldcg(&p.part_ml[(o + sp) * 2]));
+    float a = 0.f, ll = 0.f;
+    for (int sp = 0; sp < p.n_splits; ++sp) {
+      const float ms = __ldcg(&p.part_ml[(o + sp) * 2]);
+      if (ms != -INFINITY) {
+        const float c = expf(ms - mm);
+        a = fmaf(c, __ldcg(&p.part_acc[(o + sp) * HD + d]), a);
+        ll = fmaf(c, __ldcg(&p.part_ml[(o + sp) * 2 + 1]), ll);
+      }
+    }
+    ((T*)p.out)[(size_t)b * p.ldo + (size_t)head * HD + d] = from_float<T>(a / ll);
+  }
 }
 
 template <typename T, int LPK>
 int launch_decode(const DecParams& p, int B, cudaStream_t stream) {
   constexpr int HD = LPK * Ld16<T>::VEC;
   dim3 grid(B, p.Hkv * p.n_gchunks, p.n_splits);
-  attention_decode_kernel<T, LPK><<<grid, DEC_THREADS, 0, stream>>>(p);
+  launch_kernel(attention_decode_kernel<T, LPK>, dim3(grid), dim3(DEC_THREADS), 0, stream, p);
   int st = launch_status();
-  if (st != DLGO_OK || p.n_splits == 1) return st;
+  if (st != DLGO_OK || p.n_splits == 1 || p.counters != nullptr) return st;
   dim3 cgrid(B, p.Hq);
   const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
-  attention_combine_kernel<T><<<cgrid, threads, 0, stream>>>(p.part_acc, p.part_ml, (T*)p.out, p.ldo, p.Hq, HD,
+  launch_kernel(attention_combine_kernel<T>, dim3(cgrid), dim3(threads), 0, stream, p.part_acc, p.part_ml, (T*)p.out, p.ldo, p.Hq, HD,
                                                              p.n_splits);
   return launch_status();
 }
@@ -268,12 +322,14 @@ DLGO_EXPORT int dlgo_attention_decode_takes(int dtype, int hd, int page_size) {
 }
 
 // q[B, .] (row stride ldq, head h at column h*hd), one token per sequence at position token_pos[b];
-// scratch: B * Hq * n_splits * (hd + 2) floats when n_splits > 1.
+// scratch: B * Hq * n_splits * (hd + 2) floats when n_splits > 1.  counters: B * Hkv * ceil(G / 4) ints,
+// zero before the first call (the kernel leaves them zero): the last slice to finish then combines the
+// partial results itself; with counters == null a second kernel does.
 DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, const void* kpages,
                                       const void* vpages, const int* page_table, int max_pages,
                                       const int* seq_slot, const int* token_pos, void* out, int ldo, float* scratch,
-                                      int Hq, int Hkv, int hd, int page_size, int n_splits, int window, float scale,
-                                      cudaStream_t stream) {
+                                      int* counters, int Hq, int Hkv, int hd, int page_size, int n_splits,
+                                      int window, float scale, cudaStream_t stream) {
   if (B <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_splits <= 0 || n_splits > 65535) return DLGO_ERR_SIZE;
   if (dtype != DLGO_F32 && dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
@@ -285,6 +341,7 @@ DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, 
   p.seq_slot = seq_slot; p.token_pos = token_pos; p.out = out; p.ldo = ldo;
   p.part_acc = scratch;
   p.part_ml = scratch ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
+  p.counters = counters;
   p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
   p.n_gchunks = (G + DEC_GMAX - 1) / DEC_GMAX;
   p.window = window; p.scale = scale;

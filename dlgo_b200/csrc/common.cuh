@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DLGO_OK 0
 #define DLGO_ERR_SIZE (-1)      // a size the kernel does not take (never a wrong result)
@@ -67,6 +68,39 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   float t = scratch[0];
   for (int w = 1; w < nwarps; ++w) t = fmaxf(t, scratch[w]);
   return t;
+}
+
+// Programmatic dependent launch: a kernel may be scheduled while its predecessor on the stream is
+// still draining, so that launch latency and prologues overlap the predecessor's tail.  Every kernel
+// of this package calls pdl_launch_dependents() at its start and pdl_wait() before it reads or writes
+// anything a predecessor may have touched; pdl_wait() returns once all predecessors have completed
+// and their writes are visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("DLGO_PDL");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 inline int launch_status() {

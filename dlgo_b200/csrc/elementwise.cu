@@ -15,6 +15,8 @@ namespace dlgo {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int d, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
@@ -29,6 +31,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
@@ -48,6 +52,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // in: [T, 2F] with the gate in columns [0, F) and the up projection in [F, 2F).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int F, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   size_t t = i / F;
@@ -69,9 +75,9 @@ DLGO_EXPORT int dlgo_embed(const int* tokens, const void* table, int table_dtype
   if (d <= 0 || vocab <= 0) return DLGO_ERR_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == DLGO_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab);
+    launch_kernel(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
   else if (table_dtype == DLGO_BF16)
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, d, vocab);
+    launch_kernel(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();
@@ -84,9 +90,9 @@ DLGO_EXPORT int dlgo_rmsnorm(const float* x, const float* w, void* out, int out_
   if (d <= 0) return DLGO_ERR_SIZE;
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
   if (out_dtype == DLGO_F32)
-    rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, w, (float*)out, rows, d, eps);
+    launch_kernel(rmsnorm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w, (float*)out, rows, d, eps);
   else if (out_dtype == DLGO_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, d, eps);
+    launch_kernel(rmsnorm_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)out, rows, d, eps);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();
@@ -100,9 +106,9 @@ DLGO_EXPORT int dlgo_swiglu(const void* in, void* out, int dtype, int T, int F, 
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == DLGO_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)in, (float*)out, F, total);
+    launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, F, total);
   else if (dtype == DLGO_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, F,
+    launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, F,
                                                                  total);
   else
     return DLGO_ERR_DTYPE;

@@ -21,6 +21,8 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out, int M, int N, int K,
                  int lda, int ldw, int ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -84,12 +86,12 @@ int launch_gemm_simt(const void* A, const void* W, void* out, int M, int N, int 
   const T* a = (const T*)A;
   const T* w = (const T*)W;
   switch (epilogue) {
-    case EPI_STORE: gemm_simt_kernel<T, EPI_STORE><<<grid, 256, 0, stream>>>(a, w, out, M, N, K, lda, ldw, ldo); break;
+    case EPI_STORE: launch_kernel(gemm_simt_kernel<T, EPI_STORE>, dim3(grid), dim3(256), 0, stream, a, w, out, M, N, K, lda, ldw, ldo); break;
     case EPI_STORE_F32:
-      gemm_simt_kernel<T, EPI_STORE_F32><<<grid, 256, 0, stream>>>(a, w, out, M, N, K, lda, ldw, ldo);
+      launch_kernel(gemm_simt_kernel<T, EPI_STORE_F32>, dim3(grid), dim3(256), 0, stream, a, w, out, M, N, K, lda, ldw, ldo);
       break;
     case EPI_ADD_F32:
-      gemm_simt_kernel<T, EPI_ADD_F32><<<grid, 256, 0, stream>>>(a, w, out, M, N, K, lda, ldw, ldo);
+      launch_kernel(gemm_simt_kernel<T, EPI_ADD_F32>, dim3(grid), dim3(256), 0, stream, a, w, out, M, N, K, lda, ldw, ldo);
       break;
     default: return DLGO_ERR_SIZE;
   }

@@ -50,15 +50,19 @@ struct TcParams {
   int splits;
   float* workspace;   // [splits][tiles][BN][128] fp32, when splits > 1
   int* counters;      // [tiles], zero before the first launch; left zero
+  int stages;         // shared-memory ring size
+  int static_operand; // 0: none; 1: A, 2: B holds weights no earlier kernel writes (loaded before pdl_wait)
 };
 
 template <int BN> struct TcConfig {
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int MAX_STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int A_BYTES = TILE_M * TILE_K * 2;
   static constexpr int B_BYTES = BN * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int smem_bytes(int stages) {
+    return stages * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  }
 };
 
 // One row's 32 consecutive columns (or 16 when NV == 16) -> memory, per epilogue.
@@ -151,13 +155,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   // tiles want 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
-  uint64_t* empty = full + C::STAGES;
-  uint64_t* accum = empty + C::STAGES;
+  const int STAGES = p.stages;  // ring size (<= 8): as many as the K range needs, fewer to let two CTAs share an SM
+  uint64_t* full = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* last_flag = (int*)(tmem_slot + 2);
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
   const int kblocks_total = (p.K + TILE_K - 1) / TILE_K;
@@ -167,7 +173,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int nkb = max(0, kb1 - kb0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -189,10 +195,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (elect_one()) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        const uint32_t ph = (i / C::STAGES) & 1;
-        if (i >= C::STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+      // Weights do not depend on earlier kernels: their tiles for the first ring of stages are
+      // requested before waiting for the predecessor, the activations' tiles after.
+      const int npre = min(nkb, STAGES);
+      for (int i = 0; i < npre; ++i) {
+        uint8_t* a_dst = smem + i * C::STAGE_BYTES;
+        mbar_expect_tx(&full[i], C::STAGE_BYTES);
+        if (p.static_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
+        if (p.static_operand == 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
+      }
+      pdl_wait();
+      for (int i = 0; i < npre; ++i) {
+        uint8_t* a_dst = smem + i * C::STAGE_BYTES;
+        if (p.static_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
+        if (p.static_operand != 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
+      }
+      for (int i = npre; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
         uint8_t* a_dst = smem + s * C::STAGE_BYTES;
         uint8_t* b_dst = a_dst + C::A_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
@@ -204,8 +225,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN < 16 ? 16 : BN);
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        const uint32_t ph = (i / C::STAGES) & 1;
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
@@ -224,6 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // epilogue warps: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     const int row = tile_a * TILE_M + quarter * 32 + lane;
+    pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(accum, 0, abort_flag);
     tc_fence_after_sync();
@@ -343,13 +365,24 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES);
+                                         C::smem_bytes(C::MAX_STAGES));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((p.Ra + TILE_M - 1) / TILE_M, (p.Rb + BN - 1) / BN, p.splits);
   if (grid.y > 65535 || grid.z > 65535) return DLGO_ERR_SIZE;
-  gemm_tc_kernel<BN><<<grid, TC_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  TcParams q = p;
+  const int kblocks = (p.K + TILE_K - 1) / TILE_K;
+  const int per_split = (kblocks + p.splits - 1) / p.splits;
+  int stages = C::MAX_STAGES;
+  if (p.transposed) {
+    // few tokens: keep the footprint under half an SM so that two CTAs (of this kernel or of the next
+    // one, launched early) share it and one's start-up hides behind the other's streaming
+    while (stages > 2 && C::smem_bytes(stages) > 110 * 1024) --stages;
+  }
+  if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
+  q.stages = stages;
+  launch_kernel(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages), stream, ma, mb, q);
   return launch_status();
 }
 
@@ -367,9 +400,11 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 
 // A[Ra, K] (row stride lda) and B[Rb, K] (row stride ldb) in bf16; out per `transposed` and `epilogue`
 // (0 store bf16, 1 store f32, 2 add into f32, 3 SwiGLU to bf16); bn in {16, 32, 64, 128, 256}.
+// static_operand: 1 if A, 2 if B holds weights that no kernel launched before this one writes (their
+// tiles are then requested before the kernel waits for its predecessor), else 0.
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
                              int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
-                             int* counters, cudaStream_t stream) {
+                             int* counters, int static_operand, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
   if (epilogue < 0 || epilogue > 3) return DLGO_ERR_SIZE;
@@ -387,6 +422,7 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   TcParams p;
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
+  p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
   switch (bn) {
     case 16: return launch_tc<16>(ma, mb, p, stream);
     case 32: return launch_tc<32>(ma, mb, p, stream);

@@ -268,11 +268,12 @@ def gemm_tc_workspace_floats(ra: int, rb: int, bn: int, splits: int) -> int:
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, epilogue: int, bn: int,
             splits: int = 1, workspace: Optional[torch.Tensor] = None,
-            counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+            counters: Optional[torch.Tensor] = None, static_operand: int = 0) -> torch.Tensor:
     """D[Ra, Rb] = a[Ra, K] . b[Rb, K]^T on the tensor cores (bf16 in, fp32 accumulate).
 
     ``out`` receives D (``transposed``: D^T) through ``epilogue``; with ``splits`` > 1 the K range is
     shared by that many CTAs per tile, which needs ``workspace`` (fp32) and zeroed ``counters`` (int32).
+    ``static_operand`` (1: a, 2: b) names the operand that holds weights no earlier kernel writes.
     """
     for n, t in (("a", a), ("b", b)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
@@ -290,7 +291,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
             raise KernelError(f"gemm_tc: {splits} K-slices need {need} floats of workspace and {tiles} counters")
     st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
                                       _ptr(out), _i(out.stride(0)), _i(1 if transposed else 0), _i(epilogue), _i(bn),
-                                      _i(splits), _ptr(workspace), _ptr(counters), _stream())
+                                      _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _stream())
     _check(st, "gemm_tc")
     return out
 
@@ -311,8 +312,12 @@ def attention_decode_takes(dtype: torch.dtype, head_dim: int, page_size: int) ->
 def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
                      page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor, out: torch.Tensor,
                      num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                     n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of one new token per sequence over its cached keys and values."""
+                     n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
+                     counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys and values.
+
+    ``counters`` (int32, zero, at least ``B * num_kv_heads * ceil(group / 4)``): with them the slice that
+    finishes last combines the partial results; without them a second kernel does."""
     _need(out, q.dtype, "out")
     _need(kpages, q.dtype, "kpages")
     _need(vpages, q.dtype, "vpages")
@@ -322,10 +327,14 @@ def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vp
         need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention_decode: {n_splits} slices need {need} floats of scratch")
+        if counters is not None:
+            _need(counters, torch.int32, "counters")
+            if counters.numel() < B * num_kv_heads * ((num_heads // num_kv_heads + 3) // 4):
+                raise KernelError("attention_decode: too few counters")
     st = _lib("attention_decode").dlgo_attention_decode(
         _ptr(q), _i(dtype_code(q.dtype)), _i(B), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table),
         _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _ptr(scratch),
-        _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]), _i(n_splits), _i(window), _f(scale),
-        _stream())
-    _check(st, "attention_decode", 2 if n_splits > 1 else 1)
+        _ptr(counters), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]), _i(n_splits), _i(window),
+        _f(scale), _stream())
+    _check(st, "attention_decode", 2 if (n_splits > 1 and counters is None) else 1)
     return out

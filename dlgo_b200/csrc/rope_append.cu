@@ -23,6 +23,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
                                    const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
                                    T* __restrict__ vpages, int Hq, int Hkv, int hd, int rot, int page_size,
                                    int interleaved, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = hd / 2, rhalf = rot / 2;
   const int items = (Hq + 2 * Hkv) * half;
@@ -86,11 +88,11 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
   const int items = (Hq + 2 * Hkv) * (hd / 2);
   const int threads = items >= 1024 ? 256 : 128;
   if (dtype == DLGO_F32)
-    rope_append_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot,
+    launch_kernel(rope_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot,
                                                          page_table, max_pages, (float*)kpages, (float*)vpages, Hq,
                                                          Hkv, hd, rot, page_size, interleaved, write_cache);
   else if (dtype == DLGO_BF16)
-    rope_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+    launch_kernel(rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 
         (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
         (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved, write_cache);
   else

@@ -74,6 +74,8 @@ __device__ __forceinline__ void block_argmax(const float* __restrict__ row, int 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out, float* __restrict__ part_v,
               int* __restrict__ part_i) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nblk = gridDim.y;
   const int chunk = (V + nblk - 1) / nblk;
   const int begin = blockIdx.y * chunk, end = min(V, begin + chunk);
@@ -91,6 +93,8 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
 
 __global__ void argmax_finish_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nblk,
                                      int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   // one warp per row; chunks are in rising index order
   const int r = blockIdx.x;
   float best = -INFINITY;
@@ -113,6 +117,8 @@ __global__ void argmax_finish_kernel(const float* __restrict__ part_v, const int
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ request, const int* __restrict__ draw, uint64_t seed, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float csum[SAMPLE_THREADS];
   __shared__ int chosen;
@@ -190,10 +196,10 @@ DLGO_EXPORT int dlgo_argmax(const float* logits, int R, int ld, int V, int* out,
   int nblk = dlgo_argmax_chunks(R, V);
   if (part_v == nullptr || part_i == nullptr) nblk = 1;
   const int threads = V / nblk >= 8192 ? 1024 : (V / nblk >= 1024 ? 256 : 64);
-  argmax_kernel<<<dim3(R, nblk), threads, 0, stream>>>(logits, ld, V, out, part_v, part_i);
+  launch_kernel(argmax_kernel, dim3(dim3(R, nblk)), dim3(threads), 0, stream, logits, ld, V, out, part_v, part_i);
   int st = launch_status();
   if (st != DLGO_OK || nblk == 1) return st;
-  argmax_finish_kernel<<<R, 32, 0, stream>>>(part_v, part_i, nblk, out);
+  launch_kernel(argmax_finish_kernel, dim3(R), dim3(32), 0, stream, part_v, part_i, nblk, out);
   return launch_status();
 }
 
@@ -203,18 +209,20 @@ DLGO_EXPORT int dlgo_sample(const float* logits, int R, int ld, int V, const flo
   if (R <= 0) return DLGO_OK;
   if (V <= 0 || ld < V) return DLGO_ERR_SIZE;
   const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-  sample_kernel<<<R, threads, 0, stream>>>(logits, ld, V, temperature, request, draw, (uint64_t)seed, out);
+  launch_kernel(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, temperature, request, draw, (uint64_t)seed, out);
   return launch_status();
 }
 
 // the uniform a (seed, draw, request) triple yields, for tests and host-side twins
 __global__ void uniform_kernel(uint64_t seed, const int* draw, const int* request, float* out, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = philox_uniform(seed, (uint32_t)draw[i], (uint32_t)request[i]);
 }
 DLGO_EXPORT int dlgo_uniform(unsigned long long seed, const int* draw, const int* request, float* out, int n,
                              cudaStream_t stream) {
   if (n <= 0) return DLGO_OK;
-  uniform_kernel<<<(n + 255) / 256, 256, 0, stream>>>((uint64_t)seed, draw, request, out, n);
+  launch_kernel(uniform_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, (uint64_t)seed, draw, request, out, n);
   return launch_status();
 }

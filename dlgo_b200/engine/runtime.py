@@ -112,6 +112,15 @@ class StepContext:
         return t
 
 
+    def zeros(self, name: str, numel: int, dtype: torch.dtype = torch.int32) -> torch.Tensor:
+        """A buffer that is zero when first handed out; kernels that use it leave it zero."""
+        t = self._scratch.get(name)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            t = torch.zeros((max(numel, 1),), dtype=dtype, device=self.runtime.device)
+            self._scratch[name] = t
+        return t
+
+
 def build_context(runtime: Runtime, tokens: Sequence[Sequence[int]], slots: Sequence[int], starts: Sequence[int],
                   capacity: int) -> StepContext:
     """Pack a batch: ``tokens[i]`` are sequence i's next tokens, at positions ``starts[i] ...``."""

@@ -94,13 +94,14 @@ class GQAAttention(Mixer):
             # one token per sequence: the latency-shaped kernel, sliced so that every SM has several blocks
             base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
             n_splits = max(1, min(pages, -(-_DECODE_BLOCKS // base_blocks)))
-            scratch = None
+            scratch = counters = None
             if n_splits > 1:
                 scratch = ctx.scratch("attention",
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+                counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
             K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                               self.window or 0, n_splits, scratch)
+                               self.window or 0, n_splits, scratch, counters)
         else:
             qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
             tiles, n_tiles, tile_max = ctx.tiles(qt)

@@ -18,7 +18,7 @@ import torch
 from ..csrc import kernels as K
 
 SKINNY_MAX = 64          # tokens up to which the weight is the M operand
-TARGET_CTAS = 148        # one CTA per SM streams the weight
+TARGET_CTAS = 2 * 148    # two CTAs per SM stream the weight (their footprint is kept under half an SM)
 MIN_KBLOCKS_PER_SPLIT = 4
 
 _workspaces: Dict[int, List[torch.Tensor]] = {}
@@ -46,7 +46,7 @@ def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
     bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
-    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, -(-TARGET_CTAS // tiles))) if tiles < TARGET_CTAS else 1
+    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, TARGET_CTAS // tiles)) if tiles < TARGET_CTAS else 1
     return bn, max(1, min(splits, kblocks))
 
 
@@ -75,9 +75,9 @@ class TensorCorePlan:
             if splits > 1:
                 ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
                 cnt = _counter_buffer(x.device)
-            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt)
+            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1)
         bn = 256 if self.n > 128 else 128
-        return K.gemm_tc(x, self.weight, out, False, epi, bn)
+        return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2)
 
 
 def plan_for(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:

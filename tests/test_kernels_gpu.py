@@ -188,9 +188,14 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
     scratch = torch.full((max(1, k.attention_scratch_floats(T_, hq, hd, n_splits)),), float("nan"), device=DEV)
     if kernel == "decode":
         assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
-        k.attention_decode(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
-                           torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
-                           window, n_splits, scratch)
+        # even slice counts let the last slice combine (counters), odd ones use the second kernel
+        cnt = torch.zeros(T_ * hkv * ((hq // hkv + 3) // 4), dtype=torch.int32, device=DEV) if n_splits % 2 == 0 else None
+        for _ in range(2):      # twice: the counters must be left ready for the next call
+            out.fill_(float("nan"))
+            k.attention_decode(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                               torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
+                               window, n_splits, scratch, cnt)
+        assert cnt is None or int(cnt.abs().sum()) == 0
     else:
         k.attention(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
                     max(t[2] for t in tiles), torch.tensor(slots, dtype=torch.int32, device=DEV),
