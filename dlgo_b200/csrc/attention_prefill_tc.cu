@@ -1,0 +1,420 @@
+// Causal grouped-query attention for prompts on the Blackwell tensor cores (bfloat16, head size 64
+// or 128).
+//
+// Same formulas as attention.cu (models/llm/forward_batch.go:188-207: every prompt position attends
+// the keys t <= its position, read back from the cache; softmax in fp32).  A CTA takes up to 128
+// consecutive tokens of one sequence and one query head, and walks the sequence's pages 128 keys
+// (two pages) at a time:
+//   warp 0     TMA: the query tile once, then key and value pages into a two-stage ring
+//   warp 1     tcgen05.mma: S = Q K^T (128 x 128, fp32 in tensor memory), then O_blk = P V
+//   warps 2-5  one thread per query row: reads S from tensor memory, masks, keeps the running
+//              maximum and sum (fp32, exp2 on pre-scaled scores), writes P as bf16 into shared
+//              memory in the swizzled layout the tensor core reads, then adds O_blk into its
+//              row's fp32 accumulator in registers with the softmax correction
+// Values are read as the MN-major operand straight from the page layout [key][head_dim].
+// Keys that were never written (the tail of the last page, pages a window has given back) get
+// probability zero; their value rows are zeroed in shared memory so that 0 * garbage cannot
+// become NaN.
+#include <math.h>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace dlgo {
+
+using namespace sm100;
+
+constexpr int PF_THREADS = 192;
+constexpr int PF_ROWS = 128;   // query rows per CTA
+constexpr int PF_KEYS = 128;   // keys per step (two pages of 64)
+
+__device__ int g_attention_tc_error = 0;
+
+struct PfParams {
+  const int* tiles;       // [n_tiles][3]: sequence, first packed token, count (<= 128)
+  const int* seq_slot;
+  const int* token_pos;
+  const int* page_table;
+  int max_pages;
+  __nv_bfloat16* out;
+  int ldo;
+  int Hq, Hkv, window;
+  float scale_log2e;      // score scale times log2(e)
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// MN-major operand (rows of 128 bytes = 64 contiguous N elements, 8 K-rows per 1024-byte group),
+// 128-byte swizzle; `lbo_bytes` is the distance between 64-element N blocks.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PfParams p) {
+  constexpr int NCH = HD / 64;                 // 64-wide chunks of the head
+  constexpr int QBYTES = NCH * 16384;          // [128 rows][HD]
+  constexpr int KVBYTES = NCH * 16384;         // [128 keys][HD] per stage
+  constexpr int PBYTES = 2 * 16384;            // [128 rows][128 keys]
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t O_COL = 128;
+  // the swizzled tiles want 1024-byte alignment; the kernel has no static shared memory, so the
+  // dynamic window starts aligned (checked: a misaligned start ends the kernel with the error word set)
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(&g_attention_tc_error, 1);
+    return;
+  }
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + QBYTES;                 // 2 stages
+  uint8_t* v_s = k_s + 2 * KVBYTES;            // 2 stages
+  uint8_t* p_s = v_s + 2 * KVBYTES;
+  uint64_t* bars = (uint64_t*)(p_s + PBYTES);
+  uint64_t* qfull = bars;          // 1
+  uint64_t* kfull = bars + 1;      // 2
+  uint64_t* vfull = bars + 3;      // 2
+  uint64_t* kvempty = bars + 5;    // 2
+  uint64_t* s_full = bars + 7;
+  uint64_t* s_free = bars + 8;
+  uint64_t* p_full = bars + 9;
+  uint64_t* o_full = bars + 10;
+  uint64_t* o_free = bars + 11;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const int kvh = head / G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qfull, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kfull[s], 1);
+      mbar_init(&vfull[s], 1);
+      mbar_init(&kvempty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 128);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    mbar_init(o_free, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();
+  const int tile = blockIdx.x;
+  const int seq = p.tiles[3 * tile], tok0 = p.tiles[3 * tile + 1], ntok = p.tiles[3 * tile + 2];
+  const int slot = p.seq_slot[seq];
+  const int pos0 = p.token_pos[tok0];
+  const int t_end = pos0 + ntok;                                  // one past the last key any row sees
+  const int t_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int first_live_page = t_begin / 64;                       // pages before it may have been given back
+  const int kb_first = t_begin / PF_KEYS, kb_last = (t_end - 1) / PF_KEYS;
+  const int nblk = kb_last - kb_first + 1;
+  const int last_page = (t_end - 1) / 64;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(qfull, QBYTES);
+      for (int j = 0; j < NCH; ++j) tma_load_2d(q_s + j * 16384, &map_q, qfull, head * HD + j * 64, tok0);
+      for (int it = 0; it < nblk; ++it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(&kvempty[st], ((it >> 1) - 1) & 1, abort_flag)) break;
+        const int pg0 = (kb_first + it) * 2;
+        int pages[2];
+        int nload = 0;
+        for (int h = 0; h < 2; ++h) {
+          const int pg = pg0 + h;
+          pages[h] = (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
+          if (pages[h] >= 0) ++nload;
+        }
+        mbar_expect_tx(&kfull[st], nload * NCH * 8192);
+        mbar_expect_tx(&vfull[st], nload * NCH * 8192);
+        for (int h = 0; h < 2; ++h) {
+          if (pages[h] < 0) continue;
+          const int row = (pages[h] * p.Hkv + kvh) * 64;
+          for (int j = 0; j < NCH; ++j) {
+            tma_load_2d(k_s + st * KVBYTES + j * 16384 + h * 8192, &map_k, &kfull[st], j * 64, row);
+            tma_load_2d(v_s + st * KVBYTES + j * 16384 + h * 8192, &map_v, &vfull[st], j * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(PF_ROWS, PF_KEYS);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(PF_ROWS, HD) | (1u << 16);   // B is MN-major
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      bool ok = mbar_wait(qfull, 0, abort_flag) && mbar_wait(&kfull[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(k_s);
+#pragma unroll
+        for (int j = 0; j < NCH; ++j)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
+                      umma_desc_k_sw128(k_addr + j * 16384) + 2 * k, idesc_s, (j | k) != 0);
+        umma_commit(s_full);
+      }
+      for (int it = 0; ok && it < nblk; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(p_full, it & 1, abort_flag) && mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
+        if (ok && it > 0) ok = mbar_wait(o_free, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(v_s + st * KVBYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr + (kk >> 2) * 16384) + 2 * (kk & 3),
+                    umma_desc_mn_sw128(v_addr + kk * 2048, 16384), idesc_o, kk != 0);
+        umma_commit(o_full);
+        umma_commit(&kvempty[st]);
+        if (it + 1 < nblk) {
+          const int st2 = (it + 1) & 1;
+          ok = mbar_wait(&kfull[st2], ((it + 1) >> 1) & 1, abort_flag) && mbar_wait(s_free, it & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t k_addr = smem_u32(k_s + st2 * KVBYTES);
+#pragma unroll
+          for (int j = 0; j < NCH; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
+                        umma_desc_k_sw128(k_addr + j * 16384) + 2 * k, idesc_s, (j | k) != 0);
+          umma_commit(s_full);
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;            // query row of the tile and key row of a stage
+    const int pos_r = pos0 + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float acc[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) acc[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int it = 0; ok && it < nblk; ++it) {
+      const int st = it & 1;
+      const int k0 = (kb_first + it) * PF_KEYS;
+      // value rows of keys that were never written, or whose page was not loaded, must be zero
+      {
+        const int t = k0 + r;
+        if (t >= t_end || (t >> 6) < first_live_page) {
+          ok = mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
+          uint8_t* row = v_s + st * KVBYTES + (r >> 6) * 8192 + (r & 63) * 128;
+#pragma unroll
+          for (int j = 0; j < NCH; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row + j * 16384 + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (ok) ok = mbar_wait(s_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
+      // pass 1: the row's maximum over this block
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c0 = 0; c0 < PF_KEYS; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(lane_addr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int t = k0 + c0 + j;
+          if (t <= pos_r && t > lo) mx = fmaxf(mx, v[j] * p.scale_log2e);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+      const float mref = (m_new == -INFINITY) ? 0.f : m_new;
+      m = m_new;
+      // pass 2: probabilities, their sum, and P as bf16 in the swizzled K-major layout
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < PF_KEYS; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(lane_addr + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int t = k0 + c0 + j;
+          const float pr = (t <= pos_r && t > lo) ? fast_exp2(v[j] * p.scale_log2e - mref) : 0.f;
+          // the sum is taken over the rounded values the tensor core will use
+          const float prb = __bfloat162float(__float2bfloat16_rn(pr));
+          v[j] = prb;
+          sum += prb;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int ch = (c0 >> 3) + q4;                          // 8-key chunk index 0..15
+          __nv_bfloat162 h[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
+          uint8_t* dst = p_s + (ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+        }
+      }
+      l = l * corr + sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor core
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      mbar_arrive(s_free);
+      // O_blk -> registers with the correction of this block
+      ok = mbar_wait(o_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(lane_addr + O_COL + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf(acc[c0 + j], corr, v[j]);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(o_free);
+    }
+    if (ok && r < ntok) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* o = p.out + (size_t)(tok0 + r) * p.ldo + (size_t)head * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[c * 8 + 2 * e] * inv, acc[c * 8 + 2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(o + c * 8) = *reinterpret_cast<uint4*>(h);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_attention_tc_error, 1);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int make_map(CUtensorMap* m, const void* base, long long rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return DLGO_ERR_DRIVER;
+  if (((uintptr_t)base & 15) != 0 || (ld % 8) != 0) return DLGO_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
+}
+
+template <int HD>
+int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int n_tiles,
+              cudaStream_t stream) {
+  constexpr int SMEM = (HD / 64) * 16384 * 5 + 2 * 16384 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  launch_kernel(attention_prefill_tc_kernel<HD>, dim3(n_tiles, p.Hq), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernel takes these sizes (bf16, head size 64 or 128, pages of 64 keys)
+DLGO_EXPORT int dlgo_attention_prefill_tc_takes(int dtype, int hd, int page_size) {
+  return dtype == DLGO_BF16 && (hd == 64 || hd == 128) && page_size == 64;
+}
+
+// q[T, .] bf16 with row stride ldq (head h at column h*hd); pages [n_pages, Hkv, 64, hd] bf16;
+// tiles[n_tiles][3] of at most 128 tokens each; out[T, Hq*hd] bf16 with row stride ldo.
+DLGO_EXPORT int dlgo_attention_prefill_tc(const void* q, int T, int ldq, const void* kpages, const void* vpages,
+                                          int n_pages, const int* page_table, int max_pages, const int* tiles,
+                                          int n_tiles, const int* seq_slot, const int* token_pos, void* out, int ldo,
+                                          int Hq, int Hkv, int hd, int window, float scale, cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return DLGO_OK;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || !(hd == 64 || hd == 128) || Hq > 65535) return DLGO_ERR_SIZE;
+  if (ldo % 8 || ((uintptr_t)out & 15)) return DLGO_ERR_ALIGN;
+  CUtensorMap mq, mk, mv;
+  int st = make_map(&mq, q, T, Hq * hd, ldq, 128);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mk, kpages, (long long)n_pages * Hkv * 64, hd, hd, 64);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mv, vpages, (long long)n_pages * Hkv * 64, hd, hd, 64);
+  if (st != DLGO_OK) return st;
+  PfParams p;
+  p.tiles = tiles; p.seq_slot = seq_slot; p.token_pos = token_pos; p.page_table = page_table; p.max_pages = max_pages;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  if (hd == 64) return launch_pf<64>(mq, mk, mv, p, n_tiles, stream);
+  return launch_pf<128>(mq, mk, mv, p, n_tiles, stream);
+}
+
+DLGO_EXPORT int dlgo_attention_tc_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attention_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_attention_tc_error, &zero, sizeof(int));
+  return v;
+}

@@ -298,10 +298,12 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
 
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait on the device since the last check (synchronises)."""
-    if "gemm_tc" in build._loaded:
-        v = build._loaded["gemm_tc"].dlgo_gemm_tc_error()
-        if v != 0:
-            raise KernelError("a tensor-core kernel gave up a bounded wait on the device; its results are invalid")
+    for lib, fn in (("gemm_tc", "dlgo_gemm_tc_error"), ("attention_prefill_tc", "dlgo_attention_tc_error")):
+        if lib in build._loaded:
+            v = getattr(build._loaded[lib], fn)()
+            if v != 0:
+                raise KernelError(f"a tensor-core kernel ({lib}) gave up a bounded wait on the device; "
+                                  "its results are invalid")
 
 
 # ------------------------------------------------------------ decode attention
@@ -337,4 +339,32 @@ def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vp
         _ptr(counters), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]), _i(n_splits), _i(window),
         _f(scale), _stream())
     _check(st, "attention_decode", 2 if (n_splits > 1 and counters is None) else 1)
+    return out
+
+
+# ------------------------------------------------------ tensor-core prefill attention
+PREFILL_TC_TILE = 128
+
+
+def attention_prefill_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64
+
+
+def attention_prefill_tc(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor, vpages: torch.Tensor,
+                         page_table: torch.Tensor, tiles: torch.Tensor, seq_slot: torch.Tensor,
+                         token_pos: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                         scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of packed prompt tokens on the tensor cores; tiles hold at most 128 tokens each."""
+    _need(out, torch.bfloat16, "out")
+    _need(kpages, torch.bfloat16, "kpages")
+    _need(vpages, torch.bfloat16, "vpages")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc: q must be bfloat16")
+    for n, t in (("page_table", page_table), ("tiles", tiles), ("seq_slot", seq_slot), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    st = _lib("attention_prefill_tc").dlgo_attention_prefill_tc(
+        _ptr(q), _i(T), _i(ldq), _ptr(kpages), _ptr(vpages), _i(kpages.shape[0]), _ptr(page_table),
+        _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _ptr(seq_slot), _ptr(token_pos), _ptr(out),
+        _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(window), _f(scale), _stream())
+    _check(st, "attention_prefill_tc")
     return out

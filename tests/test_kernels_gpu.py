@@ -186,7 +186,18 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
         off += n
     out = torch.full((T_, hq * hd), float("nan"), dtype=DT[dtype], device=DEV)
     scratch = torch.full((max(1, k.attention_scratch_floats(T_, hq, hd, n_splits)),), float("nan"), device=DEV)
-    if kernel == "decode":
+    if kernel == "prefill_tc":
+        tl, off = [], 0
+        for i, (s_, n) in enumerate(seqs):
+            for b0 in range(0, n, 128):
+                tl.append((i, off + b0, min(128, n - b0)))
+            off += n
+        k.attention_prefill_tc(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tl, dtype=torch.int32, device=DEV),
+                               torch.tensor(slots, dtype=torch.int32, device=DEV),
+                               torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
+                               window)
+        k.check_device_errors()
+    elif kernel == "decode":
         assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
         # even slice counts let the last slice combine (counters), odd ones use the second kernel
         cnt = torch.zeros(T_ * hkv * ((hq // hkv + 3) // 4), dtype=torch.int32, device=DEV) if n_splits % 2 == 0 else None
@@ -288,6 +299,43 @@ def test_attention_decode_kernel_sizes(dtype, hq, hkv, hd):
         out, ref = _attention_case(dtype, hq, hkv, hd, [(500, 1), (0, 1), (65, 1)], n_splits=n_splits, decode=True,
                                    kernel="decode")
         torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(8, 2, 64), (3, 1, 128), (4, 4, 64)])
+@pytest.mark.parametrize("seqs", [[(0, 1)], [(0, 70)], [(0, 128)], [(0, 129)], [(0, 300), (0, 5)], [(60, 9), (129, 1), (0, 200)],
+                                  [(200, 130)], [(0, 700)]])
+def test_attention_prefill_on_the_tensor_cores(hq, hkv, hd, seqs):
+    out, ref = _attention_case("bfloat16", hq, hkv, hd, seqs, kernel="prefill_tc")
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 500, 639])
+def test_attention_prefill_tc_finds_one_far_key(far):
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[far, :, 0] = 12.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    out, ref = _attention_case("bfloat16", 4, 2, 64, [(0, 700)], special=special, kernel="prefill_tc")
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=2e-2)
+    assert float(ref[650].abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_prefill_tc_window_and_dead_pages(hd):
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[201, :, 0] = 12.0
+            Vf[201] = 7.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    out, ref = _attention_case("bfloat16", 4, 2, hd, [(250, 140)], window=100, special=special, dead_pages=True,
+                               kernel="prefill_tc")
+    torch.testing.assert_close(out, ref, atol=3e-2, rtol=2e-2)
 
 
 def test_attention_refuses_sizes_it_does_not_take():
