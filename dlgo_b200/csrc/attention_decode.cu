@@ -262,22 +262,63 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
   __syncthreads();
   if (!sm_last) return;
   __threadfence();
+  // Weights of the slices first (one round trip for all of them, through shared memory), then the
+  // weighted sum with several slices' loads in flight: no load waits on a branch.
+  float* w_s = &sm_acc[0][0][0];                 // [GC][n_splits] weights, then [GC] 1 / denominators
+  const int NS = p.n_splits;
+  const bool fits = GC * (NS + 1) <= DEC_WARPS * DEC_GMAX * HD;
+  if (fits) {
+    for (int idx = threadIdx.x; idx < GC * NS; idx += DEC_THREADS) {
+      const int g = idx / NS, sp = idx - g * NS;
+      const size_t o = ((size_t)b * p.Hq + kvh * G + g0 + g) * NS + sp;
+      w_s[idx] = __ldcg(&p.part_ml[o * 2]);      // the slice's maximum for now
+    }
+    __syncthreads();
+    if (threadIdx.x < GC) {
+      const int g = threadIdx.x;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < NS; ++sp) mm = fmaxf(mm, w_s[g * NS + sp]);
+      float ll = 0.f;
+      const size_t o = ((size_t)b * p.Hq + kvh * G + g0 + g) * NS;
+      for (int sp = 0; sp < NS; ++sp) {
+        const float ms = w_s[g * NS + sp];
+        const float c = (ms == -INFINITY) ? 0.f : expf(ms - mm);
+        w_s[g * NS + sp] = c;
+        ll = fmaf(c, __ldcg(&p.part_ml[(o + sp) * 2 + 1]), ll);
+      }
+      w_s[GC * NS + g] = 1.0f / ll;
+    }
+    __syncthreads();
+  }
   for (int idx = threadIdx.x; idx < GC * HD; idx += DEC_THREADS) {
     const int g = idx / HD, d = idx - g * HD;
     const int head = kvh * G + g0 + g;
-    const size_t o = ((size_t)b * p.Hq + head) * p.n_splits;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < p.n_splits; ++sp) mm = fmaxf(mm, __ldcg(&p.part_ml[(o + sp) * 2]));
-    float a = 0.f, ll = 0.f;
-    for (int sp = 0; sp < p.n_splits; ++sp) {
-      const float ms = __ldcg(&p.part_ml[(o + sp) * 2]);
-      if (ms != -INFINITY) {
-        const float c = expf(ms - mm);
+    const size_t o = ((size_t)b * p.Hq + head) * NS;
+    float a = 0.f, inv;
+    if (fits) {
+      int sp = 0;
+      for (; sp + 4 <= NS; sp += 4) {
+        const float x0 = __ldcg(&p.part_acc[(o + sp) * HD + d]), x1 = __ldcg(&p.part_acc[(o + sp + 1) * HD + d]);
+        const float x2 = __ldcg(&p.part_acc[(o + sp + 2) * HD + d]), x3 = __ldcg(&p.part_acc[(o + sp + 3) * HD + d]);
+        a = fmaf(w_s[g * NS + sp], x0, a);
+        a = fmaf(w_s[g * NS + sp + 1], x1, a);
+        a = fmaf(w_s[g * NS + sp + 2], x2, a);
+        a = fmaf(w_s[g * NS + sp + 3], x3, a);
+      }
+      for (; sp < NS; ++sp) a = fmaf(w_s[g * NS + sp], __ldcg(&p.part_acc[(o + sp) * HD + d]), a);
+      inv = w_s[GC * NS + g];
+    } else {
+      float mm = -INFINITY, ll = 0.f;
+      for (int sp = 0; sp < NS; ++sp) mm = fmaxf(mm, __ldcg(&p.part_ml[(o + sp) * 2]));
+      for (int sp = 0; sp < NS; ++sp) {
+        const float ms = __ldcg(&p.part_ml[(o + sp) * 2]);
+        const float c = (ms == -INFINITY) ? 0.f : expf(ms - mm);
         a = fmaf(c, __ldcg(&p.part_acc[(o + sp) * HD + d]), a);
         ll = fmaf(c, __ldcg(&p.part_ml[(o + sp) * 2 + 1]), ll);
       }
+      inv = 1.0f / ll;
     }
-    ((T*)p.out)[(size_t)b * p.ldo + (size_t)head * HD + d] = from_float<T>(a / ll);
+    ((T*)p.out)[(size_t)b * p.ldo + (size_t)head * HD + d] = from_float<T>(a * inv);
   }
 }
 

@@ -48,6 +48,47 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(xr[i] * s * w[i]);
 }
 
+// ------------------------------------------- residual += sum of partials, then RMSNorm
+// The contraction before a residual add may leave its K-slices unsummed ([S][T][d] fp32).  This
+// kernel adds them to the residual in slice order (models/llm/forward.go:163,169), writes the
+// residual back, and normalises the new row in the same pass (ops/norm.go:10-32).  With
+// `w == nullptr` it only settles the sum.  One block per row; `rows` picks the rows to do.
+template <typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ parts, int S, size_t part_stride,
+                                   const float* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
+                                   int d, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row_s[];   // the new row, kept for the second pass
+  __shared__ float scratch[32];
+  __shared__ float scale_s;
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * d;
+  const float* pr = parts + (size_t)src * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = xr[i];
+    int s = 0;
+    for (; s + 4 <= S; s += 4) {   // four slices in flight, added in order
+      const float a = pr[(size_t)s * part_stride + i], b = pr[(size_t)(s + 1) * part_stride + i];
+      const float c = pr[(size_t)(s + 2) * part_stride + i], e = pr[(size_t)(s + 3) * part_stride + i];
+      v = (((v + a) + b) + c) + e;
+    }
+    for (; s < S; ++s) v += pr[(size_t)s * part_stride + i];
+    xr[i] = v;
+    row_s[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (w == nullptr) return;
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+  __syncthreads();
+  const float sc = scale_s;
+  TO* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(row_s[i] * sc * w[i]);
+}
+
 // ------------------------------------------------------------------- SwiGLU
 // in: [T, 2F] with the gate in columns [0, F) and the up projection in [F, 2F).
 template <typename T>
@@ -112,5 +153,28 @@ DLGO_EXPORT int dlgo_swiglu(const void* in, void* out, int dtype, int T, int F, 
                                                                  total);
   else
     return DLGO_ERR_DTYPE;
+  return launch_status();
+}
+
+// x[*, d] f32 (updated in place), parts[S][*, d] f32 (slice stride part_stride floats), w[d] f32 or null,
+// out[R, d] (f32 or bf16, unused when w is null); rows[R] int32 or null
+DLGO_EXPORT int dlgo_add_rmsnorm(float* x, const float* parts, int S, long long part_stride, const float* w,
+                                 void* out, int out_dtype, const int* rows, int R, int d, float eps,
+                                 cudaStream_t stream) {
+  if (R <= 0) return DLGO_OK;
+  if (d <= 0 || S < 0 || (size_t)d * sizeof(float) > 200 * 1024) return DLGO_ERR_SIZE;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  const size_t smem = (size_t)d * sizeof(float);
+  if (out_dtype == DLGO_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(add_rmsnorm_kernel<float>, dim3(R), dim3(threads), smem, stream, x, parts, S, (size_t)part_stride, w,
+                  (float*)out, rows, d, eps);
+  } else if (out_dtype == DLGO_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(add_rmsnorm_kernel<__nv_bfloat16>, dim3(R), dim3(threads), smem, stream, x, parts, S,
+                  (size_t)part_stride, w, (__nv_bfloat16*)out, rows, d, eps);
+  } else {
+    return DLGO_ERR_DTYPE;
+  }
   return launch_status();
 }

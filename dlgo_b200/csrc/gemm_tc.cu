@@ -32,7 +32,7 @@ namespace dlgo {
 
 using namespace sm100;
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4 };
 
 constexpr int TILE_M = 128;
 constexpr int TILE_K = 64;  // 128 bytes of bf16: one swizzle row
@@ -252,7 +252,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int NV = BN >= 32 ? 32 : 16;
     const int ntiles = gridDim.x * gridDim.y;
     const int tile_lin = tile_b * gridDim.x + tile_a;
-    if (p.splits == 1) {
+    if (p.epilogue == TC_PARTIAL) {
+      // every K-slice leaves its fp32 partial in out[split][col][row] (transposed tiles only); whoever
+      // reads the result next adds the slices in order.  No ticket, no second pass here.
+      float* dst = (float*)p.out + (size_t)split * p.Rb * p.ldo;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += NV) {
+        float v[NV];
+        if (ok && nkb > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) v[j] = 0.f;
+        }
+        if (row < p.Ra) {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const int col = tile_b * BN + c0 + j;
+            if (col < p.Rb) dst[(size_t)col * p.ldo + row] = v[j];
+          }
+        }
+      }
+    } else if (p.splits == 1) {
       if (ok) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += NV) {
@@ -297,10 +320,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           float v[NV];
 #pragma unroll
           for (int j = 0; j < NV; ++j) v[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* src = p.workspace + ((size_t)s * ntiles + tile_lin) * (size_t)(BN * TILE_M);
+          // partials are added in slice order (the sum does not depend on which CTA came last), but
+          // four slices' loads are in flight at a time so the L2 round trips overlap
+          const size_t stride = (size_t)ntiles * (size_t)(BN * TILE_M);
+          const float* src0 = p.workspace + (size_t)tile_lin * (size_t)(BN * TILE_M) + (size_t)c0 * TILE_M + r_in;
+          int s = 0;
+          for (; s + 4 <= p.splits; s += 4) {
+            float t0[NV], t1[NV], t2[NV], t3[NV];
 #pragma unroll
-            for (int j = 0; j < NV; ++j) v[j] += __ldcg(&src[(size_t)(c0 + j) * TILE_M + r_in]);
+            for (int j = 0; j < NV; ++j) {
+              t0[j] = __ldcg(src0 + (size_t)(s + 0) * stride + (size_t)j * TILE_M);
+              t1[j] = __ldcg(src0 + (size_t)(s + 1) * stride + (size_t)j * TILE_M);
+              t2[j] = __ldcg(src0 + (size_t)(s + 2) * stride + (size_t)j * TILE_M);
+              t3[j] = __ldcg(src0 + (size_t)(s + 3) * stride + (size_t)j * TILE_M);
+            }
+#pragma unroll
+            for (int j = 0; j < NV; ++j) v[j] = (((v[j] + t0[j]) + t1[j]) + t2[j]) + t3[j];
+          }
+          for (; s < p.splits; ++s) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) v[j] += __ldcg(src0 + (size_t)s * stride + (size_t)j * TILE_M);
           }
           epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
         }
@@ -399,7 +438,8 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 }
 
 // A[Ra, K] (row stride lda) and B[Rb, K] (row stride ldb) in bf16; out per `transposed` and `epilogue`
-// (0 store bf16, 1 store f32, 2 add into f32, 3 SwiGLU to bf16); bn in {16, 32, 64, 128, 256}.
+// (0 store bf16, 1 store f32, 2 add into f32, 3 SwiGLU to bf16, 4 partials: out is fp32
+// [splits][Rb][ldo] and slice s writes out[s][col][row], transposed only); bn in {16, 32, 64, 128, 256}.
 // static_operand: 1 if A, 2 if B holds weights that no kernel launched before this one writes (their
 // tiles are then requested before the kernel waits for its predecessor), else 0.
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
@@ -407,9 +447,10 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
                              int* counters, int static_operand, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
-  if (epilogue < 0 || epilogue > 3) return DLGO_ERR_SIZE;
+  if (epilogue < 0 || epilogue > 4) return DLGO_ERR_SIZE;
   if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
-  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return DLGO_ERR_SIZE;
+  if (epilogue == TC_PARTIAL && !transposed) return DLGO_ERR_SIZE;
+  if (splits > 1 && epilogue != TC_PARTIAL && (workspace == nullptr || counters == nullptr)) return DLGO_ERR_SIZE;
   if (epilogue == TC_SWIGLU) {
     const int weight_rows = transposed ? Ra : Rb;
     if (weight_rows % 32 || (!transposed && bn < 32)) return DLGO_ERR_SIZE;

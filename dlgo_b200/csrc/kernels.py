@@ -103,6 +103,28 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, parts: torch.Tensor, w: Optional[torch.Tensor], eps: float,
+                out_dtype: Optional[torch.dtype], rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``x += parts.sum(0)`` (slices in order, in place), then RMSNorm of the new rows; with ``w`` None
+    only the sum.  ``parts`` is [S, T, d] fp32."""
+    _need(x, torch.float32, "x")
+    if parts.dtype != torch.float32 or parts.dim() != 3 or parts.stride(2) != 1 or parts.stride(1) != x.shape[1]:
+        raise KernelError("add_rmsnorm: parts must be [S, T, d] float32 with contiguous rows")
+    d = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    out = None
+    if w is not None:
+        _need(w, torch.float32, "w")
+        out = torch.empty((R, d), dtype=out_dtype, device=x.device)
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    st = _lib("elementwise").dlgo_add_rmsnorm(
+        _ptr(x), _ptr(parts), _i(parts.shape[0]), _ll(parts.stride(0)), _ptr(w), _ptr(out),
+        _i(dtype_code(out_dtype) if w is not None else F32), _ptr(rows), _i(R), _i(d), _f(eps), _stream())
+    _check(st, "add_rmsnorm")
+    return out
+
+
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """[T, 2F] (gate | up) -> [T, F]."""
     _need(gate_up, None, "gate_up")
@@ -150,8 +172,12 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE,
 def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos: torch.Tensor,
                 token_seq: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
                 kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                rotary_dim: int, interleaved: bool, write_cache: bool = True) -> None:
-    """Rotate q (in place) and k, and store k and v at their positions' pages."""
+                rotary_dim: int, interleaved: bool, write_cache: bool = True,
+                parts: Optional[torch.Tensor] = None) -> None:
+    """Rotate q (in place) and k, and store k and v at their positions' pages.
+
+    ``parts`` ([S, T, ld] fp32): the projection's unsummed K-slices; they are added here and ``qkv``
+    only receives the rotated q."""
     _need(qkv, None, "qkv")
     _need(cos, torch.float32, "cos")
     _need(sin, torch.float32, "sin")
@@ -165,7 +191,8 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
         _ptr(qkv), _i(dtype_code(qkv.dtype)), _i(T), _i(qkv.stride(0)), _ptr(cos), _ptr(sin), _ptr(token_pos),
         _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages), _ptr(vpages),
         _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim), _i(page_size), _i(1 if interleaved else 0),
-        _i(1 if write_cache else 0), _stream())
+        _i(1 if write_cache else 0), _ptr(parts), _i(0 if parts is None else parts.shape[0]),
+        _ll(0 if parts is None else parts.stride(0)), _stream())
     _check(st, "rope_append")
 
 
@@ -256,7 +283,7 @@ def uniform(seed: int, draw: torch.Tensor, request: torch.Tensor) -> torch.Tenso
 
 
 # ------------------------------------------------------- tensor-core contraction
-TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU = 0, 1, 2, 3
+TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_PARTIAL = 0, 1, 2, 3, 4
 TC_TILE_M, TC_TILE_K = 128, 64
 
 
@@ -284,13 +311,29 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         raise KernelError(f"gemm_tc: a has K={k}, b has K={k2}")
     if out.stride(-1) != 1:
         raise KernelError("gemm_tc: out must have unit inner stride")
-    if splits > 1:
+    if splits > 1 and epilogue != TC_PARTIAL:
         need = gemm_tc_workspace_floats(ra, rb, bn, splits)
         tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
         if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
             raise KernelError(f"gemm_tc: {splits} K-slices need {need} floats of workspace and {tiles} counters")
+    if epilogue == TC_PARTIAL:
+        # out is [slices, rb, ra]: the kernel's row stride is that of one slice's rows
+        if not transposed or out.dim() != 3 or out.dtype != torch.float32 or tuple(out.shape) != (splits, rb, ra) \
+                or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
+            raise KernelError(f"gemm_tc: partials go to a float32 [{splits}, {rb}, {ra}] tensor of a transposed product")
+        ldo = out.stride(1)
+    else:
+        want_shape = (rb, ra) if transposed else (ra, rb)
+        if epilogue == TC_SWIGLU:
+            want_shape = (rb, ra // 2) if transposed else (ra, rb // 2)
+        if out.dim() != 2 or tuple(out.shape) != want_shape:
+            raise KernelError(f"gemm_tc: out must be {list(want_shape)}, is {list(out.shape)}")
+        want_dtype = torch.bfloat16 if epilogue in (TC_STORE, TC_SWIGLU) else torch.float32
+        if out.dtype != want_dtype:
+            raise KernelError(f"gemm_tc: out must be {want_dtype}")
+        ldo = out.stride(0)
     st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
-                                      _ptr(out), _i(out.stride(0)), _i(1 if transposed else 0), _i(epilogue), _i(bn),
+                                      _ptr(out), _i(ldo), _i(1 if transposed else 0), _i(epilogue), _i(bn),
                                       _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _stream())
     _check(st, "gemm_tc")
     return out

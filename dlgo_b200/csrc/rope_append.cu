@@ -9,8 +9,9 @@
 // Only the first `rot` dims of a head are rotated, the rest pass through
 // (workers.go:151-159).  The rotation is computed in fp32.
 //
-// qkv[T, ld]: q heads, then k heads, then v heads, `hd` elements each.  q is
-// rotated in place; k (rotated) and v go to the page of their position:
+// qkv[T, ld]: q heads, then k heads, then v heads, `hd` elements each (or, with
+// `parts`, the unsummed fp32 K-slices [S][T][ld] of the projection, which are
+// added here; qkv then only receives the rotated q).  q is rotated in place; k (rotated) and v go to the page of their position:
 // pages[page_table[slot][pos / PS]][kv_head][pos % PS][:].
 #include "common.cuh"
 
@@ -22,7 +23,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
                                    const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                                    const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
                                    T* __restrict__ vpages, int Hq, int Hkv, int hd, int rot, int page_size,
-                                   int interleaved, int write_cache) {
+                                   int interleaved, int write_cache, const float* __restrict__ parts, int S,
+                                   size_t part_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -51,7 +53,20 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
       i0 = rot + 2 * (i - rhalf);
       i1 = i0 + 1;
     }
-    float x0 = to_float(h[i0]), x1 = to_float(h[i1]);
+    float x0, x1;
+    if (parts != nullptr) {
+      // the projection left its K-slices unsummed ([S][T][ld] fp32): add them in order here
+      const float* pp = parts + (size_t)t * ld + (size_t)head * hd;
+      x0 = 0.f;
+      x1 = 0.f;
+      for (int sp = 0; sp < S; ++sp) {
+        x0 += pp[(size_t)sp * part_stride + i0];
+        x1 += pp[(size_t)sp * part_stride + i1];
+      }
+    } else {
+      x0 = to_float(h[i0]);
+      x1 = to_float(h[i1]);
+    }
     if (head < Hq + Hkv && rotate) {
       const float c = cos_t[(size_t)pos * rhalf + i], s = sin_t[(size_t)pos * rhalf + i];
       const float y0 = x0 * c - x1 * s;
@@ -80,7 +95,7 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
                                  const int* token_pos, const int* token_seq, const int* seq_slot,
                                  const int* page_table, int max_pages, void* kpages, void* vpages, int Hq, int Hkv,
                                  int hd, int rot, int page_size, int interleaved, int write_cache,
-                                 cudaStream_t stream) {
+                                 const float* parts, int S, long long part_stride, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
   if (hd <= 0 || hd % 2 || rot < 0 || rot > hd || rot % 2 || Hq <= 0 || Hkv <= 0 || page_size <= 0 ||
       ld < (Hq + 2 * Hkv) * hd)
@@ -90,11 +105,13 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
   if (dtype == DLGO_F32)
     launch_kernel(rope_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot,
                                                          page_table, max_pages, (float*)kpages, (float*)vpages, Hq,
-                                                         Hkv, hd, rot, page_size, interleaved, write_cache);
+                                                         Hkv, hd, rot, page_size, interleaved, write_cache, parts, S,
+                                                         (size_t)part_stride);
   else if (dtype == DLGO_BF16)
     launch_kernel(rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 
         (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
-        (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved, write_cache);
+        (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved, write_cache, parts,
+        S, (size_t)part_stride);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

@@ -137,6 +137,7 @@ class Engine:
                 logits = decode_with_graph(self, slots, [int(t[0]) for t in tokens], starts)
             else:
                 ctx = build_context(self.runtime, tokens, slots, starts, self.max_seq_len)
+                ctx.want_identity = rows == list(range(ctx.n_tokens))
                 want_rows = (torch.tensor(rows, dtype=torch.int32).to(self.runtime.device, non_blocking=True)
                              if rows else None)
                 logits = self.model.forward(ctx, self.cache, want_rows)

@@ -29,7 +29,7 @@ class DecodeGraph:
             runtime=rt, n_tokens=batch, n_seqs=batch, token_ids=self.meta[0], token_pos=self.meta[1],
             token_seq=self.token_seq, seq_slot=self.meta[2], seq_slots_host=[0] * batch, seq_start_host=[0] * batch,
             seq_ntok_host=[1] * batch, decode=True, max_len=engine.max_seq_len, captured=True,
-            capacity=engine.max_seq_len)
+            capacity=engine.max_seq_len, want_identity=True)
         self.ctx.tiles(1)  # built before capture: a capture may not copy from pageable host memory
         self.graph = torch.cuda.CUDAGraph()
         self.logits = None

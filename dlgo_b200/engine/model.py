@@ -104,10 +104,22 @@ class CausalLM:
         """Run the step's tokens; logits [wanted, vocab] fp32 for the packed rows ``want_rows`` (int32)."""
         residual = self.embedding.forward(ctx.token_ids)
         for i, e in enumerate(self.order):
-            self.blocks[e.layer].forward(residual, ctx, cache.view(i), cache.state.view(i), self.positions)
+            blk = self.blocks[e.layer]
+            if not getattr(blk, "handles_pending", False):
+                ctx.settle(residual)
+            blk.forward(residual, ctx, cache.view(i), cache.state.view(i), self.positions)
         if want_rows is None or want_rows.numel() == 0:
+            ctx.settle(residual)
             return None
-        x = self.final_norm.forward(residual, want_rows)
+        pending = ctx.take_pending()
+        if pending is not None and ctx.want_identity and hasattr(self.final_norm, "forward_fused"):
+            # every row is wanted exactly once, so no row's slices are added twice
+            x = self.final_norm.forward_fused(residual, pending, want_rows)
+        else:
+            if pending is not None:
+                ctx.pending = pending
+                ctx.settle(residual)
+            x = self.final_norm.forward(residual, want_rows)
         return self.head.forward(x)
 
 

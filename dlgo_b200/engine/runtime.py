@@ -81,6 +81,8 @@ class StepContext:
     max_len: int                 # longest sequence after this step (host; sizes grids)
     captured: bool = False       # inside a CUDA graph: sizes must not depend on lengths
     capacity: int = 0            # longest sequence the cache can hold
+    want_identity: bool = False  # the wanted rows are exactly rows 0..T-1, each once
+    pending: Optional[torch.Tensor] = None   # fp32 [slices, T, d] still to be added to the residual stream
     _tiles: Dict[int, Tuple[torch.Tensor, int, int]] = field(default_factory=dict)
     _scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
 
@@ -111,6 +113,25 @@ class StepContext:
             self._scratch[name] = t
         return t
 
+
+    # A part whose last contraction leaves its K-slices unsummed may hand them over instead of adding
+    # them to the residual itself: the next reader of the residual (a norm that can fuse the sum, or
+    # `settle`) adds them, in slice order.
+    def defer(self, residual: torch.Tensor, parts: torch.Tensor) -> None:
+        if self.pending is not None:
+            self.settle(residual)
+        self.pending = parts
+
+    def take_pending(self) -> Optional[torch.Tensor]:
+        p, self.pending = self.pending, None
+        return p
+
+    def settle(self, residual: torch.Tensor) -> None:
+        """Add what is pending into the residual now."""
+        p = self.take_pending()
+        if p is not None:
+            from ..csrc import kernels as K
+            K.add_rmsnorm(residual, p, None, 0.0, None)
 
     def zeros(self, name: str, numel: int, dtype: torch.dtype = torch.int32) -> torch.Tensor:
         """A buffer that is zero when first handed out; kernels that use it leave it zero."""

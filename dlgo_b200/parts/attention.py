@@ -77,7 +77,12 @@ class GQAAttention(Mixer):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
         T = ctx.n_tokens
-        qkv = self.wqkv(x, STORE)
+        # few tokens: the projection leaves its K-slices unsummed and the rotation adds them
+        qkv_parts = self.wqkv.partials(x)
+        if qkv_parts is not None:
+            qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
+        else:
+            qkv = self.wqkv(x, STORE)
         if self.position_encoding is not None:
             pe = positions[self.position_encoding]
             cos, sin, rot, inter = pe.cos, pe.sin, pe.rotary_dim, pe.interleaved
@@ -85,7 +90,8 @@ class GQAAttention(Mixer):
             cos = sin = self._no_rotation
             rot, inter = 0, False
         K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
-                      cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes)
+                      cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
+                      qkv_parts)
         group = self.num_heads // self.num_kv_heads
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
@@ -121,7 +127,11 @@ class GQAAttention(Mixer):
             K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
                         ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
                         self.scale, self.window or 0, n_splits, gchunk, scratch)
-        self.wo(out, ADD_F32, residual)
+        parts = self.wo.partials(out) if hasattr(ctx, "defer") else None
+        if parts is not None:
+            ctx.defer(residual, parts)      # the next norm adds the slices to the residual
+        else:
+            self.wo(out, ADD_F32, residual)
 
 
 MIXERS.register("gqa_attention", GQAAttention)

@@ -14,12 +14,26 @@ from .base import Block, PositionEncoding
 from .registry import BLOCKS
 
 
+def norm_of(norm: Any, residual: torch.Tensor, ctx: Any) -> torch.Tensor:
+    """The norm of the residual stream, adding first whatever the previous part left pending
+    (fused into the norm's pass where the norm offers that)."""
+    pending = ctx.take_pending() if hasattr(ctx, "take_pending") else None
+    if pending is not None:
+        if hasattr(norm, "forward_fused"):
+            return norm.forward_fused(residual, pending)
+        ctx.pending = pending
+        ctx.settle(residual)
+    return norm.forward(residual)
+
+
 class PreNormBlock(Block):
+    handles_pending = True   # reads the residual only through norm_of
+
     def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
                 positions: Mapping[str, PositionEncoding]) -> None:
-        x = self.mixer_norm.forward(residual)
+        x = norm_of(self.mixer_norm, residual, ctx)
         self.mixer.forward(x, residual, ctx, cache, state, positions)
-        x = self.ffn_norm.forward(residual)
+        x = norm_of(self.ffn_norm, residual, ctx)
         self.ffn.forward(x, residual, ctx)
 
 

@@ -52,7 +52,11 @@ class SwiGLU(FeedForward):
             h = self.w_gate_up(x)
         else:
             h = K.swiglu(self.w_gate_up(x, STORE))
-        self.w_down(h, ADD_F32, residual)
+        parts = self.w_down.partials(h) if ctx is not None and hasattr(ctx, "defer") else None
+        if parts is not None:
+            ctx.defer(residual, parts)      # the next norm adds the slices to the residual
+        else:
+            self.w_down(h, ADD_F32, residual)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

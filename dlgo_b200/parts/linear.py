@@ -38,3 +38,10 @@ class Linear:
         if self._tc is not None:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
+
+    def partials(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """The product as unsummed fp32 K-slices [slices, tokens, out] where the kernel offers that
+        (few tokens on the tensor cores), else ``None``."""
+        if self._tc is not None and not self.fuses_swiglu:
+            return self._tc.partials(x)
+        return None

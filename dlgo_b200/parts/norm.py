@@ -30,4 +30,10 @@ class RMSNorm(Norm):
         return K.rmsnorm(residual, self.weight, self.eps, self.out_dtype, rows)
 
 
+    def forward_fused(self, residual: torch.Tensor, parts: torch.Tensor,
+                      rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual += parts.sum(0)`` and the norm of the new rows, in one pass."""
+        return K.add_rmsnorm(residual, parts, self.weight, self.eps, self.out_dtype, rows)
+
+
 NORMS.register("rmsnorm", RMSNorm)

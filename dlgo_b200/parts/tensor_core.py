@@ -80,6 +80,19 @@ class TensorCorePlan:
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2)
 
 
+    def partials(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
+        reads the result next adds them in order (this spares the contraction its own reduction pass).
+        ``None`` when the tokens are too many for that."""
+        t = x.shape[0]
+        if t > SKINNY_MAX or self.swiglu:
+            return None
+        bn, splits = skinny_shape(t, self.n, self.k)
+        out = torch.empty((splits, t, self.n), dtype=torch.float32, device=x.device)
+        K.gemm_tc(self.weight, x, out, True, K.TC_PARTIAL, bn, splits, static_operand=1)
+        return out
+
+
 def plan_for(weight: torch.Tensor, swiglu: bool = False) -> Optional[Callable]:
     n, k = weight.shape
     if weight.dtype != torch.bfloat16 or k % 8 or weight.stride(1) != 1 or weight.stride(0) % 8:

@@ -499,3 +499,67 @@ def test_gemm_tc_refuses_what_it_cannot_take():
         k.gemm_tc(b, b, o, False, k.TC_STORE_F32, 128, 2, ws, cnt)  # more K-slices than K blocks
     with pytest.raises(k.KernelError, match="workspace"):
         k.gemm_tc(b, b, o, False, k.TC_STORE_F32, 128, 2)           # K-slices without their workspace
+
+
+# ------------------------------------------------ partial sums handed to the next kernel
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("S,d", [(1, 50), (3, 200), (8, 2048), (9, 96)])
+def test_add_rmsnorm_settles_partials_in_order(dtype, S, d):
+    k = K()
+    torch.manual_seed(S * d)
+    x = torch.randn(6, d, device=DEV)
+    parts = torch.randn(S, 6, d, device=DEV)
+    w = 1 + 0.1 * torch.randn(d, device=DEV)
+    want = x.clone()
+    for s_ in range(S):
+        want = want + parts[s_]
+    ref = P.rmsnorm(want.cpu(), w.cpu(), 1e-5)
+    x1 = x.clone()
+    out = k.add_rmsnorm(x1, parts, w, 1e-5, DT[dtype])
+    assert torch.equal(x1, want)                                  # slices added in order: bit for bit
+    torch.testing.assert_close(out.float().cpu(), ref, **tol(dtype))
+    x2 = x.clone()
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    out2 = k.add_rmsnorm(x2, parts, w, 1e-5, DT[dtype], rows)
+    torch.testing.assert_close(out2.float().cpu(), ref[[4, 1]], **tol(dtype))
+    assert torch.equal(x2[[4, 1]], want[[4, 1]]) and torch.equal(x2[[0, 2, 3, 5]], x[[0, 2, 3, 5]])
+    x3 = x.clone()
+    assert k.add_rmsnorm(x3, parts, None, 0.0, None) is None and torch.equal(x3, want)
+
+
+@pytest.mark.parametrize("N,T_,K_,splits,bn", [(256, 5, 512, 2, 16), (384, 16, 2048, 8, 16), (130, 33, 200, 4, 64),
+                                               (128, 1, 640, 1, 16)])
+def test_gemm_tc_leaves_partials_for_the_next_kernel(N, T_, K_, splits, bn):
+    k = K()
+    torch.manual_seed(N + T_)
+    w = torch.randn(N, K_, device=DEV).to(torch.bfloat16)
+    x = torch.randn(T_, K_, device=DEV).to(torch.bfloat16)
+    parts = torch.full((splits, T_, N), float("nan"), device=DEV)
+    k.gemm_tc(w, x, parts, True, k.TC_PARTIAL, bn, splits)
+    torch.testing.assert_close(parts.sum(0), (x.double() @ w.double().t()).float(), atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
+def test_rope_append_from_partials():
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    hq, hkv, hd = 4, 2, 32
+    pe = RotaryEmbedding(hd, hd, 10000.0, 200)
+    cos, sin = (t.to(DEV) for t in pe.tables())
+    ld = (hq + 2 * hkv) * hd
+    torch.manual_seed(0)
+    parts = torch.randn(3, 2, ld, device=DEV)
+    whole = (parts[0] + parts[1] + parts[2])
+    pos = torch.tensor([5, 70], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    pt = torch.tensor([[0, -1], [1, 2]], dtype=torch.int32, device=DEV)
+    res = []
+    for use_parts in (False, True):
+        kp, vp = _paged(3, hkv, hd, "float32")
+        qkv = whole.clone() if not use_parts else torch.full((2, ld), float("nan"), device=DEV)
+        k.rope_append(qkv, cos, sin, pos, seq, slots, pt, kp, vp, hq, hkv, hd, hd, False, True, parts if use_parts else None)
+        res.append((qkv[:, :hq * hd].clone(), kp.clone(), vp.clone()))
+    assert torch.equal(res[0][0], res[1][0])
+    for a, b in zip(res[0][1:], res[1][1:]):
+        assert torch.equal(torch.nan_to_num(a, nan=-7.0), torch.nan_to_num(b, nan=-7.0))
