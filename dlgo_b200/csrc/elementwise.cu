@@ -67,18 +67,36 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   float* xr = x + (size_t)src * d;
   const float* pr = parts + (size_t)src * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float v = xr[i];
-    int s = 0;
-    for (; s + 4 <= S; s += 4) {   // four slices in flight, added in order
-      const float a = pr[(size_t)s * part_stride + i], b = pr[(size_t)(s + 1) * part_stride + i];
-      const float c = pr[(size_t)(s + 2) * part_stride + i], e = pr[(size_t)(s + 3) * part_stride + i];
-      v = (((v + a) + b) + c) + e;
+  if ((d & 3) == 0 && (part_stride & 3) == 0) {
+    // 16-byte accesses; up to eight slices' loads are in flight before the first add
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + i);
+      for (int s0 = 0; s0 < S; s0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          t[j] = (s0 + j < S) ? *reinterpret_cast<const float4*>(pr + (size_t)(s0 + j) * part_stride + i)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (s0 + j < S) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+        }
+      }
+      *reinterpret_cast<float4*>(xr + i) = v;
+      *reinterpret_cast<float4*>(row_s + i) = v;
+      ss = fmaf(v.x, v.x, ss);
+      ss = fmaf(v.y, v.y, ss);
+      ss = fmaf(v.z, v.z, ss);
+      ss = fmaf(v.w, v.w, ss);
     }
-    for (; s < S; ++s) v += pr[(size_t)s * part_stride + i];
-    xr[i] = v;
-    row_s[i] = v;
-    ss = fmaf(v, v, ss);
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float v = xr[i];
+      for (int s = 0; s < S; ++s) v += pr[(size_t)s * part_stride + i];
+      xr[i] = v;
+      row_s[i] = v;
+      ss = fmaf(v, v, ss);
+    }
   }
   if (w == nullptr) return;
   ss = block_sum(ss, scratch);
