@@ -8,7 +8,10 @@ elementary torch tensor arithmetic only.
 
 The reference's model code is Go and there is no Go toolchain on the build
 machine, so it cannot be imported or compiled for a comparison: this
-implementation rests on the formulas as read from the source.  Differences that
+implementation rests on the formulas as read from the source.  The one piece
+of the reference that does compile here, the C kernels of quant/simd_dot.c
+(softmax, SwiGLU, dot product, axpy), anchors the matching functions below
+through tests/golden/primitives.json (made by tests/golden/make_primitives.py).  Differences that
 follow from the weight layout, not from the formulas: checkpoints in the
 safetensors layout pair rotary dims (i, i + hd/2) (the reference's ``neox``
 branch, ops/rope.go:21-25), and the llama3 frequency scaling is not in the

@@ -144,3 +144,20 @@ def test_filters_match_the_reference_rules():
     k0 = torch.tensor([[1.0, 2.0]])
     apply_top_k(k0, 0); apply_top_p(k0, 1.0); apply_min_p(k0, 0.0); apply_repetition_penalty(k0, [[0]], 1.0)
     assert k0.tolist() == [[1.0, 2.0]]
+
+
+def test_plain_primitives_agree_with_the_references_own_c_kernels():
+    # tests/golden/primitives.json holds what computerex/dlgo's quant/simd_dot.c computes (made by
+    # tests/golden/make_primitives.py); its exp is a 5-digit polynomial, hence 1e-4
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "primitives.json")) as f:
+        cases = json.load(f)["cases"]
+    assert len(cases) >= 5
+    for c in cases:
+        x, g, u = (torch.tensor(c[k], dtype=torch.float32) for k in ("x", "gate", "up"))
+        torch.testing.assert_close(P.softmax(x), torch.tensor(c["softmax"]), atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(P.swiglu(g, u), torch.tensor(c["swiglu"]), atol=1e-4, rtol=2e-4)
+        assert abs(float(g @ u) - c["dot"]) <= 1e-4 * max(1.0, abs(c["dot"]))
+        # the weighted sum of values is built from this axpy (models/llm/forward.go:274-277)
+        torch.testing.assert_close(x + 0.375 * u, torch.tensor(c["scale_add_0.375"]), atol=1e-6, rtol=1e-6)
