@@ -361,6 +361,136 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Many tokens: one persistent CTA per SM walks over output tiles.  Two accumulators live in tensor
+// memory (2 x BN columns), so the epilogue of tile i (tensor memory -> registers -> global) runs
+// while the tensor core already works on tile i+1; the shared-memory ring keeps streaming across
+// tile boundaries.  Tiles are taken in an order that keeps the CTAs running at the same time on
+// the same few weight tiles (all row tiles of one column tile are neighbours), so the weights are
+// read from L2.
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          TcParams p) {
+  using C = TcConfig<BN>;
+  constexpr int STAGES = C::MAX_STAGES;
+  constexpr uint32_t TMEM_COLS = 2 * C::TMEM_COLS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;     // 2
+  uint64_t* acc_empty = acc_full + 2;      // 2
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_a = (p.Ra + TILE_M - 1) / TILE_M, tiles_b = (p.Rb + BN - 1) / BN;
+  const int n_tiles = tiles_a * tiles_b;
+  const int nkb = (p.K + TILE_K - 1) / TILE_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      pdl_wait();
+      int it = 0;  // K blocks issued so far, over all tiles
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { t = n_tiles; break; }
+          uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+          mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full[s], kb * TILE_K, tile_a * TILE_M);
+          tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[s], kb * TILE_K, tile_b * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN);
+      int it = 0, local = 0;
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have emptied this accumulator (two tiles ago)
+        if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * C::TMEM_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TILE_K / UMMA_K; ++k) umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        umma_commit(&acc_full[buf]);
+        if (!ok) break;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    pdl_wait();
+    constexpr int NV = 32;
+    int local = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++local) {
+      const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+      const int buf = local & 1;
+      const int row = tile_a * TILE_M + quarter * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += NV) {
+        float v[NV];
+        tmem_ld_32x32(tmem_base + buf * C::TMEM_COLS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_gemm_tc_error, 1);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 }  // namespace dlgo
 
 using namespace dlgo;
@@ -425,6 +555,26 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   return launch_status();
 }
 
+template <int BN>
+int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
+  using C = TcConfig<BN>;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::smem_bytes(C::MAX_STAGES));
+    if (e != cudaSuccess) { sms = 0; return (int)e; }
+  }
+  const int tiles = ((p.Ra + TILE_M - 1) / TILE_M) * ((p.Rb + BN - 1) / BN);
+  TcParams q = p;
+  q.stages = C::MAX_STAGES;
+  launch_kernel(gemm_tc_persistent_kernel<BN>, dim3(tiles < sms ? tiles : sms), dim3(TC_THREADS),
+                C::smem_bytes(C::MAX_STAGES), stream, ma, mb, q);
+  return launch_status();
+}
+
 }  // namespace
 
 // Floats of workspace and ints of counters a call with `splits` > 1 needs.
@@ -464,6 +614,10 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
+  if (!transposed && splits == 1 && (bn == 128 || bn == 256) && getenv("DLGO_GEMM_NONPERSISTENT") == nullptr) {
+    // many tokens: persistent CTAs with two accumulators in tensor memory
+    return bn == 256 ? launch_tc_persistent<256>(ma, mb, p, stream) : launch_tc_persistent<128>(ma, mb, p, stream);
+  }
   switch (bn) {
     case 16: return launch_tc<16>(ma, mb, p, stream);
     case 32: return launch_tc<32>(ma, mb, p, stream);

@@ -439,6 +439,31 @@ def test_gemm_tc_all_epilogues_both_orientations(Ra, Rb, K_, bn):
     k.check_device_errors()
 
 
+@pytest.mark.parametrize("Ra,Rb,K_,bn,epi", [(2100, 2600, 200, 256, "store"), (1300, 5000, 328, 128, "add"),
+                                             (700, 9000, 72, 256, "f32")])
+def test_gemm_tc_persistent_over_many_tiles(Ra, Rb, K_, bn, epi):
+    # more tiles than SMs: every CTA walks several tiles with its two accumulators in turn
+    k = K()
+    torch.manual_seed(Ra)
+    a = torch.randn(Ra, K_, device=DEV).to(torch.bfloat16)
+    b = torch.randn(Rb, K_, device=DEV).to(torch.bfloat16)
+    ref = _tc_ref(a, b).float()
+    if epi == "store":
+        o = torch.full((Ra, Rb), float("nan"), device=DEV, dtype=torch.bfloat16)
+        k.gemm_tc(a, b, o, False, k.TC_STORE, bn, static_operand=2)
+        torch.testing.assert_close(o.float(), ref, atol=2e-3 * math.sqrt(K_), rtol=1e-2)
+    elif epi == "add":
+        res = torch.randn(Ra, Rb, device=DEV)
+        o = res.clone()
+        k.gemm_tc(a, b, o, False, k.TC_ADD_F32, bn)
+        torch.testing.assert_close(o, res + ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    else:
+        o = torch.full((Ra, Rb), float("nan"), device=DEV)
+        k.gemm_tc(a, b, o, False, k.TC_STORE_F32, bn)
+        torch.testing.assert_close(o, ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
 @pytest.mark.parametrize("N,T_,K_,splits", [(256, 5, 512, 2), (384, 16, 2048, 8), (130, 33, 200, 4), (2048, 64, 8192, 9),
                                             (128, 1, 640, 10)])
 def test_gemm_tc_split_k_is_exact_and_repeatable(N, T_, K_, splits):
