@@ -1,0 +1,87 @@
+"""The engine at the layer sizes of Llama 3.2 1B (hidden 2048, 32/8 heads of 64, feed-forward 8192,
+vocabulary 128256, llama3 rope scaling factor 32, tied head) with FOUR layers instead of sixteen so
+that the plain implementation stays within a minute on the CPU.  These sizes take the kernels the
+tiny models never reach: the tensor-core prompt attention (head size 64), 128 x 256 GEMM tiles over
+many tiles, K-slices, a vocabulary that is no multiple of any tile.  Needs a GPU."""
+import pytest
+import torch
+
+import plain_llama as P
+import traces as T
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_layers=4, intermediate_size=8192,
+           num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256, rope_theta=500000.0,
+           rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                             original_max_position_embeddings=8192),
+           rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
+ROWS = [0, 1, 63, 64, 127, 128, 141] + list(range(142, 150))       # places compared (the last 8 are decoded)
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.weights import write_random_model
+    d = str(tmp_path_factory.mktemp("llama1b_sizes"))
+    write_random_model(config_from_dict(CFG), 2, d, device="cuda")
+    g = torch.Generator().manual_seed(3)
+    reqs = {"long": torch.randint(0, CFG["vocab_size"], (150,), generator=g).tolist(),
+            "short": torch.randint(0, CFG["vocab_size"], (21,), generator=g).tolist()}
+    cfg, w = P.read_model(d)
+    freqs = P.rope_frequencies(64, cfg["rope_theta"], cfg["rope_scaling"])
+    refs = {}
+    for rid, toks in reqs.items():
+        x = P.embedding(w["model.embed_tokens.weight"], toks)
+        for i in range(cfg["num_hidden_layers"]):
+            x = P.layer(x, w, f"model.layers.{i}.", cfg, freqs)
+        rows = [r for r in ROWS if r < len(toks)] if rid == "long" else list(range(len(toks)))
+        xn = P.rmsnorm(x[rows], w["model.norm.weight"], cfg["rms_norm_eps"])
+        refs[rid] = (rows, P.linear(xn, w["model.embed_tokens.weight"]))
+    del w
+    return d, reqs, refs
+
+
+def run(engine, reqs, refs, dtype, what):
+    long_rows = refs["long"][0]
+    n = len(reqs["long"])
+    # whole: both requests in one step; then the long one again with its last 8 tokens one by one
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": reqs["long"], "want": long_rows},
+                                      {"id": "short", "tokens": reqs["short"], "want": list(range(len(reqs["short"])))}],
+              "end": ["long", "short"]},
+             {"step": 1, "entries": [{"id": "l2", "tokens": reqs["long"][:n - 8], "want": [r for r in long_rows if r < n - 8]}],
+              "end": []}]
+    for j in range(n - 8, n):
+        steps.append({"step": len(steps), "entries": [{"id": "l2", "tokens": [reqs["long"][j]], "want": [0]}],
+                      "end": ["l2"] if j == n - 1 else []})
+    outs = T.run_in_process(engine, steps)
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    ref_long, ref_short = refs["long"][1], refs["short"][1]
+    scale = float(ref_long.abs().max())
+
+    def close(got, ref, name):
+        assert torch.isfinite(got).all(), name
+        err = float((got - ref).abs().max())
+        assert err <= tol * scale, f"{what} {name} ({dtype}): max abs diff {err:.3e} > {tol * scale:.3e}"
+
+    close(outs[0][:len(long_rows)], ref_long, "whole, long")
+    close(outs[0][len(long_rows):], ref_short, "whole, short beside it")
+    k = len([r for r in long_rows if r < n - 8])
+    close(outs[1], ref_long[:k], "prefix")
+    tail = torch.cat([outs[s] for s in range(2, 10)])
+    close(tail, ref_long[k:], "last 8 one by one")
+    from dlgo_b200.csrc import kernels
+    kernels.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_1b_sizes_against_the_plain_implementation(big, dtype):
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = big
+    eng = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256)
+    eng.cache.poison()
+    run(eng, reqs, refs, dtype, "graphs")
+    if dtype == "bfloat16":
+        eng2 = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256, cuda_graphs=False)
+        eng2.cache.poison()
+        run(eng2, reqs, refs, dtype, "no graphs")
