@@ -11,6 +11,7 @@
 //     and the values of the same tile are then streamed with the probabilities as weights;
 //   * lanes, then warps, merge their partial sums; with several slices the partial (max, sum,
 //     output) go to scratch and attention_combine_kernel finishes.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "attention_combine.cuh"
@@ -38,6 +39,16 @@ struct DecParams {
   float* part_ml;
   int* counters;         // [B * Hkv * n_gchunks] zero before the first launch and left zero, or null
   int Hq, Hkv, page_size, n_splits, n_gchunks, window;
+  // optional fusion of the rotation and the cache append (one kernel less per layer):
+  const void* qkv;       // [B, ldq] projection output (q | k | v heads) in T, or null
+  const float* parts;    // or its unsummed K-slices [S][B][ldq] fp32
+  int S;
+  size_t part_stride;
+  const float* cos_t;
+  const float* sin_t;
+  int rot, interleaved, fuse_rope, write_cache;
+  int cluster;           // 1: the slices of a (sequence, kv head) form one thread-block cluster and combine
+                         // through distributed shared memory; no scratch, no counters
   float scale;
 };
 
@@ -77,9 +88,19 @@ template <> __device__ __forceinline__ void cvt16<__nv_bfloat16>(const uint4& ra
   }
 }
 
+// exp(x) for the softmax: exact expf in the float32 path; in the bfloat16 path one ex2.approx (the
+// result is rounded to far fewer bits than it loses)
+template <typename T> __device__ __forceinline__ float soft_exp(float x);
+template <> __device__ __forceinline__ float soft_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ float soft_exp<__nv_bfloat16>(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
 // LPK lanes per key; head_dim = LPK * VEC.
 template <typename T, int LPK>
-__global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams p) {
+__global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecParams p) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int VEC = Ld16<T>::VEC;
@@ -89,6 +110,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
   __shared__ float sm_acc[DEC_WARPS][DEC_GMAX][HD];
   __shared__ float sm_ml[DEC_WARPS][DEC_GMAX][2];
   __shared__ int sm_last;
+  __shared__ float cl_acc[DEC_GMAX][HD];   // this block's merged result, read by the cluster's first block
+  __shared__ float cl_ml[DEC_GMAX][2];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK;              // which 16 bytes of the key
@@ -110,13 +133,101 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
   const int pg_e = min(pg_last + 1, pg_b + per);
 
   float q[DEC_GMAX][VEC], acc[DEC_GMAX][VEC], m[DEC_GMAX], l[DEC_GMAX];
-  const T* qrow = (const T*)p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0) * HD + sub * VEC;
+  if (!p.fuse_rope) {
+    const T* qrow = (const T*)p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0) * HD + sub * VEC;
+#pragma unroll
+    for (int g = 0; g < DEC_GMAX; ++g) {
+      if (g < GC) Ld16<T>::load(qrow + (size_t)g * HD, q[g]);
+      else
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
+    }
+  } else {
+    // The projection's output comes in unrotated (possibly as unsummed K-slices): this lane's 16
+    // bytes of a head are summed and rotated here (models/llm/forward.go:246-252), and the block
+    // whose pages hold the new position appends the token's key and value (forward.go:257).
+    auto load_vec = [&](int col, float* v) {
+      if (p.parts != nullptr) {
+        const float* src = p.parts + (size_t)b * p.ldq + col;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] = 0.f;
+        for (int sp = 0; sp < p.S; ++sp) {
+#pragma unroll
+          for (int e4 = 0; e4 < VEC; e4 += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(src + (size_t)sp * p.part_stride + e4);
+            v[e4] += t4.x; v[e4 + 1] += t4.y; v[e4 + 2] += t4.z; v[e4 + 3] += t4.w;
+          }
+        }
+      } else {
+        Ld16<T>::load((const T*)p.qkv + (size_t)b * p.ldq + col, v);
+      }
+    };
+    const int rhalf = p.rot / 2;
+    auto rotate = [&](float* v) {
+      const int d0 = sub * VEC;
+      if (p.rot == 0) return;
+      if (p.interleaved) {
+#pragma unroll
+        for (int e = 0; e < VEC; e += 2) {
+          const int i = (d0 + e) >> 1;
+          if (2 * i < p.rot) {
+            const float c = p.cos_t[(size_t)pos * rhalf + i], sn = p.sin_t[(size_t)pos * rhalf + i];
+            const float x0 = v[e], x1 = v[e + 1];
+            v[e] = x0 * c - x1 * sn;
+            v[e + 1] = x0 * sn + x1 * c;
+          }
+        }
+      } else {
+        // pairs (i, i + rot/2) with rot == head size: the partner sits LPK/2 lanes away
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[e], LPK / 2);
+          const int d = d0 + e;
+          const bool low = d < rhalf;
+          const int i = low ? d : d - rhalf;
+          const float c = p.cos_t[(size_t)pos * rhalf + i], sn = p.sin_t[(size_t)pos * rhalf + i];
+          v[e] = low ? (v[e] * c - other * sn) : (other * sn + v[e] * c);
+        }
+      }
+    };
+#pragma unroll
+    for (int g = 0; g < DEC_GMAX; ++g) {
+      if (g < GC) {
+        load_vec((kvh * G + g0 + g) * HD + sub * VEC, q[g]);
+        rotate(q[g]);
+        // the rotated query goes through the storage type, as it does on the unfused path
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) q[g][e] = to_float(from_float<T>(q[g][e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
+      }
+    }
+    const int pg_new = pos / PS;
+    if (p.write_cache && gc == 0 && pg_new >= pg_b && pg_new < pg_e) {   // block-uniform
+      if (warp == 0) {
+        float kf[VEC], vf[VEC];
+        load_vec((p.Hq + kvh) * HD + sub * VEC, kf);
+        load_vec((p.Hq + p.Hkv + kvh) * HD + sub * VEC, vf);
+        rotate(kf);
+        if (grp == 0) {
+          const int page = p.page_table[(size_t)slot * p.max_pages + pg_new];
+          const size_t o = (((size_t)page * p.Hkv + kvh) * PS + (pos % PS)) * HD + sub * VEC;
+          T* kd = (T*)p.kpages + o;
+          T* vd = (T*)p.vpages + o;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            kd[e] = from_float<T>(kf[e]);
+            vd[e] = from_float<T>(vf[e]);
+          }
+        }
+      }
+      __threadfence_block();
+      __syncthreads();   // the new row is in place before any warp of this block reads the page
+    }
+  }
 #pragma unroll
   for (int g = 0; g < DEC_GMAX; ++g) {
-    if (g < GC) Ld16<T>::load(qrow + (size_t)g * HD, q[g]);
-    else
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[g][e] = 0.f;
     m[g] = -INFINITY;
@@ -173,14 +284,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
 #pragma unroll
       for (int o = 16; o >= LPK; o >>= 1) tmax[g] = fmaxf(tmax[g], __shfl_xor_sync(0xffffffffu, tmax[g], o));
       const float m_new = fmaxf(m[g], tmax[g]);
-      const float c = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
+      const float c = (m[g] == -INFINITY) ? 0.f : soft_exp<T>(m[g] - m_new);
       m[g] = m_new;
       l[g] *= c;
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[g][e] *= c;
 #pragma unroll
       for (int it = 0; it < DEC_ITER; ++it) {
-        const float pr = (s[g][it] == -INFINITY) ? 0.f : expf(s[g][it] - m_new);
+        const float pr = (s[g][it] == -INFINITY) ? 0.f : soft_exp<T>(s[g][it] - m_new);
         s[g][it] = pr;
         l[g] += pr;
       }
@@ -240,6 +351,12 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
     const int head = kvh * G + g0 + g;
     if (p.n_splits == 1) {
       ((T*)p.out)[(size_t)b * p.ldo + (size_t)head * HD + d] = from_float<T>(a / ll);
+    } else if (p.cluster) {
+      cl_acc[g][d] = a;
+      if (d == 0) {
+        cl_ml[g][0] = mm;
+        cl_ml[g][1] = ll;
+      }
     } else {
       const size_t o = ((size_t)b * p.Hq + head) * p.n_splits + split;
       p.part_acc[o * HD + d] = a;
@@ -248,6 +365,48 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
         p.part_ml[o * 2 + 1] = ll;
       }
     }
+  }
+  if (p.n_splits > 1 && p.cluster) {
+    // The slices of this (sequence, kv head, head chunk) are the blocks of one cluster: each leaves
+    // its merged (max, sum, output) in its own shared memory, the first block reads them all through
+    // distributed shared memory and writes the result.  No global round trip, fence or ticket.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cl = cg::this_cluster();
+    cl.sync();
+    if (cl.block_rank() == 0) {
+      const int NS = p.n_splits;
+      for (int idx = threadIdx.x; idx < GC * HD; idx += DEC_THREADS) {
+        const int g = idx / HD, d = idx - g * HD;
+        float ms[8], ls[8], as[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < NS) {
+            const float* rml = cl.map_shared_rank(&cl_ml[0][0], r);
+            const float* racc = cl.map_shared_rank(&cl_acc[0][0], r);
+            ms[r] = rml[g * 2];
+            ls[r] = rml[g * 2 + 1];
+            as[r] = racc[g * HD + d];
+          } else {
+            ms[r] = -INFINITY;
+            ls[r] = 0.f;
+            as[r] = 0.f;
+          }
+        }
+        float mm = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) mm = fmaxf(mm, ms[r]);
+        float a = 0.f, ll = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const float c = (ms[r] == -INFINITY) ? 0.f : expf(ms[r] - mm);
+          a = fmaf(c, as[r], a);
+          ll = fmaf(c, ls[r], ll);
+        }
+        ((T*)p.out)[(size_t)b * p.ldo + (size_t)(kvh * G + g0 + g) * HD + d] = from_float<T>(a / ll);
+      }
+    }
+    cl.sync();   // nobody leaves while its shared memory may still be read
+    return;
   }
   if (p.n_splits == 1 || p.counters == nullptr) return;
   // the block that finishes last among the slices of this (sequence, kv head, head chunk) combines them
@@ -267,11 +426,15 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
   float* w_s = &sm_acc[0][0][0];                 // [GC][n_splits] weights, then [GC] 1 / denominators
   const int NS = p.n_splits;
   const bool fits = GC * (NS + 1) <= DEC_WARPS * DEC_GMAX * HD;
-  if (fits) {
+  float* l_sm = w_s + GC * (NS + 1);             // [GC][n_splits] the slices' sums
+  const bool fits2 = GC * (2 * NS + 1) <= DEC_WARPS * DEC_GMAX * HD;
+  if (fits && fits2) {
     for (int idx = threadIdx.x; idx < GC * NS; idx += DEC_THREADS) {
       const int g = idx / NS, sp = idx - g * NS;
       const size_t o = ((size_t)b * p.Hq + kvh * G + g0 + g) * NS + sp;
-      w_s[idx] = __ldcg(&p.part_ml[o * 2]);      // the slice's maximum for now
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(&p.part_ml[o * 2]));
+      w_s[idx] = ml.x;                           // the slice's maximum for now
+      l_sm[idx] = ml.y;
     }
     __syncthreads();
     if (threadIdx.x < GC) {
@@ -279,12 +442,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
       float mm = -INFINITY;
       for (int sp = 0; sp < NS; ++sp) mm = fmaxf(mm, w_s[g * NS + sp]);
       float ll = 0.f;
-      const size_t o = ((size_t)b * p.Hq + kvh * G + g0 + g) * NS;
       for (int sp = 0; sp < NS; ++sp) {
         const float ms = w_s[g * NS + sp];
         const float c = (ms == -INFINITY) ? 0.f : expf(ms - mm);
         w_s[g * NS + sp] = c;
-        ll = fmaf(c, __ldcg(&p.part_ml[(o + sp) * 2 + 1]), ll);
+        ll = fmaf(c, l_sm[g * NS + sp], ll);
       }
       w_s[GC * NS + g] = 1.0f / ll;
     }
@@ -295,7 +457,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(DecParams
     const int head = kvh * G + g0 + g;
     const size_t o = ((size_t)b * p.Hq + head) * NS;
     float a = 0.f, inv;
-    if (fits) {
+    if (fits && fits2) {
       int sp = 0;
       for (; sp + 4 <= NS; sp += 4) {
         const float x0 = __ldcg(&p.part_acc[(o + sp) * HD + d]), x1 = __ldcg(&p.part_acc[(o + sp + 1) * HD + d]);
@@ -326,6 +488,10 @@ template <typename T, int LPK>
 int launch_decode(const DecParams& p, int B, cudaStream_t stream) {
   constexpr int HD = LPK * Ld16<T>::VEC;
   dim3 grid(B, p.Hkv * p.n_gchunks, p.n_splits);
+  if (p.cluster && p.n_splits > 1) {
+    launch_kernel_cluster(attention_decode_kernel<T, LPK>, grid, dim3(DEC_THREADS), 0, stream, dim3(1, 1, p.n_splits), p);
+    return launch_status();
+  }
   launch_kernel(attention_decode_kernel<T, LPK>, dim3(grid), dim3(DEC_THREADS), 0, stream, p);
   int st = launch_status();
   if (st != DLGO_OK || p.n_splits == 1 || p.counters != nullptr) return st;
@@ -352,6 +518,13 @@ int dispatch_decode(const DecParams& p, int B, int hd, cudaStream_t stream) {
 
 using namespace dlgo;
 
+namespace {
+int decode_common(DecParams& p, int dtype, int B, int hd, cudaStream_t stream) {
+  if (dtype == DLGO_F32) return dispatch_decode<float>(p, B, hd, stream);
+  return dispatch_decode<__nv_bfloat16>(p, B, hd, stream);
+}
+}  // namespace
+
 // 1 if the kernel takes this head size for this element type (16 bytes per lane, 2..32 lanes per key)
 DLGO_EXPORT int dlgo_attention_decode_takes(int dtype, int hd, int page_size) {
   const int vec = dtype == DLGO_BF16 ? 8 : 4;
@@ -365,7 +538,8 @@ DLGO_EXPORT int dlgo_attention_decode_takes(int dtype, int hd, int page_size) {
 // q[B, .] (row stride ldq, head h at column h*hd), one token per sequence at position token_pos[b];
 // scratch: B * Hq * n_splits * (hd + 2) floats when n_splits > 1.  counters: B * Hkv * ceil(G / 4) ints,
 // zero before the first call (the kernel leaves them zero): the last slice to finish then combines the
-// partial results itself; with counters == null a second kernel does.
+// partial results itself; with counters == null a second kernel does.  With scratch == null and
+// 2 <= n_splits <= 8 the slices form a thread-block cluster and combine through distributed shared memory.
 DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, const void* kpages,
                                       const void* vpages, const int* page_table, int max_pages,
                                       const int* seq_slot, const int* token_pos, void* out, int ldo, float* scratch,
@@ -375,9 +549,11 @@ DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, 
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_splits <= 0 || n_splits > 65535) return DLGO_ERR_SIZE;
   if (dtype != DLGO_F32 && dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
   if (!dlgo_attention_decode_takes(dtype, hd, page_size)) return DLGO_ERR_SIZE;
-  if (n_splits > 1 && scratch == nullptr) return DLGO_ERR_SIZE;
+  const int use_cluster = (n_splits > 1 && n_splits <= 8 && scratch == nullptr) ? 1 : 0;
+  if (n_splits > 1 && scratch == nullptr && !use_cluster) return DLGO_ERR_SIZE;
   const int G = Hq / Hkv;
   DecParams p;
+  p.cluster = use_cluster;
   p.q = q; p.ldq = ldq; p.kpages = kpages; p.vpages = vpages; p.page_table = page_table; p.max_pages = max_pages;
   p.seq_slot = seq_slot; p.token_pos = token_pos; p.out = out; p.ldo = ldo;
   p.part_acc = scratch;
@@ -386,7 +562,53 @@ DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, 
   p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
   p.n_gchunks = (G + DEC_GMAX - 1) / DEC_GMAX;
   p.window = window; p.scale = scale;
+  p.qkv = nullptr; p.parts = nullptr; p.S = 0; p.part_stride = 0; p.cos_t = nullptr; p.sin_t = nullptr;
+  p.rot = 0; p.interleaved = 0; p.fuse_rope = 0; p.write_cache = 0;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;
-  if (dtype == DLGO_F32) return dispatch_decode<float>(p, B, hd, stream);
-  return dispatch_decode<__nv_bfloat16>(p, B, hd, stream);
+  return decode_common(p, dtype, B, hd, stream);
+}
+
+// 1 if the rotation and the cache append can be done inside the decode kernel for these sizes: one
+// block per (sequence, kv head) owns the head's new row (at most 4 query heads per kv head), and the
+// rotation pairs either sit in one lane (interleaved) or exactly half a head apart.
+DLGO_EXPORT int dlgo_attention_decode_fuses_rope(int dtype, int Hq, int Hkv, int hd, int rot, int interleaved,
+                                                 int page_size) {
+  if (!dlgo_attention_decode_takes(dtype, hd, page_size) || Hkv <= 0 || Hq % Hkv) return 0;
+  if (Hq / Hkv > DEC_GMAX) return 0;
+  if (rot < 0 || rot > hd || rot % 2) return 0;
+  if (rot == 0) return 1;
+  if (interleaved) return 1;
+  const int vec = dtype == DLGO_BF16 ? 8 : 4;
+  return rot == hd && hd / vec >= 2;
+}
+
+// The decode kernel with the rotation and the append inside: `qkv` [B, ldq] (q | k | v heads, unrotated)
+// in the storage type, or `parts` [S][B][ldq] fp32 (its unsummed K-slices); cos/sin [positions, rot/2].
+DLGO_EXPORT int dlgo_attention_decode_rope(const void* qkv, const float* parts, int S, long long part_stride,
+                                           int dtype, int B, int ldq, const float* cos_t, const float* sin_t,
+                                           int rot, int interleaved, int write_cache, void* kpages, void* vpages,
+                                           const int* page_table, int max_pages, const int* seq_slot,
+                                           const int* token_pos, void* out, int ldo, float* scratch, int* counters,
+                                           int Hq, int Hkv, int hd, int page_size, int n_splits, int window,
+                                           float scale, cudaStream_t stream) {
+  if (B <= 0) return DLGO_OK;
+  if (n_splits <= 0 || n_splits > 65535) return DLGO_ERR_SIZE;
+  if (dtype != DLGO_F32 && dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
+  if (!dlgo_attention_decode_fuses_rope(dtype, Hq, Hkv, hd, rot, interleaved, page_size)) return DLGO_ERR_SIZE;
+  if ((qkv == nullptr) == (parts == nullptr)) return DLGO_ERR_SIZE;
+  if (parts != nullptr && ((part_stride & 3) || (ldq & 3) || S <= 0)) return DLGO_ERR_ALIGN;
+  const int use_cluster = (n_splits > 1 && n_splits <= 8 && scratch == nullptr) ? 1 : 0;
+  if (n_splits > 1 && scratch == nullptr && !use_cluster) return DLGO_ERR_SIZE;
+  DecParams p;
+  p.cluster = use_cluster;
+  p.q = nullptr; p.ldq = ldq; p.kpages = kpages; p.vpages = vpages; p.page_table = page_table; p.max_pages = max_pages;
+  p.seq_slot = seq_slot; p.token_pos = token_pos; p.out = out; p.ldo = ldo;
+  p.part_acc = scratch;
+  p.part_ml = scratch ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
+  p.counters = counters;
+  p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits; p.n_gchunks = 1;
+  p.window = window; p.scale = scale;
+  p.qkv = qkv; p.parts = parts; p.S = S; p.part_stride = (size_t)part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
+  p.rot = rot; p.interleaved = interleaved; p.fuse_rope = 1; p.write_cache = write_cache;
+  return decode_common(p, dtype, B, hd, stream);
 }

@@ -368,7 +368,7 @@ def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vp
     _need(vpages, q.dtype, "vpages")
     for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
         _need(t, torch.int32, n)
-    if n_splits > 1:
+    if n_splits > 1 and not (scratch is None and n_splits <= 8):   # up to 8 slices can combine in a cluster
         need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention_decode: {n_splits} slices need {need} floats of scratch")
@@ -381,7 +381,7 @@ def attention_decode(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vp
         _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _ptr(scratch),
         _ptr(counters), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]), _i(n_splits), _i(window),
         _f(scale), _stream())
-    _check(st, "attention_decode", 2 if (n_splits > 1 and counters is None) else 1)
+    _check(st, "attention_decode", 2 if (n_splits > 1 and counters is None and scratch is not None) else 1)
     return out
 
 
@@ -410,4 +410,51 @@ def attention_prefill_tc(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor
         _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _ptr(seq_slot), _ptr(token_pos), _ptr(out),
         _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(window), _f(scale), _stream())
     _check(st, "attention_prefill_tc")
+    return out
+
+
+def attention_decode_fuses_rope(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+                                interleaved: bool, page_size: int) -> bool:
+    return bool(_lib("attention_decode").dlgo_attention_decode_fuses_rope(
+        _i(dtype_code(dtype)), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim),
+        _i(1 if interleaved else 0), _i(page_size)))
+
+
+def attention_decode_rope(qkv: Optional[torch.Tensor], parts: Optional[torch.Tensor], B: int, cos: torch.Tensor,
+                          sin: torch.Tensor, rotary_dim: int, interleaved: bool, write_cache: bool,
+                          kpages: torch.Tensor, vpages: torch.Tensor, page_table: torch.Tensor,
+                          seq_slot: torch.Tensor, token_pos: torch.Tensor, out: torch.Tensor, num_heads: int,
+                          num_kv_heads: int, head_dim: int, scale: float, window: int = 0, n_splits: int = 1,
+                          scratch: Optional[torch.Tensor] = None,
+                          counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention with the rotation of q and k and the append of k and v inside the kernel.
+
+    Give the projection's output either as ``qkv`` [B, ld] in the cache's type or as ``parts``
+    [S, B, ld] fp32 (its unsummed K-slices)."""
+    _need(out, kpages.dtype, "out")
+    _need(vpages, kpages.dtype, "vpages")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    if (qkv is None) == (parts is None):
+        raise KernelError("attention_decode_rope: give qkv or parts, not both")
+    if qkv is not None:
+        _need(qkv, kpages.dtype, "qkv")
+        ld, S, pstride = qkv.stride(0), 0, 0
+    else:
+        if parts.dtype != torch.float32 or parts.dim() != 3 or parts.stride(2) != 1:
+            raise KernelError("attention_decode_rope: parts must be [S, B, ld] float32")
+        ld, S, pstride = parts.stride(1), parts.shape[0], parts.stride(0)
+    if n_splits > 8 or (n_splits > 1 and scratch is not None):
+        need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
+        if scratch is None or scratch.numel() < need:
+            raise KernelError(f"attention_decode_rope: {n_splits} slices need {need} floats of scratch")
+    st = _lib("attention_decode").dlgo_attention_decode_rope(
+        _ptr(qkv), _ptr(parts), _i(S), _ll(pstride), _i(dtype_code(kpages.dtype)), _i(B), _i(ld), _ptr(cos), _ptr(sin),
+        _i(rotary_dim), _i(1 if interleaved else 0), _i(1 if write_cache else 0), _ptr(kpages), _ptr(vpages),
+        _ptr(page_table), _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)),
+        _ptr(scratch), _ptr(counters), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]),
+        _i(n_splits), _i(window), _f(scale), _stream())
+    _check(st, "attention_decode_rope", 2 if (n_splits > 1 and counters is None and scratch is not None) else 1)
     return out

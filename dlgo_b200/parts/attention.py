@@ -77,37 +77,54 @@ class GQAAttention(Mixer):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
         T = ctx.n_tokens
-        # few tokens: the projection leaves its K-slices unsummed and the rotation adds them
-        qkv_parts = self.wqkv.partials(x)
-        if qkv_parts is not None:
-            qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
-        else:
-            qkv = self.wqkv(x, STORE)
+        group = self.num_heads // self.num_kv_heads
         if self.position_encoding is not None:
             pe = positions[self.position_encoding]
             cos, sin, rot, inter = pe.cos, pe.sin, pe.rotary_dim, pe.interleaved
         else:
             cos = sin = self._no_rotation
             rot, inter = 0, False
-        K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
-                      cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                      qkv_parts)
-        group = self.num_heads // self.num_kv_heads
+        act = self.wqkv.weight.dtype
+        decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
+        fused_rope = decode_kernel and K.attention_decode_fuses_rope(
+            act, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.page_size)
+        # few tokens: the projection leaves its K-slices unsummed and whoever rotates adds them
+        qkv_parts = self.wqkv.partials(x)
+        qkv = None
+        if qkv_parts is None:
+            qkv = self.wqkv(x, STORE)
+        if not fused_rope:
+            if qkv is None:
+                qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
+            K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                          cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
+                          qkv_parts)
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
-        out = torch.empty((T, self.q_dim), dtype=qkv.dtype, device=qkv.device)
-        if ctx.decode and K.attention_decode_takes(qkv.dtype, self.head_dim, cache.page_size):
+        out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
+        if decode_kernel:
             # one token per sequence: the latency-shaped kernel, sliced so that every SM has several blocks
             base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
             n_splits = max(1, min(pages, -(-_DECODE_BLOCKS // base_blocks)))
             scratch = counters = None
-            if n_splits > 1:
+            if n_splits > 8 and pages <= 64:
+                n_splits = 8
+            if n_splits > 8:
+                # very long sequences at small batches: slices through scratch, the last one combines
                 scratch = ctx.scratch("attention",
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
                 counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
-            K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
-                               ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                               self.window or 0, n_splits, scratch, counters)
+            # (2..8 slices form a thread-block cluster and combine through distributed shared memory)
+            if fused_rope:
+                # rotation of q and k and the append of k and v happen inside the attention kernel
+                K.attention_decode_rope(qkv, qkv_parts, T, cos, sin, rot, inter, cache.writes, cache.keys,
+                                        cache.values, cache.page_table, ctx.seq_slot, ctx.token_pos, out,
+                                        self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                                        self.window or 0, n_splits, scratch, counters)
+            else:
+                K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                                   ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                                   self.window or 0, n_splits, scratch, counters)
         elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
             # prompts: 128 query rows per CTA on the tensor cores
             tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE)

@@ -13,13 +13,15 @@ from __future__ import annotations
 
 from typing import Callable, Dict, List, Optional
 
+import os
+
 import torch
 
 from ..csrc import kernels as K
 
 SKINNY_MAX = 64          # tokens up to which the weight is the M operand
-TARGET_CTAS = 2 * 148    # two CTAs per SM stream the weight (their footprint is kept under half an SM)
-MIN_KBLOCKS_PER_SPLIT = 4
+TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 2 * 148))  # two CTAs per SM stream the weight (footprint under half an SM)
+MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
 
 _workspaces: Dict[int, List[torch.Tensor]] = {}
 _counters: Dict[int, torch.Tensor] = {}

@@ -199,14 +199,21 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
         k.check_device_errors()
     elif kernel == "decode":
         assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
-        # even slice counts let the last slice combine (counters), odd ones use the second kernel
-        cnt = torch.zeros(T_ * hkv * ((hq // hkv + 3) // 4), dtype=torch.int32, device=DEV) if n_splits % 2 == 0 else None
-        for _ in range(2):      # twice: the counters must be left ready for the next call
-            out.fill_(float("nan"))
-            k.attention_decode(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
-                               torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
-                               window, n_splits, scratch, cnt)
-        assert cnt is None or int(cnt.abs().sum()) == 0
+        # three ways to combine slices: a cluster (no scratch, up to 8 slices), the last slice (scratch and
+        # counters), a second kernel (scratch only)
+        cnt = torch.zeros(T_ * hkv * ((hq // hkv + 3) // 4), dtype=torch.int32, device=DEV)
+        ways = [(scratch, cnt), (scratch, None)] + ([(None, None)] if n_splits <= 8 else [])
+        results = []
+        for sc_, cn_ in ways:
+            for _ in range(2):      # twice: the counters must be left ready for the next call
+                out.fill_(float("nan"))
+                k.attention_decode(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                                   torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd,
+                                   1.0 / math.sqrt(hd), window, n_splits, sc_, cn_)
+            results.append(out.clone())
+        assert int(cnt.abs().sum()) == 0
+        for r_ in results[1:]:
+            torch.testing.assert_close(r_.float(), results[0].float(), atol=1e-5 if dtype == "float32" else 1e-2, rtol=1e-2)
     else:
         k.attention(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
                     max(t[2] for t in tiles), torch.tensor(slots, dtype=torch.int32, device=DEV),
@@ -588,3 +595,64 @@ def test_rope_append_from_partials():
     assert torch.equal(res[0][0], res[1][0])
     for a, b in zip(res[0][1:], res[1][1:]):
         assert torch.equal(torch.nan_to_num(a, nan=-7.0), torch.nan_to_num(b, nan=-7.0))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,hd,rot,inter", [(8, 2, 64, 64, False), (3, 1, 32, 32, False), (4, 4, 128, 64, True),
+                                                 (4, 2, 16, 0, False)])
+@pytest.mark.parametrize("from_parts", [False, True])
+def test_decode_attention_with_the_rotation_and_append_inside(dtype, hq, hkv, hd, rot, inter, from_parts):
+    # the fused kernel against rope_append followed by the plain decode kernel, on the same inputs
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    if not k.attention_decode_fuses_rope(DT[dtype], hq, hkv, hd, rot, inter, 64):
+        pytest.skip("sizes the fused kernel does not take")
+    torch.manual_seed(hd + rot)
+    if rot:
+        cos, sin = (t.to(DEV) for t in RotaryEmbedding(hd, rot, 10000.0, 400, "interleaved" if inter else "split_half").tables())
+    else:
+        cos = sin = torch.zeros(1, 1, device=DEV)
+    lens = [300, 1, 64, 65]                                       # positions 299, 0, 63 (page end), 64 (page start)
+    B = len(lens)
+    pages_per = [(n + 63) // 64 for n in lens]
+    n_pages = sum(pages_per) + 1
+    perm = torch.randperm(n_pages).tolist()
+    pt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    for i, n in enumerate(pages_per):
+        for pg in range(n):
+            pt[i, pg] = perm.pop()
+    pt = pt.to(DEV)
+    ld = (hq + 2 * hkv) * hd
+    S = 3
+    parts = (torch.randn(S, B, ld, device=DEV) * 0.6)
+    whole = (parts[0] + parts[1] + parts[2])
+    if not from_parts:
+        whole = whole.to(DT[dtype]).float()
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    outs = []
+    caches = []
+    for fused in (False, True):
+        torch.manual_seed(1)
+        kp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(DT[dtype])
+        vp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(DT[dtype])
+        out = torch.full((B, hq * hd), float("nan"), device=DEV, dtype=DT[dtype])
+        for n_splits in (1, 4):
+            if not fused:
+                qkv = whole.to(DT[dtype]).clone()
+                k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, rot, inter, True,
+                              parts if from_parts else None)
+                k.attention_decode(qkv, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits)
+            else:
+                k.attention_decode_rope(None if from_parts else whole.to(DT[dtype]), parts if from_parts else None, B,
+                                        cos, sin, rot, inter, True, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5,
+                                        0, n_splits)
+            outs.append(out.float().clone())
+        caches.append((kp.float().clone(), vp.float().clone()))
+    t = dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(outs[2], outs[0], **t)
+    torch.testing.assert_close(outs[3], outs[1], **t)
+    # the same rows were appended (the two kernels may contract x0*c - x1*s differently: one ulp)
+    ct = dict(atol=1e-6, rtol=1e-6) if dtype == "float32" else dict(atol=1e-2, rtol=8e-3)
+    torch.testing.assert_close(caches[1][0], caches[0][0], **ct)
+    assert torch.equal(caches[1][1], caches[0][1])
