@@ -51,6 +51,7 @@ struct TcParams {
   float* workspace;   // [splits][tiles][BN][128] fp32, when splits > 1
   int* counters;      // [tiles], zero before the first launch; left zero
   int stages;         // shared-memory ring size
+  int staged;         // many-token kernels: epilogue through shared memory and TMA stores
   int static_operand; // 0: none; 1: A, 2: B holds weights no earlier kernel writes (loaded before pdl_wait)
 };
 
@@ -361,6 +362,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// Epilogue of the many-token kernels: one accumulator tile (128 rows x BN fp32 columns in tensor
+// memory) goes through two 16 KB staging buffers in shared memory, 128 bytes per row in the
+// 128-byte swizzle, and from there to global memory with TMA: a tile store (bf16, fp32, SwiGLU) or
+// an fp32 add-reduce for the residual (the residual is never read by the SM).  Rows are written
+// whole and coalesced, and rows or columns beyond the matrix are clipped by the tensor map.
+// Called by the 128 epilogue threads together; `chunk` counts staging buffers used so far.
+constexpr int STAGING_BYTES = 2 * 16384;
+
+template <int BN>
+__device__ __forceinline__ void staged_epilogue(const TcParams& p, const CUtensorMap* map_out, uint8_t* staging,
+                                                uint32_t acc_addr, int row0, int col0, int quarter, int lane,
+                                                bool issuer, int& chunk) {
+  const int r = quarter * 32 + lane;
+  const uint32_t lane_addr = acc_addr + ((uint32_t)(quarter * 32) << 16);
+  // accumulator columns that make one 128-byte output row chunk
+  const int step = p.epilogue == TC_STORE ? 64 : (p.epilogue == TC_SWIGLU ? 128 : 32);
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += step, ++chunk) {
+    uint8_t* buf = staging + (chunk & 1) * 16384;
+    if (issuer) tma_store_wait_read<1>();     // the store that last used this buffer has read it
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    uint8_t* row = buf + r * 128;
+    if (p.epilogue == TC_STORE) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[32];
+        tmem_ld_32x32(lane_addr + c0 + 32 * h, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 b2[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) b2[q] = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+          *reinterpret_cast<uint4*>(row + (((4 * h + j) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(b2);
+        }
+      }
+    } else if (p.epilogue == TC_SWIGLU) {
+      // per 32 accumulator columns: 16 gate values then their 16 up values -> 16 outputs
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float v[32];
+        tmem_ld_32x32(lane_addr + c0 + 32 * h, v);
+        tmem_ld_wait();
+        __nv_bfloat162 b2[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float g0 = v[2 * q], g1 = v[2 * q + 1], u0 = v[16 + 2 * q], u1 = v[16 + 2 * q + 1];
+          b2[q] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+        }
+        *reinterpret_cast<uint4*>(row + (((2 * h) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(&b2[0]);
+        *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(&b2[4]);
+      }
+    } else {
+      float v[32];
+      tmem_ld_32x32(lane_addr + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(row + ((j ^ (r & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (issuer) {
+      const int x = p.epilogue == TC_SWIGLU ? (col0 + c0) / 2 : col0 + c0;
+      if (p.epilogue == TC_ADD_F32) tma_reduce_add_2d(map_out, buf, x, row0);
+      else tma_store_2d(map_out, buf, x, row0);
+      tma_store_commit();
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Many tokens: one persistent CTA per SM walks over output tiles.  Two accumulators live in tensor
 // memory (2 x BN columns), so the epilogue of tile i (tensor memory -> registers -> global) runs
@@ -371,13 +443,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          TcParams p) {
+                          const __grid_constant__ CUtensorMap map_out, TcParams p) {
   using C = TcConfig<BN>;
-  constexpr int STAGES = C::MAX_STAGES;
+  const int STAGES = p.stages;
   constexpr uint32_t TMEM_COLS = 2 * C::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * C::STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(staging + STAGING_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;     // 2
   uint64_t* acc_empty = acc_full + 2;      // 2
@@ -457,25 +530,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
   } else {
     const int quarter = warp & 3;
+    const bool issuer = warp == 2 && lane == 0;
+    const bool staged = p.staged != 0;
     pdl_wait();
     constexpr int NV = 32;
-    int local = 0;
+    int local = 0, chunk = 0;
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++local) {
       const int tile_a = t % tiles_a, tile_b = t / tiles_a;
       const int buf = local & 1;
       const int row = tile_a * TILE_M + quarter * 32 + lane;
       if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;
       tc_fence_after_sync();
+      if (staged) {
+        staged_epilogue<BN>(p, &map_out, staging, tmem_base + buf * C::TMEM_COLS, tile_a * TILE_M, tile_b * BN, quarter,
+                            lane, issuer, chunk);
+      } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += NV) {
-        float v[NV];
-        tmem_ld_32x32(tmem_base + buf * C::TMEM_COLS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-        tmem_ld_wait();
-        epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+        for (int c0 = 0; c0 < BN; c0 += NV) {
+          float v[NV];
+          tmem_ld_32x32(tmem_base + buf * C::TMEM_COLS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+          epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+        }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[buf]);
     }
+    if (issuer) tma_store_wait_all();
   }
 
   tc_fence_before_sync();
@@ -488,6 +569,156 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Many tokens, CTA pairs: two CTAs of a cluster share one 256 x BN tile through cta_group::2.  Each
+// CTA loads 128 rows of A and HALF of the tile's B rows; the leader's MMAs read both halves from both
+// CTAs' shared memory and write 128 accumulator rows into each CTA's tensor memory.  Per CTA and
+// K block that is 16 KB + BN/2 x 128 B of shared-memory fill for the work a single CTA would need
+// 16 KB + BN x 128 B for, which is what lets the tensor pipe run near its peak.  Persistent, two
+// accumulators per CTA, no multicast loads (each CTA fetches its own halves).
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_out, TcParams p) {
+  constexpr int HALF_N = BN / 2;
+  constexpr int A_BYTES = TILE_M * TILE_K * 2;
+  constexpr int B_BYTES = HALF_N * TILE_K * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t ACC_COLS = BN;                 // fp32 columns of one accumulator
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;      // 512 for BN = 256, 256 for BN = 128
+  const int STAGES = p.stages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(staging + STAGING_BYTES);       // used in the leader only
+  uint64_t* empty = full + STAGES;                             // local in each CTA
+  uint64_t* acc_full = empty + STAGES;                         // 2, local in each CTA
+  uint64_t* acc_empty = acc_full + 2;                          // 2, used in the leader only (256 arrivals)
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_a = (p.Ra + 2 * TILE_M - 1) / (2 * TILE_M), tiles_b = (p.Rb + BN - 1) / BN;
+  const int n_tiles = tiles_a * tiles_b;
+  const int nkb = (p.K + TILE_K - 1) / TILE_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 256);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers exist before anything arrives on them remotely
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      pdl_wait();
+      int it = 0;
+      for (int t = pair; t < n_tiles; t += n_pairs) {
+        const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { t = n_tiles; break; }
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          // the leader's barrier counts the bytes of both CTAs' loads
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &map_a, bar, kb * TILE_K, tile_a * 2 * TILE_M + (int)rank * TILE_M);
+          tma_load_2d_pair(a_dst + A_BYTES, &map_b, bar, kb * TILE_K, tile_b * BN + (int)rank * HALF_N);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * TILE_M, BN);
+      int it = 0, local = 0;
+      for (int t = pair; t < n_tiles; t += n_pairs, ++local) {
+        const int buf = local & 1;
+        if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TILE_K / UMMA_K; ++k)
+            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_pair(&empty[s]);     // both CTAs may refill the stage
+        }
+        umma_commit_pair(&acc_full[buf]);  // both CTAs' epilogues may read the accumulator
+        if (!ok) break;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const bool issuer = warp == 2 && lane == 0;
+    const bool staged = p.staged != 0;
+    pdl_wait();
+    constexpr int NV = 32;
+    int local = 0, chunk = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, ++local) {
+      const int tile_a = t % tiles_a, tile_b = t / tiles_a;
+      const int buf = local & 1;
+      const int row0 = tile_a * 2 * TILE_M + (int)rank * TILE_M;
+      const int row = row0 + quarter * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;
+      tc_fence_after_sync();
+      if (staged) {
+        staged_epilogue<BN>(p, &map_out, staging, tmem_base + buf * ACC_COLS, row0, tile_b * BN, quarter, lane, issuer,
+                            chunk);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += NV) {
+          float v[NV];
+          tmem_ld_32x32(tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+          epilogue_store<NV>(p, v, row, tile_b * BN + c0, lane);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+    if (issuer) tma_store_wait_all();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();          // nobody leaves while the other CTA may still signal or be read
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_gemm_tc_error, 1);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -528,6 +759,25 @@ int make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_
   return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
 }
 
+// Output tensor map of the staged epilogue: rows of 128 bytes (64 bf16 or 32 fp32), 128 rows, swizzled.
+// Returns DLGO_ERR_ALIGN where the output cannot be described (then the direct epilogue is used).
+int make_out_map(CUtensorMap* m, const TcParams& p) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return DLGO_ERR_DRIVER;
+  const bool bf16 = p.epilogue == TC_STORE || p.epilogue == TC_SWIGLU;
+  const int esize = bf16 ? 2 : 4;
+  const long long cols = p.epilogue == TC_SWIGLU ? p.Rb / 2 : p.Rb;
+  if (((uintptr_t)p.out & 15) != 0 || ((long long)p.ldo * esize) % 16 != 0) return DLGO_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)p.Ra};
+  cuuint64_t strides[1] = {(cuuint64_t)p.ldo * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)TILE_M};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.out, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
+}
+
 template <int BN>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
   using C = TcConfig<BN>;
@@ -551,6 +801,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   }
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   q.stages = stages;
+  q.staged = 0;
   launch_kernel(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages), stream, ma, mb, q);
   return launch_status();
 }
@@ -564,14 +815,46 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcP
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::smem_bytes(C::MAX_STAGES));
+                                         C::smem_bytes(C::MAX_STAGES) + STAGING_BYTES);
     if (e != cudaSuccess) { sms = 0; return (int)e; }
   }
   const int tiles = ((p.Ra + TILE_M - 1) / TILE_M) * ((p.Rb + BN - 1) / BN);
   TcParams q = p;
+  // one CTA per SM with as deep a ring as shared memory allows beside the epilogue's staging buffers
+  int ctas_per_sm = 1;
   q.stages = C::MAX_STAGES;
-  launch_kernel(gemm_tc_persistent_kernel<BN>, dim3(tiles < sms ? tiles : sms), dim3(TC_THREADS),
-                C::smem_bytes(C::MAX_STAGES), stream, ma, mb, q);
+  const char* e = getenv("DLGO_TC_PERSISTENT_STAGES");
+  if (e != nullptr && atoi(e) >= 2 && atoi(e) <= C::MAX_STAGES) q.stages = atoi(e);
+  const int slots = sms * ctas_per_sm;
+  CUtensorMap mo = ma;   // a valid map even when unused
+  q.staged = (getenv("DLGO_TC_DIRECT_EPILOGUE") == nullptr && make_out_map(&mo, q) == DLGO_OK) ? 1 : 0;
+  launch_kernel(gemm_tc_persistent_kernel<BN>, dim3(tiles < slots ? tiles : slots), dim3(TC_THREADS),
+                C::smem_bytes(q.stages) + STAGING_BYTES, stream, ma, mb, mo, q);
+  return launch_status();
+}
+
+template <int BN>
+int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = TILE_M * TILE_K * 2 + (BN / 2) * TILE_K * 2;
+  constexpr int STAGES = BN >= 256 ? 6 : 8;
+  constexpr int SMEM = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) { sms = 0; return (int)e; }
+  }
+  const int tiles = ((p.Ra + 2 * TILE_M - 1) / (2 * TILE_M)) * ((p.Rb + BN - 1) / BN);
+  int pairs = sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  TcParams q = p;
+  q.stages = STAGES;
+  CUtensorMap mo = ma;
+  q.staged = (getenv("DLGO_TC_DIRECT_EPILOGUE") == nullptr && make_out_map(&mo, q) == DLGO_OK) ? 1 : 0;
+  launch_kernel_cluster(gemm_tc_pair_kernel<BN>, dim3(2 * pairs), dim3(TC_THREADS), SMEM, stream, dim3(2, 1, 1), ma, mb,
+                        mo, q);
   return launch_status();
 }
 
@@ -592,9 +875,11 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 // [splits][Rb][ldo] and slice s writes out[s][col][row], transposed only); bn in {16, 32, 64, 128, 256}.
 // static_operand: 1 if A, 2 if B holds weights that no kernel launched before this one writes (their
 // tiles are then requested before the kernel waits for its predecessor), else 0.
+// pair_tile: 0, or 128 / 256 to compute 256 x pair_tile tiles with pairs of CTAs (cta_group::2; many
+// tokens only: not transposed, one K-slice; bn is then ignored).
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
                              int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
-                             int* counters, int static_operand, cudaStream_t stream) {
+                             int* counters, int static_operand, int pair_tile, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
   if (epilogue < 0 || epilogue > 4) return DLGO_ERR_SIZE;
@@ -614,6 +899,13 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
+  if (!transposed && splits == 1 && pair_tile != 0) {
+    // many tokens, CTA pairs: A's box is 128 rows, B's box is half the tile's width
+    if (pair_tile != 128 && pair_tile != 256) return DLGO_ERR_SIZE;
+    st = make_map(&mb, B, Rb, K, ldb, pair_tile / 2);
+    if (st != DLGO_OK) return st;
+    return pair_tile == 256 ? launch_tc_pair<256>(ma, mb, p, stream) : launch_tc_pair<128>(ma, mb, p, stream);
+  }
   if (!transposed && splits == 1 && (bn == 128 || bn == 256) && getenv("DLGO_GEMM_NONPERSISTENT") == nullptr) {
     // many tokens: persistent CTAs with two accumulators in tensor memory
     return bn == 256 ? launch_tc_persistent<256>(ma, mb, p, stream) : launch_tc_persistent<128>(ma, mb, p, stream);

@@ -295,12 +295,13 @@ def gemm_tc_workspace_floats(ra: int, rb: int, bn: int, splits: int) -> int:
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, epilogue: int, bn: int,
             splits: int = 1, workspace: Optional[torch.Tensor] = None,
-            counters: Optional[torch.Tensor] = None, static_operand: int = 0) -> torch.Tensor:
+            counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0) -> torch.Tensor:
     """D[Ra, Rb] = a[Ra, K] . b[Rb, K]^T on the tensor cores (bf16 in, fp32 accumulate).
 
     ``out`` receives D (``transposed``: D^T) through ``epilogue``; with ``splits`` > 1 the K range is
     shared by that many CTAs per tile, which needs ``workspace`` (fp32) and zeroed ``counters`` (int32).
     ``static_operand`` (1: a, 2: b) names the operand that holds weights no earlier kernel writes.
+    ``pair_tile`` (128 or 256): many tokens, 256 x pair_tile tiles computed by pairs of CTAs (cta_group::2).
     """
     for n, t in (("a", a), ("b", b)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
@@ -334,7 +335,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         ldo = out.stride(0)
     st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
                                       _ptr(out), _i(ldo), _i(1 if transposed else 0), _i(epilogue), _i(bn),
-                                      _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _stream())
+                                      _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _i(pair_tile), _stream())
     _check(st, "gemm_tc")
     return out
 

@@ -21,6 +21,8 @@ from ..csrc import kernels as K
 
 SKINNY_MAX = 64          # tokens up to which the weight is the M operand
 TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 2 * 148))  # two CTAs per SM stream the weight (footprint under half an SM)
+PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
+PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
 MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
 
 _workspaces: Dict[int, List[torch.Tensor]] = {}
@@ -79,7 +81,10 @@ class TensorCorePlan:
                 cnt = _counter_buffer(x.device)
             return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1)
         bn = 256 if self.n > 128 else 128
-        return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2)
+        if PREFILL_BN in (128, 256):
+            bn = PREFILL_BN
+        pair = PAIR_TILE if (t > 128 and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
+        return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
 
     def partials(self, x: torch.Tensor) -> Optional[torch.Tensor]:

@@ -471,6 +471,32 @@ def test_gemm_tc_persistent_over_many_tiles(Ra, Rb, K_, bn, epi):
     k.check_device_errors()
 
 
+@pytest.mark.parametrize("Ra,Rb,K_,tile,epi", [(256, 256, 64, 256, "f32"), (300, 700, 200, 256, "store"),
+                                               (2100, 2600, 328, 256, "add"), (1000, 5000, 72, 128, "f32"),
+                                               (4000, 4200, 520, 256, "store")])
+def test_gemm_tc_cta_pairs(Ra, Rb, K_, tile, epi):
+    # 256 x tile tiles computed by pairs of CTAs (cta_group::2), persistent over many tiles
+    k = K()
+    torch.manual_seed(Ra + tile)
+    a = torch.randn(Ra, K_, device=DEV).to(torch.bfloat16)
+    b = torch.randn(Rb, K_, device=DEV).to(torch.bfloat16)
+    ref = _tc_ref(a, b).float()
+    if epi == "store":
+        o = torch.full((Ra, Rb), float("nan"), device=DEV, dtype=torch.bfloat16)
+        k.gemm_tc(a, b, o, False, k.TC_STORE, 256, pair_tile=tile)
+        torch.testing.assert_close(o.float(), ref, atol=2e-3 * math.sqrt(K_), rtol=1e-2)
+    elif epi == "add":
+        res = torch.randn(Ra, Rb, device=DEV)
+        o = res.clone()
+        k.gemm_tc(a, b, o, False, k.TC_ADD_F32, 256, pair_tile=tile)
+        torch.testing.assert_close(o, res + ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    else:
+        o = torch.full((Ra, Rb), float("nan"), device=DEV)
+        k.gemm_tc(a, b, o, False, k.TC_STORE_F32, 256, pair_tile=tile)
+        torch.testing.assert_close(o, ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
 @pytest.mark.parametrize("N,T_,K_,splits", [(256, 5, 512, 2), (384, 16, 2048, 8), (130, 33, 200, 4), (2048, 64, 8192, 9),
                                             (128, 1, 640, 10)])
 def test_gemm_tc_split_k_is_exact_and_repeatable(N, T_, K_, splits):
