@@ -108,10 +108,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&kvempty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
-    mbar_init(p_full, 128);
+    mbar_init(s_free, 4);
+    mbar_init(p_full, 4);
     mbar_init(o_full, 1);
-    mbar_init(o_free, 128);
+    mbar_init(o_free, 4);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -128,7 +128,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
 
   pdl_wait();
-  const int tile = blockIdx.x;
+  const int tile = gridDim.x - 1 - blockIdx.x;   // later tiles of a prompt see more keys: start them first
   const int seq = p.tiles[3 * tile], tok0 = p.tiles[3 * tile + 1], ntok = p.tiles[3 * tile + 2];
   const int slot = p.seq_slot[seq];
   const int pos0 = p.token_pos[tok0];
@@ -241,6 +241,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) break;
       tc_fence_after_sync();
       const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
+      // blocks that lie wholly inside every row's range need no mask (all but the diagonal ones)
+      const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && (p.window <= 0 || k0 > pos0 + ntok - 1 - p.window);
       // pass 1: the row's maximum over this block
       float mx = -INFINITY;
 #pragma unroll 1
@@ -248,12 +250,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float v[32];
         tmem_ld_32x32(lane_addr + c0, v);
         tmem_ld_wait();
+        if (full_block) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = k0 + c0 + j;
-          if (t <= pos_r && t > lo) mx = fmaxf(mx, v[j] * p.scale_log2e);
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = k0 + c0 + j;
+            if (t <= pos_r && t > lo) mx = fmaxf(mx, v[j]);
+          }
         }
       }
+      mx *= p.scale_log2e;                                       // the scale is positive: max commutes with it
       const float m_new = fmaxf(m, mx);
       const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
       const float mref = (m_new == -INFINITY) ? 0.f : m_new;
@@ -265,14 +273,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float v[32];
         tmem_ld_32x32(lane_addr + c0, v);
         tmem_ld_wait();
+        if (full_block) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = k0 + c0 + j;
-          const float pr = (t <= pos_r && t > lo) ? fast_exp2(v[j] * p.scale_log2e - mref) : 0.f;
-          // the sum is taken over the rounded values the tensor core will use
-          const float prb = __bfloat162float(__float2bfloat16_rn(pr));
-          v[j] = prb;
-          sum += prb;
+          for (int j = 0; j < 32; ++j) {
+            v[j] = fast_exp2(fmaf(v[j], p.scale_log2e, -mref));
+            sum += v[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = k0 + c0 + j;
+            v[j] = (t <= pos_r && t > lo) ? fast_exp2(fmaf(v[j], p.scale_log2e, -mref)) : 0.f;
+            sum += v[j];
+          }
         }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -287,8 +300,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       l = l * corr + sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor core
       tc_fence_before_sync();
-      mbar_arrive(p_full);
-      mbar_arrive(s_free);
+      __syncwarp();
+      if (lane == 0) {          // one arrival per warp stands for its 32 rows
+        mbar_arrive(p_full);
+        mbar_arrive(s_free);
+      }
       // O_blk -> registers with the correction of this block
       ok = mbar_wait(o_full, it & 1, abort_flag);
       if (!ok) break;
@@ -302,7 +318,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf(acc[c0 + j], corr, v[j]);
       }
       tc_fence_before_sync();
-      mbar_arrive(o_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
     }
     if (ok && r < ntok) {
       const float inv = 1.0f / l;
