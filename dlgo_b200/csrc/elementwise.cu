@@ -28,23 +28,62 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 // ------------------------------------------------------------------ RMSNorm
 // One block per output row.  `rows` (optional) picks the input row of each
 // output row, so the final norm runs on the wanted positions only.
+template <typename TO> __device__ __forceinline__ void store4(TO* o, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* o, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* o, float a, float b, float c, float d) {
+  __nv_bfloat162 h[2] = {__floats2bfloat162_rn(a, b), __floats2bfloat162_rn(c, d)};
+  *reinterpret_cast<uint2*>(o) = *reinterpret_cast<uint2*>(h);
+}
+
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
+  __shared__ float scale_s;
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  TO* o = out + (size_t)r * d;
+  constexpr int KEEP = 4;   // float4s of the row a thread keeps in registers between the two passes
+  if ((d & 3) == 0 && d <= (int)blockDim.x * 4 * KEEP) {
+    // the row is read once, 16 bytes at a time, and stays in registers for the second pass
+    float4 v[KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      v[j] = i < d ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss = fmaf(v[j].x, v[j].x, ss);
+      ss = fmaf(v[j].y, v[j].y, ss);
+      ss = fmaf(v[j].z, v[j].z, ss);
+      ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+    __syncthreads();
+    const float s = scale_s;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      if (i < d) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + i);
+        store4<TO>(o + i, v[j].x * s * ww.x, v[j].y * s * ww.y, v[j].z * s * ww.z, v[j].w * s * ww.w);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = xr[i];
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
-  const float mean = ss / (float)d + eps;
-  const float s = (float)(1.0 / sqrt((double)mean));
-  TO* o = out + (size_t)r * d;
+  if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+  __syncthreads();
+  const float s = scale_s;
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(xr[i] * s * w[i]);
 }
 

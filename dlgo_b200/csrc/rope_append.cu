@@ -87,6 +87,97 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
   }
 }
 
+// The same for the common layout (pairs (i, i + hd/2), the whole head rotated, no K-slices to add):
+// a thread takes 16 bytes from the low half of a head and the 16 bytes they pair with in the high
+// half, so prompts move through this kernel at memory speed.
+template <typename T> struct RVec;
+template <> struct RVec<float> { static constexpr int N = 4; };
+template <> struct RVec<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T>
+__device__ __forceinline__ void rv_load(const T* p, float* o);
+template <> __device__ __forceinline__ void rv_load<float>(const float* p, float* o) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <> __device__ __forceinline__ void rv_load<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void rv_store(T* p, const float* o);
+template <> __device__ __forceinline__ void rv_store<float>(float* p, const float* o) {
+  *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+}
+template <> __device__ __forceinline__ void rv_store<__nv_bfloat16>(__nv_bfloat16* p, const float* o) {
+  __nv_bfloat162 h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(h);
+}
+
+template <typename T>
+__global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                                       const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                       const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
+                                       T* __restrict__ vpages, int Hq, int Hkv, int hd, int page_size,
+                                       int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int N = RVec<T>::N;
+  const int t = blockIdx.x;
+  const int rhalf = hd / 2, per_head = rhalf / N;
+  const int items = (Hq + 2 * Hkv) * per_head;
+  const int pos = token_pos[t];
+  T* row = qkv + (size_t)t * ld;
+  size_t base = 0;
+  if (write_cache) {
+    const int slot = seq_slot[token_seq[t]];
+    const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+    base = ((size_t)page * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+  }
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    const int head = it / per_head, i = (it - head * per_head) * N;
+    T* h = row + (size_t)head * hd;
+    float lo[N], hi[N];
+    rv_load<T>(h + i, lo);
+    rv_load<T>(h + i + rhalf, hi);
+    if (head < Hq + Hkv) {
+      float c[N], sn[N];
+#pragma unroll
+      for (int e = 0; e < N; e += 4) {
+        const float4 cc = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * rhalf + i + e);
+        const float4 ss = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * rhalf + i + e);
+        c[e] = cc.x; c[e + 1] = cc.y; c[e + 2] = cc.z; c[e + 3] = cc.w;
+        sn[e] = ss.x; sn[e + 1] = ss.y; sn[e + 2] = ss.z; sn[e + 3] = ss.w;
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        const float x0 = lo[e], x1 = hi[e];
+        lo[e] = x0 * c[e] - x1 * sn[e];
+        hi[e] = x0 * sn[e] + x1 * c[e];
+      }
+    }
+    if (head < Hq) {
+      rv_store<T>(h + i, lo);
+      rv_store<T>(h + i + rhalf, hi);
+    } else if (write_cache) {
+      const bool is_k = head < Hq + Hkv;
+      const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+      T* dst = (is_k ? kpages : vpages) + base + (size_t)kvh * page_size * hd;
+      rv_store<T>(dst + i, lo);
+      rv_store<T>(dst + i + rhalf, hi);
+    }
+  }
+}
+
 }  // namespace dlgo
 
 using namespace dlgo;
@@ -100,6 +191,23 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
   if (hd <= 0 || hd % 2 || rot < 0 || rot > hd || rot % 2 || Hq <= 0 || Hkv <= 0 || page_size <= 0 ||
       ld < (Hq + 2 * Hkv) * hd)
     return DLGO_ERR_SIZE;
+  const int vec = dtype == DLGO_BF16 ? 8 : 4;
+  if (parts == nullptr && !interleaved && rot == hd && (hd / 2) % vec == 0 && ld % vec == 0 &&
+      ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)kpages & 15) == 0 && ((uintptr_t)vpages & 15) == 0) {
+    const int vitems = (Hq + 2 * Hkv) * (hd / 2 / vec);
+    const int vthreads = vitems >= 256 ? 256 : (vitems >= 128 ? 128 : 64);
+    if (dtype == DLGO_F32)
+      launch_kernel(rope_append_vec_kernel<float>, dim3(T), dim3(vthreads), 0, stream, (float*)qkv, ld, cos_t, sin_t,
+                    token_pos, token_seq, seq_slot, page_table, max_pages, (float*)kpages, (float*)vpages, Hq, Hkv, hd,
+                    page_size, write_cache);
+    else if (dtype == DLGO_BF16)
+      launch_kernel(rope_append_vec_kernel<__nv_bfloat16>, dim3(T), dim3(vthreads), 0, stream, (__nv_bfloat16*)qkv, ld,
+                    cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages, (__nv_bfloat16*)kpages,
+                    (__nv_bfloat16*)vpages, Hq, Hkv, hd, page_size, write_cache);
+    else
+      return DLGO_ERR_DTYPE;
+    return launch_status();
+  }
   const int items = (Hq + 2 * Hkv) * (hd / 2);
   const int threads = items >= 1024 ? 256 : 128;
   if (dtype == DLGO_F32)
