@@ -49,7 +49,8 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream of the current device (a C call; current_stream() builds objects)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _need(t: torch.Tensor, dt: Optional[torch.dtype], name: str) -> None:

@@ -23,6 +23,7 @@ class DecodeGraph:
         self.batch = batch
         self.meta = torch.zeros((3, batch), dtype=torch.int32, device=dev)   # ids, positions, slots
         self.host = torch.zeros((3, batch), dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()     # a view: the step's inputs are written here without tensor construction
         self.token_seq = torch.arange(batch, dtype=torch.int32, device=dev)
         self.want_rows = torch.arange(batch, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
@@ -52,12 +53,12 @@ class DecodeGraph:
         self.kernels_per_replay = kernels.LAUNCHES - before
 
     def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
-        h = self.host
         self._copied.synchronize()  # the previous step's copy out of the pinned buffer has finished
-        h[0] = torch.tensor(token_ids, dtype=torch.int32)
-        h[1] = torch.tensor(starts, dtype=torch.int32)
-        h[2] = torch.tensor(slots, dtype=torch.int32)
-        self.meta.copy_(h, non_blocking=True)
+        h = self.host_np
+        h[0, :] = token_ids
+        h[1, :] = starts
+        h[2, :] = slots
+        self.meta.copy_(self.host, non_blocking=True)
         self._copied.record()
         self.graph.replay()
         from ..csrc import kernels
@@ -77,9 +78,9 @@ def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
         g = DecodeGraph(engine, b)
         # the warm-up and the capture run the step for real, on whatever the buffers
         # hold: give them this step's inputs so they write where this step writes anyway
-        g.host[0] = torch.tensor(token_ids, dtype=torch.int32)
-        g.host[1] = torch.tensor(starts, dtype=torch.int32)
-        g.host[2] = torch.tensor(slots, dtype=torch.int32)
+        g.host_np[0, :] = token_ids
+        g.host_np[1, :] = starts
+        g.host_np[2, :] = slots
         g.meta.copy_(g.host)
         g.capture()
         engine._graphs[b] = g
