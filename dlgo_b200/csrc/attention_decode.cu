@@ -148,15 +148,28 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     // whose pages hold the new position appends the token's key and value (forward.go:257).
     auto load_vec = [&](int col, float* v) {
       if (p.parts != nullptr) {
+        // up to eight slices' loads are in flight before the first add (slices are added in order)
         const float* src = p.parts + (size_t)b * p.ldq + col;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) v[e] = 0.f;
-        for (int sp = 0; sp < p.S; ++sp) {
+        for (int s0 = 0; s0 < p.S; s0 += 8) {
+          float4 t4[8][VEC / 4];
 #pragma unroll
-          for (int e4 = 0; e4 < VEC; e4 += 4) {
-            const float4 t4 = *reinterpret_cast<const float4*>(src + (size_t)sp * p.part_stride + e4);
-            v[e4] += t4.x; v[e4 + 1] += t4.y; v[e4 + 2] += t4.z; v[e4 + 3] += t4.w;
-          }
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e4 = 0; e4 < VEC / 4; ++e4)
+              t4[j][e4] = (s0 + j < p.S)
+                              ? *reinterpret_cast<const float4*>(src + (size_t)(s0 + j) * p.part_stride + 4 * e4)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e4 = 0; e4 < VEC / 4; ++e4) {
+              v[4 * e4] += t4[j][e4].x;
+              v[4 * e4 + 1] += t4[j][e4].y;
+              v[4 * e4 + 2] += t4[j][e4].z;
+              v[4 * e4 + 3] += t4[j][e4].w;
+            }
         }
       } else {
         Ld16<T>::load((const T*)p.qkv + (size_t)b * p.ldq + col, v);

@@ -28,6 +28,17 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 // ------------------------------------------------------------------ RMSNorm
 // One block per output row.  `rows` (optional) picks the input row of each
 // output row, so the final norm runs on the wanted positions only.
+// 1 / sqrt(mean + eps): as the reference computes it (square root and reciprocal in double, ops/norm.go:21)
+// for the float32 path; for bfloat16 activations, whose 8 bits of mantissa hide the last ulps, in
+// fp32 (a double-precision square root and division cost microseconds on this GPU).
+template <typename TO> __device__ __forceinline__ float norm_scale(float mean_eps);
+template <> __device__ __forceinline__ float norm_scale<float>(float mean_eps) {
+  return (float)(1.0 / sqrt((double)mean_eps));
+}
+template <> __device__ __forceinline__ float norm_scale<__nv_bfloat16>(float mean_eps) {
+  return 1.0f / sqrtf(mean_eps);
+}
+
 template <typename TO> __device__ __forceinline__ void store4(TO* o, float a, float b, float c, float d);
 template <> __device__ __forceinline__ void store4<float>(float* o, float a, float b, float c, float d) {
   *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
@@ -62,7 +73,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
       ss = fmaf(v[j].w, v[j].w, ss);
     }
     ss = block_sum(ss, scratch);
-    if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+    if (threadIdx.x == 0) scale_s = norm_scale<TO>(ss / (float)d + eps);
     __syncthreads();
     const float s = scale_s;
 #pragma unroll
@@ -81,7 +92,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+  if (threadIdx.x == 0) scale_s = norm_scale<TO>(ss / (float)d + eps);
   __syncthreads();
   const float s = scale_s;
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(xr[i] * s * w[i]);
@@ -139,7 +150,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   }
   if (w == nullptr) return;
   ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0) scale_s = (float)(1.0 / sqrt((double)(ss / (float)d + eps)));
+  if (threadIdx.x == 0) scale_s = norm_scale<TO>(ss / (float)d + eps);
   __syncthreads();
   const float sc = scale_s;
   TO* o = out + (size_t)r * d;

@@ -14,6 +14,7 @@ and the cache group the layer's keys and values belong to.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
@@ -24,7 +25,11 @@ from .linear import ADD_F32, STORE, Linear
 from .registry import MIXERS
 
 _TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (general kernel)
-_DECODE_BLOCKS = 4 * 148  # and for the decode kernel, whose blocks are small
+# The decode kernel can also rotate q and k and append k and v itself (one launch less per layer); measured
+# inside a whole step it is no faster than the separate rope kernel, so it is opt-in: DLGO_ATTN_FUSE_ROPE=1.
+_NO_FUSE = not os.environ.get("DLGO_ATTN_FUSE_ROPE")
+_CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
+_DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
 
 class GQAAttention(Mixer):
@@ -86,7 +91,7 @@ class GQAAttention(Mixer):
             rot, inter = 0, False
         act = self.wqkv.weight.dtype
         decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
-        fused_rope = decode_kernel and K.attention_decode_fuses_rope(
+        fused_rope = decode_kernel and not _NO_FUSE and K.attention_decode_fuses_rope(
             act, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.page_size)
         # few tokens: the projection leaves its K-slices unsummed and whoever rotates adds them
         qkv_parts = self.wqkv.partials(x)
@@ -107,9 +112,9 @@ class GQAAttention(Mixer):
             base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
             n_splits = max(1, min(pages, -(-_DECODE_BLOCKS // base_blocks)))
             scratch = counters = None
-            if n_splits > 8 and pages <= 64:
-                n_splits = 8
-            if n_splits > 8:
+            if n_splits > _CLUSTER_MAX and pages <= 64 and _CLUSTER_MAX > 1:
+                n_splits = _CLUSTER_MAX
+            if n_splits > _CLUSTER_MAX:
                 # very long sequences at small batches: slices through scratch, the last one combines
                 scratch = ctx.scratch("attention",
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))

@@ -21,6 +21,7 @@ from ..csrc import kernels as K
 
 SKINNY_MAX = 64          # tokens up to which the weight is the M operand
 TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 2 * 148))  # two CTAs per SM stream the weight (footprint under half an SM)
+MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
 MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
@@ -51,7 +52,7 @@ def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
     splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, TARGET_CTAS // tiles)) if tiles < TARGET_CTAS else 1
-    return bn, max(1, min(splits, kblocks))
+    return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
 
 class TensorCorePlan:
