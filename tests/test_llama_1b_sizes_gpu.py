@@ -16,20 +16,26 @@ CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_laye
            rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                              original_max_position_embeddings=8192),
            rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
+# Llama 3.1 8B layer sizes (hidden 4096, 32/8 heads of 128, feed-forward 14336, untied head, rope factor 8),
+# two layers and a 32000 vocabulary to keep the plain implementation quick: head size 128 everywhere
+CFG_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=2, intermediate_size=14336,
+              num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=32000, rope_theta=500000.0,
+              rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                original_max_position_embeddings=8192),
+              rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=False)
 ROWS = [0, 1, 63, 64, 127, 128, 141] + list(range(142, 150))       # places compared (the last 8 are decoded)
 
 
-@pytest.fixture(scope="module")
-def big(tmp_path_factory):
+def build(tmp_path_factory, CFG, seed):
     from dlgo_b200.config import config_from_dict
     from dlgo_b200.weights import write_random_model
-    d = str(tmp_path_factory.mktemp("llama1b_sizes"))
-    write_random_model(config_from_dict(CFG), 2, d, device="cuda")
+    d = str(tmp_path_factory.mktemp("llama_sizes"))
+    write_random_model(config_from_dict(CFG), seed, d, device="cuda")
     g = torch.Generator().manual_seed(3)
     reqs = {"long": torch.randint(0, CFG["vocab_size"], (150,), generator=g).tolist(),
             "short": torch.randint(0, CFG["vocab_size"], (21,), generator=g).tolist()}
     cfg, w = P.read_model(d)
-    freqs = P.rope_frequencies(64, cfg["rope_theta"], cfg["rope_scaling"])
+    freqs = P.rope_frequencies(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"])
     refs = {}
     for rid, toks in reqs.items():
         x = P.embedding(w["model.embed_tokens.weight"], toks)
@@ -37,9 +43,20 @@ def big(tmp_path_factory):
             x = P.layer(x, w, f"model.layers.{i}.", cfg, freqs)
         rows = [r for r in ROWS if r < len(toks)] if rid == "long" else list(range(len(toks)))
         xn = P.rmsnorm(x[rows], w["model.norm.weight"], cfg["rms_norm_eps"])
-        refs[rid] = (rows, P.linear(xn, w["model.embed_tokens.weight"]))
+        head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
+        refs[rid] = (rows, P.linear(xn, head))
     del w
     return d, reqs, refs
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    return build(tmp_path_factory, CFG, 2)
+
+
+@pytest.fixture(scope="module")
+def big8(tmp_path_factory):
+    return build(tmp_path_factory, CFG_8B, 5)
 
 
 def run(engine, reqs, refs, dtype, what):
@@ -85,3 +102,12 @@ def test_llama_1b_sizes_against_the_plain_implementation(big, dtype):
         eng2 = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256, cuda_graphs=False)
         eng2.cache.poison()
         run(eng2, reqs, refs, dtype, "no graphs")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_8b_layer_sizes_against_the_plain_implementation(big8, dtype):
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = big8
+    eng = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256)
+    eng.cache.poison()
+    run(eng, reqs, refs, dtype, "8B sizes")
