@@ -460,3 +460,27 @@ def attention_decode_rope(qkv: Optional[torch.Tensor], parts: Optional[torch.Ten
         _i(n_splits), _i(window), _f(scale), _stream())
     _check(st, "attention_decode_rope", 2 if (n_splits > 1 and counters is None and scratch is not None) else 1)
     return out
+
+
+# ------------------------------------------------------------------- filters
+FILTER_MAX_K, FILTER_MAX_RECENT = 2048, 64
+
+
+def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, penalty: float,
+                  recent: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Repetition penalty, temperature, top-k, top-p and min-p in one kernel (needs 1 <= top_k <= 2048).
+    Returns the filtered, temperature-scaled logits; dropped tokens hold -inf.  ``recent`` is
+    [rows, <= 64] int32 with -1 for "none"."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 [rows, vocab] on the GPU with unit stride along the vocabulary")
+    R, V = logits.shape
+    work = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+    n_recent = 0
+    if recent is not None:
+        _need(recent, torch.int32, "recent")
+        n_recent = recent.shape[1]
+    st = _lib("sampling").dlgo_filter(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(work), _f(temperature),
+                                      _i(top_k), _f(top_p), _f(min_p), _f(penalty), _ptr(recent), _i(n_recent),
+                                      _stream())
+    _check(st, "filter")
+    return work

@@ -175,6 +175,138 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The reference's filters in one kernel (ops/sampling.go:53-165), for the usual case that top-k is
+// on: repetition penalty over the recent tokens (positive logits / penalty, negative * penalty, each
+// token once), temperature, top-k (everything below the k-th largest value goes to -inf, ties at the
+// cutoff stay), then among the survivors top-p (the shortest prefix of the descending order whose
+// probabilities reach p) and min-p (drop below min_p times the largest probability).  One block per
+// row writes the filtered, temperature-scaled logits to `work`; the draw itself is sample_kernel's.
+constexpr int FILTER_THREADS = 1024;
+constexpr int FILTER_CAP = 2048;     // survivors kept for top-p / min-p (k plus ties at the cutoff)
+constexpr int FILTER_RECENT = 64;
+
+__device__ __forceinline__ uint32_t order_key(float x) {     // monotone: a < b  <=>  key(a) < key(b)
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(FILTER_THREADS)
+filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict__ work, float inv_t, int top_k,
+              float top_p, float min_p, float penalty, const int* __restrict__ recent, int n_recent) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int rec_s[FILTER_RECENT];
+  __shared__ unsigned int count_s;
+  __shared__ float sv[FILTER_CAP];
+  __shared__ int si[FILTER_CAP];
+  __shared__ float red[32];
+  __shared__ float cut_s;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  float* out = work + (size_t)r * V;
+  // recent tokens of this row, duplicates and out-of-range ids dropped
+  if (tid < FILTER_RECENT) {
+    int tok = (recent != nullptr && tid < n_recent) ? recent[(size_t)r * n_recent + tid] : -1;
+    if (tok >= V) tok = -1;
+    for (int j = 0; j < tid && tok >= 0; ++j)
+      if (recent[(size_t)r * n_recent + j] == tok) tok = -1;
+    rec_s[tid] = tok;
+  }
+  __syncthreads();
+  // pass 0: penalty and temperature -> work
+  for (int i = tid; i < V; i += FILTER_THREADS) {
+    float v = row[i];
+    if (penalty > 1.0f) {
+      bool hit = false;
+      for (int j = 0; j < FILTER_RECENT; ++j) hit |= rec_s[j] == i;
+      if (hit) v = v > 0.f ? v / penalty : v * penalty;
+    }
+    out[i] = v * inv_t;
+  }
+  __syncthreads();
+  // top-k: the k-th largest key by bisection on the 32 bits of the order-preserving key
+  uint32_t lo = 0u, hi = 0xFFFFFFFFu;     // invariant: count(key >= lo) >= k
+  for (int bit = 31; bit >= 0; --bit) {
+    const uint32_t mid = lo | (1u << bit);
+    if (tid == 0) count_s = 0;
+    __syncthreads();
+    unsigned int c = 0;
+    for (int i = tid; i < V; i += FILTER_THREADS) c += order_key(out[i]) >= mid;
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((tid & 31) == 0 && c) atomicAdd(&count_s, c);
+    __syncthreads();
+    if (count_s >= (unsigned int)top_k) lo = mid;
+    __syncthreads();
+  }
+  (void)hi;
+  // survivors (key >= lo) into shared memory, the rest to -inf
+  if (tid == 0) count_s = 0;
+  __syncthreads();
+  for (int i = tid; i < V; i += FILTER_THREADS) {
+    const float v = out[i];
+    if (order_key(v) >= lo) {
+      const unsigned int at = atomicAdd(&count_s, 1u);
+      if (at < FILTER_CAP) { sv[at] = v; si[at] = i; }
+    } else {
+      out[i] = -INFINITY;
+    }
+  }
+  __syncthreads();
+  const int n = (int)count_s;
+  if (n > FILTER_CAP || (top_p >= 1.0f && min_p <= 0.f)) return;   // (more ties than fit: top-k alone stands)
+  // sort the survivors by value, descending (bitonic over the next power of two, padded with -inf)
+  int m = 1;
+  while (m < n) m <<= 1;
+  for (int i = n + tid; i < m; i += FILTER_THREADS) { sv[i] = -INFINITY; si[i] = -1; }
+  __syncthreads();
+  for (int k = 2; k <= m; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < m; i += FILTER_THREADS) {
+        const int l = i ^ j;
+        if (l > i) {
+          const bool desc = (i & k) == 0;
+          const float a = sv[i], b = sv[l];
+          if (desc ? a < b : a > b) {
+            sv[i] = b; sv[l] = a;
+            const int t = si[i]; si[i] = si[l]; si[l] = t;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // probabilities of the survivors and the cut: thread 0 walks the (short) sorted list
+  if (tid == 0) {
+    const float mx = sv[0];
+    float total = 0.f;
+    for (int i = 0; i < n; ++i) total += expf(sv[i] - mx);
+    float cut = -INFINITY;                 // smallest value kept
+    int keep = n;
+    if (top_p < 1.0f) {
+      float cum = 0.f;
+      for (int i = 0; i < n; ++i) {
+        cum += expf(sv[i] - mx) / total;
+        if (cum >= top_p) { keep = i + 1; break; }
+      }
+    }
+    if (min_p > 0.f) {
+      // prob_i < min_p * prob_max  <=>  exp(v_i - mx) < min_p
+      int k2 = 0;
+      while (k2 < keep && expf(sv[k2] - mx) >= min_p) ++k2;
+      keep = k2 < 1 ? 1 : k2;
+    }
+    cut = keep < n ? (float)keep : -1.f;
+    cut_s = cut;
+  }
+  __syncthreads();
+  // positions keep .. n-1 of the sorted list are dropped (ties between kept and dropped values are
+  // resolved by position in the sorted order, as the reference's sort does)
+  const int keep = cut_s < 0.f ? n : (int)cut_s;
+  for (int i = keep + tid; i < n; i += FILTER_THREADS) out[si[i]] = -INFINITY;
+}
+
 }  // namespace dlgo
 
 using namespace dlgo;
@@ -224,5 +356,19 @@ DLGO_EXPORT int dlgo_uniform(unsigned long long seed, const int* draw, const int
                              cudaStream_t stream) {
   if (n <= 0) return DLGO_OK;
   launch_kernel(uniform_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, (uint64_t)seed, draw, request, out, n);
+  return launch_status();
+}
+
+// logits[R, V] f32 (row stride ld) -> work[R, V] f32: penalty, temperature, top-k (1 <= top_k), top-p, min-p.
+// recent[R, n_recent] int32 (-1 = none), n_recent <= 64, or null.
+DLGO_EXPORT int dlgo_filter(const float* logits, int R, int ld, int V, float* work, float temperature, int top_k,
+                            float top_p, float min_p, float penalty, const int* recent, int n_recent,
+                            cudaStream_t stream) {
+  if (R <= 0) return DLGO_OK;
+  if (V <= 0 || ld < V || top_k < 1 || top_k > FILTER_CAP || n_recent < 0 || n_recent > FILTER_RECENT ||
+      !(temperature > 0.f))
+    return DLGO_ERR_SIZE;
+  launch_kernel(filter_kernel, dim3(R), dim3(FILTER_THREADS), 0, stream, logits, ld, V, work, 1.0f / temperature,
+                top_k, top_p, min_p, penalty, recent, n_recent);
   return launch_status();
 }

@@ -211,6 +211,45 @@ def sample_temperature(logits: torch.Tensor, temperature: float, u: float) -> in
     return min(idx, logits.shape[0] - 1)
 
 
+def filter_logits(logits: torch.Tensor, recent: Sequence[int], penalty: float, temperature: float, top_k: int,
+                  top_p: float, min_p: float) -> torch.Tensor:
+    """One row through the filters in the reference's order (ops/sampling.go:32-48): repetition penalty
+    (:53-69), temperature (:72-80), top-k (:83-95), top-p (:99-138), min-p (:143-165).  Returns a copy;
+    dropped tokens hold -inf."""
+    x = logits.detach().to(torch.float32).clone()
+    n = x.numel()
+    ninf = float("-inf")
+    if penalty > 1.0:
+        seen = set()
+        for tok in recent:
+            tok = int(tok)
+            if tok < 0 or tok >= n or tok in seen:
+                continue
+            seen.add(tok)
+            x[tok] = x[tok] / penalty if x[tok] > 0 else x[tok] * penalty
+    if temperature > 0 and temperature != 1.0:
+        x = x * (1.0 / temperature)
+    if 0 < top_k < n:
+        cutoff = sorted(x.tolist(), reverse=True)[top_k - 1]
+        x[x < cutoff] = ninf
+    if top_p < 1.0:
+        probs = softmax(x)
+        order = sorted(range(n), key=lambda i: -float(probs[i]))
+        cum, last = 0.0, n - 1
+        for rank, i in enumerate(order):
+            cum += float(probs[i])
+            if cum >= top_p:
+                last = rank
+                break
+        drop = torch.ones(n, dtype=torch.bool)
+        drop[order[:last + 1]] = False
+        x[drop] = ninf
+    if min_p > 0:
+        probs = softmax(x)
+        x[probs < min_p * probs.max()] = ninf
+    return x
+
+
 def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n: int) -> List[int]:
     """Greedy continuation by re-running the whole sequence each step (no cache)."""
     seq = list(prompt)

@@ -416,6 +416,64 @@ def test_sample_frequencies_follow_the_probabilities():
     assert float((freq - probs).abs().max()) < 0.03
 
 
+@pytest.mark.parametrize("V,k,p,mp,pen,temp", [(50, 5, 0.9, 0.0, 1.1, 0.7), (1000, 40, 0.9, 0.0, 1.1, 0.7),
+                                               (1000, 999, 0.5, 0.05, 1.0, 1.3), (777, 1, 1.0, 0.0, 2.0, 0.5),
+                                               (5000, 300, 0.95, 0.01, 1.5, 1.0), (128256, 40, 0.9, 0.02, 1.1, 0.7),
+                                               (4099, 64, 1.0, 0.1, 1.0, 2.0), (301, 300, 0.3, 0.0, 1.2, 0.9)])
+def test_filter_kernel_against_the_plain_filters(V, k, p, mp, pen, temp):
+    g = torch.Generator().manual_seed(V + k)
+    R = 4
+    lg = torch.randn(R, V, generator=g) * 3.0
+    lg[1, : min(V, 20)] = 7.5                                   # a block of ties at the top of row 1
+    recent = [torch.randint(0, V, (n,), generator=g).tolist() for n in (64, 10, 0, 33)]
+    recent[0][5] = recent[0][4]                                 # a repeated token counts once
+    width = 64
+    rec = torch.tensor([(r + [-1] * width)[:width] for r in recent], dtype=torch.int32, device=DEV)
+    pad = torch.full((R, V + 3), 99.0)                          # a row stride that is not the width
+    pad[:, :V] = lg
+    got = K().filter_logits(pad.to(DEV)[:, :V], temp, k, p, mp, pen, rec).cpu()
+    for r in range(R):
+        want = P.filter_logits(lg[r], recent[r], pen, temp, k, p, mp)
+        kept_w, kept_g = torch.isfinite(want), torch.isfinite(got[r])
+        if not torch.equal(kept_w, kept_g):
+            # the two may differ only on values that tie with the last kept one (the order among
+            # equal probabilities is the sort's, in the reference too) or where the running sum
+            # meets p within rounding
+            diff = (kept_w != kept_g).nonzero().flatten().tolist()
+            edge = want[kept_w].min()
+            sm = P.softmax(torch.where(kept_w | kept_g, got[r].nan_to_num(neginf=-1e30), torch.tensor(-1e30)))
+            cum_w = float(sm[kept_w].sum())
+            for i in diff:
+                v = got[r, i] if kept_g[i] else want[i]
+                assert abs(float(v - edge)) < 1e-5 or abs(cum_w - p) < 1e-4, (r, i, float(v), float(edge))
+        both = kept_w & kept_g
+        assert both.any()
+        torch.testing.assert_close(got[r][both], want[both], atol=1e-5, rtol=1e-5)
+
+
+def test_filtered_sampling_stays_inside_the_kept_set():
+    from dlgo_b200.sampling import DeviceSampler, SamplerConfig
+    g = torch.Generator().manual_seed(4)
+    V, R = 3000, 6
+    lg = (torch.randn(R, V, generator=g) * 2.0).to(DEV)
+    cfg = SamplerConfig(temperature=0.8, top_k=7, top_p=0.95, min_p=0.0, repetition_penalty=1.3)
+    recent = [torch.randint(0, V, (20,), generator=g).tolist() for _ in range(R)]
+    s = DeviceSampler(seed=5)
+    seen = [set() for _ in range(R)]
+    for d in range(40):
+        got = s.sample(lg, cfg, list(range(R)), [d] * R, recent).cpu().tolist()
+        for r in range(R):
+            seen[r].add(got[r])
+    for r in range(R):
+        want = P.filter_logits(lg[r].cpu(), recent[r], 1.3, 0.8, 7, 0.95, 0.0)
+        kept = set(torch.isfinite(want).nonzero().flatten().tolist())
+        assert seen[r] <= kept and len(seen[r]) > 1
+    # the same (seed, request, draw) gives the same token whatever else is in the batch
+    a = s.sample(lg, cfg, list(range(R)), [3] * R, recent).cpu().tolist()
+    b = s.sample(lg[2:4], cfg, [2, 3], [3, 3], recent[2:4]).cpu().tolist()
+    assert a[2:4] == b
+
+
 # ------------------------------------------------------- tensor-core contraction
 def _tc_ref(a, b):
     return a.double() @ b.double().t()

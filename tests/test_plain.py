@@ -146,6 +146,23 @@ def test_filters_match_the_reference_rules():
     assert k0.tolist() == [[1.0, 2.0]]
 
 
+def test_plain_filter_pipeline_in_the_references_order():
+    ninf = float("-inf")
+    x = torch.log(torch.tensor([0.4, 0.3, 0.15, 0.1, 0.05]))
+    assert torch.equal(P.filter_logits(x, [], 1.0, 1.0, 0, 1.0, 0.0), x)
+    k = P.filter_logits(x, [], 1.0, 1.0, 3, 1.0, 0.0)
+    assert torch.isfinite(k[:3]).all() and torch.isinf(k[3:]).all()
+    # after top-k 3 the probabilities are 0.4/0.85, 0.3/0.85, 0.15/0.85: 0.8 is reached with the second
+    kp = P.filter_logits(x, [], 1.0, 1.0, 3, 0.8, 0.0)
+    assert torch.isfinite(kp[:2]).all() and torch.isinf(kp[2:]).all()
+    m = P.filter_logits(x, [], 1.0, 1.0, 0, 1.0, 0.5)           # threshold 0.2
+    assert torch.isfinite(m[:2]).all() and torch.isinf(m[2:]).all()
+    r = P.filter_logits(torch.tensor([2.0, -2.0, 1.0]), [0, 1, 1, 99, -1], 2.0, 0.5, 0, 1.0, 0.0)
+    assert r.tolist() == [2.0, -8.0, 2.0]                       # penalty first, then the temperature
+    t = P.filter_logits(torch.tensor([1.0, 4.0, 3.0, 4.0, 2.0]), [], 1.0, 1.0, 3, 1.0, 0.0)
+    assert t.tolist() == [ninf, 4.0, 3.0, 4.0, ninf]            # ties at the cutoff stay
+
+
 def test_plain_primitives_agree_with_the_references_own_c_kernels():
     # tests/golden/primitives.json holds what computerex/dlgo's quant/simd_dot.c computes (made by
     # tests/golden/make_primitives.py); its exp is a 5-digit polynomial, hence 1e-4
