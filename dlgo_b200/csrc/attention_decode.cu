@@ -102,7 +102,6 @@ template <> __device__ __forceinline__ float soft_exp<__nv_bfloat16>(float x) {
 template <typename T, int LPK>
 __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecParams p) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int VEC = Ld16<T>::VEC;
   constexpr int HD = LPK * VEC;
   constexpr int KPW = 32 / LPK;            // keys a warp covers per iteration
@@ -131,6 +130,28 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
   const int per = (pg_last - pg_first + 1 + p.n_splits - 1) / p.n_splits;
   const int pg_b = pg_first + split * per;
   const int pg_e = min(pg_last + 1, pg_b + per);
+
+  const int tiles_per_page = PS / TILE;
+  const int n_tiles = max(0, pg_e - pg_b) * tiles_per_page;
+  // Before waiting for the kernels that make q (and the newest key): the step's own inputs above
+  // (slot, position, page ids: later loads of them hit L1) and a hint that pulls this block's keys
+  // and values into L2, so that the loads after the wait are short round trips.  The cache lines of
+  // the newest position may still be written; a prefetch of them is harmless (L2 is coherent).
+  for (int tile = warp; tile < n_tiles; tile += DEC_WARPS) {
+    const int pg = pg_b + tile / tiles_per_page;
+    const int key0 = (tile % tiles_per_page) * TILE;
+    if (pg * PS + key0 >= t_end) continue;
+    const int page = p.page_table[(size_t)slot * p.max_pages + pg];
+    const size_t base = (((size_t)page * p.Hkv + kvh) * PS + key0) * HD;
+    const char* kp = (const char*)((const T*)p.kpages + base);
+    const char* vp = (const char*)((const T*)p.vpages + base);
+    constexpr int LINES = TILE * HD * (int)sizeof(T) / 128;
+    for (int ln = lane; ln < LINES; ln += 32) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + (size_t)ln * 128));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + (size_t)ln * 128));
+    }
+  }
+  pdl_wait();
 
   float q[DEC_GMAX][VEC], acc[DEC_GMAX][VEC], m[DEC_GMAX], l[DEC_GMAX];
   if (!p.fuse_rope) {
@@ -247,8 +268,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     l[g] = 0.f;
   }
 
-  const int tiles_per_page = PS / TILE;
-  const int n_tiles = max(0, pg_e - pg_b) * tiles_per_page;
   for (int tile = warp; tile < n_tiles; tile += DEC_WARPS) {
     const int pg = pg_b + tile / tiles_per_page;
     const int key0 = (tile % tiles_per_page) * TILE;

@@ -75,6 +75,11 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // of this package calls pdl_launch_dependents() at its start and pdl_wait() before it reads or writes
 // anything a predecessor may have touched; pdl_wait() returns once all predecessors have completed
 // and their writes are visible.  Both are no-ops for a kernel launched without the attribute.
+// Before the wait a kernel may read only what no kernel of the same step writes: weights, tables,
+// and the step's own inputs (token positions, slots, page tables), which are in place before the
+// step's first kernel starts.  That first kernel (the embedding) is launched WITHOUT the attribute
+// (launch_kernel_first), so it starts only after everything before it on the stream has completed;
+// every later kernel of the chain starts after it.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -100,6 +105,20 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// For the first kernel of a step: an ordinary launch, ordered after all earlier work of the stream.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_first(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

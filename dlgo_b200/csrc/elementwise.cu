@@ -108,32 +108,39 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
                                    const float* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
                                    int d, float eps) {
   pdl_launch_dependents();
-  pdl_wait();
   extern __shared__ float row_s[];   // the new row, kept for the second pass
   __shared__ float scratch[32];
   __shared__ float scale_s;
   const int r = blockIdx.x;
-  const int src = rows ? rows[r] : r;
+  const bool vec = (d & 3) == 0 && (part_stride & 3) == 0;
+  // the norm's weight does not depend on earlier kernels: this thread's first piece of it is
+  // fetched before waiting for them
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (vec && w != nullptr && threadIdx.x * 4 < d) w0 = *reinterpret_cast<const float4*>(w + threadIdx.x * 4);
+  const int src = rows ? rows[r] : r;   // (the row list is the step's own input, like the weights)
+  pdl_wait();
   float* xr = x + (size_t)src * d;
   const float* pr = parts + (size_t)src * d;
   float ss = 0.f;
-  if ((d & 3) == 0 && (part_stride & 3) == 0) {
-    // 16-byte accesses; up to eight slices' loads are in flight before the first add
+  float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (vec) {
+    // 16-byte accesses; sixteen slices' loads and the residual's are in flight before the first add,
+    // so a row costs one round trip to memory per sixteen slices
     for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
       float4 v = *reinterpret_cast<const float4*>(xr + i);
-      for (int s0 = 0; s0 < S; s0 += 8) {
-        float4 t[8];
+      for (int s0 = 0; s0 < S; s0 += 16) {
+        float4 t[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          t[j] = (s0 + j < S) ? *reinterpret_cast<const float4*>(pr + (size_t)(s0 + j) * part_stride + i)
+        for (int j = 0; j < 16; ++j)
+          t[j] = (s0 + j < S) ? __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(s0 + j) * part_stride + i))
                               : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 16; ++j) {
           if (s0 + j < S) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
         }
       }
       *reinterpret_cast<float4*>(xr + i) = v;
-      *reinterpret_cast<float4*>(row_s + i) = v;
+      if (i == threadIdx.x * 4) first = v; else *reinterpret_cast<float4*>(row_s + i) = v;
       ss = fmaf(v.x, v.x, ss);
       ss = fmaf(v.y, v.y, ss);
       ss = fmaf(v.z, v.z, ss);
@@ -154,7 +161,21 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   __syncthreads();
   const float sc = scale_s;
   TO* o = out + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(row_s[i] * sc * w[i]);
+  if (vec) {
+    // the thread's first piece never left its registers; the rest (rows wider than four times the
+    // block) comes back from shared memory
+    if (threadIdx.x * 4 < d) {
+      store4<TO>(o + threadIdx.x * 4, first.x * sc * w0.x, first.y * sc * w0.y, first.z * sc * w0.z,
+                 first.w * sc * w0.w);
+    }
+    for (int i = (threadIdx.x + blockDim.x) * 4; i < d; i += blockDim.x * 4) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + i);
+      store4<TO>(o + i, row_s[i] * sc * ww.x, row_s[i + 1] * sc * ww.y, row_s[i + 2] * sc * ww.z,
+                 row_s[i + 3] * sc * ww.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TO>(row_s[i] * sc * w[i]);
+  }
 }
 
 // ------------------------------------------------------------------- SwiGLU
@@ -184,9 +205,9 @@ DLGO_EXPORT int dlgo_embed(const int* tokens, const void* table, int table_dtype
   if (d <= 0 || vocab <= 0) return DLGO_ERR_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == DLGO_F32)
-    launch_kernel(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
+    launch_kernel_first(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
   else if (table_dtype == DLGO_BF16)
-    launch_kernel(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab);
+    launch_kernel_first(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

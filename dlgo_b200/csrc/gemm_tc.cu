@@ -40,6 +40,13 @@ constexpr int UMMA_K = 16;
 constexpr int TC_THREADS = 192;
 
 __device__ int g_gemm_tc_error = 0;  // set when a bounded wait ran out
+#ifdef DLGO_TC_TIMING
+__device__ unsigned long long g_tc_times[512 * 8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TSTAMP(k) do { const int c_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; if (c_ < 512) g_tc_times[c_ * 8 + (k)] = gtime(); } while (0)
+#else
+#define TSTAMP(k) do {} while (0)
+#endif
 
 struct TcParams {
   int Ra, Rb, K;      // rows of A, rows of B, contraction length
@@ -53,6 +60,10 @@ struct TcParams {
   int stages;         // shared-memory ring size
   int staged;         // many-token kernels: epilogue through shared memory and TMA stores
   int static_operand; // 0: none; 1: A, 2: B holds weights no earlier kernel writes (loaded before pdl_wait)
+  int l2_ahead;       // K blocks of the static operand, beyond the ring, to pull into L2 before pdl_wait
+  int cluster;        // > 1: that many consecutive K-slices are the CTAs of a thread-block cluster; their
+                      // partial tiles meet in the first CTA through distributed shared memory, in slice
+                      // order, and only it runs the epilogue (TC_PARTIAL: one slice per cluster)
 };
 
 template <int BN> struct TcConfig {
@@ -149,6 +160,30 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
   }
 }
 
+// One element of a transposed tile (row = weight row, col = token) -> memory, per epilogue; `slice`
+// is the partials' slice.  Called by whole warps (the SwiGLU pairs lanes l and l + 16).
+__device__ __forceinline__ void epilogue_store_one(const TcParams& p, float v, int row, int col, int lane, int slice) {
+  if (p.epilogue == TC_SWIGLU) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, 16);
+    if (lane < 16 && row + 16 < p.Ra) {
+      const int feature = (row >> 5) * 16 + (row & 15);
+      ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * other);
+    }
+    return;
+  }
+  if (row >= p.Ra) return;
+  const size_t o = (size_t)col * p.ldo + row;
+  if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+  else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[o] = v;
+  else if (p.epilogue == TC_ADD_F32) ((float*)p.out)[o] += v;
+  else ((float*)p.out)[(size_t)slice * p.Rb * p.ldo + o] = v;
+}
+
+// Where a cluster's K-slices meet: fp32 [cluster][cpr][128] behind the ring and its barriers.
+__device__ __forceinline__ uint8_t* staging_of(uint8_t* smem, int stages, int stage_bytes) {
+  return smem + stages * stage_bytes + 256;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
@@ -165,6 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   int* last_flag = (int*)(tmem_slot + 2);
 
   pdl_launch_dependents();
+  if (threadIdx.x == 0) TSTAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
   const int kblocks_total = (p.K + TILE_K - 1) / TILE_K;
@@ -205,7 +241,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.static_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
         if (p.static_operand == 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
       }
+      // While the predecessors still run (and memory is often idle: norms, attention), the rest of
+      // this CTA's weights are pulled into L2, so that the ring refills from there later.
+      const int nl2 = min(nkb, npre + p.l2_ahead);
+      for (int i = npre; i < nl2; ++i) {
+        if (p.static_operand == 1) tma_prefetch_l2_2d(&map_a, (kb0 + i) * TILE_K, tile_a * TILE_M);
+        if (p.static_operand == 2) tma_prefetch_l2_2d(&map_b, (kb0 + i) * TILE_K, tile_b * BN);
+      }
+      TSTAMP(1);
       pdl_wait();
+      TSTAMP(2);
       for (int i = 0; i < npre; ++i) {
         uint8_t* a_dst = smem + i * C::STAGE_BYTES;
         if (p.static_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
@@ -229,6 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        if (i == 0) TSTAMP(3);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
         const uint64_t da = umma_desc_k_sw128(a_addr);
@@ -241,6 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
       }
       umma_commit(accum);        // the accumulator is complete
+      TSTAMP(4);
     }
   } else {
     // epilogue warps: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
@@ -249,11 +296,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(accum, 0, abort_flag);
+    if (warp == 2 && lane == 0) TSTAMP(5);
     tc_fence_after_sync();
     constexpr int NV = BN >= 32 ? 32 : 16;
     const int ntiles = gridDim.x * gridDim.y;
     const int tile_lin = tile_b * gridDim.x + tile_a;
-    if (p.epilogue == TC_PARTIAL) {
+    if (p.cluster > 1) {
+      // The K-slices of this tile are the CTAs of a cluster.  Columns (tokens) are dealt out to the
+      // CTAs, `cpr` each: every CTA sends each column of its partial tile to the column's owner (a
+      // store into the owner's shared memory, nothing waits for it), and after one cluster barrier
+      // every owner adds the slices of its columns in slice order and writes them out.
+      const uint32_t me = cluster_ctarank();
+      const int cpr = (BN + p.cluster - 1) / p.cluster;
+      const uint32_t stage0 = smem_u32(staging_of(smem, STAGES, C::STAGE_BYTES));
+      const int r_in = quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += NV) {
+        float v[NV];
+        if (ok && nkb > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int col = c0 + j;
+          if (tile_b * BN + col < p.Rb) {
+            const int owner = col / cpr, k = col - owner * cpr;
+            st_cluster_f32(map_to_cta(stage0 + (uint32_t)((((int)me * cpr + k) * TILE_M + r_in) * 4), (uint32_t)owner),
+                           v[j]);
+          }
+        }
+      }
+    } else if (p.epilogue == TC_PARTIAL) {
       // every K-slice leaves its fp32 partial in out[split][col][row] (transposed tiles only); whoever
       // reads the result next adds the slices in order.  No ticket, no second pass here.
       float* dst = (float*)p.out + (size_t)split * p.Rb * p.ldo;
@@ -350,6 +428,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
+  if (p.cluster > 1) {
+    cluster_sync_all();   // every slice's columns have reached their owners
+    if (warp >= 2) {
+      const int quarter = warp & 3;
+      const int r_in = quarter * 32 + lane;
+      const int row = tile_a * TILE_M + r_in;
+      const int me = (int)cluster_ctarank();
+      const int cpr = (BN + p.cluster - 1) / p.cluster;
+      const float* stage = (const float*)staging_of(smem, STAGES, C::STAGE_BYTES);
+      for (int k = 0; k < cpr; ++k) {
+        const int col_in = me * cpr + k;
+        const int col = tile_b * BN + col_in;
+        if (col_in >= BN || col >= p.Rb) break;            // uniform over the CTA
+        float v = 0.f;
+        for (int r = 0; r < p.cluster; ++r) v += stage[((r * cpr + k) * TILE_M) + r_in];   // slice order
+        epilogue_store_one(p, v, row, col, lane, split / p.cluster);
+      }
+    }
+  }
+  if (threadIdx.x == 0) TSTAMP(6);
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(&g_gemm_tc_error, 1);
     // give tile loads that may still be in flight time to land before shared memory is handed on
@@ -784,7 +882,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::smem_bytes(C::MAX_STAGES));
+                                         C::smem_bytes(C::MAX_STAGES));   // (a cluster's staging fits: see below)
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -802,6 +900,18 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   q.stages = stages;
   q.staged = 0;
+  if (q.cluster > 1) {
+    // the partial tile of a slice (fp32 [BN][128]) is staged in the ring's memory
+    if (q.cluster > 8 || p.splits % q.cluster || !p.transposed || BN > 64) return DLGO_ERR_SIZE;
+    const int cpr = (BN + q.cluster - 1) / q.cluster;
+    const int staging = q.cluster * cpr * TILE_M * 4;
+    while (stages > 2 && C::smem_bytes(stages) + staging > 110 * 1024) --stages;
+    if (C::smem_bytes(stages) + staging > C::smem_bytes(C::MAX_STAGES)) return DLGO_ERR_SIZE;
+    q.stages = stages;
+    launch_kernel_cluster(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages) + staging, stream,
+                          dim3(1, 1, q.cluster), ma, mb, q);
+    return launch_status();
+  }
   launch_kernel(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages), stream, ma, mb, q);
   return launch_status();
 }
@@ -877,15 +987,23 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 // tiles are then requested before the kernel waits for its predecessor), else 0.
 // pair_tile: 0, or 128 / 256 to compute 256 x pair_tile tiles with pairs of CTAs (cta_group::2; many
 // tokens only: not transposed, one K-slice; bn is then ignored).
+// cluster: 0 / 1, or 2..8 (transposed only, dividing splits): that many consecutive K-slices form a
+// thread-block cluster and are summed, in order, through distributed shared memory; no workspace, no
+// counters.  Every epilogue but 4 then needs cluster == splits; epilogue 4 writes splits / cluster
+// slices: out is [splits / cluster][Rb][ldo].
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
                              int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
-                             int* counters, int static_operand, int pair_tile, cudaStream_t stream) {
+                             int* counters, int static_operand, int pair_tile, int cluster, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
   if (epilogue < 0 || epilogue > 4) return DLGO_ERR_SIZE;
   if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
   if (epilogue == TC_PARTIAL && !transposed) return DLGO_ERR_SIZE;
-  if (splits > 1 && epilogue != TC_PARTIAL && (workspace == nullptr || counters == nullptr)) return DLGO_ERR_SIZE;
+  if (cluster < 0 || cluster > 8) return DLGO_ERR_SIZE;
+  if (cluster > 1 && (!transposed || splits % cluster || (epilogue != TC_PARTIAL && cluster != splits)))
+    return DLGO_ERR_SIZE;
+  if (splits > 1 && cluster <= 1 && epilogue != TC_PARTIAL && (workspace == nullptr || counters == nullptr))
+    return DLGO_ERR_SIZE;
   if (epilogue == TC_SWIGLU) {
     const int weight_rows = transposed ? Ra : Rb;
     if (weight_rows % 32 || (!transposed && bn < 32)) return DLGO_ERR_SIZE;
@@ -899,6 +1017,19 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
+  p.cluster = cluster > 1 ? cluster : 1;
+  p.l2_ahead = 0;
+  if (p.static_operand) {
+    // at most DLGO_TC_L2_AHEAD_MB (default 80) of weights per launch are pulled into L2 ahead of time
+    static const long long budget = [] {
+      const char* e = getenv("DLGO_TC_L2_AHEAD_MB");
+      return (e ? atoll(e) : 80LL) << 20;
+    }();
+    const long long box = (long long)(p.static_operand == 1 ? TILE_M : bn) * TILE_K * 2;
+    const long long ctas = (long long)((Ra + TILE_M - 1) / TILE_M) * ((Rb + bn - 1) / bn) * splits;
+    const long long cap = budget / (box * ctas);
+    p.l2_ahead = (int)(cap > 1024 ? 1024 : cap);
+  }
   if (!transposed && splits == 1 && pair_tile != 0) {
     // many tokens, CTA pairs: A's box is 128 rows, B's box is half the tile's width
     if (pair_tile != 128 && pair_tile != 256) return DLGO_ERR_SIZE;
@@ -927,3 +1058,9 @@ DLGO_EXPORT int dlgo_gemm_tc_error() {
   if (v) cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof(int));
   return v;
 }
+
+#ifdef DLGO_TC_TIMING
+DLGO_EXPORT int dlgo_gemm_tc_times(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_tc_times, sizeof(unsigned long long) * 512 * 8) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -296,14 +296,23 @@ def gemm_tc_workspace_floats(ra: int, rb: int, bn: int, splits: int) -> int:
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, epilogue: int, bn: int,
             splits: int = 1, workspace: Optional[torch.Tensor] = None,
-            counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0) -> torch.Tensor:
+            counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0,
+            cluster: int = 0) -> torch.Tensor:
     """D[Ra, Rb] = a[Ra, K] . b[Rb, K]^T on the tensor cores (bf16 in, fp32 accumulate).
 
     ``out`` receives D (``transposed``: D^T) through ``epilogue``; with ``splits`` > 1 the K range is
     shared by that many CTAs per tile, which needs ``workspace`` (fp32) and zeroed ``counters`` (int32).
     ``static_operand`` (1: a, 2: b) names the operand that holds weights no earlier kernel writes.
     ``pair_tile`` (128 or 256): many tokens, 256 x pair_tile tiles computed by pairs of CTAs (cta_group::2).
+    ``cluster`` (2..8, dividing ``splits``; transposed only): that many consecutive K-slices are one
+    thread-block cluster and meet through distributed shared memory instead of the workspace; partials
+    then come as ``splits // cluster`` slices, every other epilogue needs ``cluster == splits``.
     """
+    cluster = cluster if cluster > 1 else 1
+    if cluster > 1 and (not transposed or cluster > 8 or splits % cluster or
+                        (epilogue != TC_PARTIAL and cluster != splits)):
+        raise KernelError(f"gemm_tc: a cluster of {cluster} K-slices does not fit {splits} slices of this product")
+    slices_out = splits // cluster
     for n, t in (("a", a), ("b", b)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"gemm_tc: {n} must be a 2-D bfloat16 GPU tensor with unit inner stride")
@@ -313,16 +322,16 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         raise KernelError(f"gemm_tc: a has K={k}, b has K={k2}")
     if out.stride(-1) != 1:
         raise KernelError("gemm_tc: out must have unit inner stride")
-    if splits > 1 and epilogue != TC_PARTIAL:
+    if splits > 1 and cluster == 1 and epilogue != TC_PARTIAL:
         need = gemm_tc_workspace_floats(ra, rb, bn, splits)
         tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
         if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
             raise KernelError(f"gemm_tc: {splits} K-slices need {need} floats of workspace and {tiles} counters")
     if epilogue == TC_PARTIAL:
         # out is [slices, rb, ra]: the kernel's row stride is that of one slice's rows
-        if not transposed or out.dim() != 3 or out.dtype != torch.float32 or tuple(out.shape) != (splits, rb, ra) \
-                or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
-            raise KernelError(f"gemm_tc: partials go to a float32 [{splits}, {rb}, {ra}] tensor of a transposed product")
+        if not transposed or out.dim() != 3 or out.dtype != torch.float32 or \
+                tuple(out.shape) != (slices_out, rb, ra) or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
+            raise KernelError(f"gemm_tc: partials go to a float32 [{slices_out}, {rb}, {ra}] tensor of a transposed product")
         ldo = out.stride(1)
     else:
         want_shape = (rb, ra) if transposed else (ra, rb)
@@ -336,7 +345,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         ldo = out.stride(0)
     st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
                                       _ptr(out), _i(ldo), _i(1 if transposed else 0), _i(epilogue), _i(bn),
-                                      _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _i(pair_tile), _stream())
+                                      _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _i(pair_tile),
+                                      _i(cluster), _stream())
     _check(st, "gemm_tc")
     return out
 

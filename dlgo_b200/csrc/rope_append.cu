@@ -178,6 +178,88 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
   }
 }
 
+// The same when the projection left its K-slices unsummed (decode steps): one warp per (token, head),
+// so that a step's few tokens still spread over many SMs.  Everything that does not depend on the
+// projection (position, page, cos / sin) is fetched before the kernel waits for it; after the wait
+// a lane has all slices' loads of a pair in flight at once (sixteen slices per round trip).
+constexpr int RP_WARPS = 4;
+template <typename T>
+__global__ void __launch_bounds__(RP_WARPS * 32)
+rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                         const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                         const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                         const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
+                         T* __restrict__ vpages, int Hq, int Hkv, int hd, int rot, int page_size,
+                         int interleaved, int write_cache, const float* __restrict__ parts, int S,
+                         size_t part_stride) {
+  pdl_launch_dependents();
+  const int t = blockIdx.y;
+  const int head = blockIdx.x * RP_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int half = hd / 2, rhalf = rot / 2;
+  const bool active = head < Hq + 2 * Hkv;
+  const int pos = token_pos[t];
+  T* dst = nullptr;                       // where the head goes: q in place, k and v to their page
+  if (active) {
+    if (head < Hq) {
+      dst = qkv + (size_t)t * ld + (size_t)head * hd;
+    } else if (write_cache) {
+      const int slot = seq_slot[token_seq[t]];
+      const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+      const bool is_k = head < Hq + Hkv;
+      const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+      dst = (is_k ? kpages : vpages) + (((size_t)page * Hkv + kvh) * page_size + (size_t)(pos % page_size)) * hd;
+    }
+  }
+  const bool rotates = active && head < Hq + Hkv;
+  // first pair of this lane: its angle is ready before the wait
+  float c0 = 1.f, s0 = 0.f;
+  if (rotates && lane < rhalf) {
+    c0 = cos_t[(size_t)pos * rhalf + lane];
+    s0 = sin_t[(size_t)pos * rhalf + lane];
+  }
+  pdl_wait();
+  if (!active || dst == nullptr) return;
+  const float* pp = parts + (size_t)t * ld + (size_t)head * hd;
+  for (int i = lane; i < half; i += 32) {
+    int i0, i1;
+    const bool rotate = i < rhalf;
+    if (rotate) {
+      if (interleaved) { i0 = 2 * i; i1 = 2 * i + 1; }
+      else { i0 = i; i1 = i + rhalf; }
+    } else {
+      i0 = rot + 2 * (i - rhalf);
+      i1 = i0 + 1;
+    }
+    float x0 = 0.f, x1 = 0.f;
+    for (int sb = 0; sb < S; sb += 16) {
+      float a[16], b[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        a[j] = (sb + j < S) ? __ldcg(pp + (size_t)(sb + j) * part_stride + i0) : 0.f;
+        b[j] = (sb + j < S) ? __ldcg(pp + (size_t)(sb + j) * part_stride + i1) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (sb + j < S) { x0 += a[j]; x1 += b[j]; }
+      }
+    }
+    if (rotates && rotate) {
+      float c = c0, sn = s0;
+      if (i != lane) {
+        c = cos_t[(size_t)pos * rhalf + i];
+        sn = sin_t[(size_t)pos * rhalf + i];
+      }
+      const float y0 = x0 * c - x1 * sn;
+      const float y1 = x0 * sn + x1 * c;
+      x0 = y0;
+      x1 = y1;
+    }
+    dst[i0] = from_float<T>(x0);
+    dst[i1] = from_float<T>(x1);
+  }
+}
+
 }  // namespace dlgo
 
 using namespace dlgo;
@@ -204,6 +286,21 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
       launch_kernel(rope_append_vec_kernel<__nv_bfloat16>, dim3(T), dim3(vthreads), 0, stream, (__nv_bfloat16*)qkv, ld,
                     cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages, (__nv_bfloat16*)kpages,
                     (__nv_bfloat16*)vpages, Hq, Hkv, hd, page_size, write_cache);
+    else
+      return DLGO_ERR_DTYPE;
+    return launch_status();
+  }
+  if (parts != nullptr && T <= 65535) {
+    const dim3 grid((Hq + 2 * Hkv + RP_WARPS - 1) / RP_WARPS, T);
+    if (dtype == DLGO_F32)
+      launch_kernel(rope_append_parts_kernel<float>, grid, dim3(RP_WARPS * 32), 0, stream, (float*)qkv, ld, cos_t,
+                    sin_t, token_pos, token_seq, seq_slot, page_table, max_pages, (float*)kpages, (float*)vpages, Hq,
+                    Hkv, hd, rot, page_size, interleaved, write_cache, parts, S, (size_t)part_stride);
+    else if (dtype == DLGO_BF16)
+      launch_kernel(rope_append_parts_kernel<__nv_bfloat16>, grid, dim3(RP_WARPS * 32), 0, stream,
+                    (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+                    (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved,
+                    write_cache, parts, S, (size_t)part_stride);
     else
       return DLGO_ERR_DTYPE;
     return launch_status();

@@ -94,7 +94,7 @@ class GQAAttention(Mixer):
         fused_rope = decode_kernel and not _NO_FUSE and K.attention_decode_fuses_rope(
             act, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.page_size)
         # few tokens: the projection leaves its K-slices unsummed and whoever rotates adds them
-        qkv_parts = self.wqkv.partials(x)
+        qkv_parts = self.wqkv.partials(x, single_ok=False)
         qkv = None
         if qkv_parts is None:
             qkv = self.wqkv(x, STORE)

@@ -39,9 +39,10 @@ class Linear:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
 
-    def partials(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+    def partials(self, x: torch.Tensor, single_ok: bool = True) -> Optional[torch.Tensor]:
         """The product as unsummed fp32 K-slices [slices, tokens, out] where the kernel offers that
-        (few tokens on the tensor cores), else ``None``."""
+        (few tokens on the tensor cores), else ``None``; also ``None`` for a single slice unless
+        ``single_ok`` (a caller that wants the finished product in the activation type)."""
         if self._tc is not None and not self.fuses_swiglu:
-            return self._tc.partials(x)
+            return self._tc.partials(x, single_ok)
         return None

@@ -25,6 +25,10 @@ MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
 MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
+# K-slices summed on chip by a thread-block cluster (2..8; 1: off).  Off by default: measured on a
+# B200, clusters of these large CTAs start later than independent CTAs do (they cannot slip into an
+# SM one by one while the previous kernel drains), which costs more than the cheaper reduction saves.
+CLUSTER_MAX = int(os.environ.get("DLGO_TC_CLUSTER", 1))
 
 _workspaces: Dict[int, List[torch.Tensor]] = {}
 _counters: Dict[int, torch.Tensor] = {}
@@ -55,6 +59,21 @@ def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
     return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
 
+def clustered(splits: int, final: bool) -> tuple[int, int]:
+    """(splits, cluster) with the K-slices grouped into thread-block clusters that sum their partial
+    tiles on chip.  ``final``: the product needs ONE result (every epilogue but the partials), so all
+    slices must fit one cluster; partials may come as several clusters' slices."""
+    if CLUSTER_MAX <= 1 or splits <= 1:
+        return splits, 1
+    if splits <= CLUSTER_MAX:
+        return splits, splits
+    if final:
+        return CLUSTER_MAX, CLUSTER_MAX
+    groups = (splits + CLUSTER_MAX - 1) // CLUSTER_MAX
+    per = max(1, splits // groups)
+    return per * groups, per
+
+
 class TensorCorePlan:
     def __init__(self, weight: torch.Tensor, swiglu: bool = False):
         self.weight = weight
@@ -76,11 +95,12 @@ class TensorCorePlan:
                                   device=x.device)
         if t <= SKINNY_MAX:
             bn, splits = skinny_shape(t, self.n, self.k)
+            splits, cluster = clustered(splits, True)
             ws = cnt = None
-            if splits > 1:
+            if splits > 1 and cluster == 1:
                 ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
                 cnt = _counter_buffer(x.device)
-            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1)
+            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1, cluster=cluster)
         bn = 256 if self.n > 128 else 128
         if PREFILL_BN in (128, 256):
             bn = PREFILL_BN
@@ -88,16 +108,21 @@ class TensorCorePlan:
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
 
-    def partials(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+    def partials(self, x: torch.Tensor, single_ok: bool = True) -> Optional[torch.Tensor]:
         """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
-        reads the result next adds them in order (this spares the contraction its own reduction pass).
-        ``None`` when the tokens are too many for that."""
+        reads the result next adds them in order (this spares the contraction a reduction pass through
+        memory; slices of one thread-block cluster are summed on chip and come as one).
+        ``None`` when the tokens are too many for that, or, unless ``single_ok``, when there would be
+        one slice only (the caller then asks for the finished product in the type it wants)."""
         t = x.shape[0]
         if t > SKINNY_MAX or self.swiglu:
             return None
         bn, splits = skinny_shape(t, self.n, self.k)
-        out = torch.empty((splits, t, self.n), dtype=torch.float32, device=x.device)
-        K.gemm_tc(self.weight, x, out, True, K.TC_PARTIAL, bn, splits, static_operand=1)
+        splits, cluster = clustered(splits, False)
+        if splits == cluster and not single_ok:
+            return None
+        out = torch.empty((splits // cluster, t, self.n), dtype=torch.float32, device=x.device)
+        K.gemm_tc(self.weight, x, out, True, K.TC_PARTIAL, bn, splits, static_operand=1, cluster=cluster)
         return out
 
 

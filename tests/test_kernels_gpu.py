@@ -581,6 +581,53 @@ def test_gemm_tc_split_k_is_exact_and_repeatable(N, T_, K_, splits):
     k.check_device_errors()
 
 
+@pytest.mark.parametrize("N,T_,K_,splits,cluster,bn,epi", [
+    (256, 5, 512, 2, 2, 16, "store"), (384, 16, 2048, 8, 8, 16, "add"), (130, 33, 200, 4, 4, 64, "f32"),
+    (2048, 64, 8192, 8, 8, 64, "store"), (3072, 8, 2048, 8, 8, 16, "store"), (2048, 8, 8192, 18, 6, 16, "partial"),
+    (1000, 20, 1096, 6, 3, 32, "partial"), (512, 7, 640, 5, 5, 16, "partial"), (640, 9, 4096, 7, 7, 16, "swiglu")])
+def test_gemm_tc_k_slices_meet_in_a_cluster(N, T_, K_, splits, cluster, bn, epi):
+    """K-slices that form a thread-block cluster are summed through distributed shared memory: same
+    result as one slice up to the order of the fp32 sums, and the same bits on every run."""
+    g = torch.Generator().manual_seed(N + T_ + splits)
+    w = (torch.randn(N, K_, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    x = torch.randn(T_, K_, generator=g).to(torch.bfloat16).to(DEV)
+    ref = _tc_ref(x, w)                                            # [T, N] in float64
+    runs = []
+    for _ in range(2):
+        if epi == "partial":
+            out = torch.full((splits // cluster, T_, N), float("nan"), device=DEV)
+            K().gemm_tc(w, x, out, True, K().TC_PARTIAL, bn, splits, static_operand=1, cluster=cluster)
+            got = out.double().sum(0)
+        elif epi == "swiglu":
+            out = torch.empty((T_, N // 2), dtype=torch.bfloat16, device=DEV)
+            K().gemm_tc(w, x, out, True, K().TC_SWIGLU, bn, splits, static_operand=1, cluster=cluster)
+            got = out.double()
+        elif epi == "add":
+            out = torch.ones((T_, N), device=DEV)
+            K().gemm_tc(w, x, out, True, K().TC_ADD_F32, bn, splits, static_operand=1, cluster=cluster)
+            got = out.double() - 1.0
+        else:
+            dt = torch.bfloat16 if epi == "store" else torch.float32
+            out = torch.empty((T_, N), dtype=dt, device=DEV)
+            K().gemm_tc(w, x, out, True, K().TC_STORE if epi == "store" else K().TC_STORE_F32, bn, splits,
+                        static_operand=1, cluster=cluster)
+            got = out.double()
+        runs.append(out.clone())
+        if epi == "swiglu":
+            r = ref.view(T_, N // 32, 2, 16)
+            gate, up = r[:, :, 0], r[:, :, 1]
+            want = (gate / (1 + torch.exp(-gate)) * up).reshape(T_, N // 2)
+            torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+        else:
+            tol = 2e-2 if epi == "store" else 2e-4
+            torch.testing.assert_close(got, ref, atol=tol * float(ref.abs().max()), rtol=0)
+    assert torch.equal(runs[0], runs[1])
+    K().check_device_errors()
+    with pytest.raises(Exception):                                 # a cluster must divide the slices
+        K().gemm_tc(w, x, torch.empty((T_, N), dtype=torch.bfloat16, device=DEV), True, K().TC_STORE, bn, splits,
+                    static_operand=1, cluster=splits + 1 if splits < 8 else 3)
+
+
 @pytest.mark.parametrize("T_", [3, 40, 200])
 def test_gemm_tc_swiglu_epilogue(T_):
     k = K()
