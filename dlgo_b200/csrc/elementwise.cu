@@ -178,6 +178,63 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   }
 }
 
+// The same with a row spread over the CTAs of a thread-block cluster (few rows, wide rows: decode
+// steps).  A row's K-slices are S * d * 4 bytes that one SM pulls out of L2 no faster than ~100 GB/s;
+// NC CTAs pull NC times as fast.  Every CTA settles and keeps its stretch of the row in registers,
+// sends its sum of squares to all CTAs of the cluster (distributed shared memory), and after one
+// cluster barrier each adds the NC sums in rank order (the same order everywhere) and writes its
+// stretch of the normalised row.  blockDim.x * 4 >= chunk (the columns per CTA, a multiple of 4).
+template <typename TO>
+__global__ void add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* __restrict__ parts, int S,
+                                           size_t part_stride, const float* __restrict__ w, TO* __restrict__ out,
+                                           const int* __restrict__ rows, int d, float eps, int chunk) {
+  pdl_launch_dependents();
+  __shared__ float scratch[32];
+  __shared__ float ss_all[8];
+  const int r = blockIdx.y;
+  unsigned rank, nc;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nc));
+  const int i = (int)rank * chunk + threadIdx.x * 4;
+  const bool live = threadIdx.x * 4 < chunk && i < d;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live && w != nullptr) w0 = *reinterpret_cast<const float4*>(w + i);
+  const int src = rows ? rows[r] : r;
+  pdl_wait();
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    float* xr = x + (size_t)src * d;
+    const float* pr = parts + (size_t)src * d;
+    v = *reinterpret_cast<const float4*>(xr + i);
+    for (int s0 = 0; s0 < S; s0 += 16) {
+      float4 t[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        t[j] = (s0 + j < S) ? __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(s0 + j) * part_stride + i))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (s0 + j < S) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+      }
+    }
+    *reinterpret_cast<float4*>(xr + i) = v;
+  }
+  if (w == nullptr) return;     // (uniform over the cluster: nobody reaches the barrier)
+  float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x < nc) {
+    unsigned local = (unsigned)__cvta_generic_to_shared(&ss_all[rank]), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((unsigned)threadIdx.x));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(ss) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float total = 0.f;
+  for (unsigned k = 0; k < nc; ++k) total += ss_all[k];
+  const float sc = norm_scale<TO>(total / (float)d + eps);
+  if (live) store4<TO>(out + (size_t)r * d + i, v.x * sc * w0.x, v.y * sc * w0.y, v.z * sc * w0.z, v.w * sc * w0.w);
+}
+
 // ------------------------------------------------------------------- SwiGLU
 // in: [T, 2F] with the gate in columns [0, F) and the up projection in [F, 2F).
 template <typename T>
@@ -252,6 +309,25 @@ DLGO_EXPORT int dlgo_add_rmsnorm(float* x, const float* parts, int S, long long 
                                  cudaStream_t stream) {
   if (R <= 0) return DLGO_OK;
   if (d <= 0 || S < 0 || (size_t)d * sizeof(float) > 200 * 1024) return DLGO_ERR_SIZE;
+  if (out_dtype != DLGO_F32 && out_dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
+  static const int cluster_on = [] { const char* e = getenv("DLGO_NORM_CLUSTER"); return e ? atoi(e) : 8; }();
+  if (cluster_on > 1 && R <= 256 && d >= 1024 && (d & 3) == 0 && (part_stride & 3) == 0 && S > 0) {
+    // few wide rows: a cluster of CTAs per row (at least 128 columns each)
+    int nc = cluster_on > 8 ? 8 : cluster_on;
+    while (nc > 1 && d / nc < 128) nc >>= 1;
+    const int chunk = (((d + nc - 1) / nc) + 3) / 4 * 4;
+    const int threads = ((chunk / 4) + 31) / 32 * 32;
+    if (nc > 1 && threads <= 1024) {
+      if (out_dtype == DLGO_F32)
+        launch_kernel_cluster(add_rmsnorm_cluster_kernel<float>, dim3(nc, R), dim3(threads), 0, stream, dim3(nc, 1, 1),
+                              x, parts, S, (size_t)part_stride, w, (float*)out, rows, d, eps, chunk);
+      else
+        launch_kernel_cluster(add_rmsnorm_cluster_kernel<__nv_bfloat16>, dim3(nc, R), dim3(threads), 0, stream,
+                              dim3(nc, 1, 1), x, parts, S, (size_t)part_stride, w, (__nv_bfloat16*)out, rows, d, eps,
+                              chunk);
+      return launch_status();
+    }
+  }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
   const size_t smem = (size_t)d * sizeof(float);
   if (out_dtype == DLGO_F32) {

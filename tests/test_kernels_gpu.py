@@ -666,7 +666,7 @@ def test_gemm_tc_refuses_what_it_cannot_take():
 
 # ------------------------------------------------ partial sums handed to the next kernel
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("S,d", [(1, 50), (3, 200), (8, 2048), (9, 96)])
+@pytest.mark.parametrize("S,d", [(1, 50), (3, 200), (8, 2048), (9, 96), (18, 4096), (5, 1028), (17, 3000), (2, 1024)])
 def test_add_rmsnorm_settles_partials_in_order(dtype, S, d):
     k = K()
     torch.manual_seed(S * d)
