@@ -102,6 +102,7 @@ template <> __device__ __forceinline__ float soft_exp<__nv_bfloat16>(float x) {
 template <typename T, int LPK>
 __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecParams p) {
   pdl_launch_dependents();
+  if (threadIdx.x == 0) TSTAMP(0);
   constexpr int VEC = Ld16<T>::VEC;
   constexpr int HD = LPK * VEC;
   constexpr int KPW = 32 / LPK;            // keys a warp covers per iteration
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
   __shared__ float sm_acc[DEC_WARPS][DEC_GMAX][HD];
   __shared__ float sm_ml[DEC_WARPS][DEC_GMAX][2];
   __shared__ int sm_last;
+  __shared__ __align__(16) T sm_v[DEC_WARPS][TILE * HD];   // a warp's tile of values, copied in asynchronously
   __shared__ float cl_acc[DEC_GMAX][HD];   // this block's merged result, read by the cluster's first block
   __shared__ float cl_ml[DEC_GMAX][2];
 
@@ -151,7 +153,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
       asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + (size_t)ln * 128));
     }
   }
+  if (threadIdx.x == 0) TSTAMP(1);
   pdl_wait();
+  if (threadIdx.x == 0) TSTAMP(2);
 
   float q[DEC_GMAX][VEC], acc[DEC_GMAX][VEC], m[DEC_GMAX], l[DEC_GMAX];
   if (!p.fuse_rope) {
@@ -279,18 +283,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     float s[DEC_GMAX][DEC_ITER];
     bool live[DEC_ITER];
     float tmax[DEC_GMAX];
-    // all of the tile's keys AND values are requested before any arithmetic: one memory round trip
-    uint4 kraw[DEC_ITER], vraw[DEC_ITER];
+    // All of the tile's keys AND values are requested before any arithmetic: one memory round trip.
+    // The keys come into registers; the values, needed later, are copied asynchronously into this
+    // lane's own 16 bytes of shared memory (no registers held meanwhile, nothing shared between lanes).
+    uint4 kraw[DEC_ITER];
 #pragma unroll
     for (int it = 0; it < DEC_ITER; ++it) {
       const int key = key0 + it * KPW + grp;
       const int t = pg * PS + key;
       live[it] = t < t_end && t >= t_begin;
       kraw[it] = make_uint4(0u, 0u, 0u, 0u);
-      vraw[it] = make_uint4(0u, 0u, 0u, 0u);
       if (live[it]) {
         kraw[it] = *reinterpret_cast<const uint4*>(kp + (size_t)key * HD + sub * VEC);
-        vraw[it] = *reinterpret_cast<const uint4*>(vp + (size_t)key * HD + sub * VEC);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&sm_v[warp][(it * KPW + grp) * HD + sub * VEC]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vp + (size_t)key * HD + sub * VEC)
+                     : "memory");
       }
     }
 #pragma unroll
@@ -328,10 +335,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
         l[g] += pr;
       }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
     for (int it = 0; it < DEC_ITER; ++it) {
       float vf[VEC];
-      cvt16<T>(vraw[it], vf);   // zeros where the key is not live; its probability is zero as well
+      // zeros where the key is not live (nothing was copied there; its probability is zero as well)
+      const uint4 vraw = live[it] ? *reinterpret_cast<const uint4*>(&sm_v[warp][(it * KPW + grp) * HD + sub * VEC])
+                                  : make_uint4(0u, 0u, 0u, 0u);
+      cvt16<T>(vraw, vf);
 #pragma unroll
       for (int g = 0; g < DEC_GMAX; ++g)
 #pragma unroll
@@ -339,6 +350,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     }
   }
 
+  if (threadIdx.x == 0) TSTAMP(3);
   // lane groups of a warp share their maximum: sums add up.  l was counted once per lane of a
   // group, so only lanes with sub == 0 contribute it.
 #pragma unroll
@@ -404,7 +416,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     // distributed shared memory and writes the result.  No global round trip, fence or ticket.
     namespace cg = cooperative_groups;
     cg::cluster_group cl = cg::this_cluster();
+    if (threadIdx.x == 0) TSTAMP(4);
     cl.sync();
+    if (threadIdx.x == 0) TSTAMP(5);
     if (cl.block_rank() == 0) {
       const int NS = p.n_splits;
       for (int idx = threadIdx.x; idx < GC * HD; idx += DEC_THREADS) {
@@ -437,7 +451,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
         ((T*)p.out)[(size_t)b * p.ldo + (size_t)(kvh * G + g0 + g) * HD + d] = from_float<T>(a / ll);
       }
     }
+    if (threadIdx.x == 0) TSTAMP(6);
     cl.sync();   // nobody leaves while its shared memory may still be read
+    if (threadIdx.x == 0) TSTAMP(7);
     return;
   }
   if (p.n_splits == 1 || p.counters == nullptr) return;
@@ -644,3 +660,5 @@ DLGO_EXPORT int dlgo_attention_decode_rope(const void* qkv, const float* parts, 
   p.rot = rot; p.interleaved = interleaved; p.fuse_rope = 1; p.write_cache = write_cache;
   return decode_common(p, dtype, B, hd, stream);
 }
+
+DLGO_TIMES_EXPORT

@@ -143,6 +143,28 @@ inline void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Diagnostic build (-DDLGO_TIMING): kernels stamp the global timer at named points, per block, and
+// the library exports dlgo_times() to fetch the stamps (8 per block, the first 1024 blocks).
+#ifdef DLGO_TIMING
+__device__ unsigned long long g_times[1024 * 8];
+#define TSTAMP(k)                                                                              \
+  do {                                                                                         \
+    const int c_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;             \
+    if (c_ < 1024) {                                                                           \
+      unsigned long long t_;                                                                   \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                   \
+      g_times[c_ * 8 + (k)] = t_;                                                              \
+    }                                                                                          \
+  } while (0)
+#define DLGO_TIMES_EXPORT                                                                      \
+  extern "C" __attribute__((visibility("default"))) int dlgo_times(unsigned long long* out) {  \
+    return cudaMemcpyFromSymbol(out, dlgo::g_times, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : -1; \
+  }
+#else
+#define TSTAMP(k) do {} while (0)
+#define DLGO_TIMES_EXPORT
+#endif
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DLGO_OK : (int)e;

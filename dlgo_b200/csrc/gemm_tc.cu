@@ -40,13 +40,6 @@ constexpr int UMMA_K = 16;
 constexpr int TC_THREADS = 192;
 
 __device__ int g_gemm_tc_error = 0;  // set when a bounded wait ran out
-#ifdef DLGO_TC_TIMING
-__device__ unsigned long long g_tc_times[512 * 8];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TSTAMP(k) do { const int c_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; if (c_ < 512) g_tc_times[c_ * 8 + (k)] = gtime(); } while (0)
-#else
-#define TSTAMP(k) do {} while (0)
-#endif
 
 struct TcParams {
   int Ra, Rb, K;      // rows of A, rows of B, contraction length
@@ -1059,8 +1052,4 @@ DLGO_EXPORT int dlgo_gemm_tc_error() {
   return v;
 }
 
-#ifdef DLGO_TC_TIMING
-DLGO_EXPORT int dlgo_gemm_tc_times(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_tc_times, sizeof(unsigned long long) * 512 * 8) == cudaSuccess ? 0 : -1;
-}
-#endif
+DLGO_TIMES_EXPORT

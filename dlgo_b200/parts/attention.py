@@ -29,6 +29,7 @@ _TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (genera
 # inside a whole step it is no faster than the separate rope kernel, so it is opt-in: DLGO_ATTN_FUSE_ROPE=1.
 _NO_FUSE = not os.environ.get("DLGO_ATTN_FUSE_ROPE")
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
+_AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 32)) << 20   # keys and values hinted into L2 per layer
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
 
@@ -101,9 +102,14 @@ class GQAAttention(Mixer):
         if not fused_rope:
             if qkv is None:
                 qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
+            ahead = 0
+            if decode_kernel and qkv_parts is not None and _AHEAD_BYTES > 0:
+                # pages of keys and values per (sequence, kv head) to hint into L2 for the attention kernel
+                page_bytes = cache.page_size * self.head_dim * x.element_size()
+                ahead = max(1, _AHEAD_BYTES // (2 * T * self.num_kv_heads * page_bytes))
             K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                           cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                          qkv_parts)
+                          qkv_parts, ahead, self.window or 0)
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
