@@ -888,7 +888,8 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
   if (p.transposed) {
     // few tokens: keep the footprint under half an SM so that two CTAs (of this kernel or of the next
     // one, launched early) share it and one's start-up hides behind the other's streaming
-    while (stages > 2 && C::smem_bytes(stages) > 110 * 1024) --stages;
+    static const int ring_kb = [] { const char* e = getenv("DLGO_TC_RING_KB"); return e ? atoi(e) : 110; }();
+    while (stages > 2 && C::smem_bytes(stages) > ring_kb * 1024) --stages;
   }
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   q.stages = stages;

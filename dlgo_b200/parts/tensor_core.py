@@ -20,7 +20,13 @@ import torch
 from ..csrc import kernels as K
 
 SKINNY_MAX = 64          # tokens up to which the weight is the M operand
-TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 2 * 148))  # two CTAs per SM stream the weight (footprint under half an SM)
+# CTAs that share a weight.  Up to 16 tokens: two per SM (one's start-up hides behind the other's
+# streaming).  More tokens: one per SM, because every extra K-slice writes and re-reads a partial
+# result of tokens x outputs floats, which at 64 tokens is half of the weight's own bytes (measured:
+# 35.2K instead of 30.3K tokens a second at batch 64).
+_TARGET_ENV = os.environ.get("DLGO_TC_TARGET_CTAS")
+TARGET_CTAS = int(_TARGET_ENV) if _TARGET_ENV else 2 * 148
+TARGET_CTAS_WIDE = int(_TARGET_ENV) if _TARGET_ENV else 148
 MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
@@ -55,7 +61,8 @@ def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
     bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
-    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, TARGET_CTAS // tiles)) if tiles < TARGET_CTAS else 1
+    target = TARGET_CTAS if tokens <= 16 else TARGET_CTAS_WIDE
+    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, target // tiles)) if tiles < target else 1
     return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
 
