@@ -1,0 +1,367 @@
+// Decode attention in bfloat16 on the tensor cores (warp-level mma.sync, m16n8k16).
+//
+// Same formulas as attention_decode.cu (models/llm/forward.go:258-278): scores q.k * scale over the
+// keys t <= pos (t > pos - window if windowed), softmax in fp32, weighted sum of the values.  The
+// fp32-pipe kernel spends about 450 instructions per warp on 16 keys (a multiply-add per element and a
+// shuffle tree per score); here a warp spends 16 tensor-core instructions on them, which is what
+// counts once many sequences decode together.  A decode step has one query row per head, so the query
+// heads of a kv head (up to 8 per block) are the rows of the 16-row MMA tile and rows 8-15 stay zero:
+// the tensor cores are badly used and still several times faster than the fp32 pipes here.
+//
+// Nothing goes through shared memory on the way in: the k index of an MMA may be any permutation of
+// the head's dimensions as long as q and k agree, and so may the order of the output dimensions.
+// The permutations are chosen so that every lane's fragment registers are 16-byte pieces of rows as
+// they lie in the cache pages:
+//   * scores: lane (r = lane / 4, c = lane % 4) holds dimensions [c * HD/4, (c + 1) * HD/4) of query
+//     head r and of key r of each 8-key n-tile; k-step kk takes 4 of them;
+//   * values: the lane holds dimensions [r * HD/8, (r + 1) * HD/8) of keys 2c, 2c+1, 2c+8, 2c+9 of a
+//     16-key k-step; a byte permute pairs two keys' elements into one B register.  Output column
+//     nt * 8 + j of the MMA is dimension j * HD/8 + nt of the head.
+// The probabilities go from the score accumulators straight into the A registers of the second MMA
+// (rounded to bfloat16, as the prompt kernel does).
+//
+// A block takes one sequence, one kv head (8 of its query heads) and a slice of the pages; 2..8
+// slices form a thread-block cluster and combine through distributed shared memory.
+#include <cooperative_groups.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dlgo {
+
+constexpr int DM_THREADS = 128;
+constexpr int DM_WARPS = DM_THREADS / 32;
+constexpr int DM_GM = 8;   // query heads of a kv head per block
+
+struct DecMmaParams {
+  const __nv_bfloat16* q;
+  int ldq;
+  const __nv_bfloat16* kpages;
+  const __nv_bfloat16* vpages;
+  const int* page_table;
+  int max_pages;
+  const int* seq_slot;   // [B]
+  const int* token_pos;  // [B] position of the new token (its key is already in the cache)
+  __nv_bfloat16* out;
+  int ldo;
+  int Hq, Hkv, page_size, n_splits, n_gchunks, window;
+  float scale;
+};
+
+// d (rows 0-7 only) += A (rows 0-7; rows 8-15 are zero) * B
+__device__ __forceinline__ void mma_rows8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  float x2, x3;
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %10, %10};"
+      : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& u, int i) {   // i is a compile-time constant after unrolling
+  return i == 0 ? u.x : (i == 1 ? u.y : (i == 2 ? u.z : u.w));
+}
+__device__ __forceinline__ float fast_exp(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
+// NJ: 8-key n-tiles per warp iteration (2 or 4).
+template <int HD, int NJ>
+__global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode_mma_kernel(DecMmaParams p) {
+  using T = __nv_bfloat16;
+  constexpr int TK = 8 * NJ;     // keys per warp iteration
+  constexpr int KK = HD / 16;    // k-steps of the score MMA
+  constexpr int NT = HD / 8;     // n-tiles of the output MMA
+  constexpr int QV = HD / 32;    // 16-byte pieces of a lane's quarter of a key (or query) row
+  constexpr int VV = HD / 64;    // 16-byte pieces of a lane's eighth of a value row
+  __shared__ float sm_acc[DM_WARPS][DM_GM][HD];
+  __shared__ float sm_ml[DM_WARPS][DM_GM][2];
+  __shared__ float cl_acc[DM_GM][HD];   // this block's merged result, read by the cluster's first block
+  __shared__ float cl_ml[DM_GM][2];
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) TSTAMP(0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y / p.n_gchunks, gc = blockIdx.y - kvh * p.n_gchunks;
+  const int split = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int g0 = gc * DM_GM;
+  const int GC = min(DM_GM, G - g0);
+  const int PS = p.page_size;
+  // the step's own inputs (in place before the step's first kernel starts)
+  const int slot = p.seq_slot[b];
+  const int pos = p.token_pos[b];
+  const int t_end = pos + 1;
+  const int t_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int pg_first = t_begin / PS, pg_last = pos / PS;
+  const int per = (pg_last - pg_first + 1 + p.n_splits - 1) / p.n_splits;
+  const int pg_b = pg_first + split * per;
+  const int pg_e = min(pg_last + 1, pg_b + per);
+  const int tiles_per_page = PS / TK;
+  const int n_tiles = max(0, pg_e - pg_b) * tiles_per_page;
+  // page ids now (later loads of them hit L1), and a hint that pulls this block's rows into L2
+  for (int tile = warp; tile < n_tiles; tile += DM_WARPS) {
+    const int pg = pg_b + tile / tiles_per_page;
+    const int key0 = (tile % tiles_per_page) * TK;
+    if (pg * PS + key0 >= t_end) continue;
+    const int page = p.page_table[(size_t)slot * p.max_pages + pg];
+    const size_t base = (((size_t)page * p.Hkv + kvh) * PS + key0) * HD;
+    constexpr int LINES = TK * HD * 2 / 128;
+    for (int ln = lane; ln < LINES; ln += 32) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)(p.kpages + base) + (size_t)ln * 128));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)(p.vpages + base) + (size_t)ln * 128));
+    }
+  }
+  if (threadIdx.x == 0) TSTAMP(1);
+  pdl_wait();
+  if (threadIdx.x == 0) TSTAMP(2);
+
+  // query fragments: head r of this block's chunk, this lane's quarter of the dimensions
+  uint32_t qa[KK][2];
+#pragma unroll
+  for (int kk = 0; kk < KK; ++kk) qa[kk][0] = qa[kk][1] = 0u;
+  if (r < GC) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0 + r) * HD + c * (HD / 4));
+#pragma unroll
+    for (int v = 0; v < QV; ++v) {
+      const uint4 u = src[v];
+      qa[2 * v][0] = u.x; qa[2 * v][1] = u.y;
+      qa[2 * v + 1][0] = u.z; qa[2 * v + 1][1] = u.w;
+    }
+  }
+  float o[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = 0.f;
+  float m = -INFINITY, l = 0.f;   // of head r (l: this lane's share, summed over the quad at the end)
+
+  for (int tile = warp; tile < n_tiles; tile += DM_WARPS) {
+    const int pg = pg_b + tile / tiles_per_page;
+    const int key0 = (tile % tiles_per_page) * TK;
+    if (pg * PS + key0 >= t_end) continue;                       // wholly beyond the sequence (warp-uniform)
+    const int page = p.page_table[(size_t)slot * p.max_pages + pg];
+    const size_t base = ((size_t)page * p.Hkv + kvh) * PS * HD;
+    const T* kp = p.kpages + base;
+    const T* vp = p.vpages + base;
+    const int t0 = pg * PS + key0;
+    // every load of the tile is requested before any arithmetic: one memory round trip
+    uint4 ku[NJ][QV];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int key = key0 + j * 8 + r;
+      const bool live = t0 + j * 8 + r < t_end && t0 + j * 8 + r >= t_begin;   // (dead rows may hold anything: skip them)
+#pragma unroll
+      for (int v = 0; v < QV; ++v)
+        ku[j][v] = live ? *reinterpret_cast<const uint4*>(kp + (size_t)key * HD + c * (HD / 4) + v * 8)
+                        : make_uint4(0u, 0u, 0u, 0u);
+    }
+    uint4 vu[NJ / 2][4][VV];
+#pragma unroll
+    for (int ks = 0; ks < NJ / 2; ++ks) {
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int kin = ks * 16 + 2 * c + (q4 & 1) + (q4 >> 1) * 8;   // keys 2c, 2c+1, 2c+8, 2c+9 of the k-step
+        const int t = t0 + kin;
+        const bool live = t < t_end && t >= t_begin;
+#pragma unroll
+        for (int v = 0; v < VV; ++v)
+          vu[ks][q4][v] = live ? *reinterpret_cast<const uint4*>(vp + (size_t)(key0 + kin) * HD + r * (HD / 8) + v * 8)
+                               : make_uint4(0u, 0u, 0u, 0u);        // zero: its probability is zero as well
+      }
+    }
+    // scores of head r against keys j * 8 + 2c, 2c + 1
+    float s[NJ][2];
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      s[j][0] = s[j][1] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KK; ++kk) {
+        const uint32_t b0 = word_of(ku[j][kk >> 1], (kk & 1) * 2);
+        const uint32_t b1 = word_of(ku[j][kk >> 1], (kk & 1) * 2 + 1);
+        mma_rows8(s[j][0], s[j][1], qa[kk][0], qa[kk][1], b0, b1);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = t0 + j * 8 + 2 * c + e;
+        s[j][e] = (t < t_end && t >= t_begin) ? s[j][e] * p.scale : -INFINITY;
+        tmax = fmaxf(tmax, s[j][e]);
+      }
+    }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const float m_new = fmaxf(m, tmax);
+    const float corr = (m == -INFINITY) ? 0.f : fast_exp(m - m_new);
+    m = m_new;
+    l *= corr;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { o[nt][0] *= corr; o[nt][1] *= corr; }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pr = (s[j][e] == -INFINITY) ? 0.f : fast_exp(s[j][e] - m_new);
+        s[j][e] = pr;
+        l += pr;
+      }
+    // output: probabilities (A) times values (B)
+#pragma unroll
+    for (int ks = 0; ks < NJ / 2; ++ks) {
+      const uint32_t a0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+      const uint32_t a2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+#pragma unroll
+      for (int w = 0; w < NT / 2; ++w) {          // 32-bit word w of the lane's piece holds n-tiles 2w and 2w + 1
+        const uint32_t wa = word_of(vu[ks][0][w >> 2], w & 3), wb = word_of(vu[ks][1][w >> 2], w & 3);
+        const uint32_t wc = word_of(vu[ks][2][w >> 2], w & 3), wd = word_of(vu[ks][3][w >> 2], w & 3);
+        mma_rows8(o[2 * w][0], o[2 * w][1], a0, a2, __byte_perm(wa, wb, 0x5410), __byte_perm(wc, wd, 0x5410));
+        mma_rows8(o[2 * w + 1][0], o[2 * w + 1][1], a0, a2, __byte_perm(wa, wb, 0x7632), __byte_perm(wc, wd, 0x7632));
+      }
+    }
+  }
+  if (threadIdx.x == 0) TSTAMP(3);
+
+  // the quad's lanes share the maximum, so their sums add up
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (r < GC) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      // MMA column nt * 8 + 2c + e is dimension (2c + e) * HD/8 + nt of the head
+      sm_acc[warp][r][(2 * c) * (HD / 8) + nt] = o[nt][0];
+      sm_acc[warp][r][(2 * c + 1) * (HD / 8) + nt] = o[nt][1];
+    }
+    if (c == 0) {
+      sm_ml[warp][r][0] = m;
+      sm_ml[warp][r][1] = l;
+    }
+  }
+  __syncthreads();
+  // merge the warps: thread -> (head g, dim d)
+  for (int idx = threadIdx.x; idx < GC * HD; idx += DM_THREADS) {
+    const int g = idx / HD, d = idx - g * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) mm = fmaxf(mm, sm_ml[w][g][0]);
+    float a = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float mw = sm_ml[w][g][0];
+      if (mw != -INFINITY) {
+        const float cw = expf(mw - mm);
+        a = fmaf(cw, sm_acc[w][g][d], a);
+        ll = fmaf(cw, sm_ml[w][g][1], ll);
+      }
+    }
+    if (p.n_splits == 1) {
+      p.out[(size_t)b * p.ldo + (size_t)(kvh * G + g0 + g) * HD + d] = __float2bfloat16_rn(a / ll);
+    } else {
+      cl_acc[g][d] = a;
+      if (d == 0) {
+        cl_ml[g][0] = mm;
+        cl_ml[g][1] = ll;
+      }
+    }
+  }
+  if (p.n_splits == 1) return;
+  // The slices of this (sequence, kv head, head chunk) are the blocks of one cluster: each leaves its
+  // merged (max, sum, output) in its own shared memory; every block then finishes an equal share of
+  // the outputs, reading all slices' values of them through distributed shared memory.
+  namespace cg = cooperative_groups;
+  cg::cluster_group cl = cg::this_cluster();
+  if (threadIdx.x == 0) TSTAMP(4);
+  cl.sync();
+  if (threadIdx.x == 0) TSTAMP(5);
+  const int NS = p.n_splits;
+  const int me = (int)cl.block_rank();
+  const int total = GC * HD;
+  const int share = (total + NS - 1) / NS;
+  for (int idx = me * share + threadIdx.x; idx < min(total, (me + 1) * share); idx += DM_THREADS) {
+    const int g = idx / HD, d = idx - g * HD;
+    float ms[8], ls[8], as[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k < NS) {
+        const float* rml = cl.map_shared_rank(&cl_ml[0][0], k);
+        const float* racc = cl.map_shared_rank(&cl_acc[0][0], k);
+        ms[k] = rml[g * 2];
+        ls[k] = rml[g * 2 + 1];
+        as[k] = racc[g * HD + d];
+      } else {
+        ms[k] = -INFINITY;
+        ls[k] = 0.f;
+        as[k] = 0.f;
+      }
+    }
+    float mm = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mm = fmaxf(mm, ms[k]);
+    float a = 0.f, ll = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float ck = (ms[k] == -INFINITY) ? 0.f : expf(ms[k] - mm);
+      a = fmaf(ck, as[k], a);
+      ll = fmaf(ck, ls[k], ll);
+    }
+    p.out[(size_t)b * p.ldo + (size_t)(kvh * G + g0 + g) * HD + d] = __float2bfloat16_rn(a / ll);
+  }
+  if (threadIdx.x == 0) TSTAMP(6);
+  cl.sync();   // nobody leaves while its shared memory may still be read
+  if (threadIdx.x == 0) TSTAMP(7);
+}
+
+template <int HD, int NJ>
+int launch_decode_mma(const DecMmaParams& p, int B, cudaStream_t stream) {
+  dim3 grid(B, p.Hkv * p.n_gchunks, p.n_splits);
+  if (p.n_splits > 1) {
+    launch_kernel_cluster(attention_decode_mma_kernel<HD, NJ>, grid, dim3(DM_THREADS), 0, stream,
+                          dim3(1, 1, p.n_splits), p);
+  } else {
+    launch_kernel(attention_decode_mma_kernel<HD, NJ>, grid, dim3(DM_THREADS), 0, stream, p);
+  }
+  return launch_status();
+}
+
+}  // namespace dlgo
+
+using namespace dlgo;
+
+// 1 if the kernel takes these sizes: bfloat16 (implied), heads of 64 or 128, pages that hold whole tiles,
+// 1..8 slices (more than one: a thread-block cluster).
+DLGO_EXPORT int dlgo_attention_decode_mma_takes(int hd, int page_size, int n_splits) {
+  return (hd == 64 || hd == 128) && page_size % 32 == 0 && n_splits >= 1 && n_splits <= 8;
+}
+
+// q[B, .] bf16 (row stride ldq, head h at column h * hd), one token per sequence at position
+// token_pos[b] whose key and value are already in the cache; out[B, .] bf16 (row stride ldo).
+// keys_per_tile: 16 or 32 keys per warp iteration.
+DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const void* kpages, const void* vpages,
+                                          const int* page_table, int max_pages, const int* seq_slot,
+                                          const int* token_pos, void* out, int ldo, int Hq, int Hkv, int hd,
+                                          int page_size, int n_splits, int window, float scale, int keys_per_tile,
+                                          cudaStream_t stream) {
+  if (B <= 0) return DLGO_OK;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return DLGO_ERR_SIZE;
+  if (!dlgo_attention_decode_mma_takes(hd, page_size, n_splits)) return DLGO_ERR_SIZE;
+  if (keys_per_tile != 16 && keys_per_tile != 32) return DLGO_ERR_SIZE;
+  if ((ldq & 7) || ((uintptr_t)q & 15) || ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15)) return DLGO_ERR_ALIGN;
+  const int G = Hq / Hkv;
+  DecMmaParams p;
+  p.q = (const __nv_bfloat16*)q; p.ldq = ldq;
+  p.kpages = (const __nv_bfloat16*)kpages; p.vpages = (const __nv_bfloat16*)vpages;
+  p.page_table = page_table; p.max_pages = max_pages; p.seq_slot = seq_slot; p.token_pos = token_pos;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo;
+  p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
+  p.n_gchunks = (G + DM_GM - 1) / DM_GM;
+  p.window = window; p.scale = scale;
+  if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;
+  if (hd == 64) return keys_per_tile == 16 ? launch_decode_mma<64, 2>(p, B, stream) : launch_decode_mma<64, 4>(p, B, stream);
+  return keys_per_tile == 16 ? launch_decode_mma<128, 2>(p, B, stream) : launch_decode_mma<128, 4>(p, B, stream);
+}
+
+DLGO_TIMES_EXPORT

@@ -364,6 +364,35 @@ def check_device_errors() -> None:
 
 
 # ------------------------------------------------------------ decode attention
+def attention_decode_mma_takes(dtype: torch.dtype, head_dim: int, page_size: int, n_splits: int) -> bool:
+    """Whether the tensor-core decode kernel takes these sizes (bfloat16, heads of 64 or 128, 1..8 slices)."""
+    return dtype == torch.bfloat16 and bool(
+        _lib("attention_decode_mma").dlgo_attention_decode_mma_takes(_i(head_dim), _i(page_size), _i(n_splits)))
+
+
+def attention_decode_mma(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
+                         page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor,
+                         out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                         window: int = 0, n_splits: int = 1, keys_per_tile: int = 16) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys and values, bfloat16, on the
+    tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster."""
+    for n, t in (("q", q), ("out", out), ("kpages", kpages), ("vpages", vpages)):
+        _need(t, torch.bfloat16, n)
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    if seq_slot.numel() < B or token_pos.numel() < B or q.shape[0] < B or out.shape[0] < B:
+        raise KernelError("attention_decode_mma: fewer rows than sequences")
+    if q.shape[1] < num_heads * head_dim or out.shape[1] < num_heads * head_dim:
+        raise KernelError("attention_decode_mma: q and out need a column per head dimension")
+    page_size = kpages.shape[-2]
+    st = _lib("attention_decode_mma").dlgo_attention_decode_mma(
+        _ptr(q), _i(B), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table), _i(page_table.shape[1]),
+        _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim),
+        _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile), _stream())
+    _check(st, "attention_decode_mma")
+    return out
+
+
 def attention_decode_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
     return bool(_lib("attention_decode").dlgo_attention_decode_takes(_i(dtype_code(dtype)), _i(head_dim), _i(page_size)))
 

@@ -30,6 +30,7 @@ _TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (genera
 _NO_FUSE = not os.environ.get("DLGO_ATTN_FUSE_ROPE")
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
 _AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 32)) << 20   # keys and values hinted into L2 per layer
+_MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp iteration of the tensor-core decode kernel (0: off)
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
 
@@ -126,7 +127,13 @@ class GQAAttention(Mixer):
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
                 counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
             # (2..8 slices form a thread-block cluster and combine through distributed shared memory)
-            if fused_rope:
+            if (not fused_rope and scratch is None and _MMA_KEYS and
+                    K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits)):
+                # bfloat16, common head sizes: the scores and the weighted sum on the tensor cores
+                K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table,
+                                       ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
+                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS)
+            elif fused_rope:
                 # rotation of q and k and the append of k and v happen inside the attention kernel
                 K.attention_decode_rope(qkv, qkv_parts, T, cos, sin, rot, inter, cache.writes, cache.keys,
                                         cache.values, cache.page_table, ctx.seq_slot, ctx.token_pos, out,

@@ -197,6 +197,14 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
                                torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd, 1.0 / math.sqrt(hd),
                                window)
         k.check_device_errors()
+    elif kernel.startswith("decode_mma"):
+        keys = int(kernel.rsplit("_", 1)[1])
+        assert all(n == 1 for _, n in seqs) and k.attention_decode_mma_takes(DT[dtype], hd, 64, n_splits)
+        for _ in range(2):
+            out.fill_(float("nan"))
+            k.attention_decode_mma(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
+                                   torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd,
+                                   1.0 / math.sqrt(hd), window, n_splits, keys)
     elif kernel == "decode":
         assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
         # three ways to combine slices: a cluster (no scratch, up to 8 slices), the last slice (scratch and
@@ -306,6 +314,60 @@ def test_attention_decode_kernel_sizes(dtype, hq, hkv, hd):
         out, ref = _attention_case(dtype, hq, hkv, hd, [(500, 1), (0, 1), (65, 1)], n_splits=n_splits, decode=True,
                                    kernel="decode")
         torch.testing.assert_close(out, ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("keys", [16, 32])
+@pytest.mark.parametrize("hq,hkv,hd", [(8, 2, 64), (3, 1, 128), (4, 4, 64), (32, 8, 64), (24, 2, 128), (9, 1, 64)])
+def test_attention_decode_on_the_tensor_cores(hq, hkv, hd, keys):
+    # lengths around page and tile edges, a first token, several slices (clusters), more heads per
+    # kv head than one block takes (12 and 9 > 8)
+    for n_splits in (1, 2, 5, 8):
+        out, ref = _attention_case("bfloat16", hq, hkv, hd, [(500, 1), (0, 1), (65, 1), (15, 1), (16, 1), (31, 1), (127, 1)],
+                                   n_splits=n_splits, decode=True, kernel=f"decode_mma_{keys}")
+        torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
+    assert not K().attention_decode_mma_takes(torch.bfloat16, 96, 64, 1)
+    assert not K().attention_decode_mma_takes(torch.float32, 64, 64, 1)
+    assert not K().attention_decode_mma_takes(torch.bfloat16, 64, 64, 9)
+
+
+@pytest.mark.parametrize("keys", [16, 32])
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 500, 638, 639])
+def test_attention_decode_mma_finds_one_far_key(far, keys):
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[far, :, 0] = 12.0
+            Vf[far] = 7.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    for n_splits in (1, 4):
+        out, ref = _attention_case("bfloat16", 8, 2, 64, [(639, 1)], special=special, n_splits=n_splits, decode=True,
+                                   kernel=f"decode_mma_{keys}")
+        torch.testing.assert_close(out, ref, atol=3e-2, rtol=2e-2)
+        assert float((out - 7.0).abs().max()) < 0.1
+
+
+@pytest.mark.parametrize("where", ["first_inside", "last_outside"])
+def test_attention_decode_mma_window_edge_and_dead_pages(where):
+    edge = 201 if where == "first_inside" else 200
+
+    def special(i, Kf, Vf, q=None, p=None):
+        if Kf is not None:
+            Kf.mul_(0.05)
+            Kf[edge, :, 0] = 12.0
+            Vf[edge] = 7.0
+        else:
+            q.mul_(0.05)
+            q[:, 0] = 12.0
+    for n_splits, dead in ((1, False), (3, True)):
+        out, ref = _attention_case("bfloat16", 4, 2, 64, [(300, 1)], window=100, n_splits=n_splits, decode=True,
+                                   special=special, dead_pages=dead, kernel="decode_mma_16")
+        torch.testing.assert_close(out, ref, atol=3e-2, rtol=2e-2)
+        if where == "first_inside":
+            assert float((out - 7.0).abs().max()) < 0.1
+        else:
+            assert float(out.abs().max()) < 6.0
 
 
 @pytest.mark.parametrize("hq,hkv,hd", [(8, 2, 64), (3, 1, 128), (4, 4, 64)])
