@@ -1014,14 +1014,17 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.cluster = cluster > 1 ? cluster : 1;
   p.l2_ahead = 0;
   if (p.static_operand) {
-    // at most DLGO_TC_L2_AHEAD_MB (default 80) of weights per launch are pulled into L2 ahead of time
+    // DLGO_TC_L2_AHEAD_MB: at most that many MB of weights per launch are pulled into L2 ahead of
+    // time.  Off by default: measured on a B200 it does not shorten a decode step (the CTAs of the
+    // next contraction enter an SM only a few microseconds before they may run, and an SM takes data
+    // out of L2 only about twice as fast as out of memory).
     static const long long budget = [] {
       const char* e = getenv("DLGO_TC_L2_AHEAD_MB");
-      return (e ? atoll(e) : 80LL) << 20;
+      return (e ? atoll(e) : 0LL) << 20;
     }();
     const long long box = (long long)(p.static_operand == 1 ? TILE_M : bn) * TILE_K * 2;
     const long long ctas = (long long)((Ra + TILE_M - 1) / TILE_M) * ((Rb + bn - 1) / bn) * splits;
-    const long long cap = budget / (box * ctas);
+    const long long cap = budget > 0 ? budget / (box * ctas) : 0;
     p.l2_ahead = (int)(cap > 1024 ? 1024 : cap);
   }
   if (!transposed && splits == 1 && pair_tile != 0) {

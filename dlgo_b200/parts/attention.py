@@ -29,7 +29,9 @@ _TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (genera
 # inside a whole step it is no faster than the separate rope kernel, so it is opt-in: DLGO_ATTN_FUSE_ROPE=1.
 _NO_FUSE = not os.environ.get("DLGO_ATTN_FUSE_ROPE")
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
-_AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 32)) << 20   # keys and values hinted into L2 per layer
+# keys and values that the rope kernel hints into L2 for the attention kernel, per layer (0: off, the
+# default: measured on a B200 the hint does not pay, the attention kernel's own hint is early enough)
+_AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 0)) << 20
 _MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp iteration of the tensor-core decode kernel (0: off)
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
