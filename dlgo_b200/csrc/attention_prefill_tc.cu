@@ -392,6 +392,11 @@ int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM);
     if (e != cudaSuccess) return (int)e;
+    // With heads of 64 two CTAs fit an SM (2 x 112 KB of shared memory, 2 x 256 columns of tensor
+    // memory): one's softmax then runs beside the other's MMAs.  That needs the largest carve-out.
+    if (getenv("DLGO_PF_NO_CARVEOUT") == nullptr)
+      cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           (int)cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   launch_kernel(attention_prefill_tc_kernel<HD>, dim3(n_tiles, p.Hq), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
