@@ -1,5 +1,6 @@
 """Each part of a layer alone, a model whose layers differ and whose run order repeats and borrows,
-and a toy mixer with state of its own that is registered from here.  Needs a GPU."""
+and toy parts that are registered from here without a change to the framework: a mixer with state of
+its own, a feed-forward with routing, a position encoding.  Needs a GPU."""
 import dataclasses
 import math
 
@@ -320,3 +321,131 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
         got = T.collect(steps, T.run_in_process(eng, steps), reqs)
         for r in reqs:
             assert float((got[r] - refs[r]).abs().max()) <= 5e-5 * max(1.0, float(refs[r].abs().max())), r
+
+
+# ---------------- a toy feed-forward with routing and a toy position encoding, both defined here
+def register_routed_and_positions():
+    from dlgo_b200.parts import (FeedForward, Mixer, ParamSpec, PositionEncoding, register_feed_forward,
+                                 register_mixer, register_position_encoding)
+
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert whose router logit is largest (fp32 logits, first maximum):
+        y = down_e(relu(up_e x))."""
+
+        def __init__(self, hidden_size, n_experts, expert_size):
+            super().__init__(hidden_size=hidden_size, n_experts=n_experts, expert_size=expert_size)
+            self.d, self.e, self.f = hidden_size, n_experts, expert_size
+
+        def param_specs(self):
+            out = {"router.weight": ParamSpec((self.e, self.d))}
+            for i in range(self.e):
+                out[f"experts.{i}.up.weight"] = ParamSpec((self.f, self.d))
+                out[f"experts.{i}.down.weight"] = ParamSpec((self.d, self.f))
+            return out
+
+        def load(self, get, runtime):
+            self.router = get("router.weight").float()
+            self.up = [get(f"experts.{i}.up.weight").float() for i in range(self.e)]
+            self.down = [get(f"experts.{i}.down.weight").float() for i in range(self.e)]
+
+        def forward(self, x, residual, ctx):
+            xf = x.float()
+            choice = (xf @ self.router.t()).argmax(dim=1)
+            for i in range(self.e):
+                rows = (choice == i).nonzero().flatten()
+                if rows.numel():
+                    residual[rows] += torch.relu(xf[rows] @ self.up[i].t()) @ self.down[i].t()
+
+    class SineTable(PositionEncoding):
+        """table[p, i] = sin(p / period ** (i / dim)): whoever names it scales its input by 1 + table[p]."""
+
+        def __init__(self, dim, period, max_positions):
+            super().__init__(dim=dim, period=period, max_positions=max_positions)
+            self.dim, self.period, self.max_positions = dim, period, max_positions
+            self.table = None
+
+        def prepare(self, runtime):
+            p = torch.arange(self.max_positions, dtype=torch.float64)[:, None]
+            i = torch.arange(self.dim, dtype=torch.float64)[None, :]
+            self.table = torch.sin(p / self.period ** (i / self.dim)).float().to(runtime.device)
+
+    class PositionGate(Mixer):
+        """y_t = W . (x_t * (1 + table[pos_t])): no cache, no state, only the position of each token."""
+
+        def __init__(self, hidden_size, position_encoding):
+            super().__init__(hidden_size=hidden_size, position_encoding=position_encoding)
+            self.d, self.pe = hidden_size, position_encoding
+
+        def param_specs(self):
+            return {"gate.weight": ParamSpec((self.d, self.d))}
+
+        def load(self, get, runtime):
+            self.w = get("gate.weight").float()
+
+        def forward(self, x, residual, ctx, cache, state, positions):
+            assert cache is None and state is None
+            t = positions[self.pe].table[ctx.token_pos.long()]
+            residual += (x.float() * (1.0 + t)) @ self.w.t()
+
+    register_feed_forward("toy_top1_experts", Top1Experts, replace=True)
+    register_position_encoding("toy_sine_table", SineTable, replace=True)
+    register_mixer("toy_position_gate", PositionGate, replace=True)
+
+
+def routed_spec():
+    from dlgo_b200.config.spec import PartSpec, RunEntry
+    spec = mixed_spec()
+    l0 = dataclasses.replace(spec.layers[0],
+                             mixer=PartSpec("toy_position_gate", dict(hidden_size=48, position_encoding="sine")),
+                             ffn=PartSpec("toy_top1_experts", dict(hidden_size=48, n_experts=3, expert_size=20)))
+    pes = dict(spec.position_encodings)
+    pes["sine"] = PartSpec("toy_sine_table", dict(dim=48, period=50.0, max_positions=192))
+    return dataclasses.replace(spec, name="RoutedTest", layers=[l0, spec.layers[1]], order=[RunEntry(0), RunEntry(1)],
+                               position_encodings=pes)
+
+
+def plain_routed(tensors, tokens):
+    w = {k: v.float() for k, v in tensors.items()}
+    x = P.embedding(w["emb.weight"], tokens)
+    n = x.shape[0]
+    xn = P.rmsnorm(x, w["layers.0.n1.weight"], 1e-5)
+    pos = torch.arange(n, dtype=torch.float64)[:, None]
+    table = torch.sin(pos / 50.0 ** (torch.arange(48, dtype=torch.float64)[None, :] / 48)).float()
+    r = x + (xn * (1.0 + table)) @ w["layers.0.attn.gate.weight"].t()
+    xn = P.rmsnorm(r, w["layers.0.n2.weight"], 1e-5)
+    y = torch.zeros_like(r)
+    used = set()
+    for t in range(n):
+        e = P.argmax(w["layers.0.ff.router.weight"] @ xn[t])
+        used.add(e)
+        y[t] = w[f"layers.0.ff.experts.{e}.down.weight"] @ torch.relu(w[f"layers.0.ff.experts.{e}.up.weight"] @ xn[t])
+    x = r + y
+    sub = {k[len("layers.1.attn."):]: v for k, v in w.items() if k.startswith("layers.1.attn.")}
+    a, _ = plain_mixer(P.rmsnorm(x, w["layers.1.n1.weight"], 1e-3), sub, 4, 1, 32, P.rope_frequencies(16, 1e3, None))
+    r = x + a
+    y = P.feed_forward(P.rmsnorm(r, w["layers.1.n2.weight"], 1e-6), w["layers.1.ff.gate_proj.weight"],
+                       w["layers.1.ff.up_proj.weight"], w["layers.1.ff.down_proj.weight"])
+    return P.linear(P.rmsnorm(r + y, w["final.weight"], 1e-5), w["head.weight"]), used
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_need_no_change_to_the_framework():
+    import traces as T
+    from dlgo_b200.engine.engine import Engine
+    register_routed_and_positions()
+    spec = routed_spec()
+    tensors = random_tensors(spec, 8)
+    assert "layers.0.ff.experts.2.down.weight" in tensors and "layers.0.ff.gate_proj.weight" not in tensors
+    eng = Engine(spec=spec, tensors=tensors, dtype="float32", max_tokens=384, cuda_graphs=False)
+    assert sorted(eng.cache.storage) == ["full"] and not eng.cache.state.tensors
+    g = torch.Generator().manual_seed(9)
+    reqs = {f"r{i}": torch.randint(0, 100, (n,), generator=g).tolist() for i, n in enumerate([50, 4, 90])}
+    refs, used = {}, set()
+    for r_, t in reqs.items():
+        refs[r_], u = plain_routed(tensors, t)
+        used |= u
+    assert len(used) == 3, "the inputs should reach every expert"
+    # positions matter in every cutting: whole, the tail token by token, and batches of unequal lengths
+    for steps in (T.whole(reqs), T.tail_one_by_one(reqs, 16), T.batched(reqs, 2, (8, 2, 30))):
+        got = T.collect(steps, T.run_in_process(eng, steps), reqs)
+        for r_ in reqs:
+            assert float((got[r_] - refs[r_]).abs().max()) <= 5e-5 * max(1.0, float(refs[r_].abs().max())), r_
