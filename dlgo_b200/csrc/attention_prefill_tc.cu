@@ -6,11 +6,16 @@
 // consecutive tokens of one sequence and one query head, and walks the sequence's pages 128 keys
 // (two pages) at a time:
 //   warp 0     TMA: the query tile once, then key and value pages into a two-stage ring
-//   warp 1     tcgen05.mma: S = Q K^T (128 x 128, fp32 in tensor memory), then O_blk = P V
-//   warps 2-5  one thread per query row: reads S from tensor memory, masks, keeps the running
-//              maximum and sum (fp32, exp2 on pre-scaled scores), writes P as bf16 into shared
-//              memory in the swizzled layout the tensor core reads, then adds O_blk into its
-//              row's fp32 accumulator in registers with the softmax correction
+//   warp 1     tcgen05.mma: S = Q K^T (128 x 128, fp32 in tensor memory), then O += P V, the output
+//              accumulating in tensor memory over all key blocks
+//   warps 2-5  one thread per query row: reads its 128 scores from tensor memory once, masks,
+//              keeps a reference maximum and the sum (fp32, exp2 on pre-scaled scores) and writes
+//              P as bf16 into shared memory in the swizzled layout the tensor core reads.  The
+//              reference maximum follows the true one lazily: only when a block's maximum exceeds
+//              it by more than 2^8 is the row's output in tensor memory rescaled (read, multiplied,
+//              written back); otherwise probabilities are simply up to 256 times larger than with
+//              the true maximum, which fp32 sums and bf16 probabilities carry without loss, and
+//              the final division by the sum (taken against the same reference) cancels it
 // Values are read as the MN-major operand straight from the page layout [key][head_dim].
 // Keys that were never written (the tail of the last page, pages a window has given back) get
 // probability zero; their value rows are zeroed in shared memory so that 0 * garbage cannot
@@ -61,7 +66,7 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PF_THREADS, 1)
+__global__ void __launch_bounds__(PF_THREADS, HD <= 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PfParams p) {
   constexpr int NCH = HD / 64;                 // 64-wide chunks of the head
@@ -87,10 +92,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* vfull = bars + 3;      // 2
   uint64_t* kvempty = bars + 5;    // 2
   uint64_t* s_full = bars + 7;
-  uint64_t* s_free = bars + 8;
-  uint64_t* p_full = bars + 9;
-  uint64_t* o_full = bars + 10;
-  uint64_t* o_free = bars + 11;
+  uint64_t* p_full = bars + 9;     // P of a block is written, its scores are read, O is rescaled if need be
+  uint64_t* o_full = bars + 10;    // the last block's P V has completed
   uint32_t* tmem_slot = (uint32_t*)(bars + 12);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -108,10 +111,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&kvempty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_free, 4);
     mbar_init(p_full, 4);
     mbar_init(o_full, 1);
-    mbar_init(o_free, 4);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -186,19 +187,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int it = 0; ok && it < nblk; ++it) {
         const int st = it & 1;
         ok = mbar_wait(p_full, it & 1, abort_flag) && mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
-        if (ok && it > 0) ok = mbar_wait(o_free, (it - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(v_s + st * KVBYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr + (kk >> 2) * 16384) + 2 * (kk & 3),
-                    umma_desc_mn_sw128(v_addr + kk * 2048, 16384), idesc_o, kk != 0);
-        umma_commit(o_full);
+                    umma_desc_mn_sw128(v_addr + kk * 2048, 16384), idesc_o, (it | kk) != 0);
         umma_commit(&kvempty[st]);
         if (it + 1 < nblk) {
+          // the scores of block it have been read (p_full says so): the next block's may overwrite them
           const int st2 = (it + 1) & 1;
-          ok = mbar_wait(&kfull[st2], ((it + 1) >> 1) & 1, abort_flag) && mbar_wait(s_free, it & 1, abort_flag);
+          ok = mbar_wait(&kfull[st2], ((it + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t k_addr = smem_u32(k_s + st2 * KVBYTES);
@@ -208,7 +208,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int k = 0; k < 4; ++k)
               umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
                         umma_desc_k_sw128(k_addr + j * 16384) + 2 * k, idesc_s, (j | k) != 0);
+          // completes after everything issued before it, P V of block it included: whoever sees the
+          // next scores may also overwrite P and touch O
           umma_commit(s_full);
+        } else {
+          umma_commit(o_full);
         }
       }
     }
@@ -217,10 +221,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int r = quarter * 32 + lane;            // query row of the tile and key row of a stage
     const int pos_r = pos0 + r;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    float acc[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) acc[d] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;                 // reference maximum (lazy) and sum against it
     bool ok = true;
     for (int it = 0; ok && it < nblk; ++it) {
       const int st = it & 1;
@@ -237,99 +238,98 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row + j * 16384 + c * 16) = make_uint4(0, 0, 0, 0);
         }
       }
+      // the scores of this block; their barrier also tells that every earlier MMA has completed
+      // (P V of the block before included), so P may be overwritten and O touched
       if (ok) ok = mbar_wait(s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      float v[PF_KEYS];
+#pragma unroll
+      for (int c0 = 0; c0 < PF_KEYS; c0 += 32) tmem_ld_32x32(lane_addr + c0, v + c0);
+      tmem_ld_wait();
       const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
       // blocks that lie wholly inside every row's range need no mask (all but the diagonal ones)
       const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && (p.window <= 0 || k0 > pos0 + ntok - 1 - p.window);
-      // pass 1: the row's maximum over this block
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < PF_KEYS; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(lane_addr + c0, v);
-        tmem_ld_wait();
-        if (full_block) {
+      if (full_block) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
-        } else {
+        for (int j = 0; j < PF_KEYS; ++j) mx = fmaxf(mx, v[j]);
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int t = k0 + c0 + j;
-            if (t <= pos_r && t > lo) mx = fmaxf(mx, v[j]);
-          }
+        for (int j = 0; j < PF_KEYS; ++j) {
+          const int t = k0 + j;
+          if (!(t <= pos_r && t > lo)) v[j] = -INFINITY;
+          mx = fmaxf(mx, v[j]);
         }
       }
       mx *= p.scale_log2e;                                       // the scale is positive: max commutes with it
-      const float m_new = fmaxf(m, mx);
-      const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
-      const float mref = (m_new == -INFINITY) ? 0.f : m_new;
-      m = m_new;
-      // pass 2: probabilities, their sum, and P as bf16 in the swizzled K-major layout
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < PF_KEYS; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(lane_addr + c0, v);
-        tmem_ld_wait();
-        if (full_block) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = fast_exp2(fmaf(v[j], p.scale_log2e, -mref));
-            sum += v[j];
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int t = k0 + c0 + j;
-            v[j] = (t <= pos_r && t > lo) ? fast_exp2(fmaf(v[j], p.scale_log2e, -mref)) : 0.f;
-            sum += v[j];
-          }
+      // Lazy reference: move it (and rescale the row's output) only when this block's maximum exceeds
+      // it by more than 8 (a factor of 256); tensor-memory accesses are warp-wide, so the warp goes
+      // through the rescaling together and rows that need none multiply by one.
+      const bool move = mx > m + 8.0f || (m == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, move)) {
+        const float corr = move ? ((m == -INFINITY) ? 0.f : fast_exp2(m - mx)) : 1.0f;
+        if (move) {
+          m = mx;
+          l *= corr;
         }
+        if (it > 0) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int ch = (c0 >> 3) + q4;                          // 8-key chunk index 0..15
-          __nv_bfloat162 h[4];
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float o[32];
+            tmem_ld_32x32(lane_addr + O_COL + c0, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
-          uint8_t* dst = p_s + (ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+            for (int j = 0; j < 32; ++j) o[j] *= corr;
+            tmem_st_32x32(lane_addr + O_COL + c0, o);
+          }
+          tmem_st_wait();
         }
       }
-      l = l * corr + sum;
+      const float mref = (m == -INFINITY) ? 0.f : m;
+      // probabilities, their sum, and P as bf16 in the swizzled K-major layout
+      float sum = 0.f;
+#pragma unroll
+      for (int c0 = 0; c0 < PF_KEYS; c0 += 8) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // (masked scores are -inf: exp2 gives zero)
+          const float p0 = fast_exp2(fmaf(v[c0 + 2 * e], p.scale_log2e, -mref));
+          const float p1 = fast_exp2(fmaf(v[c0 + 2 * e + 1], p.scale_log2e, -mref));
+          sum += p0 + p1;
+          h[e] = __floats2bfloat162_rn(p0, p1);
+        }
+        const int ch = c0 >> 3;                                   // 8-key chunk index 0..15
+        uint8_t* dst = p_s + (ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+      }
+      l += sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor core
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {          // one arrival per warp stands for its 32 rows
-        mbar_arrive(p_full);
-        mbar_arrive(s_free);
-      }
-      // O_blk -> registers with the correction of this block
-      ok = mbar_wait(o_full, it & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(lane_addr + O_COL + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf(acc[c0 + j], corr, v[j]);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_free);
+      if (lane == 0) mbar_arrive(p_full);   // one arrival per warp stands for its 32 rows
     }
-    if (ok && r < ntok) {
+    // the finished output: out of tensor memory once, divided by the sum
+    if (ok) ok = mbar_wait(o_full, 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
       const float inv = 1.0f / l;
       __nv_bfloat16* o = p.out + (size_t)(tok0 + r) * p.ldo + (size_t)head * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        __nv_bfloat162 h[4];
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float acc[32];
+        tmem_ld_32x32(lane_addr + O_COL + c0, acc);
+        tmem_ld_wait();
+        if (r < ntok) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[c * 8 + 2 * e] * inv, acc[c * 8 + 2 * e + 1] * inv);
-        *reinterpret_cast<uint4*>(o + c * 8) = *reinterpret_cast<uint4*>(h);
+          for (int c = 0; c < 4; ++c) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[c * 8 + 2 * e] * inv, acc[c * 8 + 2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(o + c0 + c * 8) = *reinterpret_cast<uint4*>(h);
+          }
+        }
       }
     }
   }
