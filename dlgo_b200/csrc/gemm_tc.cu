@@ -70,6 +70,17 @@ template <int BN> struct TcConfig {
   }
 };
 
+// silu(g) * u = g * u / (1 + exp(-g)) (models/llm/forward.go:298-303) for a result that is rounded to
+// bfloat16: exp and the reciprocal as one approximate instruction each (relative error ~1e-6, far
+// below the rounding).  The exact expf and division cost some thirty dependent instructions per value,
+// which an epilogue with one warp per scheduler cannot hide.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-g * 1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return g * u * r;
+}
+
 // One row's 32 consecutive columns (or 16 when NV == 16) -> memory, per epilogue.
 template <int NV>
 __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v, int row, int col0, int lane) {
@@ -83,7 +94,7 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
         for (int j = 0; j < 16; ++j) {
           if (col0 + 16 + j < p.Rb) {
             const float g = v[j], u = v[16 + j];
-            o[j] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+            o[j] = __float2bfloat16_rn(silu_mul(g, u));
           }
         }
       }
@@ -96,7 +107,7 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
         if (lane < 16 && row + 16 < p.Ra && col < p.Rb) {
           const float g = v[j];
           const int feature = (row >> 5) * 16 + (row & 15);
-          ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
+          ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(silu_mul(g, other));
         }
       }
     }
@@ -160,7 +171,7 @@ __device__ __forceinline__ void epilogue_store_one(const TcParams& p, float v, i
     const float other = __shfl_xor_sync(0xffffffffu, v, 16);
     if (lane < 16 && row + 16 < p.Ra) {
       const int feature = (row >> 5) * 16 + (row & 15);
-      ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * other);
+      ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(silu_mul(v, other));
     }
     return;
   }
@@ -500,7 +511,7 @@ __device__ __forceinline__ void staged_epilogue(const TcParams& p, const CUtenso
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           const float g0 = v[2 * q], g1 = v[2 * q + 1], u0 = v[16 + 2 * q], u1 = v[16 + 2 * q + 1];
-          b2[q] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+          b2[q] = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
         }
         *reinterpret_cast<uint4*>(row + (((2 * h) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(&b2[0]);
         *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(&b2[4]);
