@@ -358,6 +358,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
+    } else if (p.splits == 1 && p.epilogue == TC_SWIGLU && p.transposed && BN >= 32 && (p.ldo & 1) == 0) {
+      // Many tokens per tile: the 64 outputs of a token (silu(gate) * up of this tile's 128 weight
+      // rows) are gathered in shared memory (the ring is idle by now) and leave as one 128-byte row
+      // per token, instead of 32 bytes per warp and token.
+      __nv_bfloat16* stage = (__nv_bfloat16*)smem;                 // [BN tokens][64 outputs]
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += NV) {
+          float v[NV];
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            if (lane < 16) stage[(c0 + j) * 64 + quarter * 16 + lane] = __float2bfloat16_rn(silu_mul(v[j], other));
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok) {
+        const int feat0 = tile_a * 64 + 2 * lane;                  // this lane's two outputs of a token
+        const int n_feat = p.Ra / 2;
+        for (int c = quarter; c < BN; c += 4) {
+          const int col = tile_b * BN + c;
+          if (col >= p.Rb) break;
+          __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)col * p.ldo + feat0;
+          if (feat0 + 1 < n_feat) *reinterpret_cast<uint32_t*>(o) = *reinterpret_cast<const uint32_t*>(&stage[c * 64 + 2 * lane]);
+          else if (feat0 < n_feat) o[0] = stage[c * 64 + 2 * lane];
+        }
+      }
     } else if (p.splits == 1) {
       if (ok) {
 #pragma unroll 1

@@ -181,7 +181,7 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
 // The same when the projection left its K-slices unsummed (decode steps): one warp per (token, head),
 // so that a step's few tokens still spread over many SMs.  Everything that does not depend on the
 // projection (position, page, cos / sin) is fetched before the kernel waits for it; after the wait
-// a lane has all slices' loads of a pair in flight at once (sixteen slices per round trip).
+// a lane has eight slices' loads of a pair in flight at once.
 constexpr int RP_WARPS = 4;
 template <typename T>
 __global__ void __launch_bounds__(RP_WARPS * 32)
@@ -254,15 +254,15 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
       i1 = i0 + 1;
     }
     float x0 = 0.f, x1 = 0.f;
-    for (int sb = 0; sb < S; sb += 16) {
-      float a[16], b[16];
+    for (int sb = 0; sb < S; sb += 8) {
+      float a[8], b[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 8; ++j) {
         a[j] = (sb + j < S) ? __ldcg(pp + (size_t)(sb + j) * part_stride + i0) : 0.f;
         b[j] = (sb + j < S) ? __ldcg(pp + (size_t)(sb + j) * part_stride + i1) : 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < 8; ++j) {
         if (sb + j < S) { x0 += a[j]; x1 += b[j]; }
       }
     }
