@@ -119,7 +119,7 @@ class GQAAttention(Mixer):
         if decode_kernel:
             # one token per sequence: the latency-shaped kernel, sliced so that every SM has several blocks
             base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
-            n_splits = max(1, min(pages, -(-_DECODE_BLOCKS // base_blocks)))
+            n_splits = max(1, min(pages, _DECODE_BLOCKS // base_blocks))   # whole waves: rounded down
             scratch = counters = None
             if n_splits > _CLUSTER_MAX and pages <= 64 and _CLUSTER_MAX > 1:
                 n_splits = _CLUSTER_MAX
