@@ -86,6 +86,7 @@ class KVCache:
             clash = [k for k in keyed if k[0] == base]
             names[key] = base if len(clash) == 1 else f"{base}/{key[1]}x{key[2]}w{key[3]}"
         self.book = CacheBook([(names[k], k[3]) for k in keyed], n_pages, page_size, self.n_slots, self.max_seq_len)
+        self._no_window = all(k[3] is None for k in keyed)
         self.storage: Dict[str, torch.Tensor] = {}
         self.page_tables: Dict[str, torch.Tensor] = {}
         self._entry_place: Dict[int, Tuple[str, int]] = {}
@@ -136,6 +137,15 @@ class KVCache:
 
     def reserve(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         """Room for each slot's new positions; mirrors changed table entries to the device."""
+        if self._no_window and all(n == 1 for n in n_new):
+            # decode steps mostly land inside the sequence's last page: nothing to take, give or mirror
+            ps = self.page_size
+            lengths = self.book._len
+            try:
+                if all(lengths[s] % ps and lengths[s] < self.max_seq_len for s in slots):
+                    return
+            except KeyError:
+                pass                        # a slot that is not held: the full path reports it
         rows: Dict[str, List[Tuple[int, int, int]]] = {}
         for slot, n in zip(slots, n_new):
             for g, ch in self.book.reserve(slot, n).items():

@@ -13,6 +13,7 @@ from typing import Any, List, Sequence
 
 import torch
 
+from ..csrc import kernels
 from .runtime import StepContext
 
 
@@ -36,6 +37,9 @@ class DecodeGraph:
         self.logits = None
         self.engine = engine
         self._copied = torch.cuda.Event()
+        self._stream = None          # the stream object of the last replay (looked up again only when it changes)
+        self._stream_raw = None
+        self._dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
 
     def capture(self) -> None:
         eng = self.engine
@@ -46,7 +50,6 @@ class DecodeGraph:
             eng.model.forward(self.ctx, eng.cache, self.want_rows)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
-        from ..csrc import kernels
         before = kernels.LAUNCHES
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
@@ -59,9 +62,11 @@ class DecodeGraph:
         h[1, :] = starts
         h[2, :] = slots
         self.meta.copy_(self.host, non_blocking=True)
-        self._copied.record()
+        raw = torch._C._cuda_getCurrentRawStream(self._dev_index)
+        if raw != self._stream_raw:
+            self._stream, self._stream_raw = torch.cuda.current_stream(self._dev_index), raw
+        self._copied.record(self._stream)
         self.graph.replay()
-        from ..csrc import kernels
         kernels.LAUNCHES += self.kernels_per_replay
         return self.logits
 
