@@ -250,18 +250,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
       // blocks that lie wholly inside every row's range need no mask (all but the diagonal ones)
       const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && (p.window <= 0 || k0 > pos0 + ntok - 1 - p.window);
-      float mx = -INFINITY;
-      if (full_block) {
-#pragma unroll
-        for (int j = 0; j < PF_KEYS; ++j) mx = fmaxf(mx, v[j]);
-      } else {
+      if (!full_block) {
 #pragma unroll
         for (int j = 0; j < PF_KEYS; ++j) {
           const int t = k0 + j;
           if (!(t <= pos_r && t > lo)) v[j] = -INFINITY;
-          mx = fmaxf(mx, v[j]);
         }
       }
+      // (four independent chains: one chain of 128 dependent maxima would cost its latency 128 times)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < PF_KEYS; j += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], v[j + e]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= p.scale_log2e;                                       // the scale is positive: max commutes with it
       // Lazy reference: move it (and rescale the row's output) only when this block's maximum exceeds
       // it by more than 8 (a factor of 256); tensor-memory accesses are warp-wide, so the warp goes
@@ -288,7 +291,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const float mref = (m == -INFINITY) ? 0.f : m;
       // probabilities, their sum, and P as bf16 in the swizzled K-major layout
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c0 = 0; c0 < PF_KEYS; c0 += 8) {
         __nv_bfloat162 h[4];
@@ -297,14 +300,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           // (masked scores are -inf: exp2 gives zero)
           const float p0 = fast_exp2(fmaf(v[c0 + 2 * e], p.scale_log2e, -mref));
           const float p1 = fast_exp2(fmaf(v[c0 + 2 * e + 1], p.scale_log2e, -mref));
-          sum += p0 + p1;
+          sum4[e] += p0 + p1;
           h[e] = __floats2bfloat162_rn(p0, p1);
         }
         const int ch = c0 >> 3;                                   // 8-key chunk index 0..15
         uint8_t* dst = p_s + (ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor core
       tc_fence_before_sync();
       __syncwarp();
