@@ -2,7 +2,9 @@
 vocabulary 128256, llama3 rope scaling factor 32, tied head) with FOUR layers instead of sixteen so
 that the plain implementation stays within a minute on the CPU.  These sizes take the kernels the
 tiny models never reach: the tensor-core prompt attention (head size 64), 128 x 256 GEMM tiles over
-many tiles, K-slices, a vocabulary that is no multiple of any tile.  Needs a GPU."""
+many tiles, K-slices, a vocabulary that is no multiple of any tile.  The same at the layer sizes of
+Llama 3.2 3B and Llama 3.1 8B (heads of 128, three and four query heads per kv head, an untied head).
+Needs a GPU."""
 import pytest
 import torch
 
@@ -23,6 +25,13 @@ CFG_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_l
               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                 original_max_position_embeddings=8192),
               rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=False)
+# Llama 3.2 3B layer sizes (hidden 3072, 24/8 heads of 128: three query heads per kv head, feed-forward 8192, tied),
+# two layers and a 32000 vocabulary
+CFG_3B = dict(architectures=["LlamaForCausalLM"], hidden_size=3072, num_hidden_layers=2, intermediate_size=8192,
+              num_attention_heads=24, num_key_value_heads=8, head_dim=128, vocab_size=32000, rope_theta=500000.0,
+              rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                original_max_position_embeddings=8192),
+              rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
 ROWS = [0, 1, 63, 64, 127, 128, 141] + list(range(142, 150))       # places compared (the last 8 are decoded)
 
 
@@ -57,6 +66,11 @@ def big(tmp_path_factory):
 @pytest.fixture(scope="module")
 def big8(tmp_path_factory):
     return build(tmp_path_factory, CFG_8B, 5)
+
+
+@pytest.fixture(scope="module")
+def big3(tmp_path_factory):
+    return build(tmp_path_factory, CFG_3B, 4)
 
 
 def run(engine, reqs, refs, dtype, what):
@@ -111,3 +125,12 @@ def test_llama_8b_layer_sizes_against_the_plain_implementation(big8, dtype):
     eng = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256)
     eng.cache.poison()
     run(eng, reqs, refs, dtype, "8B sizes")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_3b_layer_sizes_against_the_plain_implementation(big3, dtype):
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = big3
+    eng = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256)
+    eng.cache.poison()
+    run(eng, reqs, refs, dtype, "3B sizes")
