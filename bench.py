@@ -2,6 +2,7 @@
 shape, bfloat16, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 1b|3b|8b] [--layers N] [--batch B] [--only decode|prefill] [--no-graphs]
 
 A "step" is one decode step of the whole batch.  Prints ONE JSON line.  The weights a step reads
 (2.47 GB) are far larger than the L2 cache, which is stated in `config` as the timing hygiene rule asks.
@@ -29,6 +30,16 @@ MODEL = dict(
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
+# further shapes for extra measurements (`--shape`); the contract's line is measured at the default
+SHAPES = {
+    "1b": {},
+    "3b": dict(hidden_size=3072, num_hidden_layers=28, intermediate_size=8192, num_attention_heads=24,
+               num_key_value_heads=8, head_dim=128),
+    "8b": dict(hidden_size=4096, num_hidden_layers=32, intermediate_size=14336, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, tie_word_embeddings=False,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192)),
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
@@ -57,7 +68,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", "0", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", "0", "-lms", "25"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -96,7 +107,7 @@ def make_model_dir(tmp):
     cfg = config_from_dict(MODEL)
     t0 = time.time()
     write_random_model(cfg, 2, tmp, device="cuda" if torch.cuda.is_available() else "cpu")
-    print(f"[bench] wrote random 1B model in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    print(f"[bench] wrote the random model in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return tmp
 
 
@@ -191,7 +202,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the contract's Llama 3.2 1B)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one small workload (for profiling) and stop")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
@@ -207,7 +219,11 @@ def main() -> int:
     import dlgo_b200
     warmup = max(a.warmup, 3)
     pk = peaks()
-    MODEL["num_hidden_layers"] = a.layers
+    MODEL.update(SHAPES[a.shape])
+    layers_of_config = MODEL["num_hidden_layers"]
+    if a.layers > 0:
+        MODEL["num_hidden_layers"] = a.layers
+    a.layers = MODEL["num_hidden_layers"]
     tmp = tempfile.mkdtemp(prefix="dlgo_b200_bench_")
     try:
         make_model_dir(tmp)
@@ -236,14 +252,18 @@ def main() -> int:
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(PREFILL_TOKENS)
     out = {
-        "metric": "decode tok/s @ batch 8 (Llama-3.2-1B shape, bf16); points: batch 1/64; prefill tok/s @ 2,048",
+        "metric": "decode tok/s @ batch %d (%s shape, bf16); points: batch 1/64; prefill tok/s @ 2,048" % (
+            a.batch, {"1b": "Llama-3.2-1B", "3b": "Llama-3.2-3B", "8b": "Llama-3.1-8B"}[a.shape]),
         "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights seed 2)",
         "impl": "ours",
         "config": {
-            "model": "llama-3.2-1b-shape", "layers": a.layers, "layers_of_config": 16, "hidden": 2048, "heads": 32,
-            "kv_heads": 8, "head_dim": 64, "ffn": 8192, "vocab": 128256, "tied": True, "global_batch": a.batch,
+            "model": {"1b": "llama-3.2-1b-shape", "3b": "llama-3.2-3b-shape", "8b": "llama-3.1-8b-shape"}[a.shape],
+            "layers": a.layers, "layers_of_config": layers_of_config, "hidden": MODEL["hidden_size"],
+            "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"],
+            "head_dim": MODEL["head_dim"], "ffn": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"],
+            "tied": MODEL["tie_word_embeddings"], "global_batch": a.batch,
             "seq_len": CONTEXT, "prompt_len": "uniform[128,1024] seed 3", "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (weights read per step: %.2f GB)" % (weight_bytes / 1e9),
             "cuda_graph": True, "peaks": pk["source"]},
