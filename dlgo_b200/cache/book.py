@@ -15,6 +15,7 @@ every position in it is behind the window of all queries still to come.
 """
 from __future__ import annotations
 
+import heapq
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -24,13 +25,17 @@ class CacheError(RuntimeError):
 
 
 class PagePool:
-    """Free list of page numbers ``0 .. n_pages-1``."""
+    """Free page numbers ``0 .. n_pages-1``; the lowest free page is handed out first.
+
+    A prompt's pages are taken in one go, so lowest-first keeps a sequence's pages next to one another
+    in memory however the pool was used before.
+    """
 
     def __init__(self, n_pages: int):
         if n_pages <= 0:
             raise CacheError(f"a page pool needs at least one page, got {n_pages}")
         self.n_pages = n_pages
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))
+        self._free: List[int] = list(range(n_pages))      # a heap: sorted lists are heaps
         self._held = [False] * n_pages
 
     @property
@@ -40,7 +45,7 @@ class PagePool:
     def take(self) -> int:
         if not self._free:
             raise CacheError("cache is full: no free page")
-        p = self._free.pop()
+        p = heapq.heappop(self._free)
         self._held[p] = True
         return p
 
@@ -48,7 +53,7 @@ class PagePool:
         if not 0 <= page < self.n_pages or not self._held[page]:
             raise CacheError(f"page {page} given back but not held")
         self._held[page] = False
-        self._free.append(page)
+        heapq.heappush(self._free, page)
 
 
 @dataclass
