@@ -133,7 +133,10 @@ def decode_run(llm, batch, steps, warmup, sample_clocks=False):
     sampler = ClockSampler() if sample_clocks else None
     if sampler:
         sampler.start()
-        time.sleep(0.3)
+    # the prompts of a large batch are a tensor-core burst of ~100 ms that leaves the GPU at its power
+    # cap; decode steps timed right behind it came out up to 15 % slower than the same steps a moment later
+    torch.cuda.synchronize()
+    time.sleep(0.3)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     launches0 = kernels.LAUNCHES
