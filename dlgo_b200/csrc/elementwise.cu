@@ -99,6 +99,41 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 }
 
 // ------------------------------------------- residual += sum of partials, then RMSNorm
+// Many rows (prompts): one WARP per row, the row in registers (KV float4 per lane), no block-wide
+// barrier; a block of eight warps takes eight rows.  d <= 32 * 4 * KV and d % 4 == 0.
+template <typename TO, int KV>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           TO* __restrict__ out, const int* __restrict__ rows, int R,
+                                                           int d, float eps) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int src = (r < R && rows) ? rows[r] : r;
+  pdl_wait();
+  if (r >= R) return;
+  const float* xr = x + (size_t)src * d;
+  float4 v[KV];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < KV; ++j) {
+    const int i = (lane + 32 * j) * 4;
+    v[j] = i < d ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < KV; ++j) ss += (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+  ss = warp_sum(ss);
+  const float s = norm_scale<TO>(ss / (float)d + eps);
+  TO* o = out + (size_t)r * d;
+#pragma unroll
+  for (int j = 0; j < KV; ++j) {
+    const int i = (lane + 32 * j) * 4;
+    if (i < d) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + i);
+      store4<TO>(o + i, v[j].x * s * ww.x, v[j].y * s * ww.y, v[j].z * s * ww.z, v[j].w * s * ww.w);
+    }
+  }
+}
+
 // The contraction before a residual add may leave its K-slices unsummed ([S][T][d] fp32).  This
 // kernel adds them to the residual in slice order (models/llm/forward.go:163,169), writes the
 // residual back, and normalises the new row in the same pass (ops/norm.go:10-32).  With
@@ -275,6 +310,25 @@ DLGO_EXPORT int dlgo_rmsnorm(const float* x, const float* w, void* out, int out_
                              int d, float eps, cudaStream_t stream) {
   if (R <= 0) return DLGO_OK;
   if (d <= 0) return DLGO_ERR_SIZE;
+  if (out_dtype != DLGO_F32 && out_dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
+  if (R >= 256 && (d & 3) == 0 && d <= 32 * 4 * 32) {
+    // many rows: a warp per row
+    const dim3 grid((R + 7) / 8);
+#define DLGO_ROWS(KV)                                                                                             \
+  do {                                                                                                            \
+    if (out_dtype == DLGO_F32)                                                                                    \
+      launch_kernel(rmsnorm_rows_kernel<float, KV>, grid, dim3(256), 0, stream, x, w, (float*)out, rows, R, d, eps); \
+    else                                                                                                          \
+      launch_kernel(rmsnorm_rows_kernel<__nv_bfloat16, KV>, grid, dim3(256), 0, stream, x, w, (__nv_bfloat16*)out,  \
+                    rows, R, d, eps);                                                                             \
+  } while (0)
+    if (d <= 32 * 4 * 4) DLGO_ROWS(4);
+    else if (d <= 32 * 4 * 8) DLGO_ROWS(8);
+    else if (d <= 32 * 4 * 16) DLGO_ROWS(16);
+    else DLGO_ROWS(32);
+#undef DLGO_ROWS
+    return launch_status();
+  }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
   if (out_dtype == DLGO_F32)
     launch_kernel(rmsnorm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w, (float*)out, rows, d, eps);

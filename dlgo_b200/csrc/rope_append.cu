@@ -130,11 +130,11 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
                                        T* __restrict__ vpages, int Hq, int Hkv, int hd, int page_size,
                                        int write_cache) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int N = RVec<T>::N;
   const int t = blockIdx.x;
   const int rhalf = hd / 2, per_head = rhalf / N;
   const int items = (Hq + 2 * Hkv) * per_head;
+  // the step's own inputs: read before waiting for the projection
   const int pos = token_pos[t];
   T* row = qkv + (size_t)t * ld;
   size_t base = 0;
@@ -143,6 +143,7 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
     const int page = page_table[(size_t)slot * max_pages + pos / page_size];
     base = ((size_t)page * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
   }
+  pdl_wait();
   for (int it = threadIdx.x; it < items; it += blockDim.x) {
     const int head = it / per_head, i = (it - head * per_head) * N;
     T* h = row + (size_t)head * hd;

@@ -44,6 +44,20 @@ def test_rmsnorm(dtype, d, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("R,d", [(256, 48), (300, 512), (1000, 2048), (257, 3000), (260, 4096)])
+def test_rmsnorm_many_rows(dtype, R, d):
+    # many rows take the warp-per-row kernel
+    torch.manual_seed(R + d)
+    x = torch.randn(R, d, device=DEV) * 2
+    x[3] *= 50.0                                                 # rows of very different scale
+    w = 1 + 0.1 * torch.randn(d, device=DEV)
+    ref = P.rmsnorm(x.cpu(), w.cpu(), 1e-5)
+    torch.testing.assert_close(K().rmsnorm(x, w, 1e-5, DT[dtype]).float().cpu(), ref, **tol(dtype))
+    rows = torch.arange(R - 1, -1, -1, dtype=torch.int32, device=DEV)
+    torch.testing.assert_close(K().rmsnorm(x, w, 1e-5, DT[dtype], rows).float().cpu(), ref.flip(0), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_swiglu(dtype):
     gu = (torch.randn(5, 2 * 77, device=DEV) * 4).to(DT[dtype])
     ref = P.swiglu(gu.float().cpu()[:, :77], gu.float().cpu()[:, 77:])
