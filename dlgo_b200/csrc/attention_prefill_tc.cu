@@ -3,12 +3,13 @@
 //
 // Same formulas as attention.cu (models/llm/forward_batch.go:188-207: every prompt position attends
 // the keys t <= its position, read back from the cache; softmax in fp32).  A CTA takes up to 128
-// consecutive tokens of one sequence and one query head, and walks the sequence's pages 128 keys
-// (two pages) at a time:
+// consecutive tokens of one sequence and one query head, and walks the sequence's pages one page
+// (64 keys) at a time; blocks this small leave room for three CTAs on an SM (two at head size 128),
+// whose softmax phases, bound by the SM's 16 exponentials a clock, interleave with one another's MMAs:
 //   warp 0     TMA: the query tile once, then key and value pages into a two-stage ring
-//   warp 1     tcgen05.mma: S = Q K^T (128 x 128, fp32 in tensor memory), then O += P V, the output
+//   warp 1     tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory), then O += P V, the output
 //              accumulating in tensor memory over all key blocks
-//   warps 2-5  one thread per query row: reads its 128 scores from tensor memory once, masks,
+//   warps 2-5  one thread per query row: reads its 64 scores from tensor memory once, masks,
 //              keeps a reference maximum and the sum (fp32, exp2 on pre-scaled scores) and writes
 //              P as bf16 into shared memory in the swizzled layout the tensor core reads.  The
 //              reference maximum follows the true one lazily: only when a block's maximum exceeds
@@ -31,7 +32,7 @@ using namespace sm100;
 
 constexpr int PF_THREADS = 192;
 constexpr int PF_ROWS = 128;   // query rows per CTA
-constexpr int PF_KEYS = 128;   // keys per step (two pages of 64)
+constexpr int PF_KEYS = 64;    // keys per step (one page)
 
 __device__ int g_attention_tc_error = 0;
 
@@ -66,15 +67,15 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PF_THREADS, HD <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(PF_THREADS, HD <= 64 ? 3 : 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PfParams p) {
   constexpr int NCH = HD / 64;                 // 64-wide chunks of the head
   constexpr int QBYTES = NCH * 16384;          // [128 rows][HD]
-  constexpr int KVBYTES = NCH * 16384;         // [128 keys][HD] per stage
-  constexpr int PBYTES = 2 * 16384;            // [128 rows][128 keys]
-  constexpr uint32_t TMEM_COLS = 256;
-  constexpr uint32_t O_COL = 128;
+  constexpr int KVBYTES = NCH * 8192;          // [64 keys][HD] per stage
+  constexpr int PBYTES = 16384;                // [128 rows][64 keys]
+  constexpr uint32_t O_COL = PF_KEYS;          // scores in columns [0, 64), the output behind them
+  constexpr uint32_t TMEM_COLS = HD <= 64 ? 128 : 256;
   // the swizzled tiles want 1024-byte alignment; the kernel has no static shared memory, so the
   // dynamic window starts aligned (checked: a misaligned start ends the kernel with the error word set)
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -147,22 +148,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int it = 0; it < nblk; ++it) {
         const int st = it & 1;
         if (it >= 2 && !mbar_wait(&kvempty[st], ((it >> 1) - 1) & 1, abort_flag)) break;
-        const int pg0 = (kb_first + it) * 2;
-        int pages[2];
-        int nload = 0;
-        for (int h = 0; h < 2; ++h) {
-          const int pg = pg0 + h;
-          pages[h] = (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
-          if (pages[h] >= 0) ++nload;
-        }
-        mbar_expect_tx(&kfull[st], nload * NCH * 8192);
-        mbar_expect_tx(&vfull[st], nload * NCH * 8192);
-        for (int h = 0; h < 2; ++h) {
-          if (pages[h] < 0) continue;
-          const int row = (pages[h] * p.Hkv + kvh) * 64;
+        const int pg = kb_first + it;
+        const int page = (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
+        mbar_expect_tx(&kfull[st], page >= 0 ? NCH * 8192 : 0);
+        mbar_expect_tx(&vfull[st], page >= 0 ? NCH * 8192 : 0);
+        if (page >= 0) {
+          const int row = (page * p.Hkv + kvh) * 64;
           for (int j = 0; j < NCH; ++j) {
-            tma_load_2d(k_s + st * KVBYTES + j * 16384 + h * 8192, &map_k, &kfull[st], j * 64, row);
-            tma_load_2d(v_s + st * KVBYTES + j * 16384 + h * 8192, &map_v, &vfull[st], j * 64, row);
+            tma_load_2d(k_s + st * KVBYTES + j * 8192, &map_k, &kfull[st], j * 64, row);
+            tma_load_2d(v_s + st * KVBYTES + j * 8192, &map_v, &vfull[st], j * 64, row);
           }
         }
       }
@@ -181,7 +175,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
-                      umma_desc_k_sw128(k_addr + j * 16384) + 2 * k, idesc_s, (j | k) != 0);
+                      umma_desc_k_sw128(k_addr + j * 8192) + 2 * k, idesc_s, (j | k) != 0);
         umma_commit(s_full);
       }
       for (int it = 0; ok && it < nblk; ++it) {
@@ -191,9 +185,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(v_s + st * KVBYTES);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr + (kk >> 2) * 16384) + 2 * (kk & 3),
-                    umma_desc_mn_sw128(v_addr + kk * 2048, 16384), idesc_o, (it | kk) != 0);
+        for (int kk = 0; kk < PF_KEYS / 16; ++kk)
+          umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr) + 2 * kk,
+                    umma_desc_mn_sw128(v_addr + kk * 2048, 8192), idesc_o, (it | kk) != 0);
         umma_commit(&kvempty[st]);
         if (it + 1 < nblk) {
           // the scores of block it have been read (p_full says so): the next block's may overwrite them
@@ -207,7 +201,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
-                        umma_desc_k_sw128(k_addr + j * 16384) + 2 * k, idesc_s, (j | k) != 0);
+                        umma_desc_k_sw128(k_addr + j * 8192) + 2 * k, idesc_s, (j | k) != 0);
           // completes after everything issued before it, P V of block it included: whoever sees the
           // next scores may also overwrite P and touch O
           umma_commit(s_full);
@@ -228,14 +222,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int k0 = (kb_first + it) * PF_KEYS;
       // value rows of keys that were never written, or whose page was not loaded, must be zero
       {
-        const int t = k0 + r;
-        if (t >= t_end || (t >> 6) < first_live_page) {
+        const int t = k0 + r;                      // threads 0..63 stand for the stage's key rows
+        if (r < PF_KEYS && (t >= t_end || (t >> 6) < first_live_page)) {
           ok = mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
-          uint8_t* row = v_s + st * KVBYTES + (r >> 6) * 8192 + (r & 63) * 128;
+          uint8_t* row = v_s + st * KVBYTES + r * 128;
 #pragma unroll
           for (int j = 0; j < NCH; ++j)
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row + j * 16384 + c * 16) = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row + j * 8192 + c * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       // the scores of this block; their barrier also tells that every earlier MMA has completed
@@ -277,14 +271,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           l *= corr;
         }
         if (it > 0) {
-#pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            float o[32];
-            tmem_ld_32x32(lane_addr + O_COL + c0, o);
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD; c0 += 16) {     // (small pieces: the row's scores stay in registers meanwhile)
+            float o[16];
+            tmem_ld_32x16(lane_addr + O_COL + c0, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] *= corr;
-            tmem_st_32x32(lane_addr + O_COL + c0, o);
+            for (int j = 0; j < 16; ++j) o[j] *= corr;
+            tmem_st_32x16(lane_addr + O_COL + c0, o);
           }
           tmem_st_wait();
         }
@@ -303,8 +297,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           sum4[e] += p0 + p1;
           h[e] = __floats2bfloat162_rn(p0, p1);
         }
-        const int ch = c0 >> 3;                                   // 8-key chunk index 0..15
-        uint8_t* dst = p_s + (ch >> 3) * 16384 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+        const int ch = c0 >> 3;                                   // 8-key chunk index 0..7
+        uint8_t* dst = p_s + r * 128 + ((ch ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
@@ -389,14 +383,15 @@ int make_map(CUtensorMap* m, const void* base, long long rows, int cols, long lo
 template <int HD>
 int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int n_tiles,
               cudaStream_t stream) {
-  constexpr int SMEM = (HD / 64) * 16384 * 5 + 2 * 16384 + 256;
+  constexpr int SMEM = (HD / 64) * (16384 + 4 * 8192) + 16384 + 256;   // Q, 2 stages of K and of V, P, barriers
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM);
     if (e != cudaSuccess) return (int)e;
-    // With heads of 64 two CTAs fit an SM (2 x 112 KB of shared memory, 2 x 256 columns of tensor
-    // memory): one's softmax then runs beside the other's MMAs.  That needs the largest carve-out.
+    // With heads of 64 three CTAs fit an SM (3 x 64 KB of shared memory, 3 x 128 columns of tensor
+    // memory), with heads of 128 two: one's softmax runs beside the others' MMAs and maxima.  That
+    // needs the largest carve-out.
     if (getenv("DLGO_PF_NO_CARVEOUT") == nullptr)
       cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
                            (int)cudaSharedmemCarveoutMaxShared);
