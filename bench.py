@@ -111,10 +111,15 @@ def make_model_dir(tmp):
     return tmp
 
 
+PROMPT_LEN = 0     # > 0: every prompt has this many tokens (extra measurements at long contexts)
+
+
 def prompts_for(batch, seed=3):
     import torch
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(128, 1025, (batch,), generator=g).tolist()
+    if PROMPT_LEN > 0:
+        lens = [PROMPT_LEN] * batch
     return [torch.randint(0, MODEL["vocab_size"], (n,), generator=g).tolist() for n in lens]
 
 
@@ -207,6 +212,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the contract's Llama 3.2 1B)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length instead of uniform[128,1024]")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one small workload (for profiling) and stop")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
@@ -222,6 +228,8 @@ def main() -> int:
     import dlgo_b200
     warmup = max(a.warmup, 3)
     pk = peaks()
+    global PROMPT_LEN
+    PROMPT_LEN = a.prompt_len
     MODEL.update(SHAPES[a.shape])
     layers_of_config = MODEL["num_hidden_layers"]
     if a.layers > 0:
@@ -267,7 +275,7 @@ def main() -> int:
             "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"],
             "head_dim": MODEL["head_dim"], "ffn": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"],
             "tied": MODEL["tie_word_embeddings"], "global_batch": a.batch,
-            "seq_len": CONTEXT, "prompt_len": "uniform[128,1024] seed 3", "prefill_tokens": PREFILL_TOKENS,
+            "seq_len": CONTEXT, "prompt_len": ("uniform[128,1024] seed 3" if a.prompt_len <= 0 else a.prompt_len), "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (weights read per step: %.2f GB)" % (weight_bytes / 1e9),
             "cuda_graph": True, "peaks": pk["source"]},
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 3 * 4 * a.batch,
