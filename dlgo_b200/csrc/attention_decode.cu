@@ -148,9 +148,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
     const char* kp = (const char*)((const T*)p.kpages + base);
     const char* vp = (const char*)((const T*)p.vpages + base);
     constexpr int LINES = TILE * HD * (int)sizeof(T) / 128;
-    for (int ln = lane; ln < LINES; ln += 32) {
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + (size_t)ln * 128));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + (size_t)ln * 128));
+    if (n_tiles <= 4 * DEC_WARPS) {   // short slices only: hinting a long slice all at once slows it down
+      for (int ln = lane; ln < LINES; ln += 32) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + (size_t)ln * 128));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + (size_t)ln * 128));
+      }
     }
   }
   if (threadIdx.x == 0) TSTAMP(1);
