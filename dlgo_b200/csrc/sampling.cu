@@ -49,10 +49,40 @@ __device__ __forceinline__ void block_argmax(const float* __restrict__ row, int 
   __shared__ int bi[32];
   best = -INFINITY;
   besti = 0x7fffffff;
-  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    const float v = row[i];
-    // a strided scan visits indices in rising order, so strict '>' keeps the first maximum
-    if (v > best || besti == 0x7fffffff) { best = v; besti = i; }
+  if ((((uintptr_t)(row + begin)) & 15) == 0 && end - begin >= 4 * (int)blockDim.x) {
+    // 16-byte loads, two in flight per thread; a thread's indices still rise, so strict '>' keeps
+    // the first maximum
+    const int n4 = (end - begin) / 4;
+    const float4* r4 = reinterpret_cast<const float4*>(row + begin);
+    int k = threadIdx.x;
+    for (; k + (int)blockDim.x < n4; k += 2 * blockDim.x) {
+      const float4 a = r4[k], b = r4[k + blockDim.x];
+      const float va[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int i = begin + 4 * (e < 4 ? k : k + (int)blockDim.x) + (e & 3);
+        if (va[e] > best || besti == 0x7fffffff) { best = va[e]; besti = i; }
+      }
+    }
+    for (; k < n4; k += blockDim.x) {
+      const float4 a = r4[k];
+      const float va[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = begin + 4 * k + e;
+        if (va[e] > best || besti == 0x7fffffff) { best = va[e]; besti = i; }
+      }
+    }
+    for (int i = begin + 4 * n4 + threadIdx.x; i < end; i += blockDim.x) {   // the ragged end (indices above all others)
+      const float v = row[i];
+      if (v > best || besti == 0x7fffffff) { best = v; besti = i; }
+    }
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const float v = row[i];
+      // a strided scan visits indices in rising order, so strict '>' keeps the first maximum
+      if (v > best || besti == 0x7fffffff) { best = v; besti = i; }
+    }
   }
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -227,7 +257,7 @@ filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict
   }
   __syncthreads();
   // top-k: the k-th largest key by bisection on the 32 bits of the order-preserving key
-  uint32_t lo = 0u, hi = 0xFFFFFFFFu;     // invariant: count(key >= lo) >= k
+  uint32_t lo = 0u;     // invariant: count(key >= lo) >= k
   for (int bit = 31; bit >= 0; --bit) {
     const uint32_t mid = lo | (1u << bit);
     if (tid == 0) count_s = 0;
@@ -240,7 +270,6 @@ filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict
     if (count_s >= (unsigned int)top_k) lo = mid;
     __syncthreads();
   }
-  (void)hi;
   // survivors (key >= lo) into shared memory, the rest to -inf
   if (tid == 0) count_s = 0;
   __syncthreads();
@@ -314,8 +343,8 @@ using namespace dlgo;
 // Chunks the vocabulary is cut into for `R` rows (1: one kernel, no scratch).
 DLGO_EXPORT int dlgo_argmax_chunks(int R, int V) {
   if (V < 16384) return 1;
-  int c = (V + 8191) / 8192;
-  const int want = (2 * 148 + R - 1) / R;   // enough blocks for every SM
+  int c = (V + 2047) / 2048;
+  const int want = (4 * 148 + R - 1) / R;   // enough blocks for every SM
   if (c > want) c = want;
   return c < 1 ? 1 : (c > 64 ? 64 : c);
 }
