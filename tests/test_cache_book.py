@@ -20,6 +20,25 @@ def test_page_pool_take_give():
     assert p.take() == 1
 
 
+def test_page_pool_hands_out_the_lowest_free_page():
+    # whatever order pages came back in, a prompt's pages are taken next to one another again
+    p = PagePool(8)
+    held = [p.take() for _ in range(8)]
+    assert held == list(range(8))
+    for page in (5, 2, 7, 3):
+        p.give(page)
+    assert [p.take(), p.take(), p.take(), p.take()] == [2, 3, 5, 7]
+    b = CacheBook([("full", None)], n_pages=8, page_size=64, n_slots=4, max_seq_len=512)
+    s0, s1 = b.take_slot(), b.take_slot()
+    b.reserve(s0, 130); b.commit(s0, 130)
+    b.reserve(s1, 100); b.commit(s1, 100)
+    b.free_slot(s0)
+    s2 = b.take_slot()
+    b.reserve(s2, 200); b.commit(s2, 200)
+    assert b.table("full", s2) == [0, 1, 2, 5]
+    b.check()
+
+
 def test_slots_and_pages_follow_lengths():
     b = CacheBook([("full", None)], n_pages=4, page_size=64, n_slots=3, max_seq_len=256)
     s = b.take_slot()
