@@ -509,7 +509,7 @@ FILTER_MAX_K, FILTER_MAX_RECENT = 2048, 64
 
 def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, penalty: float,
                   recent: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Repetition penalty, temperature, top-k, top-p and min-p in one kernel (needs 1 <= top_k <= 2048).
+    """Repetition penalty, temperature, top-k (0: off, else up to 2048), top-p and min-p in one kernel.
     Returns the filtered, temperature-scaled logits; dropped tokens hold -inf.  ``recent`` is
     [rows, <= 64] int32 with -1 for "none"."""
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:

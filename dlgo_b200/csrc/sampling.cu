@@ -207,8 +207,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 
 
 // ---------------------------------------------------------------------------------------------
-// The reference's filters in one kernel (ops/sampling.go:53-165), for the usual case that top-k is
-// on: repetition penalty over the recent tokens (positive logits / penalty, negative * penalty, each
+// The reference's filters in one kernel (ops/sampling.go:53-165): repetition penalty over the recent tokens (positive logits / penalty, negative * penalty, each
 // token once), temperature, top-k (everything below the k-th largest value goes to -inf, ties at the
 // cutoff stay), then among the survivors top-p (the shortest prefix of the descending order whose
 // probabilities reach p) and min-p (drop below min_p times the largest probability).  One block per
@@ -256,6 +255,40 @@ filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict
     out[i] = v * inv_t;
   }
   __syncthreads();
+  if (top_k <= 0 || top_k >= V) {
+    // No top-k: nothing bounds the survivors, so there is no list to sort.  Top-p by bisection on the
+    // probability mass instead: the cutoff is the largest key whose tokens at or above it carry at
+    // least p of the mass (the shortest prefix of the descending order that reaches p; tokens that tie
+    // with the cutoff all stay).  Min-p is a threshold against the maximum.
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += FILTER_THREADS) mx = fmaxf(mx, out[i]);
+    mx = block_max(mx, red);
+    if (top_p < 1.0f) {
+      float tot = 0.f;
+      for (int i = tid; i < V; i += FILTER_THREADS) tot += expf(out[i] - mx);
+      tot = block_sum(tot, red);
+      const float target = top_p * tot;
+      uint32_t cut = 0u;     // invariant: mass(key >= cut) >= target
+      for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t mid = cut | (1u << bit);
+        float m = 0.f;
+        for (int i = tid; i < V; i += FILTER_THREADS) {
+          const float v = out[i];
+          if (order_key(v) >= mid) m += expf(v - mx);
+        }
+        m = block_sum(m, red);
+        if (m >= target) cut = mid;     // (the same value in every thread)
+      }
+      for (int i = tid; i < V; i += FILTER_THREADS)
+        if (order_key(out[i]) < cut) out[i] = -INFINITY;
+    }
+    if (min_p > 0.f) {
+      const float thr = mx + logf(min_p);     // exp(v - mx) < min_p  <=>  v < mx + ln(min_p)
+      for (int i = tid; i < V; i += FILTER_THREADS)
+        if (out[i] < thr) out[i] = -INFINITY;
+    }
+    return;
+  }
   // top-k: the k-th largest key by bisection on the 32 bits of the order-preserving key
   uint32_t lo = 0u;     // invariant: count(key >= lo) >= k
   for (int bit = 31; bit >= 0; --bit) {
@@ -388,14 +421,15 @@ DLGO_EXPORT int dlgo_uniform(unsigned long long seed, const int* draw, const int
   return launch_status();
 }
 
-// logits[R, V] f32 (row stride ld) -> work[R, V] f32: penalty, temperature, top-k (1 <= top_k), top-p, min-p.
+// logits[R, V] f32 (row stride ld) -> work[R, V] f32: penalty, temperature, top-k (0 or >= V: off; else at most
+// 2048), top-p, min-p.
 // recent[R, n_recent] int32 (-1 = none), n_recent <= 64, or null.
 DLGO_EXPORT int dlgo_filter(const float* logits, int R, int ld, int V, float* work, float temperature, int top_k,
                             float top_p, float min_p, float penalty, const int* recent, int n_recent,
                             cudaStream_t stream) {
   if (R <= 0) return DLGO_OK;
-  if (V <= 0 || ld < V || top_k < 1 || top_k > FILTER_CAP || n_recent < 0 || n_recent > FILTER_RECENT ||
-      !(temperature > 0.f))
+  if (V <= 0 || ld < V || top_k < 0 || (top_k > FILTER_CAP && top_k < V) || n_recent < 0 ||
+      n_recent > FILTER_RECENT || !(temperature > 0.f))
     return DLGO_ERR_SIZE;
   launch_kernel(filter_kernel, dim3(R), dim3(FILTER_THREADS), 0, stream, logits, ld, V, work, 1.0f / temperature,
                 top_k, top_p, min_p, penalty, recent, n_recent);

@@ -5,11 +5,11 @@ The reference's pipeline (ops/sampling.go:32-48): greedy if the temperature is
 (:72-80), top-k (:83-95), top-p (:99-138), min-p (:143-165), softmax and an
 inverse-CDF draw (:167-181).  Defaults 0.7 / 40 / 0.9 / 0 / 1.1 (:19-27).
 
-Greedy, the temperature draw and (whenever top-k is on, as it is by default)
-all filters are CUDA kernels of this package (csrc/sampling.cu); only token ids
-leave the device.  Filters set logits to -inf, which the draw treats as
-probability zero.  With top-k off and top-p or min-p on, the whole vocabulary
-has to be ordered and the tensor library's sort is used.
+Greedy, the temperature draw and all filters are CUDA kernels of this package
+(csrc/sampling.cu); only token ids leave the device.  Filters set logits to
+-inf, which the draw treats as probability zero.  The ``apply_*`` functions
+below restate the filters with tensor operations for host-side use and tests;
+generation does not call them.
 
 The uniform number of a draw is a counter-based function of (seed, request
 index, index of the draw within the request), so what a request samples does
@@ -113,28 +113,17 @@ class DeviceSampler:
         dev = logits.device
         rows = logits.shape[0]
         meta = torch.tensor([list(requests), list(draws)], dtype=torch.int32).to(dev, non_blocking=True)
-        if cfg.filtered and 1 <= cfg.top_k <= min(K.FILTER_MAX_K, logits.shape[1] - 1):
-            # the usual case (top-k on): every filter in one kernel of ours
+        if cfg.filtered:
+            # every filter in one kernel of ours; top-k off (0, or at least the vocabulary) is a path of its own there
+            top_k = cfg.top_k if 0 < cfg.top_k < logits.shape[1] else 0
+            if top_k > K.FILTER_MAX_K:
+                raise ValueError(f"top_k up to {K.FILTER_MAX_K} (or 0 for none), got {cfg.top_k}")
             rec = None
             if recent is not None and cfg.repetition_penalty > 1.0:
                 width = min(RECENT_WINDOW, K.FILTER_MAX_RECENT)
                 rec = torch.tensor([(list(r)[-width:] + [-1] * width)[:width] for r in recent],
                                    dtype=torch.int32).to(dev, non_blocking=True)
-            work = K.filter_logits(logits, cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty,
-                                   rec)
-            temp = torch.ones((rows,), dtype=torch.float32, device=dev)
-            return K.sample(work, temp, meta[0], meta[1], self.seed)
-        if cfg.filtered:
-            # top-k off but another filter on: the whole vocabulary has to be ordered; tensor-library
-            # sorting stands in here
-            work = logits * (1.0 / cfg.temperature) if cfg.temperature != 1.0 else logits.clone()
-            # the reference applies the penalty before the temperature; both orders give
-            # the same result because the penalty is a scaling of each logit
-            if recent is not None:
-                apply_repetition_penalty(work, recent, cfg.repetition_penalty)
-            apply_top_k(work, cfg.top_k)
-            apply_top_p(work, cfg.top_p)
-            apply_min_p(work, cfg.min_p)
+            work = K.filter_logits(logits, cfg.temperature, top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty, rec)
             temp = torch.ones((rows,), dtype=torch.float32, device=dev)
             return K.sample(work, temp, meta[0], meta[1], self.seed)
         temp = torch.full((rows,), float(cfg.temperature), dtype=torch.float32, device=dev)

@@ -495,7 +495,9 @@ def test_sample_frequencies_follow_the_probabilities():
 @pytest.mark.parametrize("V,k,p,mp,pen,temp", [(50, 5, 0.9, 0.0, 1.1, 0.7), (1000, 40, 0.9, 0.0, 1.1, 0.7),
                                                (1000, 999, 0.5, 0.05, 1.0, 1.3), (777, 1, 1.0, 0.0, 2.0, 0.5),
                                                (5000, 300, 0.95, 0.01, 1.5, 1.0), (128256, 40, 0.9, 0.02, 1.1, 0.7),
-                                               (4099, 64, 1.0, 0.1, 1.0, 2.0), (301, 300, 0.3, 0.0, 1.2, 0.9)])
+                                               (4099, 64, 1.0, 0.1, 1.0, 2.0), (301, 300, 0.3, 0.0, 1.2, 0.9),
+                                               (1000, 0, 0.8, 0.0, 1.0, 1.0), (5000, 0, 0.5, 0.02, 1.3, 0.7),
+                                               (128256, 0, 0.9, 0.0, 1.1, 0.7), (640, 0, 1.0, 0.2, 1.0, 1.5)])
 def test_filter_kernel_against_the_plain_filters(V, k, p, mp, pen, temp):
     g = torch.Generator().manual_seed(V + k)
     R = 4
