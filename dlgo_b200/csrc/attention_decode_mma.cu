@@ -25,6 +25,7 @@
 #include <cooperative_groups.h>
 #include <math.h>
 
+#include "attention_combine.cuh"
 #include "common.cuh"
 
 namespace dlgo {
@@ -46,6 +47,8 @@ struct DecMmaParams {
   int ldo;
   int Hq, Hkv, page_size, n_splits, n_gchunks, window;
   float scale;
+  float* part_acc;       // more than 8 slices: [B, Hq, n_splits, HD] and [B, Hq, n_splits, 2] scratch,
+  float* part_ml;        // combined by a second kernel; else null (slices of a cluster combine on chip)
 };
 
 // d (rows 0-7 only) += A (rows 0-7; rows 8-15 are zero) * B
@@ -264,6 +267,13 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
     }
     if (p.n_splits == 1) {
       p.out[(size_t)b * p.ldo + (size_t)(kvh * G + g0 + g) * HD + d] = __float2bfloat16_rn(a / ll);
+    } else if (p.part_acc != nullptr) {
+      const size_t o = ((size_t)b * p.Hq + (kvh * G + g0 + g)) * p.n_splits + split;
+      p.part_acc[o * HD + d] = a;
+      if (d == 0) {
+        p.part_ml[o * 2] = mm;
+        p.part_ml[o * 2 + 1] = ll;
+      }
     } else {
       cl_acc[g][d] = a;
       if (d == 0) {
@@ -272,7 +282,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
       }
     }
   }
-  if (p.n_splits == 1) return;
+  if (p.n_splits == 1 || p.part_acc != nullptr) return;
   // The slices of this (sequence, kv head, head chunk) are the blocks of one cluster: each leaves its
   // merged (max, sum, output) in its own shared memory; every block then finishes an equal share of
   // the outputs, reading all slices' values of them through distributed shared memory.
@@ -322,12 +332,16 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
 template <int HD, int NJ>
 int launch_decode_mma(const DecMmaParams& p, int B, cudaStream_t stream) {
   dim3 grid(B, p.Hkv * p.n_gchunks, p.n_splits);
-  if (p.n_splits > 1) {
+  if (p.n_splits > 1 && p.part_acc == nullptr) {
     launch_kernel_cluster(attention_decode_mma_kernel<HD, NJ>, grid, dim3(DM_THREADS), 0, stream,
                           dim3(1, 1, p.n_splits), p);
-  } else {
-    launch_kernel(attention_decode_mma_kernel<HD, NJ>, grid, dim3(DM_THREADS), 0, stream, p);
+    return launch_status();
   }
+  launch_kernel(attention_decode_mma_kernel<HD, NJ>, grid, dim3(DM_THREADS), 0, stream, p);
+  int st = launch_status();
+  if (st != DLGO_OK || p.n_splits == 1) return st;
+  launch_kernel(attention_combine_kernel<__nv_bfloat16>, dim3(B, p.Hq), dim3(HD >= 128 ? 128 : 64), 0, stream,
+                (const float*)p.part_acc, (const float*)p.part_ml, p.out, p.ldo, p.Hq, HD, p.n_splits);
   return launch_status();
 }
 
@@ -335,10 +349,11 @@ int launch_decode_mma(const DecMmaParams& p, int B, cudaStream_t stream) {
 
 using namespace dlgo;
 
-// 1 if the kernel takes these sizes: bfloat16 (implied), heads of 64 or 128, pages that hold whole tiles,
-// 1..8 slices (more than one: a thread-block cluster).
+// 1 if the kernel takes these sizes: bfloat16 (implied), heads of 64 or 128, pages that hold whole tiles.
+// 2..8 slices combine inside a thread-block cluster; more need scratch (B * Hq * n_splits * (hd + 2) floats)
+// and a second kernel.
 DLGO_EXPORT int dlgo_attention_decode_mma_takes(int hd, int page_size, int n_splits) {
-  return (hd == 64 || hd == 128) && page_size % 32 == 0 && n_splits >= 1 && n_splits <= 8;
+  return (hd == 64 || hd == 128) && page_size % 32 == 0 && n_splits >= 1 && n_splits <= 65535;
 }
 
 // q[B, .] bf16 (row stride ldq, head h at column h * hd), one token per sequence at position
@@ -348,11 +363,12 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
                                           const int* page_table, int max_pages, const int* seq_slot,
                                           const int* token_pos, void* out, int ldo, int Hq, int Hkv, int hd,
                                           int page_size, int n_splits, int window, float scale, int keys_per_tile,
-                                          cudaStream_t stream) {
+                                          float* scratch, cudaStream_t stream) {
   if (B <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return DLGO_ERR_SIZE;
   if (!dlgo_attention_decode_mma_takes(hd, page_size, n_splits)) return DLGO_ERR_SIZE;
   if (keys_per_tile != 16 && keys_per_tile != 32) return DLGO_ERR_SIZE;
+  if (n_splits > 8 && scratch == nullptr) return DLGO_ERR_SIZE;
   if ((ldq & 7) || ((uintptr_t)q & 15) || ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15)) return DLGO_ERR_ALIGN;
   const int G = Hq / Hkv;
   DecMmaParams p;
@@ -363,6 +379,8 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
   p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
   p.n_gchunks = (G + DM_GM - 1) / DM_GM;
   p.window = window; p.scale = scale;
+  p.part_acc = n_splits > 8 ? scratch : nullptr;
+  p.part_ml = n_splits > 8 ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;
   if (hd == 64) return keys_per_tile == 16 ? launch_decode_mma<64, 2>(p, B, stream) : launch_decode_mma<64, 4>(p, B, stream);
   return keys_per_tile == 16 ? launch_decode_mma<128, 2>(p, B, stream) : launch_decode_mma<128, 4>(p, B, stream);

@@ -373,9 +373,11 @@ def attention_decode_mma_takes(dtype: torch.dtype, head_dim: int, page_size: int
 def attention_decode_mma(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
                          page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                         window: int = 0, n_splits: int = 1, keys_per_tile: int = 16) -> torch.Tensor:
+                         window: int = 0, n_splits: int = 1, keys_per_tile: int = 16,
+                         scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys and values, bfloat16, on the
-    tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster."""
+    tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster, more go through
+    ``scratch`` (``attention_scratch_floats`` floats) and a second kernel."""
     for n, t in (("q", q), ("out", out), ("kpages", kpages), ("vpages", vpages)):
         _need(t, torch.bfloat16, n)
     for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
@@ -385,11 +387,16 @@ def attention_decode_mma(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor
     if q.shape[1] < num_heads * head_dim or out.shape[1] < num_heads * head_dim:
         raise KernelError("attention_decode_mma: q and out need a column per head dimension")
     page_size = kpages.shape[-2]
+    if n_splits > 8:
+        need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_decode_mma: {n_splits} slices need {need} floats of scratch")
     st = _lib("attention_decode_mma").dlgo_attention_decode_mma(
         _ptr(q), _i(B), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim),
-        _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile), _stream())
-    _check(st, "attention_decode_mma")
+        _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile),
+        _ptr(scratch if n_splits > 8 else None), _stream())
+    _check(st, "attention_decode_mma", 2 if n_splits > 8 else 1)
     return out
 
 

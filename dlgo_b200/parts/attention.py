@@ -129,12 +129,12 @@ class GQAAttention(Mixer):
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
                 counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
             # (2..8 slices form a thread-block cluster and combine through distributed shared memory)
-            if (not fused_rope and scratch is None and _MMA_KEYS and
+            if (not fused_rope and _MMA_KEYS and
                     K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits)):
                 # bfloat16, common head sizes: the scores and the weighted sum on the tensor cores
                 K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table,
                                        ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
-                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS)
+                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS, scratch)
             elif fused_rope:
                 # rotation of q and k and the append of k and v happen inside the attention kernel
                 K.attention_decode_rope(qkv, qkv_parts, T, cos, sin, rot, inter, cache.writes, cache.keys,

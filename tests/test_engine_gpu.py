@@ -104,6 +104,36 @@ def test_long_decoding(model_dirs, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_behind_a_prompt_of_more_than_64_pages(tmp_path_factory, dtype):
+    # 4,300 prompt tokens (68 pages), then four tokens one by one: decode attention then cuts a
+    # sequence into more slices than a cluster holds and combines them through scratch memory
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.engine.engine import Engine
+    from dlgo_b200.weights import write_random_model
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=128, num_hidden_layers=1, intermediate_size=192,
+               num_attention_heads=2, num_key_value_heads=1, head_dim=64, vocab_size=300, rope_theta=500000.0,
+               rms_norm_eps=1e-5, max_position_embeddings=8192, tie_word_embeddings=True)
+    d = _long_dir.get("d")
+    if d is None:
+        d = _long_dir["d"] = str(tmp_path_factory.mktemp("long_context"))
+        write_random_model(config_from_dict(cfg), 12, d)
+    toks = random_tokens(4304, 300, 21)
+    eng = Engine(d, dtype=dtype, max_tokens=4608, max_seq_len=8192)
+    eng.cache.poison()
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:4300], "want": [0, 2047, 4299]}], "end": []}]
+    for j in range(4300, 4304):
+        steps.append({"step": len(steps), "entries": [{"id": "x", "tokens": [toks[j]], "want": [0]}],
+                      "end": ["x"] if j == 4303 else []})
+    outs = T.run_in_process(eng, steps)
+    ref = plain_logits(d, toks)
+    got = torch.cat([outs[i] for i in range(5)])
+    assert_close(got, ref[[0, 2047, 4299, 4300, 4301, 4302, 4303]], dtype, f"long context ({dtype})")
+
+
+_long_dir = {}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
     # every token from the very first one by one: position 0, the first decoded token, the second

@@ -218,7 +218,7 @@ def _attention_case(dtype, hq, hkv, hd, seqs, window=0, n_splits=1, decode=False
             out.fill_(float("nan"))
             k.attention_decode_mma(qbuf, ld, T_, kp, vp, pt.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
                                    torch.tensor(pos, dtype=torch.int32, device=DEV), out, hq, hkv, hd,
-                                   1.0 / math.sqrt(hd), window, n_splits, keys)
+                                   1.0 / math.sqrt(hd), window, n_splits, keys, scratch if n_splits > 8 else None)
     elif kernel == "decode":
         assert all(n == 1 for _, n in seqs) and k.attention_decode_takes(DT[dtype], hd, 64)
         # three ways to combine slices: a cluster (no scratch, up to 8 slices), the last slice (scratch and
@@ -335,13 +335,19 @@ def test_attention_decode_kernel_sizes(dtype, hq, hkv, hd):
 def test_attention_decode_on_the_tensor_cores(hq, hkv, hd, keys):
     # lengths around page and tile edges, a first token, several slices (clusters), more heads per
     # kv head than one block takes (12 and 9 > 8)
-    for n_splits in (1, 2, 5, 8):
+    for n_splits in (1, 2, 5, 8, 11):      # 2..8: a cluster; more: scratch and a second kernel
         out, ref = _attention_case("bfloat16", hq, hkv, hd, [(500, 1), (0, 1), (65, 1), (15, 1), (16, 1), (31, 1), (127, 1)],
                                    n_splits=n_splits, decode=True, kernel=f"decode_mma_{keys}")
         torch.testing.assert_close(out, ref, atol=2e-2, rtol=2e-2)
     assert not K().attention_decode_mma_takes(torch.bfloat16, 96, 64, 1)
     assert not K().attention_decode_mma_takes(torch.float32, 64, 64, 1)
-    assert not K().attention_decode_mma_takes(torch.bfloat16, 64, 64, 9)
+    with pytest.raises(Exception):                               # more than 8 slices need scratch
+        K().attention_decode_mma(torch.zeros(1, 64, dtype=torch.bfloat16, device=DEV), 64, 1,
+                                 torch.zeros(1, 1, 64, 64, dtype=torch.bfloat16, device=DEV),
+                                 torch.zeros(1, 1, 64, 64, dtype=torch.bfloat16, device=DEV),
+                                 torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                                 torch.zeros(1, dtype=torch.int32, device=DEV),
+                                 torch.zeros(1, 64, dtype=torch.bfloat16, device=DEV), 1, 1, 64, 0.125, 0, 9, 16, None)
 
 
 @pytest.mark.parametrize("keys", [16, 32])
