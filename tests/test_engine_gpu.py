@@ -104,6 +104,16 @@ def test_long_decoding(model_dirs, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_requests_fed_in_pieces_of_several_tokens(model_dirs, name, dtype):
+    # several tokens at a time on top of a cache that is not empty, unequal pieces side by side
+    eng = engine_for(model_dirs, name, dtype)
+    reqs = requests_of(name)
+    steps = T.chunked(reqs, (37, 1, 64, 5, 70))
+    check(name, model_dirs, dtype, steps, T.run_in_process(eng, steps), reqs, "pieces")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_decoding_behind_a_prompt_of_more_than_64_pages(tmp_path_factory, dtype):
     # 4,300 prompt tokens (68 pages), then four tokens one by one: decode attention then cuts a
     # sequence into more slices than a cluster holds and combines them through scratch memory

@@ -101,6 +101,13 @@ def run(engine, reqs, refs, dtype, what):
     close(outs[1], ref_long[:k], "prefix")
     tail = torch.cat([outs[s] for s in range(2, 10)])
     close(tail, ref_long[k:], "last 8 one by one")
+    # the long request once more, fed in three pieces (several tokens on top of a cache that is not empty)
+    cuts = [(0, 60), (60, 130), (130, n)]
+    steps = [{"step": i, "entries": [{"id": "l3", "tokens": reqs["long"][a:b],
+                                      "want": [r - a for r in long_rows if a <= r < b]}],
+              "end": ["l3"] if b == n else []} for i, (a, b) in enumerate(cuts)]
+    outs = T.run_in_process(engine, steps)
+    close(torch.cat([outs[i] for i in range(3) if i in outs]), ref_long, "in three pieces")
     from dlgo_b200.csrc import kernels
     kernels.check_device_errors()
 

@@ -72,6 +72,27 @@ def batched(requests: Dict[str, List[int]], batch: int, decode: Sequence[int]) -
     return steps
 
 
+def chunked(requests: Dict[str, List[int]], cuts: Sequence[int]) -> List[Step]:
+    """All requests together, each fed in pieces of `cuts` tokens (cycled) however long it is; requests
+    that run out end earlier.  Not a pattern the replay program must take (its steps bring prompts or
+    single tokens), but one the step function does: several tokens on top of a cache that is not empty."""
+    pos = {r: 0 for r in requests}
+    live = list(requests)
+    steps = []
+    k = 0
+    while live:
+        entries = []
+        for r in live:
+            n = min(cuts[k % len(cuts)], len(requests[r]) - pos[r])
+            entries.append({"id": r, "tokens": requests[r][pos[r]:pos[r] + n], "want": list(range(n))})
+            pos[r] += n
+            k += 1
+        done = [r for r in live if pos[r] == len(requests[r])]
+        steps.append({"step": len(steps), "entries": entries, "end": done})
+        live = [r for r in live if r not in done]
+    return steps
+
+
 def collect(steps: List[Step], outputs: Dict[int, torch.Tensor], requests: Dict[str, List[int]]) -> Dict[str, torch.Tensor]:
     """Put the wanted rows of every step back in place: request -> logits [len, vocab] (NaN where never wanted)."""
     vocab = next(iter(outputs.values())).shape[-1]
