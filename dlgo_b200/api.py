@@ -85,6 +85,9 @@ class _EngineBackend:
 
     def step_and_sample(self, slots, tokens, requests, draws, sampler: SamplerConfig, seed: int, recent) -> List[int]:
         logits = self.engine.step(slots, tokens)
+        if sampler.greedy:
+            from .csrc import kernels
+            return kernels.argmax_to_host(logits)    # kernels, copy and wait in one native call
         smp = self._samplers.get(seed)
         if smp is None:
             smp = self._samplers[seed] = DeviceSampler(seed)

@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_tc": ["gemm_tc.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_decode_mma": ["attention_decode_mma.cu"],
+    "hoststep": ["hoststep.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "tcgen05.cuh"]

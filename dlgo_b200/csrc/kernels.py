@@ -259,6 +259,32 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return out
 
 
+_argmax_host_buffers: dict = {}
+
+
+def argmax_to_host(logits: torch.Tensor) -> list:
+    """First index of each row's maximum, as a list of ints on the host: the kernels, the copy into a
+    pinned buffer and the wait for it in one native call."""
+    _need(logits, torch.float32, "logits")
+    R, V = logits.shape
+    key = (logits.device.index, R, V)
+    buf = _argmax_host_buffers.get(key)
+    lib = _lib("sampling")
+    if buf is None:
+        chunks = lib.dlgo_argmax_chunks(_i(R), _i(V))
+        host = torch.zeros((R,), dtype=torch.int32).pin_memory()
+        buf = _argmax_host_buffers[key] = (
+            torch.empty((R,), dtype=torch.int32, device=logits.device),
+            torch.empty((R * chunks,), dtype=torch.float32, device=logits.device) if chunks > 1 else None,
+            torch.empty((R * chunks,), dtype=torch.int32, device=logits.device) if chunks > 1 else None,
+            host, host.numpy(), 2 if chunks > 1 else 1)
+    out, pv, pi, host, host_np, launches = buf
+    st = lib.dlgo_argmax_host(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(out), _ptr(pv), _ptr(pi),
+                              _ptr(host), _stream())
+    _check(st, "argmax", launches)
+    return host_np.tolist()
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tensor, draw: torch.Tensor, seed: int,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(logits, torch.float32, "logits")
@@ -532,3 +558,36 @@ def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: f
                                       _stream())
     _check(st, "filter")
     return work
+
+
+# ------------------------------------------------------------------ host side of a decode step
+class HostStep:
+    """The runtime calls of a decode step's launch as one native call: inputs out of a pinned buffer,
+    an event that frees the buffer, the captured graph."""
+
+    def __init__(self) -> None:
+        lib = _lib("hoststep")
+        lib.dlgo_hoststep_create.restype = ctypes.c_void_p
+        self._lib = lib
+        self._h = ctypes.c_void_p(lib.dlgo_hoststep_create())
+        if not self._h:
+            raise KernelError("hoststep: no event")
+
+    def wait(self) -> None:
+        st = self._lib.dlgo_hoststep_wait(self._h)
+        if st != 0:
+            raise KernelError(f"hoststep: CUDA error {st} while waiting for the input copy")
+
+    def launch(self, dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_exec: int, device_index: int) -> None:
+        st = self._lib.dlgo_hoststep_launch(
+            self._h, _ptr(dev_inputs), ctypes.c_void_p(host_inputs.data_ptr()),
+            _ll(host_inputs.numel() * host_inputs.element_size()), ctypes.c_void_p(graph_exec),
+            ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device_index)))
+        if st != 0:
+            raise KernelError(f"hoststep: CUDA error {st} at the launch of a decode step")
+
+    def __del__(self) -> None:
+        try:
+            self._lib.dlgo_hoststep_destroy(self._h)
+        except Exception:
+            pass

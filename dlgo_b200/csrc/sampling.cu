@@ -397,6 +397,16 @@ DLGO_EXPORT int dlgo_argmax(const float* logits, int R, int ld, int V, int* out,
   return launch_status();
 }
 
+// The same, and the ids brought to `host_out` (pinned host memory, R ints): returns when they are there.
+DLGO_EXPORT int dlgo_argmax_host(const float* logits, int R, int ld, int V, int* out, float* part_v, int* part_i,
+                                 int* host_out, cudaStream_t stream) {
+  int st = dlgo_argmax(logits, R, ld, V, out, part_v, part_i, stream);
+  if (st != DLGO_OK) return st;
+  cudaError_t e = cudaMemcpyAsync(host_out, out, sizeof(int) * (size_t)R, cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(stream);
+}
+
 // temperature[R] f32 (> 0), request[R] and draw[R] int32 key the uniform of each row
 DLGO_EXPORT int dlgo_sample(const float* logits, int R, int ld, int V, const float* temperature, const int* request,
                             const int* draw, unsigned long long seed, int* out, cudaStream_t stream) {

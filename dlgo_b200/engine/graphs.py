@@ -36,10 +36,10 @@ class DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         self.logits = None
         self.engine = engine
-        self._copied = torch.cuda.Event()
-        self._stream = None          # the stream object of the last replay (looked up again only when it changes)
-        self._stream_raw = None
         self._dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+        # copy of the inputs, "buffer free" event and graph launch as one native call (csrc/hoststep.cu)
+        self._native = kernels.HostStep()
+        self._exec = None
 
     def capture(self) -> None:
         eng = self.engine
@@ -54,19 +54,15 @@ class DecodeGraph:
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
         self.kernels_per_replay = kernels.LAUNCHES - before
+        self._exec = self.graph.raw_cuda_graph_exec()
 
     def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
-        self._copied.synchronize()  # the previous step's copy out of the pinned buffer has finished
+        self._native.wait()      # the previous step's copy out of the pinned buffer has finished
         h = self.host_np
         h[0, :] = token_ids
         h[1, :] = starts
         h[2, :] = slots
-        self.meta.copy_(self.host, non_blocking=True)
-        raw = torch._C._cuda_getCurrentRawStream(self._dev_index)
-        if raw != self._stream_raw:
-            self._stream, self._stream_raw = torch.cuda.current_stream(self._dev_index), raw
-        self._copied.record(self._stream)
-        self.graph.replay()
+        self._native.launch(self.meta, self.host, self._exec, self._dev_index)
         kernels.LAUNCHES += self.kernels_per_replay
         return self.logits
 
