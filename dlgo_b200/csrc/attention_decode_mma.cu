@@ -47,6 +47,15 @@ struct DecMmaParams {
   int ldo;
   int Hq, Hkv, page_size, n_splits, n_gchunks, window;
   float scale;
+  // optional: the projection's output comes in as unsummed fp32 K-slices and unrotated (q | k | v heads
+  // per token); the kernel sums them, rotates q and k at the token's position and appends k and v to the
+  // cache itself (one launch less per layer).  Whole-head rotation in the split-half pairing only.
+  const float* parts;    // [S][B][ldq] or null
+  int S;
+  size_t part_stride;
+  const float* cos_t;    // [positions][HD / 2]
+  const float* sin_t;
+  int write_cache;
   float* part_acc;       // more than 8 slices: [B, Hq, n_splits, HD] and [B, Hq, n_splits, 2] scratch,
   float* part_ml;        // combined by a second kernel; else null (slices of a cluster combine on chip)
 };
@@ -134,13 +143,94 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
   uint32_t qa[KK][2];
 #pragma unroll
   for (int kk = 0; kk < KK; ++kk) qa[kk][0] = qa[kk][1] = 0u;
-  if (r < GC) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0 + r) * HD + c * (HD / 4));
+  if (p.parts == nullptr) {
+    if (r < GC) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0 + r) * HD + c * (HD / 4));
 #pragma unroll
-    for (int v = 0; v < QV; ++v) {
-      const uint4 u = src[v];
-      qa[2 * v][0] = u.x; qa[2 * v][1] = u.y;
-      qa[2 * v + 1][0] = u.z; qa[2 * v + 1][1] = u.w;
+      for (int v = 0; v < QV; ++v) {
+        const uint4 u = src[v];
+        qa[2 * v][0] = u.x; qa[2 * v][1] = u.y;
+        qa[2 * v + 1][0] = u.z; qa[2 * v + 1][1] = u.w;
+      }
+    }
+  } else {
+    constexpr int RH = HD / 2;       // rotation pairs (i, i + HD/2)
+    // The block whose pages hold the new position appends the token's key (rotated) and value first
+    // (models/llm/forward.go:246-257): one warp, a lane per pair of dimensions.
+    const int pg_new = pos / PS;
+    if (p.write_cache && gc == 0 && pg_new >= pg_b && pg_new < pg_e) {   // block-uniform
+      if (warp == 0) {
+        const int page = p.page_table[(size_t)slot * p.max_pages + pg_new];
+        const size_t row = (((size_t)page * p.Hkv + kvh) * PS + (pos % PS)) * HD;
+        const float* kin = p.parts + (size_t)b * p.ldq + (size_t)(p.Hq + kvh) * HD;
+        const float* vin = p.parts + (size_t)b * p.ldq + (size_t)(p.Hq + p.Hkv + kvh) * HD;
+        for (int i = lane; i < RH; i += 32) {
+          float k0 = 0.f, k1 = 0.f, v0 = 0.f, v1 = 0.f;
+          for (int sl = 0; sl < p.S; ++sl) {          // slice order
+            const size_t so = (size_t)sl * p.part_stride;
+            k0 += __ldcg(kin + so + i); k1 += __ldcg(kin + so + i + RH);
+            v0 += __ldcg(vin + so + i); v1 += __ldcg(vin + so + i + RH);
+          }
+          const float cs = p.cos_t[(size_t)pos * RH + i], sn = p.sin_t[(size_t)pos * RH + i];
+          const_cast<T*>(p.kpages)[row + i] = __float2bfloat16_rn(k0 * cs - k1 * sn);
+          const_cast<T*>(p.kpages)[row + i + RH] = __float2bfloat16_rn(k0 * sn + k1 * cs);
+          const_cast<T*>(p.vpages)[row + i] = __float2bfloat16_rn(v0);
+          const_cast<T*>(p.vpages)[row + i + RH] = __float2bfloat16_rn(v1);
+        }
+      }
+      __threadfence_block();
+      __syncthreads();   // the new row is in place before any warp of this block reads the page
+    }
+    // query head r, this lane's quarter of the dimensions: sum of the slices, rotation (the partner of a
+    // dimension lies two quarters away: the lane with c ^ 2), rounding to bfloat16 as the separate
+    // rope kernel does
+    {      // (every lane takes part in the shuffles; lanes without a head carry zeros)
+      constexpr int QN = HD / 4;      // dimensions per lane
+      float x[QN];
+#pragma unroll
+      for (int k = 0; k < QN; ++k) x[k] = 0.f;
+      if (r < GC) {
+        const float* src = p.parts + (size_t)b * p.ldq + (size_t)(kvh * G + g0 + r) * HD + c * QN;
+        // eight slices of two 16-byte pieces are in flight at a time (slices are added in order)
+        for (int s0 = 0; s0 < p.S; s0 += 8) {
+#pragma unroll
+          for (int k4 = 0; k4 < QN / 4; k4 += 2) {
+            float4 t[8][2];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+              for (int e = 0; e < 2; ++e)
+                t[j][e] = (s0 + j < p.S)
+                              ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(s0 + j) * p.part_stride) + k4 + e)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                x[4 * (k4 + e)] += t[j][e].x; x[4 * (k4 + e) + 1] += t[j][e].y;
+                x[4 * (k4 + e) + 2] += t[j][e].z; x[4 * (k4 + e) + 3] += t[j][e].w;
+              }
+          }
+        }
+      }
+      const float* cs = p.cos_t + (size_t)pos * RH + (c & 1) * QN;
+      const float* sn = p.sin_t + (size_t)pos * RH + (c & 1) * QN;
+      float y[QN];
+#pragma unroll
+      for (int k = 0; k < QN; ++k) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[k], 2);
+        const float ck = cs[k], sk = sn[k];
+        y[k] = c < 2 ? (x[k] * ck - other * sk) : (other * sk + x[k] * ck);
+      }
+      if (r < GC) {
+#pragma unroll
+        for (int v = 0; v < QV; ++v) {
+          qa[2 * v][0] = pack_bf16(y[8 * v], y[8 * v + 1]);
+          qa[2 * v][1] = pack_bf16(y[8 * v + 2], y[8 * v + 3]);
+          qa[2 * v + 1][0] = pack_bf16(y[8 * v + 4], y[8 * v + 5]);
+          qa[2 * v + 1][1] = pack_bf16(y[8 * v + 6], y[8 * v + 7]);
+        }
+      }
     }
   }
   float o[NT][2];
@@ -358,18 +448,30 @@ DLGO_EXPORT int dlgo_attention_decode_mma_takes(int hd, int page_size, int n_spl
 
 // q[B, .] bf16 (row stride ldq, head h at column h * hd), one token per sequence at position
 // token_pos[b] whose key and value are already in the cache; out[B, .] bf16 (row stride ldo).
+// Or, with `parts` ([S][B][ldq] fp32, slice stride part_stride floats: the unsummed K-slices of the q | k | v
+// projection) and cos/sin tables [positions][hd / 2]: q is null, the kernel sums, rotates (whole head,
+// pairs (i, i + hd/2)) and, with write_cache, appends the token's key and value itself.
 // keys_per_tile: 16 or 32 keys per warp iteration.
 DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const void* kpages, const void* vpages,
                                           const int* page_table, int max_pages, const int* seq_slot,
                                           const int* token_pos, void* out, int ldo, int Hq, int Hkv, int hd,
                                           int page_size, int n_splits, int window, float scale, int keys_per_tile,
-                                          float* scratch, cudaStream_t stream) {
+                                          float* scratch, const float* parts, int S, long long part_stride,
+                                          const float* cos_t, const float* sin_t, int write_cache,
+                                          cudaStream_t stream) {
   if (B <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return DLGO_ERR_SIZE;
   if (!dlgo_attention_decode_mma_takes(hd, page_size, n_splits)) return DLGO_ERR_SIZE;
   if (keys_per_tile != 16 && keys_per_tile != 32) return DLGO_ERR_SIZE;
   if (n_splits > 8 && scratch == nullptr) return DLGO_ERR_SIZE;
-  if ((ldq & 7) || ((uintptr_t)q & 15) || ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15)) return DLGO_ERR_ALIGN;
+  if ((ldq & 7) || ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15)) return DLGO_ERR_ALIGN;
+  if (parts == nullptr) {
+    if ((uintptr_t)q & 15) return DLGO_ERR_ALIGN;
+  } else {
+    // fused rotation and append: one head chunk per kv head, 16-byte slices, tables present
+    if (Hq / Hkv > DM_GM || S <= 0 || (part_stride & 3) || ((uintptr_t)parts & 15) || cos_t == nullptr || sin_t == nullptr)
+      return DLGO_ERR_SIZE;
+  }
   const int G = Hq / Hkv;
   DecMmaParams p;
   p.q = (const __nv_bfloat16*)q; p.ldq = ldq;
@@ -379,6 +481,8 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
   p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
   p.n_gchunks = (G + DM_GM - 1) / DM_GM;
   p.window = window; p.scale = scale;
+  p.parts = parts; p.S = S; p.part_stride = (size_t)part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
+  p.write_cache = write_cache;
   p.part_acc = n_splits > 8 ? scratch : nullptr;
   p.part_ml = n_splits > 8 ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;

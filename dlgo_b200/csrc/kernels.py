@@ -396,22 +396,48 @@ def attention_decode_mma_takes(dtype: torch.dtype, head_dim: int, page_size: int
         _lib("attention_decode_mma").dlgo_attention_decode_mma_takes(_i(head_dim), _i(page_size), _i(n_splits)))
 
 
-def attention_decode_mma(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
+def attention_decode_mma_fuses_rope(num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+                                    interleaved: bool) -> bool:
+    """Whether the kernel can sum the projection's slices, rotate and append itself: whole-head rotation
+    in the split-half pairing, at most 8 query heads per kv head."""
+    return rotary_dim == head_dim and not interleaved and num_heads // num_kv_heads <= 8
+
+
+def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: torch.Tensor, vpages: torch.Tensor,
                          page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: int = 0, n_splits: int = 1, keys_per_tile: int = 16,
-                         scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         scratch: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None,
+                         cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                         write_cache: bool = True) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys and values, bfloat16, on the
     tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster, more go through
     ``scratch`` (``attention_scratch_floats`` floats) and a second kernel."""
-    for n, t in (("q", q), ("out", out), ("kpages", kpages), ("vpages", vpages)):
+    for n, t in (("out", out), ("kpages", kpages), ("vpages", vpages)):
         _need(t, torch.bfloat16, n)
     for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
         _need(t, torch.int32, n)
-    if seq_slot.numel() < B or token_pos.numel() < B or q.shape[0] < B or out.shape[0] < B:
+    if seq_slot.numel() < B or token_pos.numel() < B or out.shape[0] < B:
         raise KernelError("attention_decode_mma: fewer rows than sequences")
-    if q.shape[1] < num_heads * head_dim or out.shape[1] < num_heads * head_dim:
-        raise KernelError("attention_decode_mma: q and out need a column per head dimension")
+    if out.shape[1] < num_heads * head_dim:
+        raise KernelError("attention_decode_mma: out needs a column per head dimension")
+    S = part_stride = 0
+    if parts is None:
+        _need(q, torch.bfloat16, "q")
+        if q.shape[0] < B or q.shape[1] < num_heads * head_dim:
+            raise KernelError("attention_decode_mma: q needs a row per sequence and a column per head dimension")
+    else:
+        # the projection's unsummed slices [S, B, ldq] (q | k | v heads), rotated and appended by the kernel
+        _need(parts, torch.float32, "parts")
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        if parts.dim() != 3 or parts.shape[1] < B or parts.shape[2] != ldq or \
+                ldq < (num_heads + 2 * num_kv_heads) * head_dim or cos.shape[1] != head_dim // 2:
+            raise KernelError("attention_decode_mma: parts must be [slices, sequences, q|k|v columns] with cos/sin "
+                              "tables of head_dim / 2 columns")
+        if not attention_decode_mma_fuses_rope(num_heads, num_kv_heads, head_dim, head_dim, False):
+            raise KernelError("attention_decode_mma: these head counts cannot take the fused rotation")
+        S, part_stride = parts.shape[0], parts.stride(0)
     page_size = kpages.shape[-2]
     if n_splits > 8:
         need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
@@ -421,7 +447,8 @@ def attention_decode_mma(q: torch.Tensor, ldq: int, B: int, kpages: torch.Tensor
         _ptr(q), _i(B), _i(ldq), _ptr(kpages), _ptr(vpages), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim),
         _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile),
-        _ptr(scratch if n_splits > 8 else None), _stream())
+        _ptr(scratch if n_splits > 8 else None), _ptr(parts), _i(S), _ll(part_stride), _ptr(cos), _ptr(sin),
+        _i(1 if write_cache else 0), _stream())
     _check(st, "attention_decode_mma", 2 if n_splits > 8 else 1)
     return out
 

@@ -33,6 +33,10 @@ _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up t
 # default: measured on a B200 the hint does not pay, the attention kernel's own hint is early enough)
 _AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 0)) << 20
 _MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp iteration of the tensor-core decode kernel (0: off)
+# ... which can also sum the projection's slices, rotate and append itself (one launch less per layer).  Opt-in:
+# measured in a whole step it is slower (0.918 against 0.891 ms at batch 8): every slice of a sequence repeats
+# the sum of the query's K-slices, and the block that appends starts its keys a round trip later.
+_MMA_FUSE = os.environ.get("DLGO_ATTN_MMA_FUSE_ROPE", "0") == "1"
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
 
@@ -102,7 +106,11 @@ class GQAAttention(Mixer):
         qkv = None
         if qkv_parts is None:
             qkv = self.wqkv(x, STORE)
-        if not fused_rope:
+        # the tensor-core decode kernel can take the slices as they are: it sums, rotates and appends itself
+        mma_fused = (decode_kernel and _MMA_FUSE and _MMA_KEYS and qkv_parts is not None and not fused_rope and
+                     K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, 1) and
+                     K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter))
+        if not fused_rope and not mma_fused:
             if qkv is None:
                 qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
             ahead = 0
@@ -129,7 +137,12 @@ class GQAAttention(Mixer):
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
                 counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
             # (2..8 slices form a thread-block cluster and combine through distributed shared memory)
-            if (not fused_rope and _MMA_KEYS and
+            if mma_fused:
+                K.attention_decode_mma(None, qkv_parts.shape[2], T, cache.keys, cache.values, cache.page_table,
+                                       ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
+                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS, scratch,
+                                       qkv_parts, cos, sin, cache.writes)
+            elif (not fused_rope and _MMA_KEYS and
                     K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits)):
                 # bfloat16, common head sizes: the scores and the weighted sum on the tensor cores
                 K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table,

@@ -872,3 +872,51 @@ def test_decode_attention_with_the_rotation_and_append_inside(dtype, hq, hkv, hd
     ct = dict(atol=1e-6, rtol=1e-6) if dtype == "float32" else dict(atol=1e-2, rtol=8e-3)
     torch.testing.assert_close(caches[1][0], caches[0][0], **ct)
     assert torch.equal(caches[1][1], caches[0][1])
+
+
+@pytest.mark.parametrize("hq,hkv,hd,S", [(8, 2, 64, 3), (32, 8, 64, 6), (3, 1, 128, 8), (8, 1, 64, 11), (12, 4, 128, 1)])
+@pytest.mark.parametrize("keys", [16, 32])
+def test_tensor_core_decode_attention_with_the_rotation_and_append_inside(hq, hkv, hd, S, keys):
+    # the kernel fed with the projection's unsummed slices against rope_append followed by the same
+    # kernel fed with the finished q: same outputs, same rows appended to the cache
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    assert k.attention_decode_mma_fuses_rope(hq, hkv, hd, hd, False)
+    assert not k.attention_decode_mma_fuses_rope(hq, hkv, hd, hd // 2, False)
+    assert not k.attention_decode_mma_fuses_rope(hq, hkv, hd, hd, True)
+    torch.manual_seed(hd + S)
+    cos, sin = (t.to(DEV) for t in RotaryEmbedding(hd, hd, 10000.0, 700, "split_half").tables())
+    lens = [300, 1, 64, 65, 640]                                  # positions 299, 0, 63 (page end), 64 (page start), 639
+    B = len(lens)
+    pages_per = [(n + 63) // 64 for n in lens]
+    n_pages = sum(pages_per) + 1
+    perm = torch.randperm(n_pages).tolist()
+    pt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    for i, n in enumerate(pages_per):
+        for pg in range(n):
+            pt[i, pg] = perm.pop()
+    pt = pt.to(DEV)
+    ld = (hq + 2 * hkv) * hd
+    parts = torch.randn(S, B, ld, device=DEV) * 0.6
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    results = {}
+    for fused in (False, True):
+        for n_splits in (1, 4, 8):
+            torch.manual_seed(1)
+            kp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(torch.bfloat16)
+            vp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(torch.bfloat16)
+            out = torch.full((B, hq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+            if not fused:
+                qkv = torch.empty(B, ld, device=DEV, dtype=torch.bfloat16)
+                k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, hd, False, True, parts)
+                k.attention_decode_mma(qkv, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits, keys)
+            else:
+                k.attention_decode_mma(None, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits,
+                                       keys, None, parts, cos, sin, True)
+            results[(fused, n_splits)] = (out.float().clone(), kp.float().clone(), vp.float().clone())
+    for n_splits in (1, 4, 8):
+        a, b = results[(False, n_splits)], results[(True, n_splits)]
+        torch.testing.assert_close(b[0], a[0], atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(b[1], a[1], atol=1e-2, rtol=8e-3)   # (x0*c - x1*s may contract differently: one ulp)
+        assert torch.equal(b[2], a[2])
