@@ -83,6 +83,10 @@ class _EngineBackend:
         ps = self.engine.cache.page_size
         return (n_positions + ps - 1) // ps
 
+    def greedy_steps(self, slots, tokens, n_steps: int, stop_ids) -> Optional[List[List[int]]]:
+        """Several greedy decode steps in one native call (``None``: step one by one)."""
+        return self.engine.greedy_run(slots, tokens, n_steps, stop_ids)
+
     def step_and_sample(self, slots, tokens, requests, draws, sampler: SamplerConfig, seed: int, recent) -> List[int]:
         logits = self.engine.step(slots, tokens)
         if sampler.greedy:

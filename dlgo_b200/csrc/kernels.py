@@ -3,7 +3,7 @@ current stream.  Nothing here computes; a missing or failing library raises."""
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Sequence, List, Optional
 
 import torch
 
@@ -283,6 +283,36 @@ def argmax_to_host(logits: torch.Tensor) -> list:
                               _ptr(host), _stream())
     _check(st, "argmax", launches)
     return host_np.tolist()
+
+
+def greedy_run(dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_exec: int, logits: torch.Tensor,
+               stop_ids: Sequence[int], max_steps: int, device_index: int) -> List[List[int]]:
+    """Up to ``max_steps`` greedy decode steps of one batch in one native call (see dlgo_greedy_run):
+    ``host_inputs`` (pinned int32 [3, B]: ids, positions, slots) holds the first step's inputs and is
+    advanced in place; returns the ids chosen, a list per step, ending with the step in which a
+    sequence chose a stop id."""
+    import numpy as np
+    _need(logits, torch.float32, "logits")
+    B, V = logits.shape
+    key = (logits.device.index, B, V)
+    lib = _lib("sampling")
+    buf = _argmax_host_buffers.get(key)
+    if buf is None:
+        argmax_to_host(logits)                    # makes the buffers (and runs one harmless argmax)
+        buf = _argmax_host_buffers[key]
+    out, pv, pi, host, host_np, launches = buf
+    stops = np.asarray(sorted(int(t) for t in stop_ids), dtype=np.int32)
+    tokens = np.empty((max_steps, B), dtype=np.int32)
+    n = lib.dlgo_greedy_run(
+        _ptr(dev_inputs), ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec), _ptr(logits),
+        _i(logits.stride(0)), _i(V), _ptr(out), _ptr(pv), _ptr(pi), ctypes.c_void_p(host.data_ptr()),
+        stops.ctypes.data_as(ctypes.c_void_p), _i(len(stops)), _i(max_steps),
+        tokens.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device_index)))
+    if n <= 0:
+        raise KernelError(f"greedy_run: error {n}")
+    global LAUNCHES
+    LAUNCHES += launches * n
+    return tokens[:n].tolist()
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tensor, draw: torch.Tensor, seed: int,

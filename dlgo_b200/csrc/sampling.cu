@@ -407,6 +407,42 @@ DLGO_EXPORT int dlgo_argmax_host(const float* logits, int R, int ld, int V, int*
   return (int)cudaStreamSynchronize(stream);
 }
 
+// Greedy decoding of one batch for up to `max_steps` steps without returning to the caller: every
+// step copies its inputs (ids, positions, slots: `host_inputs`, pinned, [3][B]) to the device, launches
+// the captured step, takes each row's first maximum and brings the ids back (`host_ids`, pinned, [B]);
+// the ids become the next step's inputs at positions + 1.  Stops after the step in which a sequence
+// chose one of `stop_ids`.  The ids of step s go to out_tokens[s * B ...]; returns the number of steps
+// run (>= 1), or minus a CUDA error code.  (The reference's loop is compiled code too:
+// models/llm/generate.go:207-283.)
+DLGO_EXPORT int dlgo_greedy_run(void* dev_inputs, int* host_inputs, int B, void* graph_exec, const float* logits,
+                                int ld, int V, int* out_dev, float* part_v, int* part_i, int* host_ids,
+                                const int* stop_ids, int n_stop, int max_steps, int* out_tokens,
+                                cudaStream_t stream) {
+  if (B <= 0 || max_steps <= 0) return 0;
+  for (int step = 0; step < max_steps; ++step) {
+    cudaError_t e = cudaMemcpyAsync(dev_inputs, host_inputs, sizeof(int) * 3 * (size_t)B, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return -(int)e;
+    e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, stream);
+    if (e != cudaSuccess) return -(int)e;
+    int st = dlgo_argmax(logits, B, ld, V, out_dev, part_v, part_i, stream);
+    if (st != DLGO_OK) return st < 0 ? st : -st;
+    e = cudaMemcpyAsync(host_ids, out_dev, sizeof(int) * (size_t)B, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return -(int)e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return -(int)e;
+    bool stop = false;
+    for (int b = 0; b < B; ++b) {
+      const int id = host_ids[b];
+      out_tokens[(size_t)step * B + b] = id;
+      for (int k = 0; k < n_stop; ++k) stop |= stop_ids[k] == id;
+      host_inputs[b] = id;          // next step: this id at the next position
+      host_inputs[B + b] += 1;
+    }
+    if (stop) return step + 1;
+  }
+  return max_steps;
+}
+
 // temperature[R] f32 (> 0), request[R] and draw[R] int32 key the uniform of each row
 DLGO_EXPORT int dlgo_sample(const float* logits, int R, int ld, int V, const float* temperature, const int* request,
                             const int* draw, unsigned long long seed, int* out, cudaStream_t stream) {

@@ -20,7 +20,7 @@ import torch
 from ..cache.kv_cache import KVCache, PAGE_SIZE
 from ..config.registry import load_config
 from ..weights.loader import DictSource, WeightSource
-from .graphs import decode_with_graph
+from .graphs import decode_with_graph, greedy_with_graph
 from .model import CausalLM
 from .runtime import Runtime, StepContext, build_context
 
@@ -177,6 +177,42 @@ class Engine:
         for s in slots:
             lengths[s] += 1
         return logits
+
+    @torch.no_grad()
+    def greedy_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int,
+                   stop_ids: Sequence[int] = ()) -> Optional[List[List[int]]]:
+        """Run ``tokens[i]`` as the next token of the sequence in ``slots[i]`` and go on greedily, every
+        sequence one token per step, for up to ``n_steps`` steps without returning in between (the steps,
+        the argmax and the copies of the ids are one native call).  Returns the ids chosen, a list per
+        step; the run ends with the step in which a sequence chose one of ``stop_ids``.  ``None`` when
+        this engine cannot do it (no CUDA graphs, or the cache lacks room for ``n_steps`` positions):
+        the caller then steps one by one."""
+        if not self.cuda_graphs or n_steps <= 0:
+            return None
+        slots = [int(s) for s in slots]
+        ids = [int(t) for t in tokens]
+        V, limit = self.vocab_size, self.max_seq_len
+        lengths = self.cache.book._len
+        if len(slots) != len(ids) or len(set(slots)) != len(slots):
+            raise StepError("greedy_run: one token per distinct slot")
+        starts = []
+        for s, t in zip(slots, ids):
+            cur = lengths.get(s)
+            if cur is None:
+                raise StepError(f"slot {s} is not held")
+            if not 0 <= t < V:
+                raise StepError(f"token id {t} is outside the vocabulary [0, {V})")
+            if cur + n_steps > limit:
+                raise StepError(f"slot {s} would reach {cur + n_steps} positions; the limit is {limit}")
+            starts.append(cur)
+        with torch.cuda.device(self.runtime.device):
+            try:
+                self.cache.reserve(slots, [n_steps] * len(slots))     # pages for the whole run, mirrored once
+            except Exception:
+                return None
+            out = greedy_with_graph(self, slots, ids, starts, n_steps, stop_ids)
+        self.cache.commit(slots, [len(out)] * len(slots))
+        return out
 
     # ------------------------------------------------------------------ summary
     def weight_bytes(self) -> int:

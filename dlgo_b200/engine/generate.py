@@ -66,6 +66,9 @@ class Backend(Protocol):
     def step_and_sample(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], requests: Sequence[int],
                         draws: Sequence[int], sampler: SamplerConfig, seed: int,
                         recent: Sequence[Sequence[int]]) -> List[int]: ...
+    # optional: ``greedy_steps(slots, last_tokens, n_steps, stop_ids) -> per-step lists of ids | None``:
+    # up to n_steps greedy decode steps of the same sequences in one call, ending with the step in
+    # which a sequence chose a stop id
 
 
 class GenerationError(ValueError):
@@ -144,15 +147,9 @@ class GenerationLoop:
                 t0 = time.perf_counter()
                 feed: List[Sequence[int]] = [prompts[s.request] for s in live]
                 first = True
-                while live:
-                    sampled = self.backend.step_and_sample(
-                        [s.slot for s in live], feed, [s.request for s in live], [len(s.out) for s in live],
-                        cfg.sampler, seed, [s.recent for s in live])
-                    steps += 1
-                    if first:
-                        prefill_ms += (time.perf_counter() - t0) * 1e3
-                        t0 = time.perf_counter()
-                        first = False
+                def account(sampled: Sequence[int]) -> None:
+                    """One step's chosen tokens: outputs, stop tokens, who goes on."""
+                    nonlocal live, feed
                     still: List[_Live] = []
                     for s, fed, tok in zip(live, feed, sampled):
                         s.length += len(fed)
@@ -177,6 +174,31 @@ class GenerationLoop:
                             still.append(s)
                     live = still
                     feed = [[s.last] for s in live]
+
+                greedy_steps = getattr(self.backend, "greedy_steps", None)
+                while live:
+                    if not first and greedy_steps is not None and cfg.sampler.greedy and on_token is None:
+                        # Decoding greedily with nobody listening token by token: the backend may run
+                        # several steps in one call.  As many as every sequence can take before it ends
+                        # by count, so that only a stop token can end one earlier, and the backend
+                        # returns with the step in which one appeared.
+                        n = min(min(cfg.max_tokens - len(s.out), limit - 1 - s.length) for s in live)
+                        chunk = greedy_steps([s.slot for s in live], [s.last for s in live], n, sorted(stops)) \
+                            if n > 1 else None
+                        if chunk is not None:
+                            for sampled in chunk:
+                                steps += 1
+                                account(sampled)
+                            continue
+                    sampled = self.backend.step_and_sample(
+                        [s.slot for s in live], feed, [s.request for s in live], [len(s.out) for s in live],
+                        cfg.sampler, seed, [s.recent for s in live])
+                    steps += 1
+                    if first:
+                        prefill_ms += (time.perf_counter() - t0) * 1e3
+                        t0 = time.perf_counter()
+                        first = False
+                    account(sampled)
                 generate_ms += (time.perf_counter() - t0) * 1e3
             finally:
                 for s in live:

@@ -67,6 +67,25 @@ class DecodeGraph:
         return self.logits
 
 
+def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int], n_steps: int,
+                      stop_ids: Sequence[int]) -> List[List[int]]:
+    """Up to ``n_steps`` greedy decode steps through the graph of this batch size in one native call;
+    the ids chosen, a list per step (fewer than ``n_steps`` if a sequence chose a stop id)."""
+    b = len(slots)
+    g = engine._graphs.get(b)
+    if g is None:
+        decode_with_graph(engine, slots, token_ids, starts)    # captures (and runs the first step once, harmlessly)
+        g = engine._graphs[b]
+    g._native.wait()
+    h = g.host_np
+    h[0, :] = token_ids
+    h[1, :] = starts
+    h[2, :] = slots
+    out = kernels.greedy_run(g.meta, g.host, g._exec, g.logits, stop_ids, n_steps, g._dev_index)
+    kernels.LAUNCHES += g.kernels_per_replay * len(out)
+    return out
+
+
 def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
     """Logits [batch, vocab] of one decode step, through the graph of this batch size.
 

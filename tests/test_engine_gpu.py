@@ -240,3 +240,48 @@ def test_temperature_generation_is_seeded_and_independent_of_the_batch(model_dir
     assert filt == llm.generate(prompts, max_tokens=8, temperature=0.7, top_k=40, top_p=0.9, seed=3, ignore_eos=True)
     res = llm.benchmark(prompts, max_tokens=4, greedy=True, ignore_eos=True)
     assert res.output_tokens == 16 and res.tokens_per_sec > 0 and "tok/s" in str(res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_several_greedy_steps_in_one_native_call(model_dirs, dtype):
+    # Engine.greedy_run against the same steps taken one by one: same ids, same cache lengths; a stop id
+    # ends the run with the step in which it was chosen
+    from dlgo_b200.csrc import kernels
+    from dlgo_b200.engine.engine import Engine
+    eng = Engine(model_dirs["C"], dtype=dtype, max_tokens=1536)
+    prompts = [random_tokens(n, vocab_of("C"), 40 + i) for i, n in enumerate([60, 3, 130])]
+
+    def start():
+        slots = [eng.take_slot() for _ in prompts]
+        first = kernels.argmax(eng.step(slots, prompts)).cpu().tolist()
+        return slots, first
+
+    slots, first = start()
+    one_by_one, cur = [], first
+    for _ in range(70):                                          # across a page edge for every sequence
+        cur = kernels.argmax(eng.step(slots, [[t] for t in cur])).cpu().tolist()
+        one_by_one.append(cur)
+    lens_a = [eng.length(s) for s in slots]
+    for s in slots:
+        eng.free_slot(s)
+    slots, first2 = start()
+    assert first2 == first
+    run = eng.greedy_run(slots, first, 70)
+    assert run == one_by_one and [eng.length(s) for s in slots] == lens_a
+    for s in slots:
+        eng.free_slot(s)
+    # a stop id: the id sequence 1 chose at its 5th step
+    stop = one_by_one[4][1]
+    expect = next(i for i, ids in enumerate(one_by_one) if stop in ids) + 1
+    slots, _ = start()
+    run = eng.greedy_run(slots, first, 70, [stop])
+    assert len(run) == expect and run == one_by_one[:expect]
+    assert [eng.length(s) for s in slots] == [len(p) + expect for p in prompts]
+    # and the run goes on from there like the single steps
+    more = eng.greedy_run(slots, run[-1], 3)
+    assert more == one_by_one[expect:expect + 3]
+    for s in slots:
+        eng.free_slot(s)
+    eng.cache.book.check()
+    with pytest.raises(Exception):
+        eng.greedy_run([0], [5], 10)                              # a slot that is not held

@@ -150,3 +150,64 @@ def test_seed_from_the_clock_when_negative():
     be = ScriptedBackend()
     GenerationLoop(be).run([[1]], GenerateConfig(max_tokens=1, sampler=GREEDY, seed=-1))
     assert be.calls[0]["seed"] >= 0
+
+
+class MultiStepBackend(ScriptedBackend):
+    """A backend that also offers several greedy steps in one call; it has to be told which request
+    sits in which slot, so it remembers the requests of the prompt step."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.request_of: Dict[int, int] = {}
+        self.draw_of: Dict[int, int] = {}
+        self.multi_calls: List[dict] = []
+
+    def step_and_sample(self, slots, tokens, requests, draws, sampler, seed, recent):
+        for s, r, d in zip(slots, requests, draws):
+            self.request_of[s] = r
+            self.draw_of[s] = d + 1
+        return super().step_and_sample(slots, tokens, requests, draws, sampler, seed, recent)
+
+    def greedy_steps(self, slots, tokens, n_steps, stop_ids):
+        self.multi_calls.append(dict(slots=list(slots), tokens=list(tokens), n=n_steps, stops=list(stop_ids)))
+        out = []
+        for _ in range(n_steps):
+            ids = []
+            for s in slots:
+                self.held[s] += 1
+                assert self.held[s] <= self.max_seq_len
+                ids.append(self.script(self.request_of[s], self.draw_of[s]))
+                self.draw_of[s] += 1
+            out.append(ids)
+            if any(i in stop_ids for i in ids):
+                break
+        return out
+
+
+def test_several_greedy_steps_in_one_backend_call_change_no_decision():
+    script = lambda r, d: 7 if (r == 1 and d == 2) else 100 + 10 * r + d
+    prompts = [[1, 2], [3], [4, 5, 6]]
+    for kw in (dict(), dict(include_stop=True), dict(ignore_eos=True)):
+        cfg = GenerateConfig(max_tokens=6, sampler=GREEDY, seed=0, **kw)
+        plain = GenerationLoop(ScriptedBackend(script=script), model_stop_ids=[7]).run(prompts, cfg)
+        be = MultiStepBackend(script=script)
+        multi = GenerationLoop(be, model_stop_ids=[7]).run(prompts, cfg)
+        assert multi.tokens == plain.tokens and multi.steps == plain.steps and multi.output_tokens == plain.output_tokens
+        assert be.held == {} and sorted(be.free_slots) == [0, 1, 2, 3]
+        assert len(be.calls) == 1 and be.multi_calls            # the prompts one step, the rest in runs
+        if not kw:
+            # the run asked for 5 more steps came back after 2 (request 1 chose the stop token); the
+            # two others went on in a second run of 3
+            assert [c["n"] for c in be.multi_calls] == [5, 3] and be.multi_calls[1]["slots"] == [0, 2]
+    # with a listener, or when sampling, the loop steps one by one
+    be = MultiStepBackend(script=script)
+    seen = []
+    GenerationLoop(be).run(prompts, GenerateConfig(max_tokens=3, sampler=GREEDY, seed=0), lambda r, t: seen.append((r, t)))
+    assert not be.multi_calls and len(seen) == 9
+    be = MultiStepBackend(script=script)
+    GenerationLoop(be).run(prompts, GenerateConfig(max_tokens=3, sampler=SamplerConfig.plain_temperature(0.8), seed=0))
+    assert not be.multi_calls
+    # the sequence limit bounds a run like max_tokens does
+    be = MultiStepBackend(max_seq_len=8, script=script)
+    res = GenerationLoop(be).run([[1, 2, 3]], GenerateConfig(max_tokens=50, sampler=GREEDY, seed=0))
+    assert len(res.tokens[0]) == 5 and be.multi_calls[0]["n"] == 4
