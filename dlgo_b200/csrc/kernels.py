@@ -285,33 +285,25 @@ def argmax_to_host(logits: torch.Tensor) -> list:
     return host_np.tolist()
 
 
-def greedy_run(dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_exec: int, logits: torch.Tensor,
-               stop_ids: Sequence[int], max_steps: int, device_index: int) -> List[List[int]]:
-    """Up to ``max_steps`` greedy decode steps of one batch in one native call (see dlgo_greedy_run):
+def greedy_run_graph(dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_exec: int, host_ids: torch.Tensor,
+                     stop_ids: Sequence[int], max_steps: int, device_index: int, launches_per_step: int) -> List[List[int]]:
+    """Up to ``max_steps`` greedy decode steps of one batch in one native call (dlgo_greedy_run_graph).
+    The captured step ends with the argmax and the copy of the ids into ``host_ids`` (pinned int32 [B]);
     ``host_inputs`` (pinned int32 [3, B]: ids, positions, slots) holds the first step's inputs and is
-    advanced in place; returns the ids chosen, a list per step, ending with the step in which a
+    advanced in place.  Returns the ids chosen, a list per step, ending with the step in which a
     sequence chose a stop id."""
     import numpy as np
-    _need(logits, torch.float32, "logits")
-    B, V = logits.shape
-    key = (logits.device.index, B, V)
-    lib = _lib("sampling")
-    buf = _argmax_host_buffers.get(key)
-    if buf is None:
-        argmax_to_host(logits)                    # makes the buffers (and runs one harmless argmax)
-        buf = _argmax_host_buffers[key]
-    out, pv, pi, host, host_np, launches = buf
+    B = host_ids.numel()
     stops = np.asarray(sorted(int(t) for t in stop_ids), dtype=np.int32)
     tokens = np.empty((max_steps, B), dtype=np.int32)
-    n = lib.dlgo_greedy_run(
-        _ptr(dev_inputs), ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec), _ptr(logits),
-        _i(logits.stride(0)), _i(V), _ptr(out), _ptr(pv), _ptr(pi), ctypes.c_void_p(host.data_ptr()),
-        stops.ctypes.data_as(ctypes.c_void_p), _i(len(stops)), _i(max_steps),
+    n = _lib("sampling").dlgo_greedy_run_graph(
+        _ptr(dev_inputs), ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec),
+        ctypes.c_void_p(host_ids.data_ptr()), stops.ctypes.data_as(ctypes.c_void_p), _i(len(stops)), _i(max_steps),
         tokens.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device_index)))
     if n <= 0:
-        raise KernelError(f"greedy_run: error {n}")
+        raise KernelError(f"greedy_run_graph: error {n}")
     global LAUNCHES
-    LAUNCHES += launches * n
+    LAUNCHES += launches_per_step * n
     return tokens[:n].tolist()
 
 

@@ -407,35 +407,30 @@ DLGO_EXPORT int dlgo_argmax_host(const float* logits, int R, int ld, int V, int*
   return (int)cudaStreamSynchronize(stream);
 }
 
-// Greedy decoding of one batch for up to `max_steps` steps without returning to the caller: every
-// step copies its inputs (ids, positions, slots: `host_inputs`, pinned, [3][B]) to the device, launches
-// the captured step, takes each row's first maximum and brings the ids back (`host_ids`, pinned, [B]);
-// the ids become the next step's inputs at positions + 1.  Stops after the step in which a sequence
-// chose one of `stop_ids`.  The ids of step s go to out_tokens[s * B ...]; returns the number of steps
-// run (>= 1), or minus a CUDA error code.  (The reference's loop is compiled code too:
-// models/llm/generate.go:207-283.)
-DLGO_EXPORT int dlgo_greedy_run(void* dev_inputs, int* host_inputs, int B, void* graph_exec, const float* logits,
-                                int ld, int V, int* out_dev, float* part_v, int* part_i, int* host_ids,
-                                const int* stop_ids, int n_stop, int max_steps, int* out_tokens,
-                                cudaStream_t stream) {
+// Greedy decoding of one batch for up to `max_steps` steps without returning to the caller.  The
+// captured step (`graph_exec`) ends with the argmax and the copy of the chosen ids into `host_ids`
+// (pinned, [B]); a step here is the copy of its inputs (ids, positions, slots: `host_inputs`, pinned,
+// [3][B]) to the device, one graph launch and a wait.  The ids become the next step's inputs at
+// positions + 1.  Stops after the step in which a sequence chose one of `stop_ids`.  The ids of step s
+// go to out_tokens[s * B ...]; returns the number of steps run (>= 1), or minus a CUDA error code.
+// (The reference's loop is compiled code too: models/llm/generate.go:207-283.)
+DLGO_EXPORT int dlgo_greedy_run_graph(void* dev_inputs, int* host_inputs, int B, void* graph_exec,
+                                      const int* host_ids, const int* stop_ids, int n_stop, int max_steps,
+                                      int* out_tokens, cudaStream_t stream) {
   if (B <= 0 || max_steps <= 0) return 0;
   for (int step = 0; step < max_steps; ++step) {
     cudaError_t e = cudaMemcpyAsync(dev_inputs, host_inputs, sizeof(int) * 3 * (size_t)B, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return -(int)e;
     e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, stream);
     if (e != cudaSuccess) return -(int)e;
-    int st = dlgo_argmax(logits, B, ld, V, out_dev, part_v, part_i, stream);
-    if (st != DLGO_OK) return st < 0 ? st : -st;
-    e = cudaMemcpyAsync(host_ids, out_dev, sizeof(int) * (size_t)B, cudaMemcpyDeviceToHost, stream);
-    if (e != cudaSuccess) return -(int)e;
     e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return -(int)e;
     bool stop = false;
     for (int b = 0; b < B; ++b) {
-      const int id = host_ids[b];
+      const int id = ((const volatile int*)host_ids)[b];
       out_tokens[(size_t)step * B + b] = id;
       for (int k = 0; k < n_stop; ++k) stop |= stop_ids[k] == id;
-      host_inputs[b] = id;          // next step: this id at the next position
+      host_inputs[b] = id;
       host_inputs[B + b] += 1;
     }
     if (stop) return step + 1;

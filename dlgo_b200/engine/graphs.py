@@ -40,6 +40,13 @@ class DecodeGraph:
         # copy of the inputs, "buffer free" event and graph launch as one native call (csrc/hoststep.cu)
         self._native = kernels.HostStep()
         self._exec = None
+        # a second capture of the same step that ends with the argmax and the copy of the ids into pinned
+        # memory, for greedy runs (made when first asked for)
+        self.greedy_graph = None
+        self.greedy_exec = None
+        self.greedy_kernels = 0
+        self.ids_dev = torch.zeros((batch,), dtype=torch.int32, device=dev)
+        self.ids_host = torch.zeros((batch,), dtype=torch.int32).pin_memory()
 
     def capture(self) -> None:
         eng = self.engine
@@ -55,6 +62,18 @@ class DecodeGraph:
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
         self.kernels_per_replay = kernels.LAUNCHES - before
         self._exec = self.graph.raw_cuda_graph_exec()
+
+    def capture_greedy(self) -> None:
+        eng = self.engine
+        torch.cuda.synchronize()
+        before = kernels.LAUNCHES
+        self.greedy_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.greedy_graph):
+            logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+            kernels.argmax(logits, self.ids_dev)
+            self.ids_host.copy_(self.ids_dev, non_blocking=True)
+        self.greedy_kernels = kernels.LAUNCHES - before
+        self.greedy_exec = self.greedy_graph.raw_cuda_graph_exec()
 
     def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
         self._native.wait()      # the previous step's copy out of the pinned buffer has finished
@@ -76,14 +95,15 @@ def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
     if g is None:
         decode_with_graph(engine, slots, token_ids, starts)    # captures (and runs the first step once, harmlessly)
         g = engine._graphs[b]
+    if g.greedy_exec is None:
+        g.capture_greedy()
     g._native.wait()
     h = g.host_np
     h[0, :] = token_ids
     h[1, :] = starts
     h[2, :] = slots
-    out = kernels.greedy_run(g.meta, g.host, g._exec, g.logits, stop_ids, n_steps, g._dev_index)
-    kernels.LAUNCHES += g.kernels_per_replay * len(out)
-    return out
+    return kernels.greedy_run_graph(g.meta, g.host, g.greedy_exec, g.ids_host, stop_ids, n_steps, g._dev_index,
+                                    g.greedy_kernels)
 
 
 def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
