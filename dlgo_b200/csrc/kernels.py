@@ -285,10 +285,11 @@ def argmax_to_host(logits: torch.Tensor) -> list:
     return host_np.tolist()
 
 
-def greedy_run_graph(dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_exec: int, host_ids: torch.Tensor,
+def greedy_run_graph(host_inputs: torch.Tensor, graph_exec: int, host_ids: torch.Tensor,
                      stop_ids: Sequence[int], max_steps: int, device_index: int, launches_per_step: int) -> List[List[int]]:
     """Up to ``max_steps`` greedy decode steps of one batch in one native call (dlgo_greedy_run_graph).
-    The captured step ends with the argmax and the copy of the ids into ``host_ids`` (pinned int32 [B]);
+    The captured step begins with the copy of its inputs out of ``host_inputs`` and ends with the argmax
+    and the copy of the ids into ``host_ids`` (pinned int32 [B]);
     ``host_inputs`` (pinned int32 [3, B]: ids, positions, slots) holds the first step's inputs and is
     advanced in place.  Returns the ids chosen, a list per step, ending with the step in which a
     sequence chose a stop id."""
@@ -297,7 +298,7 @@ def greedy_run_graph(dev_inputs: torch.Tensor, host_inputs: torch.Tensor, graph_
     stops = np.asarray(sorted(int(t) for t in stop_ids), dtype=np.int32)
     tokens = np.empty((max_steps, B), dtype=np.int32)
     n = _lib("sampling").dlgo_greedy_run_graph(
-        _ptr(dev_inputs), ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec),
+        ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec),
         ctypes.c_void_p(host_ids.data_ptr()), stops.ctypes.data_as(ctypes.c_void_p), _i(len(stops)), _i(max_steps),
         tokens.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device_index)))
     if n <= 0:

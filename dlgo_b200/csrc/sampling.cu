@@ -408,20 +408,18 @@ DLGO_EXPORT int dlgo_argmax_host(const float* logits, int R, int ld, int V, int*
 }
 
 // Greedy decoding of one batch for up to `max_steps` steps without returning to the caller.  The
-// captured step (`graph_exec`) ends with the argmax and the copy of the chosen ids into `host_ids`
-// (pinned, [B]); a step here is the copy of its inputs (ids, positions, slots: `host_inputs`, pinned,
-// [3][B]) to the device, one graph launch and a wait.  The ids become the next step's inputs at
+// captured step (`graph_exec`) begins with the copy of its inputs (ids, positions, slots: `host_inputs`,
+// pinned, [3][B]) to the device and ends with the argmax and the copy of the chosen ids into `host_ids`
+// (pinned, [B]); a step here is one graph launch and a wait.  The ids become the next step's inputs at
 // positions + 1.  Stops after the step in which a sequence chose one of `stop_ids`.  The ids of step s
 // go to out_tokens[s * B ...]; returns the number of steps run (>= 1), or minus a CUDA error code.
 // (The reference's loop is compiled code too: models/llm/generate.go:207-283.)
-DLGO_EXPORT int dlgo_greedy_run_graph(void* dev_inputs, int* host_inputs, int B, void* graph_exec,
+DLGO_EXPORT int dlgo_greedy_run_graph(int* host_inputs, int B, void* graph_exec,
                                       const int* host_ids, const int* stop_ids, int n_stop, int max_steps,
                                       int* out_tokens, cudaStream_t stream) {
   if (B <= 0 || max_steps <= 0) return 0;
   for (int step = 0; step < max_steps; ++step) {
-    cudaError_t e = cudaMemcpyAsync(dev_inputs, host_inputs, sizeof(int) * 3 * (size_t)B, cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return -(int)e;
-    e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, stream);
+    cudaError_t e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, stream);
     if (e != cudaSuccess) return -(int)e;
     e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return -(int)e;

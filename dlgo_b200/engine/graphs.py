@@ -40,8 +40,9 @@ class DecodeGraph:
         # copy of the inputs, "buffer free" event and graph launch as one native call (csrc/hoststep.cu)
         self._native = kernels.HostStep()
         self._exec = None
-        # a second capture of the same step that ends with the argmax and the copy of the ids into pinned
-        # memory, for greedy runs (made when first asked for)
+        # a second capture of the same step that begins with the copy of its inputs out of the pinned buffer
+        # and ends with the argmax and the copy of the ids into pinned memory, for greedy runs (made when
+        # first asked for)
         self.greedy_graph = None
         self.greedy_exec = None
         self.greedy_kernels = 0
@@ -69,6 +70,7 @@ class DecodeGraph:
         before = kernels.LAUNCHES
         self.greedy_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.greedy_graph):
+            self.meta.copy_(self.host, non_blocking=True)      # the step's inputs out of the pinned buffer
             logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
             kernels.argmax(logits, self.ids_dev)
             self.ids_host.copy_(self.ids_dev, non_blocking=True)
@@ -102,7 +104,7 @@ def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
     h[0, :] = token_ids
     h[1, :] = starts
     h[2, :] = slots
-    return kernels.greedy_run_graph(g.meta, g.host, g.greedy_exec, g.ids_host, stop_ids, n_steps, g._dev_index,
+    return kernels.greedy_run_graph(g.host, g.greedy_exec, g.ids_host, stop_ids, n_steps, g._dev_index,
                                     g.greedy_kernels)
 
 
