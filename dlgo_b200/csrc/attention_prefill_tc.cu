@@ -54,6 +54,26 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Diagnostic build: cycles of the first softmax thread per phase, summed over the key blocks of a tile
+// (slot 0..6: wait for scores, read them, maximum, wait for P V, rescale, exponentials and P, hand-over;
+// slot 7: key blocks)
+#ifdef DLGO_TIMING
+#define PF_CLK_DECL long long clk_sum[7] = {0, 0, 0, 0, 0, 0, 0}; long long clk_t = clock64()
+#define PF_CLK(k) do { const long long n_ = clock64(); clk_sum[k] += n_ - clk_t; clk_t = n_; } while (0)
+#define PF_CLK_WRITE(nblk)                                                        \
+  do {                                                                            \
+    const int c_ = blockIdx.y * gridDim.x + blockIdx.x;                           \
+    if (threadIdx.x == 64 && c_ < 1024) {                                         \
+      for (int k_ = 0; k_ < 7; ++k_) g_times[c_ * 8 + k_] = (unsigned long long)clk_sum[k_]; \
+      g_times[c_ * 8 + 7] = (unsigned long long)(nblk);                           \
+    }                                                                             \
+  } while (0)
+#else
+#define PF_CLK_DECL do {} while (0)
+#define PF_CLK(k) do {} while (0)
+#define PF_CLK_WRITE(nblk) do {} while (0)
+#endif
+
 // MN-major operand (rows of 128 bytes = 64 contiguous N elements, 8 K-rows per 1024-byte group),
 // 128-byte swizzle; `lbo_bytes` is the distance between 64-element N blocks.
 __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
@@ -91,16 +111,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* qfull = bars;          // 1
   uint64_t* kfull = bars + 1;      // 2
   uint64_t* vfull = bars + 3;      // 2
-  uint64_t* kvempty = bars + 5;    // 2
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 9;     // P of a block is written, its scores are read, O is rescaled if need be
-  uint64_t* o_full = bars + 10;    // the last block's P V has completed
-  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  uint64_t* kempty = bars + 5;     // 2: the scores that read this stage's keys have completed
+  uint64_t* vempty = bars + 7;     // 2: the P V that read this stage's values has completed
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_free = bars + 10;    // the scores of a block are in registers: the next block's may overwrite them
+  uint64_t* p_full = bars + 11;    // P of a block is written and O is rescaled if need be
+  uint64_t* pv_done = bars + 12;   // a block's P V has completed: P may be overwritten, O touched
+  uint32_t* tmem_slot = (uint32_t*)(bars + 14);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;   // heads fastest: the heads of a group, which read the same keys, start together
   const int G = p.Hq / p.Hkv;
   const int kvh = head / G;
 
@@ -109,11 +131,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kfull[s], 1);
       mbar_init(&vfull[s], 1);
-      mbar_init(&kvempty[s], 1);
+      mbar_init(&kempty[s], 1);
+      mbar_init(&vempty[s], 1);
     }
     mbar_init(s_full, 1);
+    mbar_init(s_free, 4);
     mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
+    mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -130,7 +154,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
 
   pdl_wait();
-  const int tile = gridDim.x - 1 - blockIdx.x;   // later tiles of a prompt see more keys: start them first
+  const int tile = blockIdx.y;   // in table order: the caller lists the tiles that see most keys first
   const int seq = p.tiles[3 * tile], tok0 = p.tiles[3 * tile + 1], ntok = p.tiles[3 * tile + 2];
   const int slot = p.seq_slot[seq];
   const int pos0 = p.token_pos[tok0];
@@ -145,20 +169,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (elect_one()) {
       mbar_expect_tx(qfull, QBYTES);
       for (int j = 0; j < NCH; ++j) tma_load_2d(q_s + j * 16384, &map_q, qfull, head * HD + j * 64, tok0);
-      for (int it = 0; it < nblk; ++it) {
-        const int st = it & 1;
-        if (it >= 2 && !mbar_wait(&kvempty[st], ((it >> 1) - 1) & 1, abort_flag)) break;
+      // keys run one block ahead of values: a stage's keys are free once their scores have completed,
+      // its values only after the P V that follows a whole softmax later
+      auto page_of = [&](int it) {
         const int pg = kb_first + it;
-        const int page = (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
+        return (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
+      };
+      auto load_k = [&](int it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(&kempty[st], ((it >> 1) - 1) & 1, abort_flag)) return false;
+        const int page = page_of(it);
         mbar_expect_tx(&kfull[st], page >= 0 ? NCH * 8192 : 0);
+        if (page >= 0)
+          for (int j = 0; j < NCH; ++j)
+            tma_load_2d(k_s + st * KVBYTES + j * 8192, &map_k, &kfull[st], j * 64, (page * p.Hkv + kvh) * 64);
+        return true;
+      };
+      auto load_v = [&](int it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(&vempty[st], ((it >> 1) - 1) & 1, abort_flag)) return false;
+        const int page = page_of(it);
         mbar_expect_tx(&vfull[st], page >= 0 ? NCH * 8192 : 0);
-        if (page >= 0) {
-          const int row = (page * p.Hkv + kvh) * 64;
-          for (int j = 0; j < NCH; ++j) {
-            tma_load_2d(k_s + st * KVBYTES + j * 8192, &map_k, &kfull[st], j * 64, row);
-            tma_load_2d(v_s + st * KVBYTES + j * 8192, &map_v, &vfull[st], j * 64, row);
-          }
-        }
+        if (page >= 0)
+          for (int j = 0; j < NCH; ++j)
+            tma_load_2d(v_s + st * KVBYTES + j * 8192, &map_v, &vfull[st], j * 64, (page * p.Hkv + kvh) * 64);
+        return true;
+      };
+      bool ok = load_k(0);
+      for (int it = 0; ok && it < nblk; ++it) {
+        if (it + 1 < nblk) ok = load_k(it + 1);
+        if (ok) ok = load_v(it);
       }
     }
   } else if (warp == 1) {
@@ -178,21 +218,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                       umma_desc_k_sw128(k_addr + j * 8192) + 2 * k, idesc_s, (j | k) != 0);
         umma_commit(s_full);
       }
+      if (ok) umma_commit(&kempty[0]);
       for (int it = 0; ok && it < nblk; ++it) {
         const int st = it & 1;
-        ok = mbar_wait(p_full, it & 1, abort_flag) && mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(v_s + st * KVBYTES);
-#pragma unroll
-        for (int kk = 0; kk < PF_KEYS / 16; ++kk)
-          umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr) + 2 * kk,
-                    umma_desc_mn_sw128(v_addr + kk * 2048, 8192), idesc_o, (it | kk) != 0);
-        umma_commit(&kvempty[st]);
         if (it + 1 < nblk) {
-          // the scores of block it have been read (p_full says so): the next block's may overwrite them
+          // the next block's scores as soon as this block's are in registers: they are computed while
+          // the softmax threads work on this block
           const int st2 = (it + 1) & 1;
-          ok = mbar_wait(&kfull[st2], ((it + 1) >> 1) & 1, abort_flag);
+          ok = mbar_wait(s_free, it & 1, abort_flag) && mbar_wait(&kfull[st2], ((it + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t k_addr = smem_u32(k_s + st2 * KVBYTES);
@@ -202,12 +235,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int k = 0; k < 4; ++k)
               umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + j * 16384) + 2 * k,
                         umma_desc_k_sw128(k_addr + j * 8192) + 2 * k, idesc_s, (j | k) != 0);
-          // completes after everything issued before it, P V of block it included: whoever sees the
-          // next scores may also overwrite P and touch O
           umma_commit(s_full);
-        } else {
-          umma_commit(o_full);
+          umma_commit(&kempty[st2]);
         }
+        ok = mbar_wait(p_full, it & 1, abort_flag) && mbar_wait(&vfull[st], (it >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(v_s + st * KVBYTES);
+#pragma unroll
+        for (int kk = 0; kk < PF_KEYS / 16; ++kk)
+          umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr) + 2 * kk,
+                    umma_desc_mn_sw128(v_addr + kk * 2048, 8192), idesc_o, (it | kk) != 0);
+        umma_commit(&vempty[st]);
+        umma_commit(pv_done);
       }
     }
   } else {
@@ -217,9 +257,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     float m = -INFINITY, l = 0.f;                 // reference maximum (lazy) and sum against it
     bool ok = true;
+    PF_CLK_DECL;
     for (int it = 0; ok && it < nblk; ++it) {
       const int st = it & 1;
       const int k0 = (kb_first + it) * PF_KEYS;
+      PF_CLK(6);
       // value rows of keys that were never written, or whose page was not loaded, must be zero
       {
         const int t = k0 + r;                      // threads 0..63 stand for the stage's key rows
@@ -232,15 +274,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(row + j * 8192 + c * 16) = make_uint4(0, 0, 0, 0);
         }
       }
-      // the scores of this block; their barrier also tells that every earlier MMA has completed
-      // (P V of the block before included), so P may be overwritten and O touched
+      // the scores of this block, into registers; then the tensor core may write the next block's
       if (ok) ok = mbar_wait(s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      PF_CLK(0);
       float v[PF_KEYS];
 #pragma unroll
       for (int c0 = 0; c0 < PF_KEYS; c0 += 32) tmem_ld_32x32(lane_addr + c0, v + c0);
       tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      PF_CLK(1);
       const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
       // blocks that lie wholly inside every row's range need no mask (all but the diagonal ones)
       const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && (p.window <= 0 || k0 > pos0 + ntok - 1 - p.window);
@@ -264,6 +310,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // it by more than 8 (a factor of 256); tensor-memory accesses are warp-wide, so the warp goes
       // through the rescaling together and rows that need none multiply by one.
       const bool move = mx > m + 8.0f || (m == -INFINITY && mx > -INFINITY);
+      // P of the block before must have been consumed, and O be at rest, before either is touched
+      // (its P V was issued when this iteration began: it has completed by now as a rule)
+      PF_CLK(2);
+      if (it > 0) {
+        ok = mbar_wait(pv_done, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      PF_CLK(3);
       if (__any_sync(0xffffffffu, move)) {
         const float corr = move ? ((m == -INFINITY) ? 0.f : fast_exp2(m - mx)) : 1.0f;
         if (move) {
@@ -283,6 +338,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tmem_st_wait();
         }
       }
+      PF_CLK(4);
       const float mref = (m == -INFINITY) ? 0.f : m;
       // probabilities, their sum, and P as bf16 in the swizzled K-major layout
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -302,13 +358,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      PF_CLK(5);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P (and zeroed V rows) -> tensor core
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);   // one arrival per warp stands for its 32 rows
     }
+    PF_CLK_WRITE(nblk);
     // the finished output: out of tensor memory once, divided by the sum
-    if (ok) ok = mbar_wait(o_full, 0, abort_flag);
+    if (ok) ok = mbar_wait(pv_done, (nblk - 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.0f / l;
@@ -397,7 +455,7 @@ int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
                            (int)cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  launch_kernel(attention_prefill_tc_kernel<HD>, dim3(n_tiles, p.Hq), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
+  launch_kernel(attention_prefill_tc_kernel<HD>, dim3(p.Hq, n_tiles), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
   return launch_status();
 }
 
@@ -415,6 +473,7 @@ DLGO_EXPORT int dlgo_attention_prefill_tc(const void* q, int T, int ldq, const v
                                           int n_tiles, const int* seq_slot, const int* token_pos, void* out, int ldo,
                                           int Hq, int Hkv, int hd, int window, float scale, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return DLGO_OK;
+  if (n_tiles > 65535) return DLGO_ERR_SIZE;   // tiles are the grid's second dimension
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || !(hd == 64 || hd == 128) || Hq > 65535) return DLGO_ERR_SIZE;
   if (ldo % 8 || ((uintptr_t)out & 15)) return DLGO_ERR_ALIGN;
   CUtensorMap mq, mk, mv;
@@ -438,3 +497,5 @@ DLGO_EXPORT int dlgo_attention_tc_error() {
   if (v) cudaMemcpyToSymbol(g_attention_tc_error, &zero, sizeof(int));
   return v;
 }
+
+DLGO_TIMES_EXPORT

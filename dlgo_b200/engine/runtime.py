@@ -83,27 +83,33 @@ class StepContext:
     capacity: int = 0            # longest sequence the cache can hold
     want_identity: bool = False  # the wanted rows are exactly rows 0..T-1, each once
     pending: Optional[torch.Tensor] = None   # fp32 [slices, T, d] still to be added to the residual stream
-    _tiles: Dict[int, Tuple[torch.Tensor, int, int]] = field(default_factory=dict)
+    _tiles: Dict[Tuple[int, bool], Tuple[torch.Tensor, int, int]] = field(default_factory=dict)
     _scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
 
-    def tiles(self, tokens_per_tile: int) -> Tuple[torch.Tensor, int, int]:
+    def tiles(self, tokens_per_tile: int, heaviest_first: bool = False) -> Tuple[torch.Tensor, int, int]:
         """Tiles of at most ``tokens_per_tile`` consecutive tokens of one sequence:
-        (device tensor [n, 3] of (sequence, first token, count), n, largest count)."""
-        hit = self._tiles.get(tokens_per_tile)
+        (device tensor [n, 3] of (sequence, first token, count), n, largest count).  In the order of the
+        tokens, or with ``heaviest_first`` by the number of keys a tile's last token sees, most first
+        (a causal kernel whose blocks start in table order then ends with its short tiles)."""
+        hit = self._tiles.get((tokens_per_tile, heaviest_first))
         if hit is not None:
             return hit
         rows: List[Tuple[int, int, int]] = []
+        ends: List[int] = []
         off = 0
         biggest = 1
         for i, n in enumerate(self.seq_ntok_host):
             for b in range(0, n, tokens_per_tile):
                 c = min(tokens_per_tile, n - b)
                 rows.append((i, off + b, c))
+                ends.append(self.seq_start_host[i] + b + c)
                 biggest = max(biggest, c)
             off += n
+        if heaviest_first:
+            rows = [rows[j] for j in sorted(range(len(rows)), key=lambda j: -ends[j])]
         t = torch.tensor(rows, dtype=torch.int32).to(self.runtime.device, non_blocking=True)
-        self._tiles[tokens_per_tile] = (t, len(rows), biggest)
-        return self._tiles[tokens_per_tile]
+        self._tiles[(tokens_per_tile, heaviest_first)] = (t, len(rows), biggest)
+        return self._tiles[(tokens_per_tile, heaviest_first)]
 
     def scratch(self, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """A scratch buffer that lives for the step (shared by the layers, which run one after another)."""

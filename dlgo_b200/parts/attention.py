@@ -160,7 +160,7 @@ class GQAAttention(Mixer):
                                    self.window or 0, n_splits, scratch, counters)
         elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
             # prompts: 128 query rows per CTA on the tensor cores
-            tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE)
+            tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
             K.attention_prefill_tc(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles,
                                    ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
                                    self.head_dim, self.scale, self.window or 0)
