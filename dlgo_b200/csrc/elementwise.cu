@@ -52,14 +52,21 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float scale_s;
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * d;   // (`rows` is an input of the step, not a result)
   TO* o = out + (size_t)r * d;
   constexpr int KEEP = 4;   // float4s of the row a thread keeps in registers between the two passes
   if ((d & 3) == 0 && d <= (int)blockDim.x * 4 * KEEP) {
+    // the weight is nobody's output: it is fetched before the wait for the predecessor
+    float4 ww[KEEP];
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = (threadIdx.x + j * blockDim.x) * 4;
+      ww[j] = i < d ? __ldg(reinterpret_cast<const float4*>(w + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
     // the row is read once, 16 bytes at a time, and stays in registers for the second pass
     float4 v[KEEP];
     float ss = 0.f;
@@ -79,13 +86,12 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 #pragma unroll
     for (int j = 0; j < KEEP; ++j) {
       const int i = (threadIdx.x + j * blockDim.x) * 4;
-      if (i < d) {
-        const float4 ww = *reinterpret_cast<const float4*>(w + i);
-        store4<TO>(o + i, v[j].x * s * ww.x, v[j].y * s * ww.y, v[j].z * s * ww.z, v[j].w * s * ww.w);
-      }
+      if (i < d)
+        store4<TO>(o + i, v[j].x * s * ww[j].x, v[j].y * s * ww[j].y, v[j].z * s * ww[j].z, v[j].w * s * ww[j].w);
     }
     return;
   }
+  pdl_wait();
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = xr[i];

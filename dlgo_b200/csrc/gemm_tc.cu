@@ -20,6 +20,11 @@
 // (models/llm/forward.go:163,169), or SwiGLU (ops/activation.go:8-38) over a weight whose rows come
 // in blocks of 16 gate rows followed by their 16 up rows, writing h = silu(g) * u.
 //
+// Few tokens also have: partials (every K-slice leaves its fp32 tile for the reader to add), an atomic add
+// of every K-slice into an fp32 residual (no pass over partial results at all; the order of the adds,
+// hence the last bits of the sum, is not fixed), and B computed in the kernel as the RMSNorm
+// (ops/norm.go:10-32) of fp32 residual rows, which spares the norm its own launch.
+//
 // Split-K (decode): `splits` CTAs share an output tile.  Each writes its fp32 partial to a
 // workspace; the CTA that arrives last adds the partials in slice order (so the sum does not
 // depend on which one was last) and runs the epilogue.
@@ -32,7 +37,7 @@ namespace dlgo {
 
 using namespace sm100;
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4, TC_RED_F32 = 5 };
 
 constexpr int TILE_M = 128;
 constexpr int TILE_K = 64;  // 128 bytes of bf16: one swizzle row
@@ -57,6 +62,13 @@ struct TcParams {
   int cluster;        // > 1: that many consecutive K-slices are the CTAs of a thread-block cluster; their
                       // partial tiles meet in the first CTA through distributed shared memory, in slice
                       // order, and only it runs the epilogue (TC_PARTIAL: one slice per cluster)
+  // B as the RMSNorm of fp32 rows (few tokens, transposed): B[t, k] = bf16(x[t, k] * scale_t * w[k]) with
+  // scale_t = 1 / sqrt(mean_k x[t, k]^2 + eps); the epilogue warps compute it after the wait and write it
+  // into the ring's stages, no tile of B is loaded
+  const float* norm_x;  // [Rb, K] fp32, row stride norm_ld; null: B comes from memory as bf16
+  int norm_ld;
+  const float* norm_w;  // [K] fp32
+  float norm_eps;
 };
 
 template <int BN> struct TcConfig {
@@ -188,20 +200,101 @@ __device__ __forceinline__ uint8_t* staging_of(uint8_t* smem, int stages, int st
   return smem + stages * stage_bytes + 256;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+// The B operand of a few-token product as the RMSNorm of at most eight fp32 rows, by the four epilogue
+// warps (`q4` 0..3).  Every warp reads its rows whole (all loads of a pass in flight at once), reduces the
+// squares, and writes the normalised values of the CTA's K range as bf16 into `bres`: one K block of 64
+// after another, eight rows of 128 bytes each in the 128-byte swizzle, 1 KB per K block.  The tensor
+// core's tile has sixteen rows, so the tile of K block i is the 2 KB at i KB: its rows 8..15 are the next
+// K block's rows (finite numbers that land in output columns nobody stores), and behind the last K block
+// lies a kilobyte of zeros.  The operand stays in shared memory for the whole product: no stage of the
+// ring waits for it.  V float4 per lane and row (K <= 128 V), NR rows per pass, 8 = 4 NR PASSES rows.
+template <int V, int NR, int PASSES>
+__device__ __forceinline__ void norm_operand(const TcParams& p, uint8_t* bres, uint64_t* bready, int kb0, int kb1,
+                                             int tile_b, int q4, int lane) {
+  static_assert(4 * NR * PASSES == 8, "eight rows");
+  const int n4 = p.K >> 2;
+  if (q4 == 0) {
+    uint4* pad = reinterpret_cast<uint4*>(bres + (kb1 - kb0) * 1024);
+    pad[lane] = make_uint4(0u, 0u, 0u, 0u);
+    pad[lane + 32] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  float4 w4[PASSES == 1 ? V : 1];
+  if constexpr (PASSES == 1) {          // the norm's weight is nobody's output: before the wait
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int j = lane + 32 * i;
+      w4[i] = j < n4 ? __ldg(reinterpret_cast<const float4*>(p.norm_w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  pdl_wait();
+#pragma unroll
+  for (int m = 0; m < PASSES; ++m) {
+    float4 x[NR][V];
+#pragma unroll
+    for (int n = 0; n < NR; ++n) {
+      const int tok = tile_b * 16 + (m * 4 + q4) * NR + n;
+      const float4* row = reinterpret_cast<const float4*>(p.norm_x + (size_t)(tok < p.Rb ? tok : 0) * p.norm_ld);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const int j = lane + 32 * i;
+        x[n][i] = (tok < p.Rb && j < n4) ? __ldcg(row + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NR; ++n) {
+      const int t = (m * 4 + q4) * NR + n;       // row of the tile, 0..7
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        ss = fmaf(x[n][i].x, x[n][i].x, ss);
+        ss = fmaf(x[n][i].y, x[n][i].y, ss);
+        ss = fmaf(x[n][i].z, x[n][i].z, ss);
+        ss = fmaf(x[n][i].w, x[n][i].w, ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float sc = 1.0f / sqrtf(ss / (float)p.K + p.norm_eps);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const int j = lane + 32 * i;
+        const int col = 4 * j, kb = col >> 6;
+        if (kb < kb0 || kb >= kb1) continue;     // (columns past K in the last K block: x is zero there)
+        float4 w;
+        if constexpr (PASSES == 1) w = w4[i];
+        else w = j < n4 ? __ldg(reinterpret_cast<const float4*>(p.norm_w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        __nv_bfloat162 h[2] = {__floats2bfloat162_rn(x[n][i].x * sc * w.x, x[n][i].y * sc * w.y),
+                               __floats2bfloat162_rn(x[n][i].z * sc * w.z, x[n][i].w * sc * w.w)};
+        *reinterpret_cast<uint2*>(bres + (kb - kb0) * 1024 + t * 128 + ((((col & 63) >> 3) ^ t) << 4) +
+                                  ((col & 7) << 1)) = *reinterpret_cast<uint2*>(h);
+      }
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> the tensor core's reads
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bready);
+}
+
+// NORM: 0 B comes from memory; else B is a norm of at most 8 rows computed here: 1 rows of at most 2048,
+// 2 rows of at most 4096.  The ring's stages then hold A only.
+// (kernels of their own: the computed operand lives in registers that the plain kernel should not pay for,
+// since its successor shares the SM with it)
+template <int BN, int NORM>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p) {
   using C = TcConfig<BN>;
+  constexpr int STAGE = NORM != 0 ? C::A_BYTES : C::STAGE_BYTES;   // a computed B is not in the ring
   extern __shared__ uint8_t smem_raw[];
   // tiles want 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int STAGES = p.stages;  // ring size (<= 8): as many as the K range needs, fewer to let two CTAs share an SM
-  uint64_t* full = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE);
   uint64_t* empty = full + STAGES;
   uint64_t* accum = empty + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* last_flag = (int*)(tmem_slot + 2);
+  constexpr bool normed = NORM != 0;
+  uint64_t* bready = (uint64_t*)((uint8_t*)full + 192);          // the computed B is written (four warps)
+  uint8_t* bres = smem + ((STAGES * STAGE + 256 + 1023) & ~1023);  // the computed B, 1 KB per K block
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) TSTAMP(0);
@@ -219,6 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
+    mbar_init(bready, 4);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -239,9 +333,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // Weights do not depend on earlier kernels: their tiles for the first ring of stages are
       // requested before waiting for the predecessor, the activations' tiles after.
       const int npre = min(nkb, STAGES);
+      const uint32_t tx = STAGE;
       for (int i = 0; i < npre; ++i) {
-        uint8_t* a_dst = smem + i * C::STAGE_BYTES;
-        mbar_expect_tx(&full[i], C::STAGE_BYTES);
+        uint8_t* a_dst = smem + i * STAGE;
+        mbar_expect_tx(&full[i], tx);
         if (p.static_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
         if (p.static_operand == 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
       }
@@ -256,33 +351,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       pdl_wait();
       TSTAMP(2);
       for (int i = 0; i < npre; ++i) {
-        uint8_t* a_dst = smem + i * C::STAGE_BYTES;
+        uint8_t* a_dst = smem + i * STAGE;
         if (p.static_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
-        if (p.static_operand != 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
+        if (p.static_operand != 2 && !normed)
+          tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
       }
       for (int i = npre; i < nkb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+        uint8_t* a_dst = smem + s * STAGE;
         uint8_t* b_dst = a_dst + C::A_BYTES;
-        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        mbar_expect_tx(&full[s], tx);
         tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * TILE_K, tile_a * TILE_M);
-        tma_load_2d(b_dst, &map_b, &full[s], (kb0 + i) * TILE_K, tile_b * BN);
+        if (!normed) tma_load_2d(b_dst, &map_b, &full[s], (kb0 + i) * TILE_K, tile_b * BN);
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN < 16 ? 16 : BN);
-      for (int i = 0; i < nkb; ++i) {
+      bool b_ok = true;
+      if (normed && nkb > 0) b_ok = mbar_wait(bready, 0, abort_flag);
+      for (int i = 0; b_ok && i < nkb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
         if (i == 0) TSTAMP(3);
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+        const uint32_t a_addr = smem_u32(smem + s * STAGE);
         const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(a_addr + C::A_BYTES);
+        const uint64_t db = umma_desc_k_sw128(normed ? smem_u32(bres) + i * 1024 : a_addr + C::A_BYTES);
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           // inside a 128-byte swizzle row, the next K = 16 slice starts 32 bytes on (2 in 16-byte units)
@@ -297,7 +395,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // epilogue warps: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     const int row = tile_a * TILE_M + quarter * 32 + lane;
-    pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
+    if constexpr (NORM == 1) {
+      norm_operand<16, 2, 1>(p, bres, bready, kb0, kb1, tile_b, warp - 2, lane);
+    } else if constexpr (NORM == 2) {
+      norm_operand<32, 1, 2>(p, bres, bready, kb0, kb1, tile_b, warp - 2, lane);
+    } else {
+      pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
+    }
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(accum, 0, abort_flag);
     if (warp == 2 && lane == 0) TSTAMP(5);
@@ -312,7 +416,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // every owner adds the slices of its columns in slice order and writes them out.
       const uint32_t me = cluster_ctarank();
       const int cpr = (BN + p.cluster - 1) / p.cluster;
-      const uint32_t stage0 = smem_u32(staging_of(smem, STAGES, C::STAGE_BYTES));
+      const uint32_t stage0 = smem_u32(staging_of(smem, STAGES, STAGE));
       const int r_in = quarter * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += NV) {
@@ -355,6 +459,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < NV; ++j) {
             const int col = tile_b * BN + c0 + j;
             if (col < p.Rb) dst[(size_t)col * p.ldo + row] = v[j];
+          }
+        }
+      }
+    } else if (p.epilogue == TC_RED_F32) {
+      // every K-slice adds its tile into out[col][row] (fp32, transposed tiles only) with reductions at
+      // the memory: nothing is written and read again, and nobody has to come last
+      float* dst = (float*)p.out;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += NV) {
+        if (!(ok && nkb > 0)) break;
+        float v[NV];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+        tmem_ld_wait();
+        if (row < p.Ra) {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const int col = tile_b * BN + c0 + j;
+            if (col < p.Rb) atomicAdd(dst + (size_t)col * p.ldo + row, v[j]);
           }
         }
       }
@@ -471,7 +594,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = tile_a * TILE_M + r_in;
       const int me = (int)cluster_ctarank();
       const int cpr = (BN + p.cluster - 1) / p.cluster;
-      const float* stage = (const float*)staging_of(smem, STAGES, C::STAGE_BYTES);
+      const float* stage = (const float*)staging_of(smem, STAGES, STAGE);
       for (int k = 0; k < cpr; ++k) {
         const int col_in = me * cpr + k;
         const int col = tile_b * BN + col_in;
@@ -493,6 +616,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
+}
+
+template <int BN, int NORM>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ TcParams p) {
+  gemm_tc_body<BN, NORM>(map_a, map_b, p);
+}
+// The first norm variant (rows of at most 2048) under a register cap: 232 x 192 threads leave room
+// in the SM's register file for a CTA of the plain kernel, so that the product that follows can move in
+// and fetch its first weights while this one still runs.
+__global__ void __maxnreg__(232)
+gemm_tc_norm8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ TcParams p) {
+  gemm_tc_body<16, 1>(map_a, map_b, p);
+}
+template <int BN, int NORM> constexpr auto tc_kernel_of() {
+  if constexpr (BN == 16 && NORM == 1) return &gemm_tc_norm8_kernel;
+  else return &gemm_tc_kernel<BN, NORM>;
 }
 
 // Epilogue of the many-token kernels: one accumulator tile (128 rows x BN fp32 columns in tensor
@@ -911,13 +1053,14 @@ int make_out_map(CUtensorMap* m, const TcParams& p) {
   return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
 }
 
-template <int BN>
+template <int BN, int NORM = 0>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
   using C = TcConfig<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::smem_bytes(C::MAX_STAGES));   // (a cluster's staging fits: see below)
+    // (a cluster's staging fits: see below; a norm's weight, up to 4096 floats, lies behind the barriers)
+    cudaError_t e = cudaFuncSetAttribute(tc_kernel_of<BN, NORM>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         NORM ? 200 * 1024 : C::smem_bytes(C::MAX_STAGES));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -933,6 +1076,16 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
     static const int ring_kb = [] { const char* e = getenv("DLGO_TC_RING_KB"); return e ? atoi(e) : 110; }();
     while (stages > 2 && C::smem_bytes(stages) > ring_kb * 1024) --stages;
   }
+  // a computed B: stages of A only, and behind the barriers 1 KB of B per K block and a kilobyte of zeros
+  auto normed_bytes = [&](int st) { return 1024 + st * C::A_BYTES + 1024 + (per_split + 1) * 1024; };
+  if (NORM) {
+    // as deep a ring as still lets a CTA of the plain kernel (the product before or after) share the SM:
+    // 228 KB, less that CTA's ring and the kilobyte the system keeps per CTA; never under four stages
+    const int room = 228 * 1024 - (C::smem_bytes(stages) + 1024) - 1024;
+    stages = C::MAX_STAGES;
+    while (stages > 4 && normed_bytes(stages) > room) --stages;
+    if (normed_bytes(stages) > 200 * 1024) return DLGO_ERR_SIZE;
+  }
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   q.stages = stages;
   q.staged = 0;
@@ -944,11 +1097,14 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
     while (stages > 2 && C::smem_bytes(stages) + staging > 110 * 1024) --stages;
     if (C::smem_bytes(stages) + staging > C::smem_bytes(C::MAX_STAGES)) return DLGO_ERR_SIZE;
     q.stages = stages;
-    launch_kernel_cluster(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages) + staging, stream,
+    launch_kernel_cluster(tc_kernel_of<BN, NORM>(), dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages) + staging, stream,
                           dim3(1, 1, q.cluster), ma, mb, q);
     return launch_status();
   }
-  launch_kernel(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages), stream, ma, mb, q);
+  if ((NORM != 0) != (q.norm_x != nullptr)) return DLGO_ERR_SIZE;
+  if (NORM && (BN != 16 || !p.transposed || q.Rb > 8 || q.K > (NORM == 2 ? 4096 : 2048))) return DLGO_ERR_SIZE;
+  launch_kernel(tc_kernel_of<BN, NORM>(), dim3(grid), dim3(TC_THREADS),
+                NORM ? normed_bytes(stages) : C::smem_bytes(stages), stream, ma, mb, q);
   return launch_status();
 }
 
@@ -1018,7 +1174,8 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 
 // A[Ra, K] (row stride lda) and B[Rb, K] (row stride ldb) in bf16; out per `transposed` and `epilogue`
 // (0 store bf16, 1 store f32, 2 add into f32, 3 SwiGLU to bf16, 4 partials: out is fp32
-// [splits][Rb][ldo] and slice s writes out[s][col][row], transposed only); bn in {16, 32, 64, 128, 256}.
+// [splits][Rb][ldo] and slice s writes out[s][col][row], transposed only; 5 every K-slice adds itself into
+// f32 out atomically, transposed only, no workspace); bn in {16, 32, 64, 128, 256}.
 // static_operand: 1 if A, 2 if B holds weights that no kernel launched before this one writes (their
 // tiles are then requested before the kernel waits for its predecessor), else 0.
 // pair_tile: 0, or 128 / 256 to compute 256 x pair_tile tiles with pairs of CTAs (cta_group::2; many
@@ -1032,13 +1189,15 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
                              int* counters, int static_operand, int pair_tile, int cluster, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
-  if (epilogue < 0 || epilogue > 4) return DLGO_ERR_SIZE;
+  if (epilogue < 0 || epilogue > 5) return DLGO_ERR_SIZE;
   if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
-  if (epilogue == TC_PARTIAL && !transposed) return DLGO_ERR_SIZE;
+  if ((epilogue == TC_PARTIAL || epilogue == TC_RED_F32) && !transposed) return DLGO_ERR_SIZE;
   if (cluster < 0 || cluster > 8) return DLGO_ERR_SIZE;
-  if (cluster > 1 && (!transposed || splits % cluster || (epilogue != TC_PARTIAL && cluster != splits)))
+  if (cluster > 1 && (!transposed || splits % cluster || (epilogue != TC_PARTIAL && cluster != splits) ||
+                      epilogue == TC_RED_F32))
     return DLGO_ERR_SIZE;
-  if (splits > 1 && cluster <= 1 && epilogue != TC_PARTIAL && (workspace == nullptr || counters == nullptr))
+  if (splits > 1 && cluster <= 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32 &&
+      (workspace == nullptr || counters == nullptr))
     return DLGO_ERR_SIZE;
   if (epilogue == TC_SWIGLU) {
     const int weight_rows = transposed ? Ra : Rb;
@@ -1055,6 +1214,7 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
   p.cluster = cluster > 1 ? cluster : 1;
   p.l2_ahead = 0;
+  p.norm_x = nullptr; p.norm_ld = 0; p.norm_w = nullptr; p.norm_eps = 0.f;
   if (p.static_operand) {
     // DLGO_TC_L2_AHEAD_MB: at most that many MB of weights per launch are pulled into L2 ahead of
     // time.  Off by default: measured on a B200 it does not shorten a decode step (the CTAs of the
@@ -1088,6 +1248,34 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
     case 256: return launch_tc<256>(ma, mb, p, stream);
     default: return DLGO_ERR_SIZE;
   }
+}
+
+// The few-token product out^T = W[Ra, K] . norm(X)[Rb, K]^T with B computed in the kernel: the RMSNorm of
+// the fp32 rows X (row stride ldx floats) with weight norm_w[K] and eps, rounded to bf16 as a norm kernel
+// would have left it.  Rb <= 8 and K <= 4096.  Epilogues 0, 1, 3 with one
+// K-slice; 4 and 5 with any number.
+DLGO_EXPORT int dlgo_gemm_tc_normed(const void* W, int Ra, int lda, const float* X, int Rb, int ldx,
+                                    const float* norm_w, float eps, int K, void* out, int ldo, int epilogue,
+                                    int splits, cudaStream_t stream) {
+  if (Ra <= 0 || Rb <= 0) return DLGO_OK;
+  if (K <= 0 || K % 8 || lda < K || ldx < K || splits < 1 || splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
+  if (Rb > 8 || K > 4096) return DLGO_ERR_SIZE;
+  if (epilogue != TC_STORE && epilogue != TC_STORE_F32 && epilogue != TC_SWIGLU && epilogue != TC_PARTIAL &&
+      epilogue != TC_RED_F32)
+    return DLGO_ERR_SIZE;
+  if (splits > 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32) return DLGO_ERR_SIZE;
+  if (epilogue == TC_SWIGLU && Ra % 32) return DLGO_ERR_SIZE;
+  if (((uintptr_t)X & 15) != 0 || ((uintptr_t)norm_w & 15) != 0 || (ldx & 3) != 0) return DLGO_ERR_ALIGN;
+  CUtensorMap ma;
+  int st = make_map(&ma, W, Ra, K, lda, TILE_M);
+  if (st != DLGO_OK) return st;
+  TcParams p;
+  p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = 1; p.epilogue = epilogue;
+  p.splits = splits; p.workspace = nullptr; p.counters = nullptr;
+  p.static_operand = 1; p.cluster = 1; p.l2_ahead = 0;
+  p.norm_x = X; p.norm_ld = ldx; p.norm_w = norm_w; p.norm_eps = eps;
+  // (no tile of B is loaded: its map is not used)
+  return K <= 2048 ? launch_tc<16, 1>(ma, ma, p, stream) : launch_tc<16, 2>(ma, ma, p, stream);
 }
 
 // 1 if a kernel of this library gave up a bounded wait since the last call (clears the flag).

@@ -335,7 +335,7 @@ def uniform(seed: int, draw: torch.Tensor, request: torch.Tensor) -> torch.Tenso
 
 
 # ------------------------------------------------------- tensor-core contraction
-TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_PARTIAL = 0, 1, 2, 3, 4
+TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_PARTIAL, TC_RED_F32 = 0, 1, 2, 3, 4, 5
 TC_TILE_M, TC_TILE_K = 128, 64
 
 
@@ -358,8 +358,12 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
     ``cluster`` (2..8, dividing ``splits``; transposed only): that many consecutive K-slices are one
     thread-block cluster and meet through distributed shared memory instead of the workspace; partials
     then come as ``splits // cluster`` slices, every other epilogue needs ``cluster == splits``.
+    ``TC_RED_F32`` (transposed only): every K-slice adds itself into the fp32 ``out`` with reductions at the
+    memory; no workspace, and the order of the adds (the sum's last bits) is not fixed.
     """
     cluster = cluster if cluster > 1 else 1
+    if epilogue == TC_RED_F32 and (not transposed or cluster > 1):
+        raise KernelError("gemm_tc: the atomic add is for transposed products without clusters")
     if cluster > 1 and (not transposed or cluster > 8 or splits % cluster or
                         (epilogue != TC_PARTIAL and cluster != splits)):
         raise KernelError(f"gemm_tc: a cluster of {cluster} K-slices does not fit {splits} slices of this product")
@@ -373,7 +377,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         raise KernelError(f"gemm_tc: a has K={k}, b has K={k2}")
     if out.stride(-1) != 1:
         raise KernelError("gemm_tc: out must have unit inner stride")
-    if splits > 1 and cluster == 1 and epilogue != TC_PARTIAL:
+    if splits > 1 and cluster == 1 and epilogue not in (TC_PARTIAL, TC_RED_F32):
         need = gemm_tc_workspace_floats(ra, rb, bn, splits)
         tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
         if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
@@ -399,6 +403,48 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
                                       _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _i(pair_tile),
                                       _i(cluster), _stream())
     _check(st, "gemm_tc")
+    return out
+
+
+def gemm_tc_normed_takes(tokens: int, k: int) -> bool:
+    """Whether the few-token product can compute its activations as an RMSNorm of fp32 rows itself."""
+    return tokens <= 8 and k <= 4096
+
+
+def gemm_tc_normed(weight: torch.Tensor, x: torch.Tensor, norm_weight: torch.Tensor, eps: float, out: torch.Tensor,
+                   epilogue: int, splits: int = 1) -> torch.Tensor:
+    """``out^T = weight[Ra, K] . rmsnorm(x)[Rb, K]^T`` for few tokens, the norm (fp32 rows ``x``, fp32
+    ``norm_weight``, rounded to bfloat16) computed inside the product's kernel.  ``out`` as for
+    :func:`gemm_tc` with ``transposed``; more than one K-slice only with partials or the atomic add."""
+    if not weight.is_cuda or weight.dtype != torch.bfloat16 or weight.dim() != 2 or weight.stride(1) != 1:
+        raise KernelError("gemm_tc_normed: the weight must be a 2-D bfloat16 GPU tensor with unit inner stride")
+    ra, k = weight.shape
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != k or x.stride(1) != 1:
+        raise KernelError(f"gemm_tc_normed: x must be float32 [tokens, {k}] with unit inner stride")
+    rb = x.shape[0]
+    if not gemm_tc_normed_takes(rb, k):
+        raise KernelError(f"gemm_tc_normed: {rb} tokens of {k} are more than the kernel keeps in registers")
+    if norm_weight.dtype != torch.float32 or norm_weight.numel() != k or not norm_weight.is_contiguous():
+        raise KernelError(f"gemm_tc_normed: the norm's weight must be float32 [{k}]")
+    if splits > 1 and epilogue not in (TC_PARTIAL, TC_RED_F32):
+        raise KernelError("gemm_tc_normed: K-slices only with partials or the atomic add")
+    if epilogue == TC_PARTIAL:
+        if out.dim() != 3 or out.dtype != torch.float32 or tuple(out.shape) != (splits, rb, ra) or \
+                out.stride(2) != 1 or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
+            raise KernelError(f"gemm_tc_normed: partials go to a float32 [{splits}, {rb}, {ra}] tensor")
+        ldo = out.stride(1)
+    else:
+        want_shape = (rb, ra // 2) if epilogue == TC_SWIGLU else (rb, ra)
+        want_dtype = torch.bfloat16 if epilogue in (TC_STORE, TC_SWIGLU) else torch.float32
+        if epilogue not in (TC_STORE, TC_STORE_F32, TC_SWIGLU, TC_RED_F32):
+            raise KernelError(f"gemm_tc_normed: no epilogue {epilogue}")
+        if out.dim() != 2 or tuple(out.shape) != want_shape or out.dtype != want_dtype or out.stride(1) != 1:
+            raise KernelError(f"gemm_tc_normed: out must be {want_dtype} {list(want_shape)}")
+        ldo = out.stride(0)
+    st = _lib("gemm_tc").dlgo_gemm_tc_normed(_ptr(weight), _i(ra), _i(weight.stride(0)), _ptr(x), _i(rb),
+                                             _i(x.stride(0)), _ptr(norm_weight), ctypes.c_float(eps), _i(k),
+                                             _ptr(out), _i(ldo), _i(epilogue), _i(splits), _stream())
+    _check(st, "gemm_tc_normed")
     return out
 
 

@@ -41,6 +41,8 @@ _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the
 
 
 class GQAAttention(Mixer):
+    takes_deferred_norm = True   # its first contraction may compute the norm of the residual itself
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: Optional[int] = None, position_encoding: Optional[str] = "rope",
                  cache_group: str = "full"):
@@ -116,7 +118,7 @@ class GQAAttention(Mixer):
             ahead = 0
             if decode_kernel and qkv_parts is not None and _AHEAD_BYTES > 0:
                 # pages of keys and values per (sequence, kv head) to hint into L2 for the attention kernel
-                page_bytes = cache.page_size * self.head_dim * x.element_size()
+                page_bytes = cache.page_size * self.head_dim * self.wqkv.weight.element_size()
                 ahead = max(1, _AHEAD_BYTES // (2 * T * self.num_kv_heads * page_bytes))
             K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                           cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
@@ -177,7 +179,7 @@ class GQAAttention(Mixer):
             K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
                         ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
                         self.scale, self.window or 0, n_splits, gchunk, scratch)
-        parts = self.wo.partials(out) if hasattr(ctx, "defer") else None
+        parts = self.wo.partials(out, for_residual=True) if hasattr(ctx, "defer") else None
         if parts is not None:
             ctx.defer(residual, parts)      # the next norm adds the slices to the residual
         else:

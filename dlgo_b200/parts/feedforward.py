@@ -18,6 +18,8 @@ from .registry import FEED_FORWARDS
 
 
 class SwiGLU(FeedForward):
+    takes_deferred_norm = True   # its first contraction may compute the norm of the residual itself
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size)
         self.hidden_size = int(hidden_size)
@@ -47,12 +49,12 @@ class SwiGLU(FeedForward):
             self.w_gate_up = Linear(torch.cat([gate, up], dim=0), runtime)
         self.w_down = Linear(get("down_proj.weight"), runtime)
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
+    def forward(self, x: Any, residual: torch.Tensor, ctx: Any) -> None:
         if self.fused:
             h = self.w_gate_up(x)
         else:
             h = K.swiglu(self.w_gate_up(x, STORE))
-        parts = self.w_down.partials(h) if ctx is not None and hasattr(ctx, "defer") else None
+        parts = self.w_down.partials(h, for_residual=True) if ctx is not None and hasattr(ctx, "defer") else None
         if parts is not None:
             ctx.defer(residual, parts)      # the next norm adds the slices to the residual
         else:

@@ -36,6 +36,16 @@ MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
 # SM one by one while the previous kernel drains), which costs more than the cheaper reduction saves.
 CLUSTER_MAX = int(os.environ.get("DLGO_TC_CLUSTER", 1))
 
+# Few tokens: a contraction whose result goes into the residual stream adds its K-slices there with
+# reductions at the memory (bit 0; up to RED_MAX_TOKENS tokens) instead of leaving them for the norm's
+# kernel to add.  Measured on a B200 (Llama 3.2 1B sizes, tokens a second): 8.99K -> 9.90K at batch 8,
+# 1.19K -> 1.32K at batch 1, 45.8K -> 49.0K at batch 64.
+# Bit 1: a contraction that follows a norm computes the norm itself on its way in (at most 8 tokens),
+# which spares the norm's launch.  Off: every CTA then reads all rows of the residual, 148 times 64 KB out
+# of L2 at once, and that takes longer (3.5 us) than the norm's own kernel (8.75K against 9.85K at batch 8).
+NORM_IN_GEMM = int(os.environ.get("DLGO_NORM_IN_GEMM", 1))   # bit 0: the atomic add, bit 1: the norm
+RED_MAX_TOKENS = int(os.environ.get("DLGO_TC_RED_MAX_TOKENS", 64))
+
 _workspaces: Dict[int, List[torch.Tensor]] = {}
 _counters: Dict[int, torch.Tensor] = {}
 
@@ -86,8 +96,15 @@ class TensorCorePlan:
         self.n, self.k = weight.shape
         self.swiglu = swiglu
 
-    def __call__(self, x: torch.Tensor, epilogue: int, out: Optional[torch.Tensor]) -> torch.Tensor:
+    def takes_norm(self, x) -> bool:
+        """Whether this product computes the deferred norm ``x`` inside its kernel."""
+        return ((NORM_IN_GEMM & 2) != 0 and x.kind == "rmsnorm" and x.dtype == torch.bfloat16 and
+                x.residual.dtype == torch.float32 and x.residual.stride(1) == 1 and x.residual.stride(0) % 4 == 0 and
+                x.weight.dtype == torch.float32 and K.gemm_tc_normed_takes(x.shape[0], self.k))
+
+    def __call__(self, x, epilogue: int, out: Optional[torch.Tensor]) -> torch.Tensor:
         t = x.shape[0]
+        normed = not isinstance(x, torch.Tensor)
         if self.swiglu:
             epi = K.TC_SWIGLU
             if out is None:
@@ -99,8 +116,18 @@ class TensorCorePlan:
                     raise K.KernelError("the add epilogue needs the tensor to add into")
                 out = torch.empty((t, self.n), dtype=torch.bfloat16 if epilogue == K.EPI_STORE else torch.float32,
                                   device=x.device)
+        if normed:
+            # one K-slice unless the epilogue can take several (the atomic add)
+            _, splits = skinny_shape(t, self.n, self.k)
+            if epi == K.TC_ADD_F32:
+                epi = K.TC_RED_F32
+            elif epi != K.TC_RED_F32:
+                splits = 1
+            return K.gemm_tc_normed(self.weight, x.residual, x.weight, x.eps, out, epi, splits)
         if t <= SKINNY_MAX:
             bn, splits = skinny_shape(t, self.n, self.k)
+            if (NORM_IN_GEMM & 1) and epi == K.TC_ADD_F32 and splits > 1 and t <= RED_MAX_TOKENS:
+                return K.gemm_tc(self.weight, x, out, True, K.TC_RED_F32, bn, splits, static_operand=1)
             splits, cluster = clustered(splits, True)
             ws = cnt = None
             if splits > 1 and cluster == 1:
@@ -114,16 +141,25 @@ class TensorCorePlan:
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
 
-    def partials(self, x: torch.Tensor, single_ok: bool = True) -> Optional[torch.Tensor]:
+    def partials(self, x, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
         reads the result next adds them in order (this spares the contraction a reduction pass through
         memory; slices of one thread-block cluster are summed on chip and come as one).
         ``None`` when the tokens are too many for that, or, unless ``single_ok``, when there would be
-        one slice only (the caller then asks for the finished product in the type it wants)."""
+        one slice only (the caller then asks for the finished product in the type it wants), or, with
+        ``for_residual``, when the add epilogue would add the slices into the residual by itself."""
         t = x.shape[0]
         if t > SKINNY_MAX or self.swiglu:
             return None
+        if for_residual and (NORM_IN_GEMM & 1) and t <= RED_MAX_TOKENS:
+            return None                     # the caller's add epilogue adds the slices into the residual
         bn, splits = skinny_shape(t, self.n, self.k)
+        if not isinstance(x, torch.Tensor):
+            # a deferred norm, computed by the kernel
+            if splits == 1 and not single_ok:
+                return None
+            out = torch.empty((splits, t, self.n), dtype=torch.float32, device=x.device)
+            return K.gemm_tc_normed(self.weight, x.residual, x.weight, x.eps, out, K.TC_PARTIAL, splits)
         splits, cluster = clustered(splits, False)
         if splits == cluster and not single_ok:
             return None

@@ -665,6 +665,90 @@ def test_gemm_tc_split_k_is_exact_and_repeatable(N, T_, K_, splits):
     k.check_device_errors()
 
 
+@pytest.mark.parametrize("N,T_,K_,splits", [(384, 8, 2048, 8), (130, 13, 200, 3), (2048, 40, 8192, 9), (128, 1, 640, 10)])
+def test_gemm_tc_k_slices_add_themselves_into_the_residual(N, T_, K_, splits):
+    """Every K-slice adds its tile into the fp32 target with reductions at the memory: the sum of all, in
+    an order that is not fixed (so compared with a tolerance of fp32 rounding, not bit for bit)."""
+    k = K()
+    g = torch.Generator().manual_seed(N + T_)
+    w = torch.randn(N, K_, generator=g).to(torch.bfloat16).to(DEV)
+    x = torch.randn(T_, K_, generator=g).to(torch.bfloat16).to(DEV)
+    bn = 16 if T_ <= 16 else (32 if T_ <= 32 else 64)
+    ref = _tc_ref(x, w).float()
+    res = torch.randn(T_, N, generator=g).to(DEV)
+    acc = res.clone()
+    k.gemm_tc(w, x, acc, True, k.TC_RED_F32, bn, splits, static_operand=1)
+    torch.testing.assert_close(acc, res + ref, atol=1e-4 * math.sqrt(K_), rtol=1e-5)
+    k.check_device_errors()
+
+
+def _normed_ref(x, nw, eps):
+    """RMSNorm of fp32 rows (ops/norm.go:10-32), rounded to bfloat16 as the norm kernel leaves it."""
+    xd = x.double()
+    return (xd * (1.0 / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps)) * nw.double()).float().to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("N,T_,K_,splits,epi", [
+    (3072, 8, 2048, 6, "partial"), (256, 3, 2048, 1, "store"), (16384, 8, 2048, 1, "swiglu"), (200, 7, 520, 2, "red"),
+    (512, 5, 4096, 4, "red"), (640, 8, 1096, 3, "partial"), (130, 1, 72, 1, "f32"), (4096, 8, 3072, 4, "partial"),
+    (1024, 6, 4096, 1, "swiglu")])
+def test_gemm_tc_computes_the_norm_of_its_activations_itself(N, T_, K_, splits, epi):
+    """The few-token product with B = RMSNorm(fp32 rows) computed in the kernel, against the product of the
+    separately normed, bfloat16-rounded rows.  Rows differ in scale by orders of magnitude, and one row
+    has a single large element, so a wrong or shared sum of squares shows."""
+    k = K()
+    g = torch.Generator().manual_seed(N + T_ + K_)
+    w = (torch.randn(N, K_, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    x = torch.randn(T_, K_, generator=g) * (10.0 ** torch.arange(T_).remainder(5).sub(2).float()).view(T_, 1)
+    x[T_ // 2, K_ - 1] = 300.0
+    x = x.to(DEV)
+    nw = (1.0 + 0.3 * torch.randn(K_, generator=g)).to(DEV)
+    eps = 1e-5
+    xn = _normed_ref(x, nw, eps)
+    ref = _tc_ref(xn, w)                                            # [T, N] float64
+    if epi == "partial":
+        out = torch.full((splits, T_, N), float("nan"), device=DEV)
+        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_PARTIAL, splits)
+        got = out.double().sum(0)
+    elif epi == "red":
+        res = torch.randn(T_, N, generator=g).to(DEV)
+        out = res.clone()
+        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_RED_F32, splits)
+        got = out.double() - res.double()
+    elif epi == "swiglu":
+        out = torch.empty((T_, N // 2), dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_SWIGLU)
+        r = ref.view(T_, N // 32, 2, 16)
+        want = (r[:, :, 0] / (1.0 + torch.exp(-r[:, :, 0])) * r[:, :, 1]).reshape(T_, N // 2)
+        torch.testing.assert_close(out.double(), want, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=1e-2)
+        k.check_device_errors()
+        return
+    elif epi == "store":
+        out = torch.empty((T_, N), dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_STORE)
+        torch.testing.assert_close(out.double(), ref, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=1e-2)
+        k.check_device_errors()
+        return
+    else:
+        out = torch.full((T_, N), float("nan"), device=DEV)
+        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_STORE_F32)
+        got = out.double()
+    # the normed rows may differ from the reference's by one bfloat16 rounding where the fp32 sum of squares
+    # differs in its last bit: a few 1e-3 relative on single elements, far less on the sums
+    torch.testing.assert_close(got, ref, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=2e-3)
+    k.check_device_errors()
+
+
+def test_gemm_tc_normed_refuses_what_it_does_not_keep_in_registers():
+    k = K()
+    w = torch.zeros(128, 4096, dtype=torch.bfloat16, device=DEV)
+    nw = torch.ones(4096, device=DEV)
+    with pytest.raises(k.KernelError):
+        k.gemm_tc_normed(w, torch.zeros(9, 4096, device=DEV), nw, 1e-5, torch.empty(9, 128, device=DEV), k.TC_STORE_F32)
+    with pytest.raises(k.KernelError):   # K-slices need an epilogue that can take them
+        k.gemm_tc_normed(w, torch.zeros(4, 4096, device=DEV), nw, 1e-5, torch.empty(4, 128, device=DEV), k.TC_STORE_F32, 2)
+
+
 @pytest.mark.parametrize("N,T_,K_,splits,cluster,bn,epi", [
     (256, 5, 512, 2, 2, 16, "store"), (384, 16, 2048, 8, 8, 16, "add"), (130, 33, 200, 4, 4, 64, "f32"),
     (2048, 64, 8192, 8, 8, 64, "store"), (3072, 8, 2048, 8, 8, 16, "store"), (2048, 8, 8192, 18, 6, 16, "partial"),
