@@ -22,6 +22,18 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
   const bool ok = tok >= 0 && tok < vocab;
   const TW* row = table + (size_t)(ok ? tok : 0) * d;
   float* o = out + (size_t)t * d;
+  if (sizeof(TW) == 2 && (d & 7) == 0 && ((uintptr_t)table & 15) == 0) {
+    // 16 bytes of the row per thread and trip: the whole row is in flight at once
+    for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) {
+      uint4 u = ok ? __ldg(reinterpret_cast<const uint4*>(row + i)) : make_uint4(0u, 0u, 0u, 0u);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      const float2 c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
+      *reinterpret_cast<float4*>(o + i) = make_float4(a.x, a.y, b.x, b.y);
+      *reinterpret_cast<float4*>(o + i + 4) = make_float4(c.x, c.y, e.x, e.y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
 }
 

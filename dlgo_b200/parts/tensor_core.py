@@ -27,6 +27,11 @@ SKINNY_MAX = 64          # tokens up to which the weight is the M operand
 # the consumer's sum longer.  Measured on a B200 (tokens a second, 148 against 296 CTAs): 8.95K
 # against 8.77K at batch 8, 35.2K against 30.3K at batch 64.
 TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 148))
+# At most 16 tokens a partial tile is small (and, where it goes into the residual, is added there with
+# reductions at the memory and never read again): three CTAs per two SMs then stream better than one per
+# SM.  Measured (tokens a second, 148 / 222 / 296): 9.90K / 10.10K / 10.05K at batch 8, 1.32K / 1.40K /
+# 1.38K at batch 1; at batch 64, with tiles four times as wide, 49.0K / 42.9K / 39.7K.
+TARGET_CTAS_FEW = int(os.environ.get("DLGO_TC_TARGET_CTAS_FEW", 222))
 MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
@@ -71,7 +76,8 @@ def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
     bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
-    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, TARGET_CTAS // tiles)) if tiles < TARGET_CTAS else 1
+    target = TARGET_CTAS_FEW if tokens <= 16 else TARGET_CTAS
+    splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, target // tiles)) if tiles < target else 1
     return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
 
