@@ -174,13 +174,15 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
                 token_seq: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
                 kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                 rotary_dim: int, interleaved: bool, write_cache: bool = True,
-                parts: Optional[torch.Tensor] = None, ahead_pages: int = 0, ahead_window: int = 0) -> None:
+                parts: Optional[torch.Tensor] = None, ahead_pages: int = 0, ahead_window: int = 0,
+                clear_parts: bool = False) -> None:
     """Rotate q (in place) and k, and store k and v at their positions' pages.
 
     ``parts`` ([S, T, ld] fp32): the projection's unsummed K-slices; they are added here and ``qkv``
     only receives the rotated q.  With ``parts`` and ``ahead_pages`` > 0 the kernel also hints the most
     recent pages of every sequence's keys and values (within ``ahead_window`` keys, if > 0) into L2
-    for the attention kernel that follows."""
+    for the attention kernel that follows.  ``clear_parts``: the kernel leaves zeros where it read
+    ``parts`` (a sum that the projection adds into and that must be zero again for the next step)."""
     _need(qkv, None, "qkv")
     _need(cos, torch.float32, "cos")
     _need(sin, torch.float32, "sin")
@@ -195,7 +197,8 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
         _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages), _ptr(vpages),
         _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim), _i(page_size), _i(1 if interleaved else 0),
         _i(1 if write_cache else 0), _ptr(parts), _i(0 if parts is None else parts.shape[0]),
-        _ll(0 if parts is None else parts.stride(0)), _i(ahead_pages), _i(ahead_window), _stream())
+        _ll(0 if parts is None else parts.stride(0)), _i(ahead_pages), _i(ahead_window),
+        _i(1 if clear_parts else 0), _stream())
     _check(st, "rope_append")
 
 

@@ -183,8 +183,10 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
 // so that a step's few tokens still spread over many SMs.  Everything that does not depend on the
 // projection (position, page, cos / sin) is fetched before the kernel waits for it; after the wait
 // a lane has eight slices' loads of a pair in flight at once.
+// SUM: `parts` is one fp32 sum that the projection's K-slices added themselves into (S = 1); it is read
+// once, here, and left zero for the next step's projection.
 constexpr int RP_WARPS = 4;
-template <typename T>
+template <typename T, bool SUM>
 __global__ void __launch_bounds__(RP_WARPS * 32)
 rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
                          const float* __restrict__ sin_t, const int* __restrict__ token_pos,
@@ -242,7 +244,7 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
     s0 = sin_t[(size_t)pos * rhalf + lane];
   }
   pdl_wait();
-  if (!active || dst == nullptr) return;
+  if (!active || (dst == nullptr && !SUM)) return;
   const float* pp = parts + (size_t)t * ld + (size_t)head * hd;
   for (int i = lane; i < half; i += 32) {
     int i0, i1;
@@ -255,7 +257,15 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
       i1 = i0 + 1;
     }
     float x0 = 0.f, x1 = 0.f;
-    for (int sb = 0; sb < S; sb += 8) {
+    if constexpr (SUM) {
+      float* sum = const_cast<float*>(pp);
+      x0 = __ldcg(sum + i0);
+      x1 = __ldcg(sum + i1);
+      sum[i0] = 0.f;
+      sum[i1] = 0.f;
+      if (dst == nullptr) continue;
+    }
+    for (int sb = 0; !SUM && sb < S; sb += 8) {
       float a[8], b[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -292,7 +302,7 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
                                  const int* page_table, int max_pages, void* kpages, void* vpages, int Hq, int Hkv,
                                  int hd, int rot, int page_size, int interleaved, int write_cache,
                                  const float* parts, int S, long long part_stride, int ahead_pages, int ahead_window,
-                                 cudaStream_t stream) {
+                                 int clear_parts, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
   if (hd <= 0 || hd % 2 || rot < 0 || rot > hd || rot % 2 || Hq <= 0 || Hkv <= 0 || page_size <= 0 ||
       ld < (Hq + 2 * Hkv) * hd)
@@ -314,20 +324,21 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
       return DLGO_ERR_DTYPE;
     return launch_status();
   }
+  if (clear_parts && (parts == nullptr || S != 1 || T > 65535)) return DLGO_ERR_SIZE;
   if (parts != nullptr && T <= 65535) {
     const dim3 grid((Hq + 2 * Hkv + RP_WARPS - 1) / RP_WARPS, T);
-    if (dtype == DLGO_F32)
-      launch_kernel(rope_append_parts_kernel<float>, grid, dim3(RP_WARPS * 32), 0, stream, (float*)qkv, ld, cos_t,
-                    sin_t, token_pos, token_seq, seq_slot, page_table, max_pages, (float*)kpages, (float*)vpages, Hq,
-                    Hkv, hd, rot, page_size, interleaved, write_cache, parts, S, (size_t)part_stride, ahead_pages,
-                    ahead_window);
-    else if (dtype == DLGO_BF16)
-      launch_kernel(rope_append_parts_kernel<__nv_bfloat16>, grid, dim3(RP_WARPS * 32), 0, stream,
-                    (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
-                    (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, Hq, Hkv, hd, rot, page_size, interleaved,
-                    write_cache, parts, S, (size_t)part_stride, ahead_pages, ahead_window);
-    else
+#define DLGO_ROPE_PARTS(TT, SUM)                                                                                  \
+  launch_kernel(rope_append_parts_kernel<TT, SUM>, grid, dim3(RP_WARPS * 32), 0, stream, (TT*)qkv, ld, cos_t, sin_t, \
+                token_pos, token_seq, seq_slot, page_table, max_pages, (TT*)kpages, (TT*)vpages, Hq, Hkv, hd, rot, \
+                page_size, interleaved, write_cache, parts, S, (size_t)part_stride, ahead_pages, ahead_window)
+    if (dtype == DLGO_F32) {
+      if (clear_parts) DLGO_ROPE_PARTS(float, true); else DLGO_ROPE_PARTS(float, false);
+    } else if (dtype == DLGO_BF16) {
+      if (clear_parts) DLGO_ROPE_PARTS(__nv_bfloat16, true); else DLGO_ROPE_PARTS(__nv_bfloat16, false);
+    } else {
       return DLGO_ERR_DTYPE;
+    }
+#undef DLGO_ROPE_PARTS
     return launch_status();
   }
   const int items = (Hq + 2 * Hkv) * (hd / 2);

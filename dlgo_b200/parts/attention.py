@@ -36,6 +36,7 @@ _MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp ite
 # ... which can also sum the projection's slices, rotate and append itself (one launch less per layer).  Opt-in:
 # measured in a whole step it is slower (0.918 against 0.891 ms at batch 8): every slice of a sequence repeats
 # the sum of the query's K-slices, and the block that appends starts its keys a round trip later.
+_QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))   # the projection's K-slices meet in one fp32 sum
 _MMA_FUSE = os.environ.get("DLGO_ATTN_MMA_FUSE_ROPE", "0") == "1"
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
 
@@ -104,8 +105,17 @@ class GQAAttention(Mixer):
         fused_rope = decode_kernel and not _NO_FUSE and K.attention_decode_fuses_rope(
             act, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.page_size)
         # few tokens: the projection leaves its K-slices unsummed and whoever rotates adds them
-        qkv_parts = self.wqkv.partials(x, single_ok=False)
         qkv = None
+        clear_parts = False
+        if _QKV_SUM and self.wqkv.sums_slices_at_memory(T) and not (fused_rope or _MMA_FUSE):
+            # ... or its K-slices add themselves, at the memory, into one fp32 sum that is zero between
+            # steps: the rotation reads it once and leaves zeros behind
+            n = self.q_dim + 2 * self.kv_dim
+            qkv_parts = ctx.zeros(f"qkv_sum{n}", T * n, torch.float32)[:T * n].view(1, T, n)
+            self.wqkv(x, ADD_F32, qkv_parts[0])
+            clear_parts = True
+        else:
+            qkv_parts = self.wqkv.partials(x, single_ok=False)
         if qkv_parts is None:
             qkv = self.wqkv(x, STORE)
         # the tensor-core decode kernel can take the slices as they are: it sums, rotates and appends itself
@@ -122,7 +132,7 @@ class GQAAttention(Mixer):
                 ahead = max(1, _AHEAD_BYTES // (2 * T * self.num_kv_heads * page_bytes))
             K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                           cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                          qkv_parts, ahead, self.window or 0)
+                          qkv_parts, ahead, self.window or 0, clear_parts)
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)

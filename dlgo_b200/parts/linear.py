@@ -46,6 +46,11 @@ class Linear:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
 
+    def sums_slices_at_memory(self, tokens: int) -> bool:
+        """Whether, for this many tokens, the add epilogue runs as several K-slices that add themselves
+        into the target with reductions at the memory (the target may then be a plain zeroed sum)."""
+        return self._tc is not None and not self.fuses_swiglu and self._tc.sums_slices_at_memory(tokens)
+
     def partials(self, x: Any, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """The product as unsummed fp32 K-slices [slices, tokens, out] where the kernel offers that
         (few tokens on the tensor cores), else ``None``; also ``None`` for a single slice unless

@@ -147,6 +147,11 @@ class TensorCorePlan:
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
 
+    def sums_slices_at_memory(self, tokens: int) -> bool:
+        if not (NORM_IN_GEMM & 1) or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):
+            return False
+        return skinny_shape(tokens, self.n, self.k)[1] > 1
+
     def partials(self, x, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
         reads the result next adds them in order (this spares the contraction a reduction pass through

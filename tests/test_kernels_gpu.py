@@ -897,6 +897,41 @@ def test_rope_append_from_partials():
         torch.testing.assert_close(torch.nan_to_num(b, nan=-7.0), torch.nan_to_num(a, nan=-7.0), atol=1e-6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("write_cache", [True, False])
+def test_rope_append_from_a_sum_that_it_leaves_zero(write_cache):
+    """The projection's K-slices may have added themselves into one fp32 sum: the rotation reads it once
+    and leaves zeros behind, also where it has nothing to write (an entry that borrows another's cache)."""
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    hq, hkv, hd = 5, 2, 48
+    pe = RotaryEmbedding(hd, 32, 10000.0, 200)
+    cos, sin = (t.to(DEV) for t in pe.tables())
+    ld = (hq + 2 * hkv) * hd
+    torch.manual_seed(1)
+    whole = torch.randn(3, ld, device=DEV)
+    pos = torch.tensor([5, 70, 127], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 1, 1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    pt = torch.tensor([[0, -1], [1, 2]], dtype=torch.int32, device=DEV)
+    kp0, vp0 = _paged(3, hkv, hd, "bfloat16")
+    q0 = whole.to(torch.bfloat16)
+    k.rope_append(q0, cos, sin, pos, seq, slots, pt, kp0, vp0, hq, hkv, hd, 32, False, write_cache)
+    kp1, vp1 = _paged(3, hkv, hd, "bfloat16")
+    q1 = torch.full((3, ld), float("nan"), device=DEV, dtype=torch.bfloat16)
+    total = whole.clone().view(1, 3, ld)
+    k.rope_append(q1, cos, sin, pos, seq, slots, pt, kp1, vp1, hq, hkv, hd, 32, False, write_cache, total, 0, 0, True)
+    assert int((total != 0).sum()) == 0, "the sum was not left zero"
+    # (the plain path rounds the projection to bfloat16 before it rotates, this one after: one rounding apart)
+    torch.testing.assert_close(q1[:, :hq * hd].float(), q0[:, :hq * hd].float(), atol=4e-2, rtol=2e-2)
+    for a, b in ((kp0, kp1), (vp0, vp1)):
+        assert torch.equal(torch.isnan(a.float()), torch.isnan(b.float()))
+        torch.testing.assert_close(torch.nan_to_num(b.float(), nan=-7.0), torch.nan_to_num(a.float(), nan=-7.0),
+                                   atol=4e-2, rtol=2e-2)
+    with pytest.raises(k.KernelError):      # two slices are not a sum
+        k.rope_append(q1, cos, sin, pos, seq, slots, pt, kp1, vp1, hq, hkv, hd, 32, False, True,
+                      torch.zeros(2, 3, ld, device=DEV), 0, 0, True)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hq,hkv,hd,rot,inter", [(8, 2, 64, 64, False), (3, 1, 32, 32, False), (4, 4, 128, 64, True),
                                                  (4, 2, 16, 0, False)])
