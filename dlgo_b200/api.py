@@ -87,6 +87,11 @@ class _EngineBackend:
         """Several greedy decode steps in one native call (``None``: step one by one)."""
         return self.engine.greedy_run(slots, tokens, n_steps, stop_ids)
 
+    def sampled_steps(self, slots, tokens, n_steps: int, stop_ids, sampler: SamplerConfig, seed: int, requests,
+                      draws, recent) -> Optional[List[List[int]]]:
+        """Several sampled decode steps in one native call (``None``: step one by one)."""
+        return self.engine.sampled_run(slots, tokens, n_steps, stop_ids, sampler, seed, requests, draws, recent)
+
     def step_and_sample(self, slots, tokens, requests, draws, sampler: SamplerConfig, seed: int, recent) -> List[int]:
         logits = self.engine.step(slots, tokens)
         if sampler.greedy:

@@ -311,8 +311,36 @@ def greedy_run_graph(host_inputs: torch.Tensor, graph_exec: int, host_ids: torch
     return tokens[:n].tolist()
 
 
+def sampled_run_graph(host_inputs: torch.Tensor, graph_exec: int, host_ids: torch.Tensor, stop_ids: Sequence[int],
+                      max_steps: int, draw_inputs: torch.Tensor, window: int, device_index: int,
+                      launches_per_step: int) -> List[List[int]]:
+    """:func:`greedy_run_graph` for sampled decoding (dlgo_sampled_run_graph): the captured step also copies
+    ``draw_inputs`` (pinned int32: [2] seed, [B] requests, [B] draw indices, [B, window] recent tokens,
+    [B] tokens produced so far) and ends with the filters and the draw; draw indices and windows are
+    advanced in place."""
+    import numpy as np
+    B = host_ids.numel()
+    if draw_inputs.numel() != 2 + 3 * B + B * window or draw_inputs.dtype != torch.int32 or not draw_inputs.is_pinned():
+        raise KernelError("sampled_run_graph: draw_inputs must be pinned int32 [2 + 3 B + B window]")
+    stops = np.asarray(sorted(int(t) for t in stop_ids), dtype=np.int32)
+    tokens = np.empty((max_steps, B), dtype=np.int32)
+    n = _lib("sampling").dlgo_sampled_run_graph(
+        ctypes.c_void_p(host_inputs.data_ptr()), _i(B), ctypes.c_void_p(graph_exec),
+        ctypes.c_void_p(host_ids.data_ptr()), stops.ctypes.data_as(ctypes.c_void_p), _i(len(stops)), _i(max_steps),
+        tokens.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(draw_inputs.data_ptr()), _i(window),
+        ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device_index)))
+    if n <= 0:
+        raise KernelError(f"sampled_run_graph: error {n}")
+    global LAUNCHES
+    LAUNCHES += launches_per_step * n
+    return tokens[:n].tolist()
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tensor, draw: torch.Tensor, seed: int,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, seed_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row from softmax(logits / temperature) by inverse CDF; the uniform is a function of
+    (seed, draw, request).  ``seed_dev`` (two int32 on the device, 8-byte aligned): the kernel reads the seed
+    there instead (a captured step whose seed changes between replays)."""
     _need(logits, torch.float32, "logits")
     _need(temperature, torch.float32, "temperature")
     _need(request, torch.int32, "request")
@@ -320,9 +348,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tenso
     R, V = logits.shape
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    if seed_dev is not None and (seed_dev.dtype != torch.int32 or seed_dev.numel() < 2 or not seed_dev.is_cuda):
+        raise KernelError("sample: seed_dev must be two int32 on the GPU")
     st = _lib("sampling").dlgo_sample(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(temperature),
-                                      _ptr(request), _ptr(draw), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(out),
-                                      _stream())
+                                      _ptr(request), _ptr(draw), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                                      _ptr(seed_dev), _ptr(out), _stream())
     _check(st, "sample")
     return out
 

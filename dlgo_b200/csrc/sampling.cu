@@ -142,66 +142,85 @@ __global__ void argmax_finish_kernel(const float* __restrict__ part_v, const int
   if (threadIdx.x == 0) out[r] = besti == 0x7fffffff ? 0 : besti;
 }
 
-// One block per row.  Each thread owns a contiguous chunk of the vocabulary, so
-// "first index whose running sum reaches r" keeps its meaning.
+// One block per row.  Each WARP owns a contiguous chunk of the vocabulary and walks it 32 consecutive
+// entries at a time (coalesced), so "first index whose running sum reaches the target" keeps its meaning:
+// warps in order, groups of 32 in order, lanes in order.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
-              const int* __restrict__ request, const int* __restrict__ draw, uint64_t seed, int* __restrict__ out) {
+              const int* __restrict__ request, const int* __restrict__ draw, uint64_t seed,
+              const unsigned long long* __restrict__ seed_dev, int* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
+  if (seed_dev != nullptr) seed = *seed_dev;   // (a captured step takes its seed from memory)
   __shared__ float scratch[32];
-  __shared__ float csum[SAMPLE_THREADS];
+  __shared__ float wsum[SAMPLE_THREADS / 32];
   __shared__ int chosen;
+  __shared__ float rest_s;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float inv_t = 1.0f / temperature[r];
-  const int chunk = (V + blockDim.x - 1) / blockDim.x;
-  const int b = threadIdx.x * chunk, e = min(V, b + chunk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int chunk = ((V + n_warps - 1) / n_warps + 31) / 32 * 32;   // whole groups of 32 per warp
+  const int b = warp * chunk, e = min(V, b + chunk);
   float mx = -INFINITY;
-  for (int i = b; i < e; ++i) mx = fmaxf(mx, row[i] * inv_t);
+  for (int i = b + lane; i < e; i += 32) mx = fmaxf(mx, row[i] * inv_t);
   mx = block_max(mx, scratch);
   float s = 0.f;
-  for (int i = b; i < e; ++i) {
+  for (int i = b + lane; i < e; i += 32) {
     const float v = row[i] * inv_t;
     s += (v == -INFINITY) ? 0.f : expf(v - mx);
   }
-  csum[threadIdx.x] = s;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) wsum[warp] = s;
   if (threadIdx.x == 0) chosen = -1;
   __syncthreads();
   if (threadIdx.x == 0) {
     float total = 0.f;
-    for (int i = 0; i < (int)blockDim.x; ++i) total += csum[i];
+    for (int i = 0; i < n_warps; ++i) total += wsum[i];
     const float u = philox_uniform(seed, (uint32_t)draw[r], (uint32_t)request[r]);
     const float target = u * total;
     float run = 0.f;
     int owner = -1;
-    for (int i = 0; i < (int)blockDim.x; ++i) {
-      if (run + csum[i] >= target && csum[i] > 0.f) { owner = i; break; }
-      run += csum[i];
+    for (int i = 0; i < n_warps; ++i) {
+      if (run + wsum[i] >= target && wsum[i] > 0.f) { owner = i; break; }
+      run += wsum[i];
     }
     if (owner < 0) {
-      // rounding left the target above the total: the last index with weight
-      for (int i = (int)blockDim.x - 1; i >= 0; --i)
-        if (csum[i] > 0.f) { owner = i; break; }
-      scratch[0] = -1.f;  // sentinel: take the chunk's last weighted index
+      // rounding left the target above the total: the last chunk with weight
+      for (int i = n_warps - 1; i >= 0; --i)
+        if (wsum[i] > 0.f) { owner = i; break; }
+      rest_s = -1.f;  // sentinel: take the chunk's last weighted index
     } else {
-      scratch[0] = target - run;
+      rest_s = target - run;
     }
     chosen = owner;
   }
   __syncthreads();
-  if ((int)threadIdx.x == chosen) {
-    const float rest = scratch[0];
+  if (warp == chosen) {
+    const float rest = rest_s;
     float run = 0.f;
-    int pick = -1, last = b;
-    for (int i = b; i < e; ++i) {
-      const float v = row[i] * inv_t;
-      const float pr = (v == -INFINITY) ? 0.f : expf(v - mx);
-      if (pr > 0.f) last = i;
-      run += pr;
-      if (rest >= 0.f && pr > 0.f && run >= rest) { pick = i; break; }
+    int pick = -1, last = -1;
+    for (int g = b; g < e && pick < 0; g += 32) {
+      const int i = g + lane;
+      float pr = 0.f;
+      if (i < e) {
+        const float v = row[i] * inv_t;
+        pr = (v == -INFINITY) ? 0.f : expf(v - mx);
+      }
+      float incl = pr;                       // inclusive scan over the lanes, in lane order
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const unsigned weighted = __ballot_sync(0xffffffffu, pr > 0.f);
+      if (weighted) last = g + 31 - __clz(weighted);
+      const unsigned hit = __ballot_sync(0xffffffffu, rest >= 0.f && pr > 0.f && run + incl >= rest);
+      if (hit) pick = g + __ffs(hit) - 1;
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    out[r] = pick >= 0 ? pick : last;
+    if (lane == 0) out[r] = pick >= 0 ? pick : (last >= 0 ? last : b);
   }
 }
 
@@ -244,15 +263,12 @@ filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict
     rec_s[tid] = tok;
   }
   __syncthreads();
-  // pass 0: penalty and temperature -> work
-  for (int i = tid; i < V; i += FILTER_THREADS) {
-    float v = row[i];
-    if (penalty > 1.0f) {
-      bool hit = false;
-      for (int j = 0; j < FILTER_RECENT; ++j) hit |= rec_s[j] == i;
-      if (hit) v = v > 0.f ? v / penalty : v * penalty;
-    }
-    out[i] = v * inv_t;
+  // pass 0: temperature -> work; then the penalty on the (few, distinct) recent tokens
+  for (int i = tid; i < V; i += FILTER_THREADS) out[i] = row[i] * inv_t;
+  __syncthreads();
+  if (penalty > 1.0f && tid < FILTER_RECENT && rec_s[tid] >= 0) {
+    const float v = row[rec_s[tid]];
+    out[rec_s[tid]] = (v > 0.f ? v / penalty : v * penalty) * inv_t;
   }
   __syncthreads();
   if (top_k <= 0 || top_k >= V) {
@@ -289,19 +305,56 @@ filter_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict
     }
     return;
   }
-  // top-k: the k-th largest key by bisection on the 32 bits of the order-preserving key
-  uint32_t lo = 0u;     // invariant: count(key >= lo) >= k
-  for (int bit = 31; bit >= 0; --bit) {
-    const uint32_t mid = lo | (1u << bit);
-    if (tid == 0) count_s = 0;
-    __syncthreads();
-    unsigned int c = 0;
-    for (int i = tid; i < V; i += FILTER_THREADS) c += order_key(out[i]) >= mid;
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if ((tid & 31) == 0 && c) atomicAdd(&count_s, c);
-    __syncthreads();
-    if (count_s >= (unsigned int)top_k) lo = mid;
-    __syncthreads();
+  // top-k: the k-th largest of the order-preserving keys, digit by digit from the top (11, 11 and 10
+  // bits): a histogram of the digit over the keys that share the digits found so far, then the highest
+  // bin at which the count from the top reaches what is still wanted.  Three passes over the row.
+  uint32_t lo = 0u;                       // the digits found so far, in place
+  {
+    int* hist = si;                       // (the survivors' list is not in use yet: 2048 bins fit)
+    __shared__ unsigned int want_s, digit_s;
+    if (tid == 0) want_s = (unsigned int)top_k;
+    for (int level = 0; level < 3; ++level) {
+      const int shift = level == 0 ? 21 : (level == 1 ? 10 : 0);
+      const int nb = level < 2 ? 2048 : 1024;
+      const uint32_t above = level == 0 ? 0u : ~((1u << (shift + (level < 2 ? 11 : 10))) - 1u);
+      for (int i = tid; i < nb; i += FILTER_THREADS) hist[i] = 0;
+      __syncthreads();
+      for (int i = tid; i < V; i += FILTER_THREADS) {
+        const uint32_t key = order_key(out[i]);
+        if ((key & above) == lo) atomicAdd(&hist[(key >> shift) & (uint32_t)(nb - 1)], 1);
+      }
+      __syncthreads();
+      if (tid < 32) {
+        // lane l owns bins [nb - (l + 1) * per, nb - l * per): lane 0 the highest
+        const int per = nb / 32;
+        const int top = nb - tid * per;
+        unsigned int mine = 0;
+        for (int j = 0; j < per; ++j) mine += (unsigned int)hist[top - 1 - j];
+        unsigned int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const unsigned int t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (tid >= o) incl += t;
+        }
+        const unsigned int want = want_s;
+        const unsigned int before = incl - mine;                     // keys in the lanes above this one
+        const unsigned owners = __ballot_sync(0xffffffffu, incl >= want);
+        const int owner = owners ? __ffs(owners) - 1 : 31;         // (k <= V: some lane reaches it)
+        if (tid == owner) {
+          unsigned int run = before;
+          int bin = top - per;
+          for (int j = 0; j < per; ++j) {
+            run += (unsigned int)hist[top - 1 - j];
+            if (run >= want) { bin = top - 1 - j; run -= (unsigned int)hist[bin]; break; }
+          }
+          digit_s = (unsigned int)bin;
+          want_s = want - run;                                       // still wanted inside the bin
+        }
+      }
+      __syncthreads();
+      lo |= digit_s << shift;
+      __syncthreads();
+    }
   }
   // survivors (key >= lo) into shared memory, the rest to -inf
   if (tid == 0) count_s = 0;
@@ -437,13 +490,52 @@ DLGO_EXPORT int dlgo_greedy_run_graph(int* host_inputs, int B, void* graph_exec,
 }
 
 // temperature[R] f32 (> 0), request[R] and draw[R] int32 key the uniform of each row
+// seed_dev: null, or where the kernel reads the seed (then `seed` is ignored)
 DLGO_EXPORT int dlgo_sample(const float* logits, int R, int ld, int V, const float* temperature, const int* request,
-                            const int* draw, unsigned long long seed, int* out, cudaStream_t stream) {
+                            const int* draw, unsigned long long seed, const unsigned long long* seed_dev, int* out,
+                            cudaStream_t stream) {
   if (R <= 0) return DLGO_OK;
   if (V <= 0 || ld < V) return DLGO_ERR_SIZE;
+  if (((uintptr_t)seed_dev & 7) != 0) return DLGO_ERR_ALIGN;
   const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-  launch_kernel(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, temperature, request, draw, (uint64_t)seed, out);
+  launch_kernel(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, temperature, request, draw,
+                (uint64_t)seed, seed_dev, out);
   return launch_status();
+}
+
+// The same loop for sampled decoding: the captured step (`graph_exec`) begins with the copies of its inputs
+// and of the draw's inputs out of pinned memory and ends with the filters, the draw and the copy of the ids
+// into `host_ids`.  `draw_inputs` (pinned int32): [2] seed, [B] request index, [B] index of the draw within
+// the request, [B][W] the request's most recent tokens (-1: none), [B] how many tokens it has produced in
+// all (the slot of the window that the next one takes is that count modulo W).  Per step every sequence's
+// draw index advances and its token enters its window, as the loop above the engine would do it.
+DLGO_EXPORT int dlgo_sampled_run_graph(int* host_inputs, int B, void* graph_exec, const int* host_ids,
+                                       const int* stop_ids, int n_stop, int max_steps, int* out_tokens,
+                                       int* draw_inputs, int W, cudaStream_t stream) {
+  if (B <= 0 || max_steps <= 0) return 0;
+  if (W <= 0 || draw_inputs == nullptr) return -(int)cudaErrorInvalidValue;
+  int* draws = draw_inputs + 2 + B;
+  int* recent = draw_inputs + 2 + 2 * B;
+  int* counts = recent + (size_t)B * W;
+  for (int step = 0; step < max_steps; ++step) {
+    cudaError_t e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, stream);
+    if (e != cudaSuccess) return -(int)e;
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return -(int)e;
+    bool stop = false;
+    for (int b = 0; b < B; ++b) {
+      const int id = ((const volatile int*)host_ids)[b];
+      out_tokens[(size_t)step * B + b] = id;
+      for (int k = 0; k < n_stop; ++k) stop |= stop_ids[k] == id;
+      host_inputs[b] = id;
+      host_inputs[B + b] += 1;
+      draws[b] += 1;
+      recent[(size_t)b * W + (counts[b] % W)] = id;
+      counts[b] += 1;
+    }
+    if (stop) return step + 1;
+  }
+  return max_steps;
 }
 
 // the uniform a (seed, draw, request) triple yields, for tests and host-side twins

@@ -20,7 +20,7 @@ import torch
 from ..cache.kv_cache import KVCache, PAGE_SIZE
 from ..config.registry import load_config
 from ..weights.loader import DictSource, WeightSource
-from .graphs import decode_with_graph, greedy_with_graph
+from .graphs import decode_with_graph, greedy_with_graph, sampled_with_graph
 from .model import CausalLM
 from .runtime import Runtime, StepContext, build_context
 
@@ -179,8 +179,16 @@ class Engine:
         return logits
 
     @torch.no_grad()
+    def sampled_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, stop_ids: Sequence[int],
+                    sampler: Any, seed: int, requests: Sequence[int], draws: Sequence[int],
+                    recents: Sequence[Sequence[int]]) -> Optional[List[List[int]]]:
+        """:meth:`greedy_run` with a sampler configuration's filters and draw in the place of the argmax
+        (``sampler`` is not greedy).  ``requests[i]`` and ``draws[i]`` key sequence i's uniform numbers, the
+        draw index advancing by one per step; ``recents[i]`` are its latest tokens, oldest first."""
+        return self.greedy_run(slots, tokens, n_steps, stop_ids, (sampler, seed, requests, draws, recents))
+
     def greedy_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int,
-                   stop_ids: Sequence[int] = ()) -> Optional[List[List[int]]]:
+                   stop_ids: Sequence[int] = (), _draw: Optional[tuple] = None) -> Optional[List[List[int]]]:
         """Run ``tokens[i]`` as the next token of the sequence in ``slots[i]`` and go on greedily, every
         sequence one token per step, for up to ``n_steps`` steps without returning in between (the steps,
         the argmax and the copies of the ids are one native call).  Returns the ids chosen, a list per
@@ -210,7 +218,10 @@ class Engine:
                 self.cache.reserve(slots, [n_steps] * len(slots))     # pages for the whole run, mirrored once
             except Exception:
                 return None
-            out = greedy_with_graph(self, slots, ids, starts, n_steps, stop_ids)
+            if _draw is None:
+                out = greedy_with_graph(self, slots, ids, starts, n_steps, stop_ids)
+            else:
+                out = sampled_with_graph(self, slots, ids, starts, n_steps, stop_ids, *_draw)
         self.cache.commit(slots, [len(out)] * len(slots))
         return out
 

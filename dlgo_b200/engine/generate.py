@@ -176,15 +176,22 @@ class GenerationLoop:
                     feed = [[s.last] for s in live]
 
                 greedy_steps = getattr(self.backend, "greedy_steps", None)
+                sampled_steps = getattr(self.backend, "sampled_steps", None)
+                many_steps = greedy_steps if cfg.sampler.greedy else sampled_steps
                 while live:
-                    if not first and greedy_steps is not None and cfg.sampler.greedy and on_token is None:
-                        # Decoding greedily with nobody listening token by token: the backend may run
-                        # several steps in one call.  As many as every sequence can take before it ends
-                        # by count, so that only a stop token can end one earlier, and the backend
+                    if not first and many_steps is not None and on_token is None:
+                        # Decoding with nobody listening token by token: the backend may run several
+                        # steps in one call.  As many as every sequence can take before it ends by
+                        # count, so that only a stop token can end one earlier, and the backend
                         # returns with the step in which one appeared.
                         n = min(min(cfg.max_tokens - len(s.out), limit - 1 - s.length) for s in live)
-                        chunk = greedy_steps([s.slot for s in live], [s.last for s in live], n, sorted(stops)) \
-                            if n > 1 else None
+                        chunk = None
+                        if n > 1 and cfg.sampler.greedy:
+                            chunk = greedy_steps([s.slot for s in live], [s.last for s in live], n, sorted(stops))
+                        elif n > 1:
+                            chunk = sampled_steps([s.slot for s in live], [s.last for s in live], n, sorted(stops),
+                                                  cfg.sampler, seed, [s.request for s in live],
+                                                  [len(s.out) for s in live], [s.recent for s in live])
                         if chunk is not None:
                             for sampled in chunk:
                                 steps += 1

@@ -48,6 +48,12 @@ class DecodeGraph:
         self.greedy_kernels = 0
         self.ids_dev = torch.zeros((batch,), dtype=torch.int32, device=dev)
         self.ids_host = torch.zeros((batch,), dtype=torch.int32).pin_memory()
+        # captures per sampler configuration that end with the filters and the draw, for sampled runs; the
+        # draw's inputs (seed, request and draw indices, recent tokens, token counts) come out of one pinned
+        # buffer, so that one capture serves every seed and every set of requests
+        self.sampled = {}
+        self.draw_host = None
+        self.draw_dev = None
 
     def capture(self) -> None:
         eng = self.engine
@@ -76,6 +82,37 @@ class DecodeGraph:
             self.ids_host.copy_(self.ids_dev, non_blocking=True)
         self.greedy_kernels = kernels.LAUNCHES - before
         self.greedy_exec = self.greedy_graph.raw_cuda_graph_exec()
+
+    def capture_sampled(self, cfg: Any) -> tuple:
+        """(graph exec, kernels per replay) of the step followed by ``cfg``'s filters and draw."""
+        from ..sampling.sampler import RECENT_WINDOW, draw_on_device, temperature_rows
+        hit = self.sampled.get(cfg)
+        if hit is not None:
+            return hit[1], hit[2]
+        if len(self.sampled) >= 4:
+            self.sampled.pop(next(iter(self.sampled)))      # (a handful of configurations at a time)
+        eng, b, w = self.engine, self.batch, RECENT_WINDOW
+        dev = eng.runtime.device
+        if self.draw_host is None:
+            self.draw_host = torch.zeros((2 + 3 * b + b * w,), dtype=torch.int32).pin_memory()
+            self.draw_host[2 + 2 * b:2 + 2 * b + b * w] = -1
+            self.draw_dev = torch.zeros((2 + 2 * b + b * w,), dtype=torch.int32, device=dev)
+        d = self.draw_dev
+        requests, draws, recent = d[2:2 + b], d[2 + b:2 + 2 * b], d[2 + 2 * b:].view(b, w)
+        temperature = temperature_rows(cfg, b, dev)
+        torch.cuda.synchronize()
+        before = kernels.LAUNCHES
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.meta.copy_(self.host, non_blocking=True)
+            d.copy_(self.draw_host[:d.numel()], non_blocking=True)
+            logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+            draw_on_device(logits, cfg, requests, draws, recent, 0, seed_dev=d[0:2], out=self.ids_dev,
+                           temperature=temperature)
+            self.ids_host.copy_(self.ids_dev, non_blocking=True)
+        n = kernels.LAUNCHES - before
+        self.sampled[cfg] = (graph, graph.raw_cuda_graph_exec(), n, temperature)
+        return self.sampled[cfg][1], n
 
     def run(self, slots: Sequence[int], token_ids: Sequence[int], starts: Sequence[int]) -> torch.Tensor:
         self._native.wait()      # the previous step's copy out of the pinned buffer has finished
@@ -106,6 +143,40 @@ def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
     h[2, :] = slots
     return kernels.greedy_run_graph(g.host, g.greedy_exec, g.ids_host, stop_ids, n_steps, g._dev_index,
                                     g.greedy_kernels)
+
+
+def sampled_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int], n_steps: int,
+                       stop_ids: Sequence[int], cfg: Any, seed: int, requests: Sequence[int], draws: Sequence[int],
+                       recents: Sequence[Sequence[int]]) -> List[List[int]]:
+    """:func:`greedy_with_graph` with ``cfg``'s filters and draw instead of the argmax: ``requests[i]`` and
+    ``draws[i]`` key the uniform numbers of sequence i (the draw index advances with every step), and
+    ``recents[i]`` are its latest tokens, oldest first, for the repetition penalty."""
+    from ..sampling.sampler import RECENT_WINDOW
+    b, w = len(slots), RECENT_WINDOW
+    g = engine._graphs.get(b)
+    if g is None:
+        decode_with_graph(engine, slots, token_ids, starts)
+        g = engine._graphs[b]
+    graph_exec, n_kernels = g.capture_sampled(cfg)
+    g._native.wait()
+    h = g.host_np
+    h[0, :] = token_ids
+    h[1, :] = starts
+    h[2, :] = slots
+    dh = g.draw_host.numpy()
+    seed &= (1 << 64) - 1
+    dh[0:2] = [((seed & 0xFFFFFFFF) ^ 0x80000000) - 0x80000000, ((seed >> 32) ^ 0x80000000) - 0x80000000]
+    dh[2:2 + b] = list(requests)
+    dh[2 + b:2 + 2 * b] = list(draws)
+    rec = dh[2 + 2 * b:2 + 2 * b + b * w].reshape(b, w)
+    cnt = dh[2 + 2 * b + b * w:]
+    for i, r in enumerate(recents):
+        r = list(r)[-w:]
+        rec[i, :len(r)] = r
+        rec[i, len(r):] = -1
+        cnt[i] = len(r)                 # the oldest lies first: a full window wraps to it
+    return kernels.sampled_run_graph(g.host, graph_exec, g.ids_host, stop_ids, n_steps, g.draw_host, w,
+                                     g._dev_index, n_kernels)
 
 
 def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:

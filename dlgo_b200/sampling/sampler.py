@@ -99,6 +99,32 @@ def apply_min_p(logits: torch.Tensor, min_p: float) -> None:
     logits.masked_fill_(probs < thr, float("-inf"))
 
 
+def temperature_rows(cfg: SamplerConfig, rows: int, device: torch.device) -> torch.Tensor:
+    """The per-row temperature the draw divides by: the filters already applied it, if there are any."""
+    return torch.full((rows,), 1.0 if cfg.filtered else float(cfg.temperature), dtype=torch.float32, device=device)
+
+
+def draw_on_device(logits: torch.Tensor, cfg: SamplerConfig, requests: torch.Tensor, draws: torch.Tensor,
+                   recent: Optional[torch.Tensor], seed: int, seed_dev: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, temperature: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Filters and the draw for a sampled (not greedy) configuration, everything already on the device:
+    ``requests`` and ``draws`` int32 [rows], ``recent`` int32 [rows, <= 64] with -1 for none (or ``None``).
+    ``seed_dev``: the seed is read from device memory (a captured step); ``temperature``: the constant of
+    :func:`temperature_rows`, made once by a caller that runs this many times."""
+    rows = logits.shape[0]
+    if temperature is None:
+        temperature = temperature_rows(cfg, rows, logits.device)
+    if cfg.filtered:
+        # every filter in one kernel of ours; top-k off (0, or at least the vocabulary) is a path of its own there
+        top_k = cfg.top_k if 0 < cfg.top_k < logits.shape[1] else 0
+        if top_k > K.FILTER_MAX_K:
+            raise ValueError(f"top_k up to {K.FILTER_MAX_K} (or 0 for none), got {cfg.top_k}")
+        rec = recent if cfg.repetition_penalty > 1.0 else None
+        work = K.filter_logits(logits, cfg.temperature, top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty, rec)
+        return K.sample(work, temperature, requests, draws, seed, out, seed_dev)
+    return K.sample(logits, temperature, requests, draws, seed, out, seed_dev)
+
+
 class DeviceSampler:
     """Samples one token per row of a logits tensor, on the device."""
 
@@ -111,20 +137,10 @@ class DeviceSampler:
         if cfg.greedy:
             return K.argmax(logits)
         dev = logits.device
-        rows = logits.shape[0]
         meta = torch.tensor([list(requests), list(draws)], dtype=torch.int32).to(dev, non_blocking=True)
-        if cfg.filtered:
-            # every filter in one kernel of ours; top-k off (0, or at least the vocabulary) is a path of its own there
-            top_k = cfg.top_k if 0 < cfg.top_k < logits.shape[1] else 0
-            if top_k > K.FILTER_MAX_K:
-                raise ValueError(f"top_k up to {K.FILTER_MAX_K} (or 0 for none), got {cfg.top_k}")
-            rec = None
-            if recent is not None and cfg.repetition_penalty > 1.0:
-                width = min(RECENT_WINDOW, K.FILTER_MAX_RECENT)
-                rec = torch.tensor([(list(r)[-width:] + [-1] * width)[:width] for r in recent],
-                                   dtype=torch.int32).to(dev, non_blocking=True)
-            work = K.filter_logits(logits, cfg.temperature, top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty, rec)
-            temp = torch.ones((rows,), dtype=torch.float32, device=dev)
-            return K.sample(work, temp, meta[0], meta[1], self.seed)
-        temp = torch.full((rows,), float(cfg.temperature), dtype=torch.float32, device=dev)
-        return K.sample(logits, temp, meta[0], meta[1], self.seed)
+        rec = None
+        if cfg.filtered and recent is not None and cfg.repetition_penalty > 1.0:
+            width = min(RECENT_WINDOW, K.FILTER_MAX_RECENT)
+            rec = torch.tensor([(list(r)[-width:] + [-1] * width)[:width] for r in recent],
+                               dtype=torch.int32).to(dev, non_blocking=True)
+        return draw_on_device(logits, cfg, meta[0], meta[1], rec, self.seed)

@@ -300,3 +300,26 @@ def test_decoding_with_the_norm_computed_inside_the_contraction(model_dirs, name
     steps = T.tail_one_by_one(reqs, 12)
     check(name, model_dirs, "bfloat16", steps, T.run_in_process(eng, steps), reqs, "norm in the contraction")
 
+
+def test_sampled_steps_in_one_native_call_draw_what_single_steps_draw(model_dirs):
+    """Sampled generation with nobody listening token by token runs many steps per native call (a captured
+    step that ends with the filters and the draw; draw indices and the repetition penalty's window advance
+    in that call): the same tokens as stepping one by one, with every filter on, past a full window of 64
+    recent tokens, with sequences that end at different times, and with a second seed through the same
+    capture."""
+    import dlgo_b200
+    llm = dlgo_b200.load_llm(model_dirs["B"], dtype="float32", max_tokens=1536)
+    prompts = [random_tokens(n, 384, 90 + n) for n in (3, 40, 70)]
+    for seed in (5, 6):
+        opts = dict(max_tokens=90, temperature=0.7, top_k=40, top_p=0.9, min_p=0.02, repetition_penalty=1.3, seed=seed)
+        stepped = [[] for _ in prompts]
+        llm.generate_stream(prompts, lambda r, t: stepped[r].append(t), **opts)      # one step per call
+        native = llm.generate(prompts, **opts)
+        assert native == stepped, f"seed {seed}"
+    plain_t = dict(max_tokens=30, temperature=1.1, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=11, ignore_eos=True)
+    stepped = [[] for _ in prompts]
+    llm.generate_stream(prompts, lambda r, t: stepped[r].append(t), **plain_t)
+    assert llm.generate(prompts, **plain_t) == stepped
+    llm.engine.cache.book.check()
+    assert llm.engine.cache.book.live_slots() == []
+

@@ -184,6 +184,36 @@ class MultiStepBackend(ScriptedBackend):
         return out
 
 
+class MultiSampledBackend(MultiStepBackend):
+    """... and several sampled steps in one call: it checks what the loop tells it about each sequence."""
+
+    def sampled_steps(self, slots, tokens, n_steps, stop_ids, sampler, seed, requests, draws, recent):
+        assert not sampler.greedy and seed >= 0
+        for s, r, d, rec in zip(slots, requests, draws, recent):
+            assert self.request_of[s] == r and self.draw_of[s] == d, "request and draw index of every sequence"
+            assert len(rec) <= 64 and (d == 0 or len(rec) > 0)
+        self.sampled_calls = getattr(self, "sampled_calls", 0) + 1
+        return self.greedy_steps(slots, tokens, n_steps, stop_ids)
+
+
+def test_several_sampled_steps_in_one_backend_call_change_no_decision():
+    script = lambda r, d: 7 if (r == 1 and d == 2) else 100 + 10 * r + d
+    prompts = [[1, 2], [3], [4, 5, 6]]
+    sampler = SamplerConfig(temperature=0.7, top_k=40, top_p=0.9, min_p=0.0, repetition_penalty=1.1)
+    for kw in (dict(), dict(include_stop=True), dict(ignore_eos=True)):
+        cfg = GenerateConfig(max_tokens=6, sampler=sampler, seed=3, **kw)
+        plain = GenerationLoop(ScriptedBackend(script=script), model_stop_ids=[7]).run(prompts, cfg)
+        be = MultiSampledBackend(script=script)
+        multi = GenerationLoop(be, model_stop_ids=[7]).run(prompts, cfg)
+        assert multi.tokens == plain.tokens and multi.steps == plain.steps
+        assert be.held == {} and be.sampled_calls >= 1 and len(be.calls) == 1
+        # somebody listening token by token: one step per call
+        be2 = MultiSampledBackend(script=script)
+        seen = []
+        GenerationLoop(be2, model_stop_ids=[7]).run(prompts, cfg, lambda r, t: seen.append((r, t)))
+        assert not hasattr(be2, "sampled_calls") and len(be2.calls) > 1
+
+
 def test_several_greedy_steps_in_one_backend_call_change_no_decision():
     script = lambda r, d: 7 if (r == 1 and d == 2) else 100 + 10 * r + d
     prompts = [[1, 2], [3], [4, 5, 6]]
