@@ -1,8 +1,12 @@
 """Benchmark: decode tok/s at batch 8 (also 1 and 64) and prefill tok/s at 2,048 tokens, Llama 3.2 1B
 shape, bfloat16, random weights, one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference|plain-cpu]
                     [--shape 1b|3b|8b] [--layers N] [--batch B] [--only decode|prefill] [--no-graphs]
+
+`--impl plain-cpu` times the plain float32 implementation under tests/ on the CPU (no GPU needed), with
+the reference's own protocol: wall-clock prefill and generation times and tokens a second
+(models/llm/generate.go:227-229,275-282).
 
 A "step" is one decode step of the whole batch.  Prints ONE JSON line.  The weights a step reads
 (2.47 GB) are far larger than the L2 cache, which is stated in `config` as the timing hygiene rule asks.
@@ -112,12 +116,13 @@ def make_model_dir(tmp):
 
 
 PROMPT_LEN = 0     # > 0: every prompt has this many tokens (extra measurements at long contexts)
+PROMPT_RANGE = (128, 1024)     # prompt lengths are uniform in this range (inclusive), seed 3
 
 
 def prompts_for(batch, seed=3):
     import torch
     g = torch.Generator().manual_seed(seed)
-    lens = torch.randint(128, 1025, (batch,), generator=g).tolist()
+    lens = torch.randint(PROMPT_RANGE[0], PROMPT_RANGE[1] + 1, (batch,), generator=g).tolist()
     if PROMPT_LEN > 0:
         lens = [PROMPT_LEN] * batch
     return [torch.randint(0, MODEL["vocab_size"], (n,), generator=g).tolist() for n in lens]
@@ -203,16 +208,73 @@ def e2e_run(llm, batch, steps):
     return batch * steps / (res.generate_ms / 1e3)
 
 
+def plain_cpu_baseline() -> dict:
+    """The plain implementation (tests/plain_llama.py: whole sequences, no cache, float32, CPU) timed as the
+    reference times itself: prefill = the prompt's forward pass, generation = the tokens after the first,
+    tokens a second over the generation time (models/llm/generate.go:227-229,275-282).  Tiny A and Tiny B
+    with their workloads, and one single-token forward pass at the benchmark's layer sizes."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama as P
+    from tiny_configs import TINY, random_tokens, write_tiny
+    out = {"impl": "plain-cpu", "threads": torch.get_num_threads()}
+    for name, lens, n_new in (("A", (5, 17, 32), 16), ("B", (1, 9, 70, 130), 24)):
+        with tempfile.TemporaryDirectory() as tmp:
+            cfg, w = P.read_model(write_tiny(name, tmp))
+        pre = gen = 0.0
+        toks = 0
+        for i, n in enumerate(lens):
+            seq = random_tokens(n, cfg["vocab_size"], 100 + i)
+            t0 = time.perf_counter()
+            nxt = P.argmax(P.forward(cfg, w, seq)[-1])
+            t1 = time.perf_counter()
+            for _ in range(n_new - 1):
+                seq.append(nxt)
+                nxt = P.argmax(P.forward(cfg, w, seq)[-1])     # no cache: the whole sequence again
+            t2 = time.perf_counter()
+            pre += t1 - t0
+            gen += t2 - t1
+            toks += n_new - 1
+        out[f"tiny_{name}"] = {"requests": len(lens), "prompt_tokens": sum(lens), "new_tokens": n_new,
+                               "prefill_ms": round(pre * 1e3, 1), "generate_ms": round(gen * 1e3, 1),
+                               "tok_s": round(toks / gen, 2)}
+    # one token through all layers at the benchmark's sizes (what a decode step computes, without a cache to read)
+    m = MODEL
+    torch.manual_seed(2)
+    d, f, hq, hkv, hd = (m["hidden_size"], m["intermediate_size"], m["num_attention_heads"],
+                         m["num_key_value_heads"], m["head_dim"])
+    w = {"model.embed_tokens.weight": torch.randn(m["vocab_size"], d) * 0.02, "model.norm.weight": torch.ones(d)}
+    for i in range(m["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        for n, shape in (("self_attn.q_proj", (hq * hd, d)), ("self_attn.k_proj", (hkv * hd, d)),
+                         ("self_attn.v_proj", (hkv * hd, d)), ("self_attn.o_proj", (d, hq * hd)),
+                         ("mlp.gate_proj", (f, d)), ("mlp.up_proj", (f, d)), ("mlp.down_proj", (d, f))):
+            w[p + n + ".weight"] = torch.randn(shape) * 0.02
+        w[p + "input_layernorm.weight"] = torch.ones(d)
+        w[p + "post_attention_layernorm.weight"] = torch.ones(d)
+    times = []
+    for r in range(4):
+        t0 = time.perf_counter()
+        P.forward(m, w, [r + 1])
+        times.append(time.perf_counter() - t0)
+    ms = statistics.median(times[1:]) * 1e3
+    out["llama_1b_one_token"] = {"ms": round(ms, 1), "tok_s": round(1e3 / ms, 2), "weights_gb_fp32": round(
+        sum(t.numel() for t in w.values()) * 4 / 1e9, 2)}
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the contract's Llama 3.2 1B)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length instead of uniform[128,1024]")
+    ap.add_argument("--prompt-range", default="", help="LO,HI: prompt lengths uniform in [LO, HI] (default 128,1024)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the cache is sized for")
     ap.add_argument("--only", choices=["decode", "prefill"], help="run one small workload (for profiling) and stop")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
@@ -221,6 +283,9 @@ def main() -> int:
                           "computerex/dlgo is a Go module (no setup.py/pyproject.toml: pip cannot install it), no Go "
                           "toolchain is in the image, and its GPU path is Vulkan, which is unavailable on this box"}))
         return 0
+    if a.impl == "plain-cpu":
+        print(json.dumps(plain_cpu_baseline()))
+        return 0
     if a.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
@@ -228,8 +293,11 @@ def main() -> int:
     import dlgo_b200
     warmup = max(a.warmup, 3)
     pk = peaks()
-    global PROMPT_LEN
+    global PROMPT_LEN, PROMPT_RANGE
     PROMPT_LEN = a.prompt_len
+    if a.prompt_range:
+        lo, hi = (int(v) for v in a.prompt_range.split(","))
+        PROMPT_RANGE = (lo, hi)
     MODEL.update(SHAPES[a.shape])
     layers_of_config = MODEL["num_hidden_layers"]
     if a.layers > 0:
@@ -238,14 +306,19 @@ def main() -> int:
     tmp = tempfile.mkdtemp(prefix="dlgo_b200_bench_")
     try:
         make_model_dir(tmp)
-        llm = dlgo_b200.load_llm(tmp, CONTEXT, dtype="bfloat16", max_batch=64, cuda_graphs=not a.no_graphs)
+        llm = dlgo_b200.load_llm(tmp, a.context, dtype="bfloat16", max_batch=max(64, a.batch),
+                                 cuda_graphs=not a.no_graphs)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
     eng = llm.engine
     if a.only == "decode":
         r = decode_run(llm, a.batch, a.steps, warmup)
-        print(json.dumps({"only": "decode", "batch": a.batch, "ms_per_step": round(r["ms_per_step"], 4),
-                          "tok_s": round(r["tok_s"], 1), "launches": r["launches"]}))
+        kv = sum(2 * n.num_kv_heads * n.head_dim for n in eng.model.cache_needs()[0] if n is not None) * 2
+        gbs = (eng.weight_bytes() + a.batch * r["mean_context"] * kv) / (r["ms_per_step"] / 1e3) / 1e9
+        print(json.dumps({"only": "decode", "shape": a.shape, "layers": a.layers, "batch": a.batch,
+                          "mean_context": round(r["mean_context"], 1), "ms_per_step": round(r["ms_per_step"], 4),
+                          "tok_s": round(r["tok_s"], 1), "launches": r["launches"], "hbm_gbs": round(gbs, 1),
+                          "hbm_frac": round(gbs / pk["hbm_gbs"], 4), "peaks": pk["source"]}))
         return 0
     if a.only == "prefill":
         ms = prefill_run(llm, PREFILL_TOKENS, reps=max(1, a.steps))
@@ -275,7 +348,7 @@ def main() -> int:
             "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"],
             "head_dim": MODEL["head_dim"], "ffn": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"],
             "tied": MODEL["tie_word_embeddings"], "global_batch": a.batch,
-            "seq_len": CONTEXT, "prompt_len": ("uniform[128,1024] seed 3" if a.prompt_len <= 0 else a.prompt_len), "prefill_tokens": PREFILL_TOKENS,
+            "seq_len": a.context, "prompt_len": ("uniform[%d,%d] seed 3" % PROMPT_RANGE if a.prompt_len <= 0 else a.prompt_len), "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "none (1 GPU)", "l2": "inputs larger than L2 (weights read per step: %.2f GB)" % (weight_bytes / 1e9),
             "cuda_graph": True, "peaks": pk["source"]},
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 3 * 4 * a.batch,

@@ -64,7 +64,6 @@ class _EngineBackend:
     def __init__(self, engine: Engine):
         self.engine = engine
         self.max_seq_len = engine.max_seq_len
-        self._samplers = {}
 
     def take_slot(self) -> int:
         return self.engine.take_slot()
@@ -97,10 +96,7 @@ class _EngineBackend:
         if sampler.greedy:
             from .csrc import kernels
             return kernels.argmax_to_host(logits)    # kernels, copy and wait in one native call
-        smp = self._samplers.get(seed)
-        if smp is None:
-            smp = self._samplers[seed] = DeviceSampler(seed)
-        ids = smp.sample(logits, sampler, requests, draws, recent)
+        ids = DeviceSampler(seed).sample(logits, sampler, requests, draws, recent)   # holds the seed, nothing else
         return ids.cpu().tolist()   # the only device-to-host traffic of a step: one id per sequence
 
 

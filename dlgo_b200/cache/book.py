@@ -131,40 +131,79 @@ class CacheBook:
         return max(need - len(g.tables[slot]) for g in self.groups.values()) if self.groups else 0
 
     def reserve(self, slot: int, n_new: int) -> Dict[str, List[Tuple[int, int]]]:
-        """Room for positions ``len .. len+n_new-1``; returns {group: [(page index, page)]} of changes."""
-        cur = self.length(slot)
-        if n_new <= 0:
-            raise CacheError("a step must bring at least one token per sequence")
-        new_len = cur + n_new
-        if new_len > self.max_seq_len:
-            raise CacheError(f"sequence would reach {new_len} positions; the limit is {self.max_seq_len}")
-        need = (new_len + self.page_size - 1) // self.page_size
-        changes: Dict[str, List[Tuple[int, int]]] = {}
-        taken: List[Tuple[GroupBook, int]] = []
-        try:
-            for g in self.groups.values():
+        """Room for positions ``len .. len+n_new-1``; returns {group: [(page index, page)]} of changes.
+        A refusal changes nothing."""
+        return {g: [(idx, page) for _, idx, page in ch] for g, ch in self.reserve_batch([slot], [n_new]).items()}
+
+    def reserve_batch(self, slots: Sequence[int], n_new: Sequence[int]) -> Dict[str, List[Tuple[int, int, int]]]:
+        """:meth:`reserve` for all sequences of a step, all or nothing.
+
+        Every check (slots held, lengths within the limit, pages of every pool) is made before the
+        first page changes hands, so a refused step leaves the book exactly as it was: the reference
+        likewise refuses a request before it touches its cache (models/llm/generate.go:85-90).
+        Returns {group: [(slot, page index, page)]} of the entries that changed.
+        """
+        if len(slots) != len(n_new):
+            raise CacheError(f"{len(slots)} slots for {len(n_new)} token counts")
+        if len(set(slots)) != len(slots):
+            raise CacheError("a slot appears twice in one step")
+        ps = self.page_size
+        plan: List[Tuple[int, int, int]] = []        # (slot, current length, pages needed afterwards)
+        for slot, n in zip(slots, n_new):
+            cur = self.length(slot)
+            if n <= 0:
+                raise CacheError("a step must bring at least one token per sequence")
+            if cur + n > self.max_seq_len:
+                raise CacheError(f"sequence would reach {cur + n} positions; the limit is {self.max_seq_len}")
+            plan.append((slot, cur, (cur + n + ps - 1) // ps))
+        for g in self.groups.values():
+            takes = gives = 0
+            for slot, cur, need in plan:
                 table = g.tables[slot]
-                ch: List[Tuple[int, int]] = []
+                takes += max(0, need - len(table))
                 if g.window is not None:
-                    # keys at t <= cur - window are behind every query from position cur on
-                    dead_before = cur - g.window + 1  # first position still visible
-                    for idx in range(min(len(table), max(0, dead_before) // self.page_size)):
-                        if table[idx] >= 0:
-                            g.pool.give(table[idx])
-                            table[idx] = -1
-                            ch.append((idx, -1))
+                    dead = min(len(table), max(0, cur - g.window + 1) // ps)
+                    gives += sum(1 for idx in range(dead) if table[idx] >= 0)
+            if takes > g.pool.n_free + gives:
+                raise CacheError(f"cache is full: group {g.name} needs {takes} more pages for this step, "
+                                 f"{g.pool.n_free + gives} are free")
+        changes: Dict[str, List[Tuple[int, int, int]]] = {g: [] for g in self.groups}
+        # every give-back first, so that the pages a window released are there for the takes
+        for g in self.groups.values():
+            if g.window is None:
+                continue
+            for slot, cur, _ in plan:
+                table = g.tables[slot]
+                for idx in range(min(len(table), max(0, cur - g.window + 1) // ps)):
+                    if table[idx] >= 0:
+                        g.pool.give(table[idx])
+                        table[idx] = -1
+                        changes[g.name].append((slot, idx, -1))
+        for g in self.groups.values():
+            for slot, _, need in plan:
+                table = g.tables[slot]
                 while len(table) < need:
-                    p = g.pool.take()
-                    taken.append((g, p))
-                    table.append(p)
-                    ch.append((len(table) - 1, p))
-                changes[g.name] = ch
-        except CacheError:
-            for g, p in taken:  # leave the book as it was
-                g.tables[slot].remove(p)
-                g.pool.give(p)
-            raise
+                    table.append(g.pool.take())
+                    changes[g.name].append((slot, len(table) - 1, table[-1]))
         return changes
+
+    def pages_short(self, slots: Sequence[int], n_new: Sequence[int]) -> Optional[str]:
+        """``None`` if the pools hold the pages this step needs, else a sentence that says what is missing.
+        Slots must be held and distinct; nothing changes."""
+        ps = self.page_size
+        for g in self.groups.values():
+            takes = gives = 0
+            for slot, n in zip(slots, n_new):
+                cur = self.length(slot)
+                table = g.tables[slot]
+                takes += max(0, (cur + n + ps - 1) // ps - len(table))
+                if g.window is not None:
+                    dead = min(len(table), max(0, cur - g.window + 1) // ps)
+                    gives += sum(1 for idx in range(dead) if table[idx] >= 0)
+            if takes > g.pool.n_free + gives:
+                return (f"the cache is full: group {g.name} needs {takes} more pages for this step, "
+                        f"{g.pool.n_free + gives} are free")
+        return None
 
     def commit(self, slot: int, n_new: int) -> None:
         self._len[slot] = self.length(slot) + n_new

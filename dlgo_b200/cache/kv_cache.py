@@ -146,10 +146,8 @@ class KVCache:
                     return
             except KeyError:
                 pass                        # a slot that is not held: the full path reports it
-        rows: Dict[str, List[Tuple[int, int, int]]] = {}
-        for slot, n in zip(slots, n_new):
-            for g, ch in self.book.reserve(slot, n).items():
-                rows.setdefault(g, []).extend((slot, idx, page) for idx, page in ch)
+        # all or nothing: a refused step takes no page, so the device tables never fall behind the book
+        rows = self.book.reserve_batch(slots, n_new)
         for g, ch in rows.items():
             if not ch:
                 continue
@@ -157,6 +155,10 @@ class KVCache:
             idx = torch.tensor([s * pt.shape[1] + i for s, i, _ in ch], dtype=torch.int64)
             val = torch.tensor([p for _, _, p in ch], dtype=torch.int32)
             pt.view(-1).index_copy_(0, idx.to(self.device, non_blocking=True), val.to(self.device, non_blocking=True))
+
+    def pages_short(self, slots: Sequence[int], n_new: Sequence[int]) -> Optional[str]:
+        """``None`` if the pools hold the pages this step needs, else what is missing (nothing changes)."""
+        return self.book.pages_short(slots, n_new)
 
     def commit(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         for slot, n in zip(slots, n_new):

@@ -265,8 +265,7 @@ class LlamaConfig:
                 block="prenorm",
                 mixer=mixer,
                 ffn=ffn,
-                mixer_norm=norm,
-                ffn_norm=norm,
+                norms={"mixer_norm": norm, "ffn_norm": norm},
                 names={"mixer": "self_attn.", "ffn": "mlp.",
                        "mixer_norm": "input_layernorm.", "ffn_norm": "post_attention_layernorm."},
             ))

@@ -35,18 +35,31 @@ class PartSpec:
 class LayerSpec:
     """One layer: an arrangement ("block") of a mixer, a feed-forward and norms.
 
-    ``prefix`` is the layer's tensor-name prefix in the weight file; ``names``
-    maps each role (``mixer``, ``ffn``, ``mixer_norm``, ``ffn_norm``) to the
-    sub-prefix its tensors carry below ``prefix``.
+    ``norms`` maps a role name to a norm, as many as the block reads: the
+    pre-norm block reads ``mixer_norm`` and ``ffn_norm``; a block with norms
+    after its parts as well (the reference's ``PostAttnNorm`` / ``PostFFNNorm``,
+    models/llm/forward.go:158-182) names four.  ``mixer`` or ``ffn`` may be
+    ``None`` for a block that has no such part.  ``prefix`` is the layer's
+    tensor-name prefix in the weight file; ``names`` maps each role (``mixer``,
+    ``ffn`` and every norm role) to the sub-prefix its tensors carry below
+    ``prefix``.
     """
 
     prefix: str
     block: str
-    mixer: PartSpec
-    ffn: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    mixer: Optional[PartSpec]
+    ffn: Optional[PartSpec]
+    norms: Mapping[str, PartSpec]
     names: Mapping[str, str]
+
+    def roles(self) -> Sequence[str]:
+        """Every role of the layer that has a part, norms first in their own order."""
+        out = list(self.norms)
+        if self.mixer is not None:
+            out.append("mixer")
+        if self.ffn is not None:
+            out.append("ffn")
+        return out
 
 
 @dataclass(frozen=True)
@@ -87,6 +100,12 @@ class ArchitectureSpec:
             raise ValueError("architecture has no layers")
         if not self.order:
             raise ValueError("architecture has an empty run order")
+        for j, ls in enumerate(self.layers):
+            missing = [r for r in ls.roles() if r not in ls.names]
+            if missing:
+                raise ValueError(f"layer {j}: no tensor-name prefix for the role(s) {', '.join(missing)}")
+            if set(ls.norms) & {"mixer", "ffn"}:
+                raise ValueError(f"layer {j}: a norm cannot take the role name 'mixer' or 'ffn'")
         for i, e in enumerate(self.order):
             if not 0 <= e.layer < n:
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {n} layers")

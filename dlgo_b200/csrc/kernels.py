@@ -489,6 +489,9 @@ def check_device_errors() -> None:
             if v != 0:
                 raise KernelError(f"a tensor-core kernel ({lib}) gave up a bounded wait on the device; "
                                   "its results are invalid")
+    if "rope_append" in build._loaded and build._loaded["rope_append"].dlgo_rope_append_error() != 0:
+        raise KernelError("a token's position had no page in the cache's table: its keys and values were not "
+                          "stored and the step's results are invalid")
 
 
 # ------------------------------------------------------------ decode attention

@@ -17,6 +17,10 @@
 
 namespace dlgo {
 
+// Set when a token's position had no page in the table (-1): the append is skipped, never written
+// through a negative page number, and the host reads the word (dlgo_rope_append_error).
+__device__ int g_rope_append_error = 0;
+
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, const int* __restrict__ token_pos,
@@ -37,7 +41,11 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int ld, const float* __r
   if (write_cache) {
     const int slot = seq_slot[token_seq[t]];
     const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-    const size_t base = ((size_t)page * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+    if (page < 0) {
+      write_cache = 0;
+      if (threadIdx.x == 0) atomicExch(&g_rope_append_error, 1);
+    }
+    const size_t base = ((size_t)max(page, 0) * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
     kdst = kpages + base;
     vdst = vpages + base;
   }
@@ -141,7 +149,11 @@ __global__ void rope_append_vec_kernel(T* __restrict__ qkv, int ld, const float*
   if (write_cache) {
     const int slot = seq_slot[token_seq[t]];
     const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-    base = ((size_t)page * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
+    if (page < 0) {
+      write_cache = 0;
+      if (threadIdx.x == 0) atomicExch(&g_rope_append_error, 1);
+    }
+    base = ((size_t)max(page, 0) * Hkv) * page_size * hd + (size_t)(pos % page_size) * hd;
   }
   pdl_wait();
   for (int it = threadIdx.x; it < items; it += blockDim.x) {
@@ -211,7 +223,10 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
       const int page = page_table[(size_t)slot * max_pages + pos / page_size];
       const bool is_k = head < Hq + Hkv;
       const int kvh = is_k ? head - Hq : head - Hq - Hkv;
-      dst = (is_k ? kpages : vpages) + (((size_t)page * Hkv + kvh) * page_size + (size_t)(pos % page_size)) * hd;
+      if (page >= 0)
+        dst = (is_k ? kpages : vpages) + (((size_t)page * Hkv + kvh) * page_size + (size_t)(pos % page_size)) * hd;
+      else if (lane == 0)
+        atomicExch(&g_rope_append_error, 1);
     }
   }
   // The attention kernel that follows reads this sequence's cached keys and values; the warp of a
@@ -356,4 +371,12 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
   else
     return DLGO_ERR_DTYPE;
   return launch_status();
+}
+
+// 1 if an append was skipped since the last call because its position had no page (clears the word).
+DLGO_EXPORT int dlgo_rope_append_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_rope_append_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_rope_append_error, &zero, sizeof(int));
+  return v;
 }

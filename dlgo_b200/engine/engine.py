@@ -17,6 +17,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from ..cache.book import CacheError
 from ..cache.kv_cache import KVCache, PAGE_SIZE
 from ..config.registry import load_config
 from ..weights.loader import DictSource, WeightSource
@@ -32,11 +33,13 @@ class StepError(ValueError):
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, dtype="bfloat16", device="cuda:0",
                  max_tokens: Optional[int] = None, max_seq_len: Optional[int] = None, cuda_graphs: bool = True,
-                 default_batch: int = 1, spec: Any = None, tensors: Optional[Dict[str, torch.Tensor]] = None):
+                 default_batch: int = 1, spec: Any = None, tensors: Optional[Dict[str, torch.Tensor]] = None,
+                 max_slots: Optional[int] = None):
         """``max_tokens``: positions live sequences may hold in total (each sequence's count
         rounded up to a multiple of 64); it sizes the cache.  ``max_seq_len``: longest single
         sequence, clamped to the model's context like the reference's ``maxSeqLen``
-        (models/llm/generate.go:56-58).
+        (models/llm/generate.go:56-58).  ``max_slots``: sequences that may be live at once (default:
+        one per page of the cache, but no more than keep a group's page table within 64 MB).
 
         A model comes from ``model_dir`` (config.json chooses the architecture), or from an
         :class:`ArchitectureSpec` and its tensors given in memory (``spec``, ``tensors``)."""
@@ -68,8 +71,14 @@ class Engine:
             free, _ = torch.cuda.mem_get_info(self.runtime.device)
             fits = max(PAGE_SIZE, int(free * 0.5) // max(per_position, 1))
             max_tokens = max(min(max_seq_len * max(default_batch, 1), fits), min(max_seq_len, fits))
+        n_pages = max(1, (max_tokens + PAGE_SIZE - 1) // PAGE_SIZE)
+        if max_slots is None or max_slots <= 0:
+            # a live sequence holds at least one page, so more slots than pages are never used; a slot's row
+            # of the page table has one entry per page of the longest sequence
+            row_bytes = 4 * ((min(max_seq_len, n_pages * PAGE_SIZE) + PAGE_SIZE - 1) // PAGE_SIZE)
+            max_slots = min(n_pages, max(default_batch, 256, (64 << 20) // row_bytes))
         self.cache = KVCache(needs, borrows, states, max_tokens, max_seq_len, self.runtime.dtype, self.runtime.device,
-                             PAGE_SIZE)
+                             PAGE_SIZE, n_slots=max_slots)
         self.max_seq_len = self.cache.max_seq_len
         self.vocab_size = self.spec.vocab_size
         self.cuda_graphs = cuda_graphs
@@ -110,6 +119,9 @@ class Engine:
                 for w in want[i]:
                     if not 0 <= int(w) < len(tk):
                         raise StepError(f"sequence {i}: wanted place {w} is outside its {len(tk)} tokens")
+        short = self.cache.pages_short(slots, [len(t) for t in tokens])
+        if short is not None:
+            raise StepError(short)      # refused before anything changes, like every other check
 
     @torch.no_grad()
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
@@ -216,8 +228,8 @@ class Engine:
         with torch.cuda.device(self.runtime.device):
             try:
                 self.cache.reserve(slots, [n_steps] * len(slots))     # pages for the whole run, mirrored once
-            except Exception:
-                return None
+            except CacheError:
+                return None             # no room for the whole run; nothing was taken (all or nothing)
             if _draw is None:
                 out = greedy_with_graph(self, slots, ids, starts, n_steps, stop_ids)
             else:
@@ -239,7 +251,7 @@ class Engine:
             total += t.numel() * t.element_size()
 
         for blk in self.model.blocks:
-            for part in (blk.mixer, blk.ffn, blk.mixer_norm, blk.ffn_norm):
+            for part in blk.parts().values():
                 for v in vars(part).values():
                     if isinstance(v, torch.Tensor):
                         add(v)

@@ -17,6 +17,21 @@ from ..csrc import kernels
 from .runtime import StepContext
 
 
+class NotOnHost:
+    """Stands where a captured step has no host-side value (slots, start positions): a replay serves
+    whatever sequences the step brings, so a part must read ``ctx.seq_slot`` and ``ctx.token_pos`` on
+    the device instead.  Any use of it says so."""
+
+    def __init__(self, what: str):
+        self._what = what
+
+    def _refuse(self, *a: Any, **k: Any):
+        raise RuntimeError(f"{self._what} is not known on the host inside a captured decode step: read the "
+                           "device tensors ctx.seq_slot / ctx.token_pos (or build the engine with cuda_graphs=False)")
+
+    __iter__ = __len__ = __getitem__ = __bool__ = __index__ = _refuse
+
+
 class DecodeGraph:
     def __init__(self, engine: Any, batch: int):
         rt = engine.runtime
@@ -29,10 +44,14 @@ class DecodeGraph:
         self.want_rows = torch.arange(batch, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
             runtime=rt, n_tokens=batch, n_seqs=batch, token_ids=self.meta[0], token_pos=self.meta[1],
-            token_seq=self.token_seq, seq_slot=self.meta[2], seq_slots_host=[0] * batch, seq_start_host=[0] * batch,
+            token_seq=self.token_seq, seq_slot=self.meta[2], seq_slots_host=NotOnHost("a sequence's slot"),
+            seq_start_host=NotOnHost("a sequence's start position"),
             seq_ntok_host=[1] * batch, decode=True, max_len=engine.max_seq_len, captured=True,
             capacity=engine.max_seq_len, want_identity=True)
-        self.ctx.tiles(1)  # built before capture: a capture may not copy from pageable host memory
+        # one token per sequence: the tile table is the same for every replay (built before capture: a
+        # capture may not copy from pageable host memory)
+        self.ctx._tiles[(1, False)] = (torch.stack([self.token_seq, self.token_seq, torch.ones_like(self.token_seq)],
+                                                   dim=1).contiguous(), batch, 1)
         self.graph = torch.cuda.CUDAGraph()
         self.logits = None
         self.engine = engine

@@ -14,7 +14,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..config.spec import ArchitectureSpec, LayerSpec
+from ..config.spec import ArchitectureSpec, PartSpec
 from ..parts import registry as R
 from ..parts.base import Block, CacheNeed, ParamSpec, Part, StateNeed
 
@@ -29,16 +29,15 @@ class CausalLM:
         self.positions = {name: R.POSITION_ENCODINGS.build(ps) for name, ps in spec.position_encodings.items()}
         self.blocks: List[Block] = []
         for ls in spec.layers:
-            mixer = R.MIXERS.build(ls.mixer)
-            ffn = R.FEED_FORWARDS.build(ls.ffn)
-            mixer_norm = R.NORMS.build(ls.mixer_norm)
-            ffn_norm = R.NORMS.build(ls.ffn_norm)
-            self.blocks.append(R.BLOCKS.build(ls_block(ls, mixer, ffn, mixer_norm, ffn_norm)))
+            mixer = R.MIXERS.build(ls.mixer) if ls.mixer is not None else None
+            ffn = R.FEED_FORWARDS.build(ls.ffn) if ls.ffn is not None else None
+            norms = {role: R.NORMS.build(ns) for role, ns in ls.norms.items()}
+            self.blocks.append(R.BLOCKS.build(PartSpec(ls.block, {"mixer": mixer, "ffn": ffn, "norms": norms})))
         self.order = list(spec.order)
         for i, e in enumerate(self.order):
             if e.cache_of is not None:
-                mine = self.blocks[e.layer].mixer.cache_need()
-                theirs = self.blocks[self.order[e.cache_of].layer].mixer.cache_need()
+                mine = self._cache_need(e.layer)
+                theirs = self._cache_need(self.order[e.cache_of].layer)
                 if mine is None or theirs is None or (mine.num_kv_heads, mine.head_dim) != (
                         theirs.num_kv_heads, theirs.head_dim):
                     raise ValueError(f"run entry {i} cannot read the cache of entry {e.cache_of}: their shapes differ")
@@ -48,10 +47,8 @@ class CausalLM:
     def _named_parts(self) -> List[Tuple[str, Part]]:
         out: List[Tuple[str, Part]] = [(self.spec.embedding_prefix, self.embedding)]
         for ls, blk in zip(self.spec.layers, self.blocks):
-            out.append((ls.prefix + ls.names["mixer_norm"], blk.mixer_norm))
-            out.append((ls.prefix + ls.names["mixer"], blk.mixer))
-            out.append((ls.prefix + ls.names["ffn_norm"], blk.ffn_norm))
-            out.append((ls.prefix + ls.names["ffn"], blk.ffn))
+            for role, part in blk.parts().items():      # whatever the block declares: any number of norms
+                out.append((ls.prefix + ls.names[role], part))
         out.append((self.spec.final_norm_prefix, self.final_norm))
         out.append((self.spec.head_prefix, self.head))
         return out
@@ -67,6 +64,10 @@ class CausalLM:
                 table[name] = ps
         return table
 
+    def _cache_need(self, layer: int) -> Optional[CacheNeed]:
+        mixer = self.blocks[layer].mixer
+        return mixer.cache_need() if mixer is not None else None
+
     def cache_needs(self) -> Tuple[List[Optional[CacheNeed]], List[Optional[int]], Dict[int, StateNeed]]:
         """Per run entry: what it keeps per position, whose cache it borrows, its fixed-size state."""
         needs: List[Optional[CacheNeed]] = []
@@ -74,9 +75,9 @@ class CausalLM:
         states: Dict[int, StateNeed] = {}
         for i, e in enumerate(self.order):
             mixer = self.blocks[e.layer].mixer
-            needs.append(mixer.cache_need())
+            needs.append(mixer.cache_need() if mixer is not None else None)
             borrows.append(e.cache_of)
-            sn = mixer.state_need()
+            sn = mixer.state_need() if mixer is not None else None
             if sn is not None:
                 states[i] = sn
         return needs, borrows, states
@@ -121,8 +122,3 @@ class CausalLM:
                 ctx.settle(residual)
             x = self.final_norm.forward(residual, want_rows)
         return self.head.forward(x)
-
-
-def ls_block(ls: LayerSpec, mixer: Any, ffn: Any, mixer_norm: Any, ffn_norm: Any):
-    from ..config.spec import PartSpec
-    return PartSpec(ls.block, {"mixer": mixer, "ffn": ffn, "mixer_norm": mixer_norm, "ffn_norm": ffn_norm})

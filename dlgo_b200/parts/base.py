@@ -135,13 +135,26 @@ class FeedForward(Part):
 
 
 class Block:
-    """Arrangement of one layer's parts."""
+    """Arrangement of one layer's parts.
 
-    def __init__(self, mixer: Mixer, ffn: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+    ``norms`` maps the role names of the layer's description to the norms built for them, as many as
+    the arrangement reads; ``mixer`` or ``ffn`` is ``None`` where the layer has none.  A subclass's
+    ``forward`` decides who reads the residual stream when.
+    """
+
+    def __init__(self, mixer: Optional[Mixer], ffn: Optional[FeedForward], norms: Mapping[str, Norm]):
         self.mixer = mixer
         self.ffn = ffn
-        self.mixer_norm = mixer_norm
-        self.ffn_norm = ffn_norm
+        self.norms: Dict[str, Norm] = dict(norms)
+
+    def parts(self) -> Dict[str, Part]:
+        """Every part of the layer by role (norm roles, ``mixer``, ``ffn``): what holds its tensors."""
+        out: Dict[str, Part] = dict(self.norms)
+        if self.mixer is not None:
+            out["mixer"] = self.mixer
+        if self.ffn is not None:
+            out["ffn"] = self.ffn
+        return out
 
     def forward(self, residual: torch.Tensor, ctx: "Any", cache: "Any", state: Optional[torch.Tensor],
                 positions: Mapping[str, PositionEncoding]) -> None:

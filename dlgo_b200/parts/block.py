@@ -33,6 +33,15 @@ def norm_of(norm: Any, residual: torch.Tensor, ctx: Any, reader: Any = None) -> 
 class PreNormBlock(Block):
     handles_pending = True   # reads the residual only through norm_of
 
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any]):
+        super().__init__(mixer, ffn, norms)
+        missing = [r for r in ("mixer_norm", "ffn_norm") if r not in self.norms]
+        if missing or mixer is None or ffn is None:
+            raise ValueError("a pre-norm block needs a mixer, a feed-forward and the norms 'mixer_norm' and 'ffn_norm'"
+                             + (f" (missing: {', '.join(missing)})" if missing else ""))
+        self.mixer_norm = self.norms["mixer_norm"]
+        self.ffn_norm = self.norms["ffn_norm"]
+
     def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
                 positions: Mapping[str, PositionEncoding]) -> None:
         x = norm_of(self.mixer_norm, residual, ctx, self.mixer)

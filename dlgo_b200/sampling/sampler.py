@@ -7,9 +7,7 @@ inverse-CDF draw (:167-181).  Defaults 0.7 / 40 / 0.9 / 0 / 1.1 (:19-27).
 
 Greedy, the temperature draw and all filters are CUDA kernels of this package
 (csrc/sampling.cu); only token ids leave the device.  Filters set logits to
--inf, which the draw treats as probability zero.  The ``apply_*`` functions
-below restate the filters with tensor operations for host-side use and tests;
-generation does not call them.
+-inf, which the draw treats as probability zero.
 
 The uniform number of a draw is a counter-based function of (seed, request
 index, index of the draw within the request), so what a request samples does
@@ -51,52 +49,6 @@ class SamplerConfig:
 
 
 RECENT_WINDOW = 64  # tokens the repetition penalty looks back over (models/llm/generate.go:143)
-
-
-def apply_repetition_penalty(logits: torch.Tensor, recent: Sequence[Sequence[int]], penalty: float) -> None:
-    """In place: positive logits of recent tokens are divided by the penalty, negative ones multiplied."""
-    if penalty <= 1.0:
-        return
-    V = logits.shape[1]
-    for r, toks in enumerate(recent):
-        ids = sorted({int(t) for t in toks if 0 <= int(t) < V})
-        if not ids:
-            continue
-        idx = torch.tensor(ids, dtype=torch.int64, device=logits.device)
-        v = logits[r, idx]
-        logits[r, idx] = torch.where(v > 0, v / penalty, v * penalty)
-
-
-def apply_top_k(logits: torch.Tensor, k: int) -> None:
-    """In place: everything below the k-th largest value becomes -inf (ties at the cutoff stay)."""
-    if k <= 0 or k >= logits.shape[1]:
-        return
-    kth = torch.topk(logits, k, dim=1).values[:, -1:]
-    logits.masked_fill_(logits < kth, float("-inf"))
-
-
-def apply_top_p(logits: torch.Tensor, p: float) -> None:
-    """In place: keep the shortest prefix of the descending-probability order whose sum reaches p."""
-    if p >= 1.0:
-        return
-    probs = torch.softmax(logits, dim=1)
-    sp, order = torch.sort(probs, dim=1, descending=True, stable=True)
-    cum = torch.cumsum(sp, dim=1)
-    # position i is kept if the sum BEFORE it is still below p
-    keep_sorted = (cum - sp) < p
-    keep_sorted[:, 0] = True
-    keep = torch.zeros_like(keep_sorted)
-    keep.scatter_(1, order, keep_sorted)
-    logits.masked_fill_(~keep, float("-inf"))
-
-
-def apply_min_p(logits: torch.Tensor, min_p: float) -> None:
-    """In place: drop tokens whose probability is below min_p times the largest."""
-    if min_p <= 0:
-        return
-    probs = torch.softmax(logits, dim=1)
-    thr = probs.max(dim=1, keepdim=True).values * min_p
-    logits.masked_fill_(probs < thr, float("-inf"))
 
 
 def temperature_rows(cfg: SamplerConfig, rows: int, device: torch.device) -> torch.Tensor:

@@ -118,3 +118,72 @@ def test_random_walk_never_loses_or_doubles_anything():
         for s, n in live.items():
             assert b.length(s) == n
     assert set(b.live_slots()) == set(live)
+
+
+def test_a_refused_batch_takes_nothing():
+    # two sequences at a page's end, one free page: the step that would need two pages is refused whole
+    b = CacheBook([("full", None)], n_pages=3, page_size=64, n_slots=2, max_seq_len=256)
+    s0, s1 = b.take_slot(), b.take_slot()
+    b.reserve_batch([s0, s1], [64, 64])
+    b.commit(s0, 64)
+    b.commit(s1, 64)
+    before = (b.table("full", s0), b.table("full", s1), b.groups["full"].pool.n_free)
+    assert b.pages_short([s0, s1], [1, 1]) is not None
+    with pytest.raises(CacheError, match="full"):
+        b.reserve_batch([s0, s1], [1, 1])
+    assert (b.table("full", s0), b.table("full", s1), b.groups["full"].pool.n_free) == before
+    b.check()
+    with pytest.raises(CacheError, match="limit"):
+        b.reserve_batch([s0, s1], [1, 500])          # the second slot's fault: the first keeps its pages
+    assert (b.table("full", s0), b.table("full", s1), b.groups["full"].pool.n_free) == before
+    with pytest.raises(CacheError, match="twice"):
+        b.reserve_batch([s0, s0], [1, 1])
+    ch = b.reserve_batch([s0], [1])
+    assert ch["full"] == [(s0, 1, 2)] and b.pages_short([s1], [1]) is not None
+    b.check()
+
+
+def test_a_window_gives_back_before_the_batch_takes():
+    # the windowed pool is full, but the step itself releases the pages it then needs
+    b = CacheBook([("win", 64)], n_pages=4, page_size=64, n_slots=2, max_seq_len=1024)
+    s0, s1 = b.take_slot(), b.take_slot()
+    b.reserve_batch([s0, s1], [128, 128])
+    b.commit(s0, 128)
+    b.commit(s1, 128)
+    assert b.groups["win"].pool.n_free == 0 and b.pages_short([s0, s1], [1, 1]) is None
+    ch = b.reserve_batch([s0, s1], [1, 1])["win"]
+    assert sorted(c for c in ch if c[2] == -1) == [(s0, 0, -1), (s1, 0, -1)]
+    assert sorted((c[0], c[1]) for c in ch if c[2] >= 0) == [(s0, 2), (s1, 2)]
+    b.check()
+
+
+def test_device_tables_follow_the_book_after_a_refusal():
+    # the cache's mirror of the page tables (on the CPU here: no kernel runs) equals the book whatever was refused
+    import torch
+    from dlgo_b200.cache import KVCache
+    from dlgo_b200.parts.base import CacheNeed
+    kv = KVCache([CacheNeed("full", 1, 16)], [None], {}, max_tokens=3 * 64, max_seq_len=192, dtype=torch.float32,
+                 device=torch.device("cpu"), n_slots=2)
+    a, c = kv.take_slot(), kv.take_slot()
+    kv.reserve([a, c], [64, 64])
+    kv.commit([a, c], [64, 64])
+
+    def mirrored():
+        for s in (a, c):
+            row = kv.page_tables["full"][s].tolist()
+            held = kv.book.table("full", s)
+            assert row[:len(held)] == held and all(p == -1 for p in row[len(held):]), (s, row, held)
+
+    mirrored()
+    with pytest.raises(CacheError, match="full"):
+        kv.reserve([a, c], [1, 1])
+    mirrored()
+    assert kv.book.table("full", a) == [0] and kv.pages_short([a], [1]) is None
+    kv.reserve([a], [1])
+    kv.commit([a], [1])
+    mirrored()
+    assert kv.book.table("full", a)[1] >= 0
+    kv.free_slot(a)
+    kv.free_slot(c)
+    kv.book.check()
+    assert kv.page_tables["full"].eq(-1).all()

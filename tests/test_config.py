@@ -96,7 +96,7 @@ def test_architecture_spec_carries_every_constant():
     m = spec.layers[0].mixer.params
     assert (m["num_heads"], m["num_kv_heads"], m["head_dim"]) == (3, 1, 32)
     assert abs(m["scale"] - 32 ** -0.5) < 1e-12
-    assert spec.layers[0].mixer_norm.params["eps"] == 1e-6
+    assert spec.layers[0].norms["mixer_norm"].params["eps"] == 1e-6
     assert spec.position_encodings["rope"].params["scaling"]["factor"] == 4.0
     assert spec.head.params["tied_to"] is None
     assert config_from_dict(TINY["A"]["cfg"]).architecture_spec().head.params["tied_to"] == "model.embed_tokens.weight"
@@ -112,3 +112,19 @@ def test_run_order_is_validated():
         dataclasses.replace(spec, order=[RunEntry(0, cache_of=1), RunEntry(1)]).validate()
     with pytest.raises(ValueError, match="borrows"):
         dataclasses.replace(spec, order=[RunEntry(0), RunEntry(1, cache_of=0), RunEntry(0, cache_of=1)]).validate()
+
+
+def test_command_line_writes_and_describes_a_model_folder(tmp_path):
+    # the commands that need no GPU: random-model and info (python -m dlgo_b200 ...)
+    import json
+    from dlgo_b200.__main__ import main
+    from tiny_configs import TINY
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY["A"]["cfg"]))
+    out = tmp_path / "model"
+    assert main(["random-model", "--config", str(cfg_path), "--seed", "3", "--out", str(out)]) == 0
+    assert (out / "config.json").exists() and (out / "model.safetensors").exists()
+    assert main(["info", str(out)]) == 0
+    # generate refuses bad options before it looks for a GPU
+    assert main(["generate", str(out), "--max-tokens", "0", "--prompt-ids", "1,2"]) == 2
+    assert main(["generate", str(out)]) == 2

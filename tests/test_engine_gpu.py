@@ -323,3 +323,38 @@ def test_sampled_steps_in_one_native_call_draw_what_single_steps_draw(model_dirs
     llm.engine.cache.book.check()
     assert llm.engine.cache.book.live_slots() == []
 
+
+
+def _cli(*args):
+    import subprocess
+    import sys
+    from traces import ROOT
+    p = subprocess.run([sys.executable, "-m", "dlgo_b200", *args], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    return p.stdout, p.stderr
+
+
+def test_the_command_line_generates_what_the_python_entry_point_does(model_dirs):
+    # `python -m dlgo_b200 generate` as a user runs it (the reference's counterpart:
+    # examples/simple_chat/main.go:19-22 over dlgo.go:51-115), greedy and sampled, plain and streamed
+    import dlgo_b200
+    d = model_dirs["B"]
+    p1, p2 = random_tokens(9, 384, 41), random_tokens(3, 384, 42)
+    ids = [",".join(map(str, p1)), " ".join(map(str, p2))]
+    llm = dlgo_b200.load_llm(d, dtype="bfloat16")
+    out, err = _cli("generate", d, "--prompt-ids", ids[0], "--prompt-ids", ids[1], "--max-tokens", "6", "--greedy",
+                    "--ignore-eos")
+    assert "Model: LlamaForCausalLM (3 layers" in err
+    want = llm.generate([p1, p2], max_tokens=6, greedy=True, ignore_eos=True)
+    assert [[int(t) for t in line.split()] for line in out.strip().splitlines()] == want
+    out, _ = _cli("generate", d, "--prompt-ids", ids[0], "--prompt-ids", ids[1], "--max-tokens", "5", "--temp", "0.8",
+                  "--seed", "7", "--stream", "--ignore-eos")
+    want = llm.generate([p1, p2], max_tokens=5, temperature=0.8, seed=7, ignore_eos=True)
+    seen = [[], []]
+    for line in out.strip().splitlines():
+        r, t = line.split("\t")
+        seen[int(r)].append(int(t))
+    assert seen == want
+    out, err = _cli("generate", d, "--prompt-ids", ids[1], "--max-tokens", "4", "--greedy", "--bench", "--ctx", "64",
+                    "--dtype", "float32", "--ignore-eos")
+    assert len(out.split()) == 4 and "tok/s" in err and "prompt tokens: 3" in err

@@ -141,3 +141,152 @@ def test_llama_3b_layer_sizes_against_the_plain_implementation(big3, dtype):
     eng = Engine(d, dtype=dtype, max_tokens=512, max_seq_len=256)
     eng.cache.poison()
     run(eng, reqs, refs, dtype, "3B sizes")
+
+
+# ---------------------------------------------------------------------------------------------------
+# The schedule that decoding at real sizes takes: several sequences of unequal lengths, some longer than
+# 512 tokens (so that decode attention works in slices), prompts in one step and then one token each
+# through the captured graph; contractions cut into K-slices that add themselves into the residual, the
+# q/k/v sum that the rotation reads and clears.  Two layers keep the plain implementation quick.
+CFG_2L = dict(CFG, num_hidden_layers=2)
+BATCH_LENS = [530, 37, 700, 8, 129, 612, 64, 250]     # prompt lengths; 8 more tokens are decoded
+N_DECODE = 8
+
+
+@pytest.fixture(scope="module")
+def batch8(tmp_path_factory):
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.weights import write_random_model
+    d = str(tmp_path_factory.mktemp("llama_batch8"))
+    write_random_model(config_from_dict(CFG_2L), 2, d, device="cuda")
+    g = torch.Generator().manual_seed(11)
+    reqs = {f"r{i}": torch.randint(0, CFG_2L["vocab_size"], (n + N_DECODE,), generator=g).tolist()
+            for i, n in enumerate(BATCH_LENS)}
+    cfg, w = P.read_model(d)
+    freqs = P.rope_frequencies(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"])
+    refs = {}
+    for (rid, toks), n in zip(reqs.items(), BATCH_LENS):
+        x = P.embedding(w["model.embed_tokens.weight"], toks)
+        for i in range(cfg["num_hidden_layers"]):
+            x = P.layer(x, w, f"model.layers.{i}.", cfg, freqs)
+        xn = P.rmsnorm(x[n - 1:], w["model.norm.weight"], cfg["rms_norm_eps"])
+        refs[rid] = P.linear(xn, w["model.embed_tokens.weight"])       # rows n-1 .. n+7: the prompt's end, 8 decoded
+    del w
+    return d, reqs, refs
+
+
+def batch_steps(reqs):
+    ids = list(reqs)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:n], "want": [n - 1]} for r, n in zip(ids, BATCH_LENS)],
+              "end": []}]
+    for j in range(N_DECODE):
+        steps.append({"step": j + 1, "entries": [{"id": r, "tokens": [reqs[r][n + j]], "want": [0]}
+                                                  for r, n in zip(ids, BATCH_LENS)],
+                      "end": ids if j == N_DECODE - 1 else []})
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dtype):
+    from dlgo_b200.csrc import kernels
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = batch8
+    eng = Engine(d, dtype=dtype, max_tokens=8 * 1024, max_seq_len=1024)      # grids sized for 16 pages a sequence
+    eng.cache.poison()
+    outs = T.run_in_process(eng, batch_steps(reqs))
+    assert 8 in eng._graphs, "the decode steps should have replayed the graph of batch 8"
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for i, rid in enumerate(reqs):
+        ref = refs[rid]
+        scale = float(ref.abs().max())
+        for s in range(N_DECODE + 1):
+            got = outs[s][i]
+            assert torch.isfinite(got).all(), (rid, s)
+            err = float((got - ref[s]).abs().max())
+            assert err <= tol * scale, f"{rid} ({BATCH_LENS[i]} tokens), step {s} ({dtype}): {err:.3e} > {tol * scale:.3e}"
+    kernels.check_device_errors()
+
+
+def test_default_cache_sizing_and_a_very_long_capacity(batch8):
+    # no max_tokens: the cache is sized from the context (131072 positions here), so a captured step's grids
+    # cover 2048 pages a sequence and decode attention takes its many-slices path
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = batch8
+    eng = Engine(d, dtype="bfloat16")
+    assert eng.max_seq_len == 131072 and eng.cache.n_pages >= 2048
+    ids = list(reqs)[:3]
+    lens = BATCH_LENS[:3]
+    slots = [eng.take_slot() for _ in ids]
+    lg = [eng.step(slots, [reqs[r][:n] for r, n in zip(ids, lens)]).float().cpu()]
+    for j in range(3):
+        lg.append(eng.step(slots, [[reqs[r][n + j]] for r, n in zip(ids, lens)]).float().cpu().clone())
+    for s in slots:
+        eng.free_slot(s)
+    for i, rid in enumerate(ids):
+        scale = float(refs[rid].abs().max())
+        for s in range(4):
+            assert float((lg[s][i] - refs[rid][s]).abs().max()) <= 3e-2 * scale, (rid, s)
+
+
+def test_native_runs_at_real_sizes_agree_with_single_steps(batch8):
+    # greedy and sampled runs of several steps in one native call (what generate() uses) against the same
+    # engine stepped one by one.  In bfloat16 the K-slices add themselves into the residual in no fixed
+    # order, so two runs may differ in the last bits: a different token is accepted only where the two
+    # candidates' logits are nearly tied.
+    from dlgo_b200.csrc import kernels
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, _ = batch8
+    eng = Engine(d, dtype="bfloat16", max_tokens=8 * 1024, max_seq_len=1024)
+    ids = list(reqs)
+    prompts = [reqs[r][:n] for r, n in zip(ids, BATCH_LENS)]
+
+    def start():
+        slots = [eng.take_slot() for _ in ids]
+        first = kernels.argmax(eng.step(slots, prompts)).cpu().tolist()
+        return slots, first
+
+    slots, first = start()
+    run = eng.greedy_run(slots, first, 6)
+    assert run is not None and len(run) == 6
+    for s in slots:
+        eng.free_slot(s)
+    slots, again = start()
+    assert again == first
+    feed = list(first)
+    alive = [True] * len(ids)
+    for step in range(6):
+        lg = eng.step(slots, [[t] for t in feed]).float().cpu()
+        for i in range(len(ids)):
+            if not alive[i]:
+                continue
+            got, want = run[step][i], int(lg[i].argmax())
+            if got != want:
+                gap = float(lg[i, want] - lg[i, got])
+                assert gap <= 2e-2 * float(lg[i].abs().max()), (ids[i], step, got, want, gap)
+                alive[i] = False            # from here on the two runs see different tokens
+        feed = [run[step][i] if alive[i] else int(lg[i].argmax()) for i in range(len(ids))]
+        if not all(alive):
+            break
+    for s in slots:
+        eng.free_slot(s)
+    assert sum(alive) >= 6, "most sequences should choose the same tokens in both runs"
+    kernels.check_device_errors()
+
+
+def test_sampled_generation_at_real_sizes(batch8):
+    # generate() with a temperature through the Python entry point: the same requests alone and in a batch
+    # draw the same tokens (a draw depends on seed, request and draw index only), up to the rare draw that
+    # falls on a boundary moved by the last bits of the logits
+    import dlgo_b200
+    d, reqs, _ = batch8
+    llm = dlgo_b200.load_llm(d, dtype="bfloat16", max_tokens=8 * 1024, max_seq_len=1024, max_batch=8)
+    prompts = [reqs[r][:n] for r, n in zip(reqs, BATCH_LENS)]
+    opts = dict(max_tokens=6, temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=5, ignore_eos=True)
+    together = llm.generate(prompts, **opts)
+    assert all(len(t) == 6 for t in together)
+    # request i keeps its index in a smaller batch (requests 0..i): the batch size and its graph differ
+    same = 0
+    for i in (0, 2, 5):
+        smaller = llm.generate(prompts[:i + 1], **opts)[i]
+        same += smaller == together[i]
+    assert same >= 2, (together,)

@@ -168,13 +168,15 @@ def mixed_spec():
                    PartSpec("gqa_attention", dict(hidden_size=d, num_heads=3, num_kv_heads=3, head_dim=16, scale=0.25,
                                                   window=40, position_encoding="rope_a", cache_group="win")),
                    PartSpec("swiglu", dict(hidden_size=d, intermediate_size=72)),
-                   PartSpec("rmsnorm", dict(size=d, eps=1e-5)), PartSpec("rmsnorm", dict(size=d, eps=1e-5)), names)
+                   {"mixer_norm": PartSpec("rmsnorm", dict(size=d, eps=1e-5)),
+                    "ffn_norm": PartSpec("rmsnorm", dict(size=d, eps=1e-5))}, names)
     l1 = LayerSpec("layers.1.", "prenorm",
                    PartSpec("gqa_attention", dict(hidden_size=d, num_heads=4, num_kv_heads=1, head_dim=32,
                                                   scale=32 ** -0.5, window=None, position_encoding="rope_b",
                                                   cache_group="full")),
                    PartSpec("swiglu", dict(hidden_size=d, intermediate_size=56)),
-                   PartSpec("rmsnorm", dict(size=d, eps=1e-3)), PartSpec("rmsnorm", dict(size=d, eps=1e-6)), names)
+                   {"mixer_norm": PartSpec("rmsnorm", dict(size=d, eps=1e-3)),
+                    "ffn_norm": PartSpec("rmsnorm", dict(size=d, eps=1e-6))}, names)
     return ArchitectureSpec(
         name="MixedTest", hidden_size=d, vocab_size=V, max_positions=192,
         embedding=PartSpec("token_embedding", dict(vocab_size=V, hidden_size=d)), embedding_prefix="emb.",
@@ -264,6 +266,13 @@ def register_toy():
 
         def forward(self, x, residual, ctx, cache, state, positions):
             assert cache is None and state is not None
+            if ctx.decode:
+                # one token per sequence: slots come from the device (a captured step has no host copy of them)
+                slots = ctx.seq_slot.long()
+                s = self.decay * state[slots] + x.float()
+                state[slots] = s
+                residual += s @ self.w.t()
+                return
             off = 0
             for slot, n in zip(ctx.seq_slots_host, ctx.seq_ntok_host):
                 for j in range(n):
@@ -310,7 +319,7 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
     spec = toy_spec()
     tensors = random_tensors(spec, 5)
     assert "layers.0.attn.mix.weight" in tensors and "layers.0.attn.q_proj.weight" not in tensors
-    eng = Engine(spec=spec, tensors=tensors, dtype="float32", max_tokens=384, cuda_graphs=False)
+    eng = Engine(spec=spec, tensors=tensors, dtype="float32", max_tokens=384)     # decode steps replay a graph
     assert list(eng.cache.state.tensors) == [0] and eng.cache.state.tensors[0].shape[1:] == (48,)
     assert sorted(eng.cache.storage) == ["full"] and eng.cache.storage["full"].shape[0] == 1
     g = torch.Generator().manual_seed(6)
@@ -321,6 +330,79 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
         got = T.collect(steps, T.run_in_process(eng, steps), reqs)
         for r in reqs:
             assert float((got[r] - refs[r]).abs().max()) <= 5e-5 * max(1.0, float(refs[r].abs().max())), r
+    assert eng._graphs, "the decode steps should have gone through a captured graph"
+    # a part that asks the captured step for host-side slots is told where to look instead
+    with pytest.raises(RuntimeError, match="ctx.seq_slot"):
+        list(next(iter(eng._graphs.values())).ctx.seq_slots_host)
+
+
+# ------------------------------------------------ a block with norms after its parts too, defined here
+def register_sandwich():
+    from dlgo_b200.parts import Block, register_block
+
+    class SandwichBlock(Block):
+        """r = x + post_mixer_norm(mixer(mixer_norm(x))); x = r + post_ffn_norm(ffn(ffn_norm(r))): four norms
+        (the reference's PostAttnNorm / PostFFNNorm wiring, models/llm/forward.go:158-182)."""
+
+        def forward(self, residual, ctx, cache, state, positions):
+            n = self.norms
+            for pre, part, post, args in ((n["mixer_norm"], self.mixer, n["post_mixer_norm"], (cache, state, positions)),
+                                          (n["ffn_norm"], self.ffn, n["post_ffn_norm"], ())):
+                branch = torch.zeros_like(residual)
+                if part is self.mixer:
+                    part.forward(pre.forward(residual), branch, ctx, *args)
+                else:
+                    part.forward(pre.forward(residual), branch, ctx)
+                ctx.settle(branch)              # slices a contraction may have left unsummed
+                residual += post.forward(branch).float()
+
+    register_block("toy_sandwich", SandwichBlock, replace=True)
+
+
+def sandwich_spec():
+    from dlgo_b200.config.spec import PartSpec, RunEntry
+    spec = mixed_spec()
+    l1 = spec.layers[1]
+    norms = dict(l1.norms)
+    norms["post_mixer_norm"] = PartSpec("rmsnorm", dict(size=48, eps=1e-4))
+    norms["post_ffn_norm"] = PartSpec("rmsnorm", dict(size=48, eps=1e-2))
+    names = dict(l1.names)
+    names.update(post_mixer_norm="p1.", post_ffn_norm="p2.")
+    l1 = dataclasses.replace(l1, block="toy_sandwich", norms=norms, names=names)
+    return dataclasses.replace(spec, name="SandwichTest", layers=[l1], order=[RunEntry(0), RunEntry(0)])
+
+
+def plain_sandwich(tensors, tokens):
+    w = {k: v.float() for k, v in tensors.items()}
+    x = P.embedding(w["emb.weight"], tokens)
+    sub = {k[len("layers.1.attn."):]: v for k, v in w.items() if k.startswith("layers.1.attn.")}
+    for _ in range(2):
+        a, _ = plain_mixer(P.rmsnorm(x, w["layers.1.n1.weight"], 1e-3), sub, 4, 1, 32,
+                           P.rope_frequencies(16, 1e3, None))
+        r = x + P.rmsnorm(a, w["layers.1.p1.weight"], 1e-4)
+        y = P.feed_forward(P.rmsnorm(r, w["layers.1.n2.weight"], 1e-6), w["layers.1.ff.gate_proj.weight"],
+                           w["layers.1.ff.up_proj.weight"], w["layers.1.ff.down_proj.weight"])
+        x = r + P.rmsnorm(y, w["layers.1.p2.weight"], 1e-2)
+    return P.linear(P.rmsnorm(x, w["final.weight"], 1e-5), w["head.weight"])
+
+
+def test_a_block_with_four_norms_needs_no_change_to_the_framework():
+    import traces as T
+    from dlgo_b200.engine.engine import Engine
+    register_sandwich()
+    spec = sandwich_spec()
+    tensors = random_tensors(spec, 12)
+    assert {"layers.1.p1.weight", "layers.1.p2.weight", "layers.1.n1.weight", "layers.1.n2.weight"} <= set(tensors)
+    eng = Engine(spec=spec, tensors=tensors, dtype="float32", max_tokens=384)
+    per_layer = sum(v.numel() * 4 for k, v in tensors.items() if k.startswith("layers.1."))
+    assert eng.weight_bytes() == per_layer + 4 * (48 + 100 * 48)       # every norm of the block is counted
+    g = torch.Generator().manual_seed(13)
+    reqs = {f"s{i}": torch.randint(0, 100, (n,), generator=g).tolist() for i, n in enumerate([45, 6, 80])}
+    refs = {r: plain_sandwich(tensors, t) for r, t in reqs.items()}
+    for steps in (T.whole(reqs), T.tail_one_by_one(reqs, 16), T.batched(reqs, 2, (8, 2, 30))):
+        got = T.collect(steps, T.run_in_process(eng, steps), reqs)
+        for r in reqs:
+            assert float((got[r] - refs[r]).abs().max()) <= 1e-4 * max(1.0, float(refs[r].abs().max())), r
 
 
 # ---------------- a toy feed-forward with routing and a toy position encoding, both defined here
