@@ -51,6 +51,16 @@ class StateArea:
         for t in self.tensors.values():
             t[slot].zero_()
 
+    def snapshot(self, slots: Sequence[int]) -> Dict[int, torch.Tensor]:
+        """Copies of the given slots' state (a run that must leave no trace restores them afterwards)."""
+        idx = torch.tensor(list(slots), dtype=torch.int64)
+        return {e: t[idx.to(t.device)].clone() for e, t in self.tensors.items()}
+
+    def restore(self, slots: Sequence[int], saved: Dict[int, torch.Tensor]) -> None:
+        idx = torch.tensor(list(slots), dtype=torch.int64)
+        for e, t in self.tensors.items():
+            t[idx.to(t.device)] = saved[e]
+
     def bytes_per_slot(self) -> int:
         return sum(t[0].numel() * t.element_size() for t in self.tensors.values())
 

@@ -76,13 +76,19 @@ class DecodeGraph:
 
     def capture(self) -> None:
         eng = self.engine
-        # Warm-up runs on a side stream (lazy initialisations must not land in the capture).
+        # Warm-up runs on a side stream (lazy initialisations must not land in the capture).  It runs the
+        # step for real: keys and values land where the step itself writes them again, but fixed-size
+        # state would be advanced twice, so the batch's state is put back afterwards.
+        slots = [int(v) for v in self.host_np[2]]
+        saved = eng.cache.state.snapshot(slots) if eng.cache.state.tensors else None
         s = torch.cuda.Stream(device=eng.runtime.device)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             eng.model.forward(self.ctx, eng.cache, self.want_rows)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        if saved is not None:
+            eng.cache.state.restore(slots, saved)
         before = kernels.LAUNCHES
         with torch.cuda.graph(self.graph):
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
@@ -149,10 +155,7 @@ def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
     """Up to ``n_steps`` greedy decode steps through the graph of this batch size in one native call;
     the ids chosen, a list per step (fewer than ``n_steps`` if a sequence chose a stop id)."""
     b = len(slots)
-    g = engine._graphs.get(b)
-    if g is None:
-        decode_with_graph(engine, slots, token_ids, starts)    # captures (and runs the first step once, harmlessly)
-        g = engine._graphs[b]
+    g = graph_for(engine, slots, token_ids, starts)
     if g.greedy_exec is None:
         g.capture_greedy()
     g._native.wait()
@@ -172,10 +175,7 @@ def sampled_with_graph(engine: Any, slots: List[int], token_ids: List[int], star
     ``recents[i]`` are its latest tokens, oldest first, for the repetition penalty."""
     from ..sampling.sampler import RECENT_WINDOW
     b, w = len(slots), RECENT_WINDOW
-    g = engine._graphs.get(b)
-    if g is None:
-        decode_with_graph(engine, slots, token_ids, starts)
-        g = engine._graphs[b]
+    g = graph_for(engine, slots, token_ids, starts)
     graph_exec, n_kernels = g.capture_sampled(cfg)
     g._native.wait()
     h = g.host_np
@@ -198,22 +198,27 @@ def sampled_with_graph(engine: Any, slots: List[int], token_ids: List[int], star
                                      g._dev_index, n_kernels)
 
 
-def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
-    """Logits [batch, vocab] of one decode step, through the graph of this batch size.
-
-    The returned tensor is the graph's output buffer: it is overwritten by the next
-    decode step of the same batch size.
-    """
+def graph_for(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> DecodeGraph:
+    """The captured step of this batch size, made when first asked for."""
     b = len(slots)
     g = engine._graphs.get(b)
     if g is None:
         g = DecodeGraph(engine, b)
-        # the warm-up and the capture run the step for real, on whatever the buffers
-        # hold: give them this step's inputs so they write where this step writes anyway
+        # the warm-up before the capture runs the step for real, on whatever the buffers hold: give it
+        # this step's inputs so that it writes where this step writes anyway
         g.host_np[0, :] = token_ids
         g.host_np[1, :] = starts
         g.host_np[2, :] = slots
         g.meta.copy_(g.host)
         g.capture()
         engine._graphs[b] = g
-    return g.run(slots, token_ids, starts)
+    return g
+
+
+def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
+    """Logits [batch, vocab] of one decode step, through the graph of this batch size.
+
+    The returned tensor is the graph's output buffer: it is overwritten by the next
+    decode step of the same batch size.
+    """
+    return graph_for(engine, slots, token_ids, starts).run(slots, token_ids, starts)
