@@ -37,8 +37,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_decode_mma": ["attention_decode_mma.cu"],
     "hoststep": ["hoststep.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
+    "decode_layers": ["decode_layers.cu"],
 }
-_HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "tcgen05.cuh"]
+_HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

@@ -489,6 +489,13 @@ def check_device_errors() -> None:
             if v != 0:
                 raise KernelError(f"a tensor-core kernel ({lib}) gave up a bounded wait on the device; "
                                   "its results are invalid")
+    if "decode_layers" in build._loaded:
+        v = build._loaded["decode_layers"].dlgo_decode_layers_error()
+        if v == 1:
+            raise KernelError("the persistent decode kernel gave up a bounded wait on the device; its results are "
+                              "invalid and its counters must be zeroed again (build a new engine)")
+        if v != 0:
+            raise KernelError("a token's position had no page in the cache's table (persistent decode kernel)")
     if "rope_append" in build._loaded and build._loaded["rope_append"].dlgo_rope_append_error() != 0:
         raise KernelError("a token's position had no page in the cache's table: its keys and values were not "
                           "stored and the step's results are invalid")
@@ -723,3 +730,84 @@ class HostStep:
             self._lib.dlgo_hoststep_destroy(self._h)
         except Exception:
             pass
+
+
+# ------------------------------------------------- a run of layers as one persistent kernel (decode steps)
+def decode_layers_takes(tokens: int, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, ffn: int,
+                        page_size: int) -> bool:
+    """Whether the persistent decode kernel takes these sizes (see csrc/decode_layers.cu)."""
+    return bool(_lib("decode_layers").dlgo_decode_layers_takes(_i(tokens), _i(hidden), _i(num_heads), _i(num_kv_heads),
+                                                               _i(head_dim), _i(ffn), _i(page_size)))
+
+
+def decode_layers_grid() -> int:
+    return int(_lib("decode_layers").dlgo_decode_layers_grid())
+
+
+def decode_layers_describe(layers: Sequence[dict], hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                           ffn: int, device: torch.device) -> torch.Tensor:
+    """The descriptor array of a run of layers, in device memory.  Each entry of ``layers`` gives the tensors
+    ``w_qkv, w_o, w_gu, w_down`` (bfloat16, contiguous), ``norm1_w, norm2_w`` (float32), ``kpages, vpages``, and
+    ``eps1, eps2, write_cache``.  The caller keeps those tensors alive as long as the descriptors are used."""
+    lib = _lib("decode_layers")
+    size = int(lib.dlgo_decode_layers_desc_bytes())
+    raw = ctypes.create_string_buffer(size * len(layers) + 64)
+    base = (ctypes.addressof(raw) + 63) & ~63
+    for i, L in enumerate(layers):
+        for n in ("w_qkv", "w_o", "w_gu", "w_down"):
+            _need(L[n], torch.bfloat16, n)
+        for n in ("norm1_w", "norm2_w"):
+            _need(L[n], torch.float32, n)
+        if L["kpages"].dtype != torch.bfloat16 or L["vpages"].dtype != torch.bfloat16:
+            raise KernelError("decode_layers: the cache must be bfloat16")
+        st = lib.dlgo_decode_layers_describe(
+            ctypes.c_void_p(base + i * size), _ptr(L["w_qkv"]), _ptr(L["w_o"]), _ptr(L["w_gu"]), _ptr(L["w_down"]),
+            _ptr(L["norm1_w"]), _ptr(L["norm2_w"]), _f(L["eps1"]), _f(L["eps2"]), _ptr(L["kpages"]), _ptr(L["vpages"]),
+            _i(1 if L["write_cache"] else 0), _i(hidden), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(ffn))
+        _check(st, "decode_layers_describe", 0)
+    host = torch.frombuffer(bytearray(ctypes.string_at(base, size * len(layers))), dtype=torch.uint8)
+    # device allocations are 256-byte aligned, which the tensor maps inside need
+    return host.to(device)
+
+
+def decode_layers_scratch_floats(tokens: int, num_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(_lib("decode_layers").dlgo_decode_layers_scratch_floats(_i(tokens), _i(num_heads), _i(head_dim),
+                                                                         _i(n_splits)))
+
+
+def decode_layers(desc: torch.Tensor, n_layers: int, residual: torch.Tensor, hidden: int, num_heads: int,
+                  num_kv_heads: int, head_dim: int, ffn: int, scale: float, qkv_sum: torch.Tensor,
+                  scale1: torch.Tensor, attn_out: torch.Tensor, h: torch.Tensor, scratch: Optional[torch.Tensor],
+                  tickets: torch.Tensor, page_table: torch.Tensor, seq_slot: torch.Tensor, token_pos: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, page_size: int, n_splits: int, sync: torch.Tensor,
+                  first: bool = False) -> None:
+    """``n_layers`` decoder layers on the residual stream [T, hidden] (fp32, in place), one new token per
+    sequence: see csrc/decode_layers.cu.  ``qkv_sum``, ``tickets`` and ``sync`` must be zero and are left zero."""
+    T = residual.shape[0]
+    _need(residual, torch.float32, "residual")
+    _need(qkv_sum, torch.float32, "qkv_sum")
+    _need(scale1, torch.float32, "scale1")
+    _need(attn_out, torch.bfloat16, "attn_out")
+    _need(h, torch.bfloat16, "h")
+    for n, t in (("tickets", tickets), ("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos),
+                 ("sync", sync)):
+        _need(t, torch.int32, n)
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    qkv_n = (num_heads + 2 * num_kv_heads) * head_dim
+    if (residual.shape[1] != hidden or qkv_sum.numel() < T * qkv_n or scale1.numel() < T or
+            attn_out.numel() < T * num_heads * head_dim or h.numel() < T * ffn or tickets.numel() < T * num_kv_heads or
+            sync.numel() < 2 or seq_slot.numel() < T or token_pos.numel() < T):
+        raise KernelError("decode_layers: a buffer is too small for these sizes")
+    if cos.shape[1] * 2 != head_dim or sin.shape != cos.shape:
+        raise KernelError("decode_layers: whole-head rotation tables [positions, head_dim / 2] only")
+    if n_splits > 1:
+        need = decode_layers_scratch_floats(T, num_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"decode_layers: {n_splits} page slices need {need} floats of scratch")
+    st = _lib("decode_layers").dlgo_decode_layers(
+        _ptr(desc), _i(n_layers), _i(T), _i(hidden), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(ffn), _f(scale),
+        _ptr(residual), _i(residual.stride(0)), _ptr(qkv_sum), _ptr(scale1), _ptr(attn_out), _ptr(h), _ptr(scratch),
+        _ptr(tickets), _ptr(page_table), _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(cos), _ptr(sin),
+        _i(page_size), _i(n_splits), _i(0), _ptr(sync), _i(1 if first else 0), _stream())
+    _check(st, "decode_layers")

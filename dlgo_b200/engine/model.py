@@ -42,6 +42,7 @@ class CausalLM:
                         theirs.num_kv_heads, theirs.head_dim):
                     raise ValueError(f"run entry {i} cannot read the cache of entry {e.cache_of}: their shapes differ")
         self.runtime: Any = None
+        self.fused_runs: Dict[int, Any] = {}
 
     # ------------------------------------------------------------ declarations
     def _named_parts(self) -> List[Tuple[str, Part]]:
@@ -99,16 +100,27 @@ class CausalLM:
         for pe in self.positions.values():
             pe.prepare(runtime)
         runtime.forget_copies()
+        from .fused_decode import plan_runs
+        self.fused_runs = plan_runs(self, runtime)
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: Any, cache: Any, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens; logits [wanted, vocab] fp32 for the packed rows ``want_rows`` (int32)."""
         residual = self.embedding.forward(ctx.token_ids)
-        for i, e in enumerate(self.order):
-            blk = self.blocks[e.layer]
+        i = 0
+        while i < len(self.order):
+            run = self.fused_runs.get(i) if ctx.decode else None
+            if run is not None and run.takes(ctx, cache):
+                # a run of like blocks on a decode step: one persistent kernel instead of eight a layer
+                ctx.settle(residual)
+                run.run(self, residual, ctx, cache)
+                i += run.n
+                continue
+            blk = self.blocks[self.order[i].layer]
             if not getattr(blk, "handles_pending", False):
                 ctx.settle(residual)
             blk.forward(residual, ctx, cache.view(i), cache.state.view(i), self.positions)
+            i += 1
         if want_rows is None or want_rows.numel() == 0:
             ctx.settle(residual)
             return None

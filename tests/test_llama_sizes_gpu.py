@@ -195,6 +195,9 @@ def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dt
     eng.cache.poison()
     outs = T.run_in_process(eng, batch_steps(reqs))
     assert 8 in eng._graphs, "the decode steps should have replayed the graph of batch 8"
+    if dtype == "bfloat16" and eng.model.fused_runs:
+        # both layers as one persistent kernel: embedding, that kernel, final norm, head
+        assert eng._graphs[8].kernels_per_replay <= 6, eng._graphs[8].kernels_per_replay
     tol = 1e-4 if dtype == "float32" else 3e-2
     for i, rid in enumerate(reqs):
         ref = refs[rid]
@@ -281,7 +284,9 @@ def test_sampled_generation_at_real_sizes(batch8):
     d, reqs, _ = batch8
     llm = dlgo_b200.load_llm(d, dtype="bfloat16", max_tokens=8 * 1024, max_seq_len=1024, max_batch=8)
     prompts = [reqs[r][:n] for r, n in zip(reqs, BATCH_LENS)]
-    opts = dict(max_tokens=6, temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=5, ignore_eos=True)
+    # (random weights give nearly flat distributions over 128,256 tokens, where the last bit of a logit
+    # moves the draw; a low temperature makes the draw depend on the logits' leading digits)
+    opts = dict(max_tokens=6, temperature=0.02, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=5, ignore_eos=True)
     together = llm.generate(prompts, **opts)
     assert all(len(t) == 6 for t in together)
     # request i keeps its index in a smaller batch (requests 0..i): the batch size and its graph differ
