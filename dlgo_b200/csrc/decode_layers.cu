@@ -43,6 +43,22 @@ constexpr int DL_GM = 8;                   // query heads of a kv head at most
 
 __device__ int g_decode_layers_error = 0;
 
+// Diagnostic build (-DDLGO_TIMING): compute thread 0 of every CTA stamps the global timer at the phase
+// boundaries of the launch's second layer (16 stamps per CTA; dlgo_decode_layers_times fetches them).
+#ifdef DLGO_TIMING
+__device__ unsigned long long g_dl_times[256 * 16];
+#define DL_STAMP(k)                                                        \
+  do {                                                                     \
+    if (li == 1 && ctid == 0 && cta < 256) {                               \
+      unsigned long long t_;                                               \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));               \
+      g_dl_times[cta * 16 + (k)] = t_;                                     \
+    }                                                                      \
+  } while (0)
+#else
+#define DL_STAMP(k) do {} while (0)
+#endif
+
 struct DlGemm {
   int rows, K, tiles, kblocks, splits, per;   // weight [rows, K]; tiles of 128 rows; K-slices of `per` K blocks
 };
@@ -82,6 +98,7 @@ struct DlParams {
   unsigned int* sync;         // [0] barrier arrivals of this launch, [1] CTAs that left; zero between launches
   int stages;
   int operand_bytes;
+  int l2_ahead;               // weight tiles beyond the ring that the loader asks into L2 ahead of time
 };
 
 // ------------------------------------------------------------------------------------------- helpers
@@ -121,39 +138,54 @@ __device__ __forceinline__ uint32_t operand_offset(int j, int t, int c8) {
 
 // Token operand from fp32 rows times a weight vector (the norm without its per-token scale), K blocks
 // [kb0, kb1).  With SS the CTA also gets every row's RMSNorm scale (rows read whole: kb0 = 0, kb1 = all).
-// A thread takes the same four columns of every row, all rows' loads in flight at once.
-template <bool SS>
+// A thread takes the same four columns of every row; TM rows (8 or 16) times U column groups are in flight
+// at once (32 loads of 16 bytes a thread: an SM needs that many to take 64 KB out of L2 in one round trip).
+template <bool SS, int TM>
 __device__ __forceinline__ void build_operand_f32(uint8_t* dst, const float* __restrict__ x, int ld,
                                                   const float* __restrict__ w, int K, int T, int kb0, int kb1,
                                                   int ctid, float eps, float* red /* [4][16] */,
                                                   float* scales /* [16] */) {
+  constexpr int U = 32 / TM;
   const int n4 = (kb1 - kb0) * (DL_TILE_K / 4);
   const int k_base = kb0 * DL_TILE_K;
-  float ss[DL_BN];
+  float ss[TM];
 #pragma unroll
-  for (int t = 0; t < DL_BN; ++t) ss[t] = 0.f;
-  for (int j4 = ctid; j4 < n4; j4 += DL_CT) {
-    const int kk = 4 * j4, k = k_base + kk;
-    const bool in = k < K;        // K is a multiple of 8
-    float4 v[DL_BN];
+  for (int t = 0; t < TM; ++t) ss[t] = 0.f;
+  for (int j0 = ctid; j0 < n4; j0 += U * DL_CT) {
+    float4 v[U][TM];
+    float4 wv[U];
 #pragma unroll
-    for (int t = 0; t < DL_BN; ++t)
-      v[t] = (in && t < T) ? __ldcg(reinterpret_cast<const float4*>(x + (size_t)t * ld + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 wv = in ? __ldg(reinterpret_cast<const float4*>(w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int u = 0; u < U; ++u) {
+      const int j4 = j0 + u * DL_CT;
+      const int k = k_base + 4 * j4;
+      const bool in = j4 < n4 && k < K;        // K is a multiple of 8
 #pragma unroll
-    for (int t = 0; t < DL_BN; ++t) {
-      if (t < T) {
-        if (SS) ss[t] = fmaf(v[t].x, v[t].x, fmaf(v[t].y, v[t].y, fmaf(v[t].z, v[t].z, fmaf(v[t].w, v[t].w, ss[t]))));
-        __nv_bfloat162 hh[2] = {__floats2bfloat162_rn(v[t].x * wv.x, v[t].y * wv.y),
-                                __floats2bfloat162_rn(v[t].z * wv.z, v[t].w * wv.w)};
-        *reinterpret_cast<uint2*>(dst + operand_offset(kk >> 6, t, (kk & 63) >> 3) + ((kk & 7) << 1)) =
-            *reinterpret_cast<uint2*>(hh);
+      for (int t = 0; t < TM; ++t)
+        v[u][t] = (in && t < T) ? __ldcg(reinterpret_cast<const float4*>(x + (size_t)t * ld + k))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+      wv[u] = in ? __ldg(reinterpret_cast<const float4*>(w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j4 = j0 + u * DL_CT;
+      if (j4 >= n4) break;
+      const int kk = 4 * j4;
+#pragma unroll
+      for (int t = 0; t < TM; ++t) {
+        if (t < T) {
+          const float4 e = v[u][t];
+          if (SS) ss[t] = fmaf(e.x, e.x, fmaf(e.y, e.y, fmaf(e.z, e.z, fmaf(e.w, e.w, ss[t]))));
+          __nv_bfloat162 hh[2] = {__floats2bfloat162_rn(e.x * wv[u].x, e.y * wv[u].y),
+                                  __floats2bfloat162_rn(e.z * wv[u].z, e.w * wv[u].w)};
+          *reinterpret_cast<uint2*>(dst + operand_offset(kk >> 6, t, (kk & 63) >> 3) + ((kk & 7) << 1)) =
+              *reinterpret_cast<uint2*>(hh);
+        }
       }
     }
   }
   if (SS) {
 #pragma unroll
-    for (int t = 0; t < DL_BN; ++t) {
+    for (int t = 0; t < TM; ++t) {
       const float tot = warp_sum(ss[t]);
       if ((ctid & 31) == 0) red[(ctid >> 5) * 16 + t] = tot;
     }
@@ -213,6 +245,45 @@ struct UnitIter {
     const int split = u / tiles;
     kb0 = split * per;
     kb1 = min(kblocks, kb0 + per);
+  }
+};
+
+// This CTA's weight tiles in the order the ring takes them: layers, products, units, K blocks.
+struct TileWalker {
+  const DlParams& p;
+  int cta, grid;
+  int li = 0, ph = 0, u = 0, kb = 0, kb1 = 0, tile = 0;
+  bool open = false;     // a unit is open (kb .. kb1 remain)
+  __device__ __forceinline__ TileWalker(const DlParams& p_, int cta_, int grid_) : p(p_), cta(cta_), grid(grid_), u(cta_) {}
+  __device__ __forceinline__ const DlGemm& gemm() const { return ph == 0 ? p.qkv : (ph == 1 ? p.o : (ph == 2 ? p.gu : p.down)); }
+  // false when no tile is left
+  __device__ __forceinline__ bool next(const CUtensorMap*& map, int& x, int& y) {
+    for (;;) {
+      if (li >= p.n_layers) return false;
+      if (!open) {
+        const UnitIter it(gemm());
+        if (u < it.count()) {
+          int kb0;
+          it.unit(u, tile, kb0, kb1);
+          kb = kb0;
+          open = true;
+        } else {
+          u = cta;
+          if (++ph == 4) { ph = 0; ++li; }
+          continue;
+        }
+      }
+      if (kb < kb1) {
+        const DlLayer& L = p.layers[li];
+        map = ph == 0 ? &L.w_qkv : (ph == 1 ? &L.w_o : (ph == 2 ? &L.w_gu : &L.w_down));
+        x = kb * DL_TILE_K;
+        y = tile * DL_TILE_M;
+        ++kb;
+        return true;
+      }
+      open = false;
+      u += grid;
+    }
   }
 };
 
@@ -464,25 +535,29 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
   if (warp == 0) {
     // ------------------------------------------------------------------ weights: one stream for all phases
     if (elect_one()) {
-      uint32_t sc = 0;     // stages filled so far
-      bool ok = true;
-      for (int li = 0; ok && li < p.n_layers; ++li) {
-        const DlLayer& L = p.layers[li];
-        for (int ph = 0; ok && ph < 4; ++ph) {
-          const DlGemm& g = ph == 0 ? p.qkv : (ph == 1 ? p.o : (ph == 2 ? p.gu : p.down));
-          const CUtensorMap* map = ph == 0 ? &L.w_qkv : (ph == 1 ? &L.w_o : (ph == 2 ? &L.w_gu : &L.w_down));
-          const UnitIter it(g);
-          for (int u = cta; ok && u < it.count(); u += grid) {
-            int tile, kb0, kb1;
-            it.unit(u, tile, kb0, kb1);
-            for (int kb = kb0; kb < kb1; ++kb, ++sc) {
-              const uint32_t s = sc % (uint32_t)STAGES, phs = (sc / (uint32_t)STAGES) & 1u;
-              if (!mbar_wait(&sh.empty[s], phs ^ 1u, abort_flag)) { ok = false; break; }
-              mbar_expect_tx(&sh.full[s], DL_A_BYTES);
-              tma_load_2d(sh.ring + (size_t)s * DL_A_BYTES, map, &sh.full[s], kb * DL_TILE_K, tile * DL_TILE_M);
-            }
+      // one walker feeds the ring; a second one runs `l2_ahead` tiles in front of it and asks for those tiles
+      // to be brought into L2, so that memory keeps streaming while a phase that reads little (attention, the
+      // barriers) holds the ring up, and the ring later refills from L2
+      TileWalker load(p, cta, grid), ahead(p, cta, grid);
+      uint32_t sc = 0, pf = 0;     // tiles loaded / prefetched so far
+      bool more_ahead = true;
+      const CUtensorMap* map;
+      int x, y;
+      while (load.next(map, x, y)) {
+        while (more_ahead && pf < sc + (uint32_t)STAGES + (uint32_t)p.l2_ahead) {
+          const CUtensorMap* m2;
+          int x2, y2;
+          more_ahead = ahead.next(m2, x2, y2);
+          if (more_ahead) {
+            if (pf >= sc + (uint32_t)STAGES) tma_prefetch_l2_2d(m2, x2, y2);   // (tiles the ring takes at once need no hint)
+            ++pf;
           }
         }
+        const uint32_t s = sc % (uint32_t)STAGES, phs = (sc / (uint32_t)STAGES) & 1u;
+        if (!mbar_wait(&sh.empty[s], phs ^ 1u, abort_flag)) break;
+        mbar_expect_tx(&sh.full[s], DL_A_BYTES);
+        tma_load_2d(sh.ring + (size_t)s * DL_A_BYTES, map, &sh.full[s], x, y);
+        ++sc;
       }
     }
   } else if (warp == 1) {
@@ -585,11 +660,17 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     for (int li = 0; li < p.n_layers; ++li) {
       const DlLayer& L = p.layers[li];
       int kb0, kb1;
+      DL_STAMP(0);
       // ---- P1: q|k|v sums
       my_range(p.qkv, kb0, kb1);
-      build_operand_f32<false>(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid, 0.f, sh.red,
-                               sh.scales);
+      if (p.T <= 8)
+        build_operand_f32<false, 8>(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid, 0.f, sh.red,
+                                    sh.scales);
+      else
+        build_operand_f32<false, 16>(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid, 0.f,
+                                     sh.red, sh.scales);
       operand_ready();
+      DL_STAMP(1);
       if (cta < p.T) {        // this CTA computes the norm's scale of token `cta`
         float ss = 0.f;
         const float* row = p.residual + (size_t)cta * p.ld_res;
@@ -604,7 +685,9 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
           p.scale1[cta] = 1.0f / sqrtf((sh.red[0] + sh.red[1] + sh.red[2] + sh.red[3]) / (float)p.d + L.eps1);
       }
       epilogue(p.qkv, DL_EPI_RED, p.qkv_sum, ldq);
+      DL_STAMP(2);
       grid_barrier(p.sync, ++nbar * (unsigned)grid, ctid, abort_flag);
+      DL_STAMP(3);
       if (li == 0 && ctid == 0) pdl_launch_dependents();   // every CTA of this grid is resident by now
 
       // ---- P2: rotation, append, attention
@@ -616,35 +699,51 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
           attention_item<HD>(p, L, bk / p.Hkv, bk % p.Hkv, split, ctid, (float*)sh.operand, sh.flag);
         }
       }
+      DL_STAMP(4);
       grid_barrier(p.sync, ++nbar * (unsigned)grid, ctid, abort_flag);
+      DL_STAMP(5);
 
       // ---- P3: residual += Wo . attention
       my_range(p.o, kb0, kb1);
       build_operand_bf16(sh.operand, p.attn_out, p.q_dim, p.q_dim, p.T, kb0, kb1, ctid);
       operand_ready();
+      DL_STAMP(6);
       {   // the sums were read by everyone: zero again for the next layer
         const int n4 = p.T * ldq / 4;
         float4* z = reinterpret_cast<float4*>(p.qkv_sum);
         for (int i = cta * DL_CT + ctid; i < n4; i += grid * DL_CT) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
       epilogue(p.o, DL_EPI_RED, p.residual, p.ld_res);
+      DL_STAMP(7);
       grid_barrier(p.sync, ++nbar * (unsigned)grid, ctid, abort_flag);
+      DL_STAMP(8);
 
       // ---- P4: h = silu(s g) * (s u)
       my_range(p.gu, kb0, kb1);
-      if (kb1 > kb0)
-        build_operand_f32<true>(sh.operand, p.residual, p.ld_res, L.norm2_w, p.d, p.T, 0, p.gu.kblocks, ctid, L.eps2,
-                                sh.red, sh.scales);
+      if (kb1 > kb0) {
+        if (p.T <= 8)
+          build_operand_f32<true, 8>(sh.operand, p.residual, p.ld_res, L.norm2_w, p.d, p.T, 0, p.gu.kblocks, ctid,
+                                     L.eps2, sh.red, sh.scales);
+        else
+          build_operand_f32<true, 16>(sh.operand, p.residual, p.ld_res, L.norm2_w, p.d, p.T, 0, p.gu.kblocks, ctid,
+                                      L.eps2, sh.red, sh.scales);
+      }
       operand_ready();
+      DL_STAMP(9);
       epilogue(p.gu, DL_EPI_SWIGLU, nullptr, 0);
+      DL_STAMP(10);
       grid_barrier(p.sync, ++nbar * (unsigned)grid, ctid, abort_flag);
+      DL_STAMP(11);
 
       // ---- P5: residual += Wd . h
       my_range(p.down, kb0, kb1);
       build_operand_bf16(sh.operand, p.h, p.F, p.F, p.T, kb0, kb1, ctid);
       operand_ready();
+      DL_STAMP(12);
       epilogue(p.down, DL_EPI_RED, p.residual, p.ld_res);
+      DL_STAMP(13);
       if (li + 1 < p.n_layers) grid_barrier(p.sync, ++nbar * (unsigned)grid, ctid, abort_flag);
+      DL_STAMP(14);
     }
     // the barrier counters are zero again for the next launch once every CTA has left its last wait
     cbar();
@@ -851,6 +950,8 @@ DLGO_EXPORT int dlgo_decode_layers(const void* layers, int n_layers, int T, int 
   p.sync = sync;
   p.stages = layout(p.qkv, p.o, p.gu, p.down, hd, &p.operand_bytes);
   if (p.stages <= 0) return DLGO_ERR_SIZE;
+  static const int l2_ahead = [] { const char* e = getenv("DLGO_DL_L2_AHEAD"); return e ? atoi(e) : 0; }();
+  p.l2_ahead = l2_ahead < 0 ? 0 : l2_ahead;
   const int smem = p.stages * DL_A_BYTES + p.operand_bytes + 1024 /* control */ + 1024 /* alignment */;
   auto kernel = hd == 64 ? decode_layers_kernel<64> : decode_layers_kernel<128>;
   static bool configured[2] = {false, false};
@@ -875,3 +976,10 @@ DLGO_EXPORT int dlgo_decode_layers_error() {
   if (v) cudaMemcpyToSymbol(g_decode_layers_error, &zero, sizeof(int));
   return v;
 }
+
+#ifdef DLGO_TIMING
+// Diagnostic build only: the phase stamps of the last launch's second layer, 16 per CTA for 256 CTAs.
+DLGO_EXPORT int dlgo_decode_layers_times(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, dlgo::g_dl_times, sizeof(unsigned long long) * 256 * 16) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -11,7 +11,12 @@ run one by one) for anything it does not take: other blocks, mixers,
 feed-forwards or norms, windows, partial or interleaved rotation, other head
 sizes, float32, more tokens.
 
-``DLGO_FUSED_DECODE=0`` switches it off.
+Off by default (``DLGO_FUSED_DECODE=1`` switches it on): measured on a B200 at the
+layer sizes of Llama 3.2 1B and batch 8, a layer takes 54 us in the persistent
+kernel against 44 us as eight kernels chained by programmatic dependent launch.
+Every phase ends in a grid-wide barrier (1.3 to 1.5 us each, five a layer) and
+starts with a round trip to L2 for its operand that nothing overlaps, while the
+separate kernels' prologues run under their predecessors' tails.
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ from ..parts.feedforward import SwiGLU
 from ..parts.norm import RMSNorm
 from ..parts.rope import RotaryEmbedding
 
-ENABLED = os.environ.get("DLGO_FUSED_DECODE", "1") != "0"
+ENABLED = os.environ.get("DLGO_FUSED_DECODE", "0") == "1"
 MAX_TOKENS = 16
 
 

@@ -186,8 +186,28 @@ def batch_steps(reqs):
     return steps
 
 
+@pytest.fixture
+def persistent_decode(monkeypatch):
+    """Engines built inside the test run their decode steps' layers as one persistent kernel."""
+    from dlgo_b200.engine import fused_decode
+    monkeypatch.setattr(fused_decode, "ENABLED", True)
+
+
+def test_the_persistent_decode_kernel_against_the_plain_implementation(batch8, persistent_decode):
+    test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, "bfloat16", fused=True)
+
+
+def test_the_persistent_decode_kernel_at_8b_and_3b_layer_sizes(big8, big3, persistent_decode):
+    from dlgo_b200.engine.engine import Engine
+    for d, reqs, refs in (big8, big3):
+        eng = Engine(d, dtype="bfloat16", max_tokens=512, max_seq_len=256)
+        assert eng.model.fused_runs
+        eng.cache.poison()
+        run(eng, reqs, refs, "bfloat16", "persistent kernel")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dtype):
+def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dtype, fused=False):
     from dlgo_b200.csrc import kernels
     from dlgo_b200.engine.engine import Engine
     d, reqs, refs = batch8
@@ -195,7 +215,8 @@ def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dt
     eng.cache.poison()
     outs = T.run_in_process(eng, batch_steps(reqs))
     assert 8 in eng._graphs, "the decode steps should have replayed the graph of batch 8"
-    if dtype == "bfloat16" and eng.model.fused_runs:
+    assert bool(eng.model.fused_runs) == fused
+    if fused:
         # both layers as one persistent kernel: embedding, that kernel, final norm, head
         assert eng._graphs[8].kernels_per_replay <= 6, eng._graphs[8].kernels_per_replay
     tol = 1e-4 if dtype == "float32" else 3e-2
