@@ -57,6 +57,9 @@ struct DecMmaParams {
   const float* cos_t;    // [positions][HD / 2]
   const float* sin_t;
   int write_cache;
+  int clear_parts;       // S = 1 and `parts` is a sum that must be zero again for the next step: the block (or the
+                         // cluster's first block) clears this (sequence, kv head)'s columns once all have read them
+  const float* row_scale;  // [B] or null: factor on the sums of a token (a norm's scale applied after the product)
   float* part_acc;       // more than 8 slices: [B, Hq, n_splits, HD] and [B, Hq, n_splits, 2] scratch,
   float* part_ml;        // combined by a second kernel; else null (slices of a cluster combine on chip)
 };
@@ -114,9 +117,16 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
       }
     }
   }
+  if (p.parts != nullptr && threadIdx.x < 2 * ((HD * 2 + 127) / 128)) {
+    // the position's cos / sin row (a table nobody writes): on its way before the wait
+    constexpr int LN = (HD * 2 + 127) / 128;
+    const float* tbl = (threadIdx.x < LN ? p.cos_t : p.sin_t) + (size_t)pos * (HD / 2);
+    asm volatile("prefetch.global.L1 [%0];" ::"l"((const char*)tbl + (size_t)(threadIdx.x % LN) * 128));
+  }
   if (threadIdx.x == 0) TSTAMP(1);
   pdl_wait();
   if (threadIdx.x == 0) TSTAMP(2);
+  const float rs = (p.parts != nullptr && p.row_scale != nullptr) ? __ldcg(p.row_scale + b) : 1.f;
 
   // query fragments: head r of this block's chunk, this lane's quarter of the dimensions
   uint32_t qa[KK][2];
@@ -151,6 +161,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
             v0 += __ldcg(vin + so + i); v1 += __ldcg(vin + so + i + RH);
           }
           const float cs = p.cos_t[(size_t)pos * RH + i], sn = p.sin_t[(size_t)pos * RH + i];
+          k0 *= rs; k1 *= rs; v0 *= rs; v1 *= rs;
           const_cast<T*>(p.kpages)[row + i] = __float2bfloat16_rn(k0 * cs - k1 * sn);
           const_cast<T*>(p.kpages)[row + i + RH] = __float2bfloat16_rn(k0 * sn + k1 * cs);
           const_cast<T*>(p.vpages)[row + i] = __float2bfloat16_rn(v0);
@@ -194,6 +205,8 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
       }
       const float* cs = p.cos_t + (size_t)pos * RH + (c & 1) * QN;
       const float* sn = p.sin_t + (size_t)pos * RH + (c & 1) * QN;
+#pragma unroll
+      for (int k = 0; k < QN; ++k) x[k] *= rs;
       float y[QN];
 #pragma unroll
       for (int k = 0; k < QN; ++k) {
@@ -270,7 +283,21 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
       }
     }
   }
-  if (p.n_splits == 1 || p.part_acc != nullptr) return;
+  // the sums this (sequence, kv head) read: zero again for the next step's projection (every warp of the
+  // block is past its reads: the merge above begins behind a block-wide barrier)
+  auto clear_sums = [&]() {
+    float* row = const_cast<float*>(p.parts) + (size_t)b * p.ldq;
+    for (int i = threadIdx.x; i < GC * HD; i += DM_THREADS) row[(size_t)(kvh * G + g0) * HD + i] = 0.f;
+    if (gc == 0)
+      for (int i = threadIdx.x; i < HD; i += DM_THREADS) {
+        row[(size_t)(p.Hq + kvh) * HD + i] = 0.f;
+        row[(size_t)(p.Hq + p.Hkv + kvh) * HD + i] = 0.f;
+      }
+  };
+  if (p.n_splits == 1 || p.part_acc != nullptr) {
+    if (p.clear_parts) clear_sums();
+    return;
+  }
   // The slices of this (sequence, kv head, head chunk) are the blocks of one cluster: each leaves its
   // merged (max, sum, output) in its own shared memory; every block then finishes an equal share of
   // the outputs, reading all slices' values of them through distributed shared memory.
@@ -281,6 +308,7 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
   if (threadIdx.x == 0) TSTAMP(5);
   const int NS = p.n_splits;
   const int me = (int)cl.block_rank();
+  if (p.clear_parts && me == NS - 1) clear_sums();      // every slice of the cluster has read them
   const int total = GC * HD;
   const int share = (total + NS - 1) / NS;
   for (int idx = me * share + threadIdx.x; idx < min(total, (me + 1) * share); idx += DM_THREADS) {
@@ -355,8 +383,8 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
                                           const int* token_pos, void* out, int ldo, int Hq, int Hkv, int hd,
                                           int page_size, int n_splits, int window, float scale, int keys_per_tile,
                                           float* scratch, const float* parts, int S, long long part_stride,
-                                          const float* cos_t, const float* sin_t, int write_cache,
-                                          cudaStream_t stream) {
+                                          const float* cos_t, const float* sin_t, int write_cache, int clear_parts,
+                                          const float* row_scale, cudaStream_t stream) {
   if (B <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return DLGO_ERR_SIZE;
   if (!dlgo_attention_decode_mma_takes(hd, page_size, n_splits)) return DLGO_ERR_SIZE;
@@ -369,7 +397,10 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
     // fused rotation and append: one head chunk per kv head, 16-byte slices, tables present
     if (Hq / Hkv > DM_GM || S <= 0 || (part_stride & 3) || ((uintptr_t)parts & 15) || cos_t == nullptr || sin_t == nullptr)
       return DLGO_ERR_SIZE;
+    // clearing needs one sum whose readers meet: a single block or one cluster per (sequence, kv head)
+    if (clear_parts && (S != 1 || n_splits > 8)) return DLGO_ERR_SIZE;
   }
+  if (parts == nullptr && (clear_parts || row_scale != nullptr)) return DLGO_ERR_SIZE;
   const int G = Hq / Hkv;
   DecMmaParams p;
   p.q = (const __nv_bfloat16*)q; p.ldq = ldq;
@@ -381,6 +412,8 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
   p.window = window; p.scale = scale;
   p.parts = parts; p.S = S; p.part_stride = (size_t)part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
   p.write_cache = write_cache;
+  p.clear_parts = clear_parts;
+  p.row_scale = row_scale;
   p.part_acc = n_splits > 8 ? scratch : nullptr;
   p.part_ml = n_splits > 8 ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;

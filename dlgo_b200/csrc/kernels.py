@@ -521,10 +521,14 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
                          window: int = 0, n_splits: int = 1, keys_per_tile: int = 16,
                          scratch: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None,
                          cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
-                         write_cache: bool = True) -> torch.Tensor:
+                         write_cache: bool = True, clear_parts: bool = False,
+                         row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys and values, bfloat16, on the
     tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster, more go through
-    ``scratch`` (``attention_scratch_floats`` floats) and a second kernel."""
+    ``scratch`` (``attention_scratch_floats`` floats) and a second kernel.  With ``parts`` (the q|k|v
+    projection as fp32 [slices, sequences, columns], unrotated) the kernel sums the slices, rotates q and k
+    and appends k and v itself; ``clear_parts`` (one slice, at most 8 page slices): the sum is left zero;
+    ``row_scale`` [sequences]: a factor on each token's sums."""
     for n, t in (("out", out), ("kpages", kpages), ("vpages", vpages)):
         _need(t, torch.bfloat16, n)
     for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
@@ -550,6 +554,14 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
         if not attention_decode_mma_fuses_rope(num_heads, num_kv_heads, head_dim, head_dim, False):
             raise KernelError("attention_decode_mma: these head counts cannot take the fused rotation")
         S, part_stride = parts.shape[0], parts.stride(0)
+        if clear_parts and (S != 1 or n_splits > 8):
+            raise KernelError("attention_decode_mma: only one summed slice read by at most 8 page slices can be cleared")
+        if row_scale is not None:
+            _need(row_scale, torch.float32, "row_scale")
+            if row_scale.numel() < B:
+                raise KernelError("attention_decode_mma: row_scale needs a factor per sequence")
+    if parts is None and (clear_parts or row_scale is not None):
+        raise KernelError("attention_decode_mma: clear_parts and row_scale go with parts")
     page_size = kpages.shape[-2]
     if n_splits > 8:
         need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
@@ -560,7 +572,7 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
         _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim),
         _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile),
         _ptr(scratch if n_splits > 8 else None), _ptr(parts), _i(S), _ll(part_stride), _ptr(cos), _ptr(sin),
-        _i(1 if write_cache else 0), _stream())
+        _i(1 if write_cache else 0), _i(1 if clear_parts else 0), _ptr(row_scale), _stream())
     _check(st, "attention_decode_mma", 2 if n_splits > 8 else 1)
     return out
 

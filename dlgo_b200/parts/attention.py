@@ -24,21 +24,18 @@ from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
 from .linear import ADD_F32, STORE, Linear
 from .registry import MIXERS
 
-_TARGET_BLOCKS = 2 * 148  # blocks wanted in flight for decode attention (general kernel)
-# The decode kernel can also rotate q and k and append k and v itself (one launch less per layer); measured
-# inside a whole step it is no faster than the separate rope kernel, so it is opt-in: DLGO_ATTN_FUSE_ROPE=1.
-_NO_FUSE = not os.environ.get("DLGO_ATTN_FUSE_ROPE")
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
-# keys and values that the rope kernel hints into L2 for the attention kernel, per layer (0: off, the
-# default: measured on a B200 the hint does not pay, the attention kernel's own hint is early enough)
-_AHEAD_BYTES = int(os.environ.get("DLGO_ATTN_AHEAD_MB", 0)) << 20
 _MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp iteration of the tensor-core decode kernel (0: off)
-# ... which can also sum the projection's slices, rotate and append itself (one launch less per layer).  Opt-in:
-# measured in a whole step it is slower (0.918 against 0.891 ms at batch 8): every slice of a sequence repeats
-# the sum of the query's K-slices, and the block that appends starts its keys a round trip later.
-_QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))   # the projection's K-slices meet in one fp32 sum
-_MMA_FUSE = os.environ.get("DLGO_ATTN_MMA_FUSE_ROPE", "0") == "1"
-_DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 4 * 148))  # and for the decode kernel, whose blocks are small
+# few tokens: the projection's K-slices meet in one fp32 sum (reductions at the memory) that is zero between steps
+_QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))
+# ... which the tensor-core decode kernel reads itself: it rotates q and k, appends k and v and clears the sum, so
+# the rotation needs no launch of its own.  Measured on a B200 (Llama 3.2 1B sizes, batch 8): see DESIGN.md.
+_FUSE_ROPE = int(os.environ.get("DLGO_ATTN_FUSE_ROPE", 1))
+
+
+def _sm_count(device: torch.device) -> int:
+    from .tensor_core import sm_count
+    return sm_count(device)
 
 
 class GQAAttention(Mixer):
@@ -90,6 +87,21 @@ class GQAAttention(Mixer):
         self._no_rotation = torch.zeros((1, 1), dtype=torch.float32, device=runtime.device)
 
     # -------------------------------------------------------------------- forward
+    def _decode_slices(self, ctx: Any, cache: Any, T: int, group: int, pages: int):
+        """(page slices per sequence, scratch, counters) of the decode kernels: slices so that every SM has
+        several blocks (whole waves: rounded down); 2..8 slices form a thread-block cluster and combine
+        through distributed shared memory, more (one very long sequence alone) go through scratch memory."""
+        blocks = 4 * _sm_count(cache.keys.device)
+        base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
+        n_splits = max(1, min(pages, blocks // base_blocks))
+        scratch = counters = None
+        if n_splits > _CLUSTER_MAX and pages <= 64 and _CLUSTER_MAX > 1:
+            n_splits = _CLUSTER_MAX
+        if n_splits > _CLUSTER_MAX:
+            scratch = ctx.scratch("attention", K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+            counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
+        return n_splits, scratch, counters
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
         T = ctx.n_tokens
@@ -101,75 +113,53 @@ class GQAAttention(Mixer):
             cos = sin = self._no_rotation
             rot, inter = 0, False
         act = self.wqkv.weight.dtype
-        decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
-        fused_rope = decode_kernel and not _NO_FUSE and K.attention_decode_fuses_rope(
-            act, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.page_size)
-        # few tokens: the projection leaves its K-slices unsummed and whoever rotates adds them
-        qkv = None
-        clear_parts = False
-        if _QKV_SUM and self.wqkv.sums_slices_at_memory(T) and not (fused_rope or _MMA_FUSE):
-            # ... or its K-slices add themselves, at the memory, into one fp32 sum that is zero between
-            # steps: the rotation reads it once and leaves zeros behind
-            n = self.q_dim + 2 * self.kv_dim
-            qkv_parts = ctx.zeros(f"qkv_sum{n}", T * n, torch.float32)[:T * n].view(1, T, n)
-            self.wqkv(x, ADD_F32, qkv_parts[0])
-            clear_parts = True
-        else:
-            qkv_parts = self.wqkv.partials(x, single_ok=False)
-        if qkv_parts is None:
-            qkv = self.wqkv(x, STORE)
-        # the tensor-core decode kernel can take the slices as they are: it sums, rotates and appends itself
-        mma_fused = (decode_kernel and _MMA_FUSE and _MMA_KEYS and qkv_parts is not None and not fused_rope and
-                     K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, 1) and
-                     K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter))
-        if not fused_rope and not mma_fused:
-            if qkv is None:
-                qkv = torch.empty((T, self.q_dim + 2 * self.kv_dim), dtype=x.dtype, device=x.device)
-            ahead = 0
-            if decode_kernel and qkv_parts is not None and _AHEAD_BYTES > 0:
-                # pages of keys and values per (sequence, kv head) to hint into L2 for the attention kernel
-                page_bytes = cache.page_size * self.head_dim * self.wqkv.weight.element_size()
-                ahead = max(1, _AHEAD_BYTES // (2 * T * self.num_kv_heads * page_bytes))
-            K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
-                          cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                          qkv_parts, ahead, self.window or 0, clear_parts)
+        n_cols = self.q_dim + 2 * self.kv_dim
         longest = ctx.capacity if ctx.captured else ctx.max_len
         pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
+        decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
+        n_splits, scratch, counters = self._decode_slices(ctx, cache, T, group, pages) if decode_kernel else (1, None, None)
+        # bfloat16, common head sizes, one token per sequence: scores and weighted sum on the tensor cores
+        mma = (decode_kernel and _MMA_KEYS > 0 and
+               K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits))
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
-        if decode_kernel:
-            # one token per sequence: the latency-shaped kernel, sliced so that every SM has several blocks
-            base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
-            n_splits = max(1, min(pages, _DECODE_BLOCKS // base_blocks))   # whole waves: rounded down
-            scratch = counters = None
-            if n_splits > _CLUSTER_MAX and pages <= 64 and _CLUSTER_MAX > 1:
-                n_splits = _CLUSTER_MAX
-            if n_splits > _CLUSTER_MAX:
-                # very long sequences at small batches: slices through scratch, the last one combines
-                scratch = ctx.scratch("attention",
-                                      K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
-                counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
-            # (2..8 slices form a thread-block cluster and combine through distributed shared memory)
-            if mma_fused:
-                K.attention_decode_mma(None, qkv_parts.shape[2], T, cache.keys, cache.values, cache.page_table,
-                                       ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
-                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS, scratch,
-                                       qkv_parts, cos, sin, cache.writes)
-            elif (not fused_rope and _MMA_KEYS and
-                    K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits)):
-                # bfloat16, common head sizes: the scores and the weighted sum on the tensor cores
-                K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table,
-                                       ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
-                                       self.head_dim, self.scale, self.window or 0, n_splits, _MMA_KEYS, scratch)
-            elif fused_rope:
-                # rotation of q and k and the append of k and v happen inside the attention kernel
-                K.attention_decode_rope(qkv, qkv_parts, T, cos, sin, rot, inter, cache.writes, cache.keys,
-                                        cache.values, cache.page_table, ctx.seq_slot, ctx.token_pos, out,
-                                        self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                                        self.window or 0, n_splits, scratch, counters)
+        qkv = None
+        rotated = False
+        if _QKV_SUM and self.wqkv.sums_slices_at_memory(T):
+            # few tokens: the projection's K-slices add themselves, at the memory, into one fp32 sum that is zero
+            # between steps; whoever rotates reads it once and leaves zeros behind
+            qkv_sum = ctx.zeros(f"qkv_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(1, T, n_cols)
+            self.wqkv(x, ADD_F32, qkv_sum[0])
+            if (mma and _FUSE_ROPE and n_splits <= 8 and
+                    K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter)):
+                # the decode kernel rotates, appends and clears itself: no launch for the rotation
+                K.attention_decode_mma(None, n_cols, T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                                       ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                                       self.scale, self.window or 0, n_splits, _MMA_KEYS, None, qkv_sum, cos, sin,
+                                       cache.writes, clear_parts=True)
+                rotated = True
             else:
-                K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                qkv = torch.empty((T, n_cols), dtype=x.dtype, device=x.device)
+                K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                              cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
+                              qkv_sum, 0, self.window or 0, True)
+        else:
+            # ... or leaves its K-slices unsummed for the rotation to add in order; else the finished product
+            qkv_parts = self.wqkv.partials(x, single_ok=False)
+            qkv = (self.wqkv(x, STORE) if qkv_parts is None else
+                   torch.empty((T, n_cols), dtype=x.dtype, device=x.device))
+            K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                          cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
+                          qkv_parts, 0, self.window or 0, False)
+        if rotated:
+            pass
+        elif mma:
+            K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                    ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                                   self.window or 0, n_splits, scratch, counters)
+                                   self.window or 0, n_splits, _MMA_KEYS, scratch)
+        elif decode_kernel:
+            K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                               ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                               self.window or 0, n_splits, scratch, counters)
         elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
             # prompts: 128 query rows per CTA on the tensor cores
             tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
@@ -181,7 +171,8 @@ class GQAAttention(Mixer):
             tiles, n_tiles, tile_max = ctx.tiles(qt)
             n_gchunks = (group + gchunk - 1) // gchunk
             base_blocks = n_tiles * self.num_kv_heads * n_gchunks
-            n_splits = max(1, min(pages, -(-_TARGET_BLOCKS // base_blocks))) if ctx.decode else 1
+            target = 2 * _sm_count(x.device)
+            n_splits = max(1, min(pages, -(-target // base_blocks))) if ctx.decode else 1
             scratch = None
             if n_splits > 1:
                 scratch = ctx.scratch("attention",

@@ -26,12 +26,12 @@ SKINNY_MAX = 64          # tokens up to which the weight is the M operand
 # partial result of tokens x outputs floats (at 64 tokens half of the weight's own bytes) and makes
 # the consumer's sum longer.  Measured on a B200 (tokens a second, 148 against 296 CTAs): 8.95K
 # against 8.77K at batch 8, 35.2K against 30.3K at batch 64.
-TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 148))
+TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 0))          # 0: the device's SM count
 # At most 16 tokens a partial tile is small (and, where it goes into the residual, is added there with
 # reductions at the memory and never read again): three CTAs per two SMs then stream better than one per
 # SM.  Measured (tokens a second, 148 / 222 / 296): 9.90K / 10.10K / 10.05K at batch 8, 1.32K / 1.40K /
 # 1.38K at batch 1; at batch 64, with tiles four times as wide, 49.0K / 42.9K / 39.7K.
-TARGET_CTAS_FEW = int(os.environ.get("DLGO_TC_TARGET_CTAS_FEW", 222))
+TARGET_CTAS_FEW = int(os.environ.get("DLGO_TC_TARGET_CTAS_FEW", 0))  # 0: one and a half times the SM count
 MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
@@ -71,12 +71,27 @@ def _counter_buffer(device: torch.device) -> torch.Tensor:
     return c
 
 
-def skinny_shape(tokens: int, n: int, k: int) -> tuple[int, int]:
+_sm_counts: Dict[int, int] = {}
+
+
+def sm_count(device: Optional[torch.device] = None) -> int:
+    """SMs of the device (asked once per device)."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
+def skinny_shape(tokens: int, n: int, k: int, device: Optional[torch.device] = None) -> tuple[int, int]:
     """(bn, splits) for ``tokens`` <= SKINNY_MAX against a weight [n, k]."""
     bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
-    target = TARGET_CTAS_FEW if tokens <= 16 else TARGET_CTAS
+    if tokens <= 16:
+        target = TARGET_CTAS_FEW or (3 * sm_count(device)) // 2
+    else:
+        target = TARGET_CTAS or sm_count(device)
     splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, target // tiles)) if tiles < target else 1
     return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
@@ -124,14 +139,14 @@ class TensorCorePlan:
                                   device=x.device)
         if normed:
             # one K-slice unless the epilogue can take several (the atomic add)
-            _, splits = skinny_shape(t, self.n, self.k)
+            _, splits = skinny_shape(t, self.n, self.k, self.weight.device)
             if epi == K.TC_ADD_F32:
                 epi = K.TC_RED_F32
             elif epi != K.TC_RED_F32:
                 splits = 1
             return K.gemm_tc_normed(self.weight, x.residual, x.weight, x.eps, out, epi, splits)
         if t <= SKINNY_MAX:
-            bn, splits = skinny_shape(t, self.n, self.k)
+            bn, splits = skinny_shape(t, self.n, self.k, self.weight.device)
             if (NORM_IN_GEMM & 1) and epi == K.TC_ADD_F32 and splits > 1 and t <= RED_MAX_TOKENS:
                 return K.gemm_tc(self.weight, x, out, True, K.TC_RED_F32, bn, splits, static_operand=1)
             splits, cluster = clustered(splits, True)
@@ -150,7 +165,7 @@ class TensorCorePlan:
     def sums_slices_at_memory(self, tokens: int) -> bool:
         if not (NORM_IN_GEMM & 1) or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):
             return False
-        return skinny_shape(tokens, self.n, self.k)[1] > 1
+        return skinny_shape(tokens, self.n, self.k, self.weight.device)[1] > 1
 
     def partials(self, x, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
@@ -164,7 +179,7 @@ class TensorCorePlan:
             return None
         if for_residual and (NORM_IN_GEMM & 1) and t <= RED_MAX_TOKENS:
             return None                     # the caller's add epilogue adds the slices into the residual
-        bn, splits = skinny_shape(t, self.n, self.k)
+        bn, splits = skinny_shape(t, self.n, self.k, self.weight.device)
         if not isinstance(x, torch.Tensor):
             # a deferred norm, computed by the kernel
             if splits == 1 and not single_ok:

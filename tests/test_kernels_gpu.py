@@ -1039,3 +1039,50 @@ def test_tensor_core_decode_attention_with_the_rotation_and_append_inside(hq, hk
         torch.testing.assert_close(b[0], a[0], atol=2e-2, rtol=2e-2)
         torch.testing.assert_close(b[1], a[1], atol=1e-2, rtol=8e-3)   # (x0*c - x1*s may contract differently: one ulp)
         assert torch.equal(b[2], a[2])
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 64), (24, 8, 128), (8, 1, 64)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_tensor_core_decode_attention_reads_scales_and_clears_the_projections_sum(hq, hkv, hd, n_splits):
+    # the schedule of a decode step: the q|k|v projection's K-slices have added themselves into ONE fp32 sum;
+    # the attention kernel scales it per token, rotates, appends, attends, and leaves the sum zero.  Against
+    # rope_append (on the scaled sum) followed by the kernel fed with the finished q.
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    torch.manual_seed(hd + n_splits)
+    cos, sin = (t.to(DEV) for t in RotaryEmbedding(hd, hd, 10000.0, 700, "split_half").tables())
+    lens = [300, 1, 64, 65, 640, 129]
+    B = len(lens)
+    pages_per = [(n + 63) // 64 for n in lens]
+    n_pages = sum(pages_per) + 1
+    perm = torch.randperm(n_pages).tolist()
+    pt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    for i, n in enumerate(pages_per):
+        for pg in range(n):
+            pt[i, pg] = perm.pop()
+    pt = pt.to(DEV)
+    ld = (hq + 2 * hkv) * hd
+    total = torch.randn(1, B, ld, device=DEV) * 0.6
+    factor = (torch.rand(B, device=DEV) + 0.5).contiguous()
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    got = {}
+    for fused in (False, True):
+        torch.manual_seed(1)
+        kp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(torch.bfloat16)
+        vp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(torch.bfloat16)
+        out = torch.full((B, hq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+        if not fused:
+            qkv = torch.empty(B, ld, device=DEV, dtype=torch.bfloat16)
+            k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, hd, False, True,
+                          (total * factor[None, :, None]).contiguous())
+            k.attention_decode_mma(qkv, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits, 32)
+        else:
+            work = total.clone()
+            k.attention_decode_mma(None, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits, 32,
+                                   None, work, cos, sin, True, clear_parts=True, row_scale=factor)
+            assert float(work.abs().max()) == 0.0, "the sum must be zero again for the next step"
+        got[fused] = (out.float().clone(), kp.float().clone(), vp.float().clone())
+    torch.testing.assert_close(got[True][0], got[False][0], atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got[True][1], got[False][1], atol=1e-2, rtol=8e-3)
+    torch.testing.assert_close(got[True][2], got[False][2], atol=1e-2, rtol=8e-3)
