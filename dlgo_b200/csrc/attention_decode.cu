@@ -39,14 +39,6 @@ struct DecParams {
   float* part_ml;
   int* counters;         // [B * Hkv * n_gchunks] zero before the first launch and left zero, or null
   int Hq, Hkv, page_size, n_splits, n_gchunks, window;
-  // optional fusion of the rotation and the cache append (one kernel less per layer):
-  const void* qkv;       // [B, ldq] projection output (q | k | v heads) in T, or null
-  const float* parts;    // or its unsummed K-slices [S][B][ldq] fp32
-  int S;
-  size_t part_stride;
-  const float* cos_t;
-  const float* sin_t;
-  int rot, interleaved, fuse_rope, write_cache;
   int cluster;           // 1: the slices of a (sequence, kv head) form one thread-block cluster and combine
                          // through distributed shared memory; no scratch, no counters
   float scale;
@@ -160,7 +152,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
   if (threadIdx.x == 0) TSTAMP(2);
 
   float q[DEC_GMAX][VEC], acc[DEC_GMAX][VEC], m[DEC_GMAX], l[DEC_GMAX];
-  if (!p.fuse_rope) {
+  {
     const T* qrow = (const T*)p.q + (size_t)b * p.ldq + (size_t)(kvh * G + g0) * HD + sub * VEC;
 #pragma unroll
     for (int g = 0; g < DEC_GMAX; ++g) {
@@ -168,102 +160,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
       else
 #pragma unroll
         for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
-    }
-  } else {
-    // The projection's output comes in unrotated (possibly as unsummed K-slices): this lane's 16
-    // bytes of a head are summed and rotated here (models/llm/forward.go:246-252), and the block
-    // whose pages hold the new position appends the token's key and value (forward.go:257).
-    auto load_vec = [&](int col, float* v) {
-      if (p.parts != nullptr) {
-        // up to eight slices' loads are in flight before the first add (slices are added in order)
-        const float* src = p.parts + (size_t)b * p.ldq + col;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) v[e] = 0.f;
-        for (int s0 = 0; s0 < p.S; s0 += 8) {
-          float4 t4[8][VEC / 4];
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int e4 = 0; e4 < VEC / 4; ++e4)
-              t4[j][e4] = (s0 + j < p.S)
-                              ? *reinterpret_cast<const float4*>(src + (size_t)(s0 + j) * p.part_stride + 4 * e4)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int e4 = 0; e4 < VEC / 4; ++e4) {
-              v[4 * e4] += t4[j][e4].x;
-              v[4 * e4 + 1] += t4[j][e4].y;
-              v[4 * e4 + 2] += t4[j][e4].z;
-              v[4 * e4 + 3] += t4[j][e4].w;
-            }
-        }
-      } else {
-        Ld16<T>::load((const T*)p.qkv + (size_t)b * p.ldq + col, v);
-      }
-    };
-    const int rhalf = p.rot / 2;
-    auto rotate = [&](float* v) {
-      const int d0 = sub * VEC;
-      if (p.rot == 0) return;
-      if (p.interleaved) {
-#pragma unroll
-        for (int e = 0; e < VEC; e += 2) {
-          const int i = (d0 + e) >> 1;
-          if (2 * i < p.rot) {
-            const float c = p.cos_t[(size_t)pos * rhalf + i], sn = p.sin_t[(size_t)pos * rhalf + i];
-            const float x0 = v[e], x1 = v[e + 1];
-            v[e] = x0 * c - x1 * sn;
-            v[e + 1] = x0 * sn + x1 * c;
-          }
-        }
-      } else {
-        // pairs (i, i + rot/2) with rot == head size: the partner sits LPK/2 lanes away
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float other = __shfl_xor_sync(0xffffffffu, v[e], LPK / 2);
-          const int d = d0 + e;
-          const bool low = d < rhalf;
-          const int i = low ? d : d - rhalf;
-          const float c = p.cos_t[(size_t)pos * rhalf + i], sn = p.sin_t[(size_t)pos * rhalf + i];
-          v[e] = low ? (v[e] * c - other * sn) : (other * sn + v[e] * c);
-        }
-      }
-    };
-#pragma unroll
-    for (int g = 0; g < DEC_GMAX; ++g) {
-      if (g < GC) {
-        load_vec((kvh * G + g0 + g) * HD + sub * VEC, q[g]);
-        rotate(q[g]);
-        // the rotated query goes through the storage type, as it does on the unfused path
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) q[g][e] = to_float(from_float<T>(q[g][e]));
-      } else {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) q[g][e] = 0.f;
-      }
-    }
-    const int pg_new = pos / PS;
-    if (p.write_cache && gc == 0 && pg_new >= pg_b && pg_new < pg_e) {   // block-uniform
-      if (warp == 0) {
-        float kf[VEC], vf[VEC];
-        load_vec((p.Hq + kvh) * HD + sub * VEC, kf);
-        load_vec((p.Hq + p.Hkv + kvh) * HD + sub * VEC, vf);
-        rotate(kf);
-        if (grp == 0) {
-          const int page = p.page_table[(size_t)slot * p.max_pages + pg_new];
-          const size_t o = (((size_t)page * p.Hkv + kvh) * PS + (pos % PS)) * HD + sub * VEC;
-          T* kd = (T*)p.kpages + o;
-          T* vd = (T*)p.vpages + o;
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            kd[e] = from_float<T>(kf[e]);
-            vd[e] = from_float<T>(vf[e]);
-          }
-        }
-      }
-      __threadfence_block();
-      __syncthreads();   // the new row is in place before any warp of this block reads the page
     }
   }
 #pragma unroll
@@ -612,54 +508,7 @@ DLGO_EXPORT int dlgo_attention_decode(const void* q, int dtype, int B, int ldq, 
   p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits;
   p.n_gchunks = (G + DEC_GMAX - 1) / DEC_GMAX;
   p.window = window; p.scale = scale;
-  p.qkv = nullptr; p.parts = nullptr; p.S = 0; p.part_stride = 0; p.cos_t = nullptr; p.sin_t = nullptr;
-  p.rot = 0; p.interleaved = 0; p.fuse_rope = 0; p.write_cache = 0;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;
-  return decode_common(p, dtype, B, hd, stream);
-}
-
-// 1 if the rotation and the cache append can be done inside the decode kernel for these sizes: one
-// block per (sequence, kv head) owns the head's new row (at most 4 query heads per kv head), and the
-// rotation pairs either sit in one lane (interleaved) or exactly half a head apart.
-DLGO_EXPORT int dlgo_attention_decode_fuses_rope(int dtype, int Hq, int Hkv, int hd, int rot, int interleaved,
-                                                 int page_size) {
-  if (!dlgo_attention_decode_takes(dtype, hd, page_size) || Hkv <= 0 || Hq % Hkv) return 0;
-  if (Hq / Hkv > DEC_GMAX) return 0;
-  if (rot < 0 || rot > hd || rot % 2) return 0;
-  if (rot == 0) return 1;
-  if (interleaved) return 1;
-  const int vec = dtype == DLGO_BF16 ? 8 : 4;
-  return rot == hd && hd / vec >= 2;
-}
-
-// The decode kernel with the rotation and the append inside: `qkv` [B, ldq] (q | k | v heads, unrotated)
-// in the storage type, or `parts` [S][B][ldq] fp32 (its unsummed K-slices); cos/sin [positions, rot/2].
-DLGO_EXPORT int dlgo_attention_decode_rope(const void* qkv, const float* parts, int S, long long part_stride,
-                                           int dtype, int B, int ldq, const float* cos_t, const float* sin_t,
-                                           int rot, int interleaved, int write_cache, void* kpages, void* vpages,
-                                           const int* page_table, int max_pages, const int* seq_slot,
-                                           const int* token_pos, void* out, int ldo, float* scratch, int* counters,
-                                           int Hq, int Hkv, int hd, int page_size, int n_splits, int window,
-                                           float scale, cudaStream_t stream) {
-  if (B <= 0) return DLGO_OK;
-  if (n_splits <= 0 || n_splits > 65535) return DLGO_ERR_SIZE;
-  if (dtype != DLGO_F32 && dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
-  if (!dlgo_attention_decode_fuses_rope(dtype, Hq, Hkv, hd, rot, interleaved, page_size)) return DLGO_ERR_SIZE;
-  if ((qkv == nullptr) == (parts == nullptr)) return DLGO_ERR_SIZE;
-  if (parts != nullptr && ((part_stride & 3) || (ldq & 3) || S <= 0)) return DLGO_ERR_ALIGN;
-  const int use_cluster = (n_splits > 1 && n_splits <= 8 && scratch == nullptr) ? 1 : 0;
-  if (n_splits > 1 && scratch == nullptr && !use_cluster) return DLGO_ERR_SIZE;
-  DecParams p;
-  p.cluster = use_cluster;
-  p.q = nullptr; p.ldq = ldq; p.kpages = kpages; p.vpages = vpages; p.page_table = page_table; p.max_pages = max_pages;
-  p.seq_slot = seq_slot; p.token_pos = token_pos; p.out = out; p.ldo = ldo;
-  p.part_acc = scratch;
-  p.part_ml = scratch ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
-  p.counters = counters;
-  p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.n_splits = n_splits; p.n_gchunks = 1;
-  p.window = window; p.scale = scale;
-  p.qkv = qkv; p.parts = parts; p.S = S; p.part_stride = (size_t)part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
-  p.rot = rot; p.interleaved = interleaved; p.fuse_rope = 1; p.write_cache = write_cache;
   return decode_common(p, dtype, B, hd, stream);
 }
 

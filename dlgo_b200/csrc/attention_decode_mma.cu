@@ -59,7 +59,6 @@ struct DecMmaParams {
   int write_cache;
   int clear_parts;       // S = 1 and `parts` is a sum that must be zero again for the next step: the block (or the
                          // cluster's first block) clears this (sequence, kv head)'s columns once all have read them
-  const float* row_scale;  // [B] or null: factor on the sums of a token (a norm's scale applied after the product)
   float* part_acc;       // more than 8 slices: [B, Hq, n_splits, HD] and [B, Hq, n_splits, 2] scratch,
   float* part_ml;        // combined by a second kernel; else null (slices of a cluster combine on chip)
 };
@@ -126,7 +125,6 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
   if (threadIdx.x == 0) TSTAMP(1);
   pdl_wait();
   if (threadIdx.x == 0) TSTAMP(2);
-  const float rs = (p.parts != nullptr && p.row_scale != nullptr) ? __ldcg(p.row_scale + b) : 1.f;
 
   // query fragments: head r of this block's chunk, this lane's quarter of the dimensions
   uint32_t qa[KK][2];
@@ -161,7 +159,6 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
             v0 += __ldcg(vin + so + i); v1 += __ldcg(vin + so + i + RH);
           }
           const float cs = p.cos_t[(size_t)pos * RH + i], sn = p.sin_t[(size_t)pos * RH + i];
-          k0 *= rs; k1 *= rs; v0 *= rs; v1 *= rs;
           const_cast<T*>(p.kpages)[row + i] = __float2bfloat16_rn(k0 * cs - k1 * sn);
           const_cast<T*>(p.kpages)[row + i + RH] = __float2bfloat16_rn(k0 * sn + k1 * cs);
           const_cast<T*>(p.vpages)[row + i] = __float2bfloat16_rn(v0);
@@ -205,8 +202,6 @@ __global__ void __launch_bounds__(DM_THREADS, HD <= 64 ? 4 : 3) attention_decode
       }
       const float* cs = p.cos_t + (size_t)pos * RH + (c & 1) * QN;
       const float* sn = p.sin_t + (size_t)pos * RH + (c & 1) * QN;
-#pragma unroll
-      for (int k = 0; k < QN; ++k) x[k] *= rs;
       float y[QN];
 #pragma unroll
       for (int k = 0; k < QN; ++k) {
@@ -384,7 +379,7 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
                                           int page_size, int n_splits, int window, float scale, int keys_per_tile,
                                           float* scratch, const float* parts, int S, long long part_stride,
                                           const float* cos_t, const float* sin_t, int write_cache, int clear_parts,
-                                          const float* row_scale, cudaStream_t stream) {
+                                          cudaStream_t stream) {
   if (B <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return DLGO_ERR_SIZE;
   if (!dlgo_attention_decode_mma_takes(hd, page_size, n_splits)) return DLGO_ERR_SIZE;
@@ -400,7 +395,7 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
     // clearing needs one sum whose readers meet: a single block or one cluster per (sequence, kv head)
     if (clear_parts && (S != 1 || n_splits > 8)) return DLGO_ERR_SIZE;
   }
-  if (parts == nullptr && (clear_parts || row_scale != nullptr)) return DLGO_ERR_SIZE;
+  if (parts == nullptr && clear_parts) return DLGO_ERR_SIZE;
   const int G = Hq / Hkv;
   DecMmaParams p;
   p.q = (const __nv_bfloat16*)q; p.ldq = ldq;
@@ -413,7 +408,6 @@ DLGO_EXPORT int dlgo_attention_decode_mma(const void* q, int B, int ldq, const v
   p.parts = parts; p.S = S; p.part_stride = (size_t)part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
   p.write_cache = write_cache;
   p.clear_parts = clear_parts;
-  p.row_scale = row_scale;
   p.part_acc = n_splits > 8 ? scratch : nullptr;
   p.part_ml = n_splits > 8 ? scratch + (size_t)B * Hq * n_splits * hd : nullptr;
   if ((long long)Hkv * p.n_gchunks > 65535) return DLGO_ERR_SIZE;

@@ -20,10 +20,9 @@
 // (models/llm/forward.go:163,169), or SwiGLU (ops/activation.go:8-38) over a weight whose rows come
 // in blocks of 16 gate rows followed by their 16 up rows, writing h = silu(g) * u.
 //
-// Few tokens also have: partials (every K-slice leaves its fp32 tile for the reader to add), an atomic add
+// Few tokens also have: partials (every K-slice leaves its fp32 tile for the reader to add) and an atomic add
 // of every K-slice into an fp32 residual (no pass over partial results at all; the order of the adds,
-// hence the last bits of the sum, is not fixed), and B computed in the kernel as the RMSNorm
-// (ops/norm.go:10-32) of fp32 residual rows, which spares the norm its own launch.
+// hence the last bits of the sum, is not fixed).
 //
 // Split-K (decode): `splits` CTAs share an output tile.  Each writes its fp32 partial to a
 // workspace; the CTA that arrives last adds the partials in slice order (so the sum does not
@@ -58,17 +57,6 @@ struct TcParams {
   int stages;         // shared-memory ring size
   int staged;         // many-token kernels: epilogue through shared memory and TMA stores
   int static_operand; // 0: none; 1: A, 2: B holds weights no earlier kernel writes (loaded before pdl_wait)
-  int l2_ahead;       // K blocks of the static operand, beyond the ring, to pull into L2 before pdl_wait
-  int cluster;        // > 1: that many consecutive K-slices are the CTAs of a thread-block cluster; their
-                      // partial tiles meet in the first CTA through distributed shared memory, in slice
-                      // order, and only it runs the epilogue (TC_PARTIAL: one slice per cluster)
-  // B as the RMSNorm of fp32 rows (few tokens, transposed): B[t, k] = bf16(x[t, k] * scale_t * w[k]) with
-  // scale_t = 1 / sqrt(mean_k x[t, k]^2 + eps); the epilogue warps compute it after the wait and write it
-  // into the ring's stages, no tile of B is loaded
-  const float* norm_x;  // [Rb, K] fp32, row stride norm_ld; null: B comes from memory as bf16
-  int norm_ld;
-  const float* norm_w;  // [K] fp32
-  float norm_eps;
 };
 
 template <int BN> struct TcConfig {
@@ -176,112 +164,10 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
   }
 }
 
-// One element of a transposed tile (row = weight row, col = token) -> memory, per epilogue; `slice`
-// is the partials' slice.  Called by whole warps (the SwiGLU pairs lanes l and l + 16).
-__device__ __forceinline__ void epilogue_store_one(const TcParams& p, float v, int row, int col, int lane, int slice) {
-  if (p.epilogue == TC_SWIGLU) {
-    const float other = __shfl_xor_sync(0xffffffffu, v, 16);
-    if (lane < 16 && row + 16 < p.Ra) {
-      const int feature = (row >> 5) * 16 + (row & 15);
-      ((__nv_bfloat16*)p.out)[(size_t)col * p.ldo + feature] = __float2bfloat16_rn(silu_mul(v, other));
-    }
-    return;
-  }
-  if (row >= p.Ra) return;
-  const size_t o = (size_t)col * p.ldo + row;
-  if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
-  else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[o] = v;
-  else if (p.epilogue == TC_ADD_F32) ((float*)p.out)[o] += v;
-  else ((float*)p.out)[(size_t)slice * p.Rb * p.ldo + o] = v;
-}
-
-// Where a cluster's K-slices meet: fp32 [cluster][cpr][128] behind the ring and its barriers.
-__device__ __forceinline__ uint8_t* staging_of(uint8_t* smem, int stages, int stage_bytes) {
-  return smem + stages * stage_bytes + 256;
-}
-
-// The B operand of a few-token product as the RMSNorm of at most eight fp32 rows, by the four epilogue
-// warps (`q4` 0..3).  Every warp reads its rows whole (all loads of a pass in flight at once), reduces the
-// squares, and writes the normalised values of the CTA's K range as bf16 into `bres`: one K block of 64
-// after another, eight rows of 128 bytes each in the 128-byte swizzle, 1 KB per K block.  The tensor
-// core's tile has sixteen rows, so the tile of K block i is the 2 KB at i KB: its rows 8..15 are the next
-// K block's rows (finite numbers that land in output columns nobody stores), and behind the last K block
-// lies a kilobyte of zeros.  The operand stays in shared memory for the whole product: no stage of the
-// ring waits for it.  V float4 per lane and row (K <= 128 V), NR rows per pass, 8 = 4 NR PASSES rows.
-template <int V, int NR, int PASSES>
-__device__ __forceinline__ void norm_operand(const TcParams& p, uint8_t* bres, uint64_t* bready, int kb0, int kb1,
-                                             int tile_b, int q4, int lane) {
-  static_assert(4 * NR * PASSES == 8, "eight rows");
-  const int n4 = p.K >> 2;
-  if (q4 == 0) {
-    uint4* pad = reinterpret_cast<uint4*>(bres + (kb1 - kb0) * 1024);
-    pad[lane] = make_uint4(0u, 0u, 0u, 0u);
-    pad[lane + 32] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  float4 w4[PASSES == 1 ? V : 1];
-  if constexpr (PASSES == 1) {          // the norm's weight is nobody's output: before the wait
-#pragma unroll
-    for (int i = 0; i < V; ++i) {
-      const int j = lane + 32 * i;
-      w4[i] = j < n4 ? __ldg(reinterpret_cast<const float4*>(p.norm_w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-  }
-  pdl_wait();
-#pragma unroll
-  for (int m = 0; m < PASSES; ++m) {
-    float4 x[NR][V];
-#pragma unroll
-    for (int n = 0; n < NR; ++n) {
-      const int tok = tile_b * 16 + (m * 4 + q4) * NR + n;
-      const float4* row = reinterpret_cast<const float4*>(p.norm_x + (size_t)(tok < p.Rb ? tok : 0) * p.norm_ld);
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const int j = lane + 32 * i;
-        x[n][i] = (tok < p.Rb && j < n4) ? __ldcg(row + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < NR; ++n) {
-      const int t = (m * 4 + q4) * NR + n;       // row of the tile, 0..7
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        ss = fmaf(x[n][i].x, x[n][i].x, ss);
-        ss = fmaf(x[n][i].y, x[n][i].y, ss);
-        ss = fmaf(x[n][i].z, x[n][i].z, ss);
-        ss = fmaf(x[n][i].w, x[n][i].w, ss);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float sc = 1.0f / sqrtf(ss / (float)p.K + p.norm_eps);
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const int j = lane + 32 * i;
-        const int col = 4 * j, kb = col >> 6;
-        if (kb < kb0 || kb >= kb1) continue;     // (columns past K in the last K block: x is zero there)
-        float4 w;
-        if constexpr (PASSES == 1) w = w4[i];
-        else w = j < n4 ? __ldg(reinterpret_cast<const float4*>(p.norm_w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        __nv_bfloat162 h[2] = {__floats2bfloat162_rn(x[n][i].x * sc * w.x, x[n][i].y * sc * w.y),
-                               __floats2bfloat162_rn(x[n][i].z * sc * w.z, x[n][i].w * sc * w.w)};
-        *reinterpret_cast<uint2*>(bres + (kb - kb0) * 1024 + t * 128 + ((((col & 63) >> 3) ^ t) << 4) +
-                                  ((col & 7) << 1)) = *reinterpret_cast<uint2*>(h);
-      }
-    }
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> the tensor core's reads
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bready);
-}
-
-// NORM: 0 B comes from memory; else B is a norm of at most 8 rows computed here: 1 rows of at most 2048,
-// 2 rows of at most 4096.  The ring's stages then hold A only.
-// (kernels of their own: the computed operand lives in registers that the plain kernel should not pay for,
-// since its successor shares the SM with it)
-template <int BN, int NORM>
+template <int BN>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p) {
   using C = TcConfig<BN>;
-  constexpr int STAGE = NORM != 0 ? C::A_BYTES : C::STAGE_BYTES;   // a computed B is not in the ring
+  constexpr int STAGE = C::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // tiles want 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -292,9 +178,6 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
   uint32_t* tmem_slot = (uint32_t*)(accum + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* last_flag = (int*)(tmem_slot + 2);
-  constexpr bool normed = NORM != 0;
-  uint64_t* bready = (uint64_t*)((uint8_t*)full + 192);          // the computed B is written (four warps)
-  uint8_t* bres = smem + ((STAGES * STAGE + 256 + 1023) & ~1023);  // the computed B, 1 KB per K block
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) TSTAMP(0);
@@ -312,7 +195,6 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
-    mbar_init(bready, 4);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -340,20 +222,13 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
         if (p.static_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
         if (p.static_operand == 2) tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
       }
-      // While the predecessors still run (and memory is often idle: norms, attention), the rest of
-      // this CTA's weights are pulled into L2, so that the ring refills from there later.
-      const int nl2 = min(nkb, npre + p.l2_ahead);
-      for (int i = npre; i < nl2; ++i) {
-        if (p.static_operand == 1) tma_prefetch_l2_2d(&map_a, (kb0 + i) * TILE_K, tile_a * TILE_M);
-        if (p.static_operand == 2) tma_prefetch_l2_2d(&map_b, (kb0 + i) * TILE_K, tile_b * BN);
-      }
       TSTAMP(1);
       pdl_wait();
       TSTAMP(2);
       for (int i = 0; i < npre; ++i) {
         uint8_t* a_dst = smem + i * STAGE;
         if (p.static_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], (kb0 + i) * TILE_K, tile_a * TILE_M);
-        if (p.static_operand != 2 && !normed)
+        if (p.static_operand != 2)
           tma_load_2d(a_dst + C::A_BYTES, &map_b, &full[i], (kb0 + i) * TILE_K, tile_b * BN);
       }
       for (int i = npre; i < nkb; ++i) {
@@ -364,15 +239,13 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
         uint8_t* b_dst = a_dst + C::A_BYTES;
         mbar_expect_tx(&full[s], tx);
         tma_load_2d(a_dst, &map_a, &full[s], (kb0 + i) * TILE_K, tile_a * TILE_M);
-        if (!normed) tma_load_2d(b_dst, &map_b, &full[s], (kb0 + i) * TILE_K, tile_b * BN);
+        tma_load_2d(b_dst, &map_b, &full[s], (kb0 + i) * TILE_K, tile_b * BN);
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN < 16 ? 16 : BN);
-      bool b_ok = true;
-      if (normed && nkb > 0) b_ok = mbar_wait(bready, 0, abort_flag);
-      for (int i = 0; b_ok && i < nkb; ++i) {
+      for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
@@ -380,7 +253,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * STAGE);
         const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(normed ? smem_u32(bres) + i * 1024 : a_addr + C::A_BYTES);
+        const uint64_t db = umma_desc_k_sw128(a_addr + C::A_BYTES);
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           // inside a 128-byte swizzle row, the next K = 16 slice starts 32 bytes on (2 in 16-byte units)
@@ -395,13 +268,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
     // epilogue warps: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     const int row = tile_a * TILE_M + quarter * 32 + lane;
-    if constexpr (NORM == 1) {
-      norm_operand<16, 2, 1>(p, bres, bready, kb0, kb1, tile_b, warp - 2, lane);
-    } else if constexpr (NORM == 2) {
-      norm_operand<32, 1, 2>(p, bres, bready, kb0, kb1, tile_b, warp - 2, lane);
-    } else {
-      pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
-    }
+    pdl_wait();  // the output, the workspace and the counters may still be in use by the predecessor
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(accum, 0, abort_flag);
     if (warp == 2 && lane == 0) TSTAMP(5);
@@ -409,37 +276,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
     constexpr int NV = BN >= 32 ? 32 : 16;
     const int ntiles = gridDim.x * gridDim.y;
     const int tile_lin = tile_b * gridDim.x + tile_a;
-    if (p.cluster > 1) {
-      // The K-slices of this tile are the CTAs of a cluster.  Columns (tokens) are dealt out to the
-      // CTAs, `cpr` each: every CTA sends each column of its partial tile to the column's owner (a
-      // store into the owner's shared memory, nothing waits for it), and after one cluster barrier
-      // every owner adds the slices of its columns in slice order and writes them out.
-      const uint32_t me = cluster_ctarank();
-      const int cpr = (BN + p.cluster - 1) / p.cluster;
-      const uint32_t stage0 = smem_u32(staging_of(smem, STAGES, STAGE));
-      const int r_in = quarter * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += NV) {
-        float v[NV];
-        if (ok && nkb > 0) {
-          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-          if (NV == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < NV; ++j) v[j] = 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-          const int col = c0 + j;
-          if (tile_b * BN + col < p.Rb) {
-            const int owner = col / cpr, k = col - owner * cpr;
-            st_cluster_f32(map_to_cta(stage0 + (uint32_t)((((int)me * cpr + k) * TILE_M + r_in) * 4), (uint32_t)owner),
-                           v[j]);
-          }
-        }
-      }
-    } else if (p.epilogue == TC_PARTIAL) {
+    if (p.epilogue == TC_PARTIAL) {
       // every K-slice leaves its fp32 partial in out[split][col][row] (transposed tiles only); whoever
       // reads the result next adds the slices in order.  No ticket, no second pass here.
       float* dst = (float*)p.out + (size_t)split * p.Rb * p.ldo;
@@ -586,25 +423,6 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
 
   tc_fence_before_sync();
   __syncthreads();
-  if (p.cluster > 1) {
-    cluster_sync_all();   // every slice's columns have reached their owners
-    if (warp >= 2) {
-      const int quarter = warp & 3;
-      const int r_in = quarter * 32 + lane;
-      const int row = tile_a * TILE_M + r_in;
-      const int me = (int)cluster_ctarank();
-      const int cpr = (BN + p.cluster - 1) / p.cluster;
-      const float* stage = (const float*)staging_of(smem, STAGES, STAGE);
-      for (int k = 0; k < cpr; ++k) {
-        const int col_in = me * cpr + k;
-        const int col = tile_b * BN + col_in;
-        if (col_in >= BN || col >= p.Rb) break;            // uniform over the CTA
-        float v = 0.f;
-        for (int r = 0; r < p.cluster; ++r) v += stage[((r * cpr + k) * TILE_M) + r_in];   // slice order
-        epilogue_store_one(p, v, row, col, lane, split / p.cluster);
-      }
-    }
-  }
   if (threadIdx.x == 0) TSTAMP(6);
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(&g_gemm_tc_error, 1);
@@ -618,23 +436,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_a, const CUt
   }
 }
 
-template <int BN, int NORM>
+template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ TcParams p) {
-  gemm_tc_body<BN, NORM>(map_a, map_b, p);
-}
-// The first norm variant (rows of at most 2048) under a register cap: 232 x 192 threads leave room
-// in the SM's register file for a CTA of the plain kernel, so that the product that follows can move in
-// and fetch its first weights while this one still runs.
-__global__ void __maxnreg__(232)
-gemm_tc_norm8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const __grid_constant__ TcParams p) {
-  gemm_tc_body<16, 1>(map_a, map_b, p);
-}
-template <int BN, int NORM> constexpr auto tc_kernel_of() {
-  if constexpr (BN == 16 && NORM == 1) return &gemm_tc_norm8_kernel;
-  else return &gemm_tc_kernel<BN, NORM>;
+  gemm_tc_body<BN>(map_a, map_b, p);
 }
 
 // Epilogue of the many-token kernels: one accumulator tile (128 rows x BN fp32 columns in tensor
@@ -1053,14 +859,13 @@ int make_out_map(CUtensorMap* m, const TcParams& p) {
   return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
 }
 
-template <int BN, int NORM = 0>
+template <int BN>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
   using C = TcConfig<BN>;
   static bool configured = false;
   if (!configured) {
-    // (a cluster's staging fits: see below; a norm's weight, up to 4096 floats, lies behind the barriers)
-    cudaError_t e = cudaFuncSetAttribute(tc_kernel_of<BN, NORM>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         NORM ? 200 * 1024 : C::smem_bytes(C::MAX_STAGES));
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::smem_bytes(C::MAX_STAGES));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -1076,35 +881,10 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, c
     static const int ring_kb = [] { const char* e = getenv("DLGO_TC_RING_KB"); return e ? atoi(e) : 110; }();
     while (stages > 2 && C::smem_bytes(stages) > ring_kb * 1024) --stages;
   }
-  // a computed B: stages of A only, and behind the barriers 1 KB of B per K block and a kilobyte of zeros
-  auto normed_bytes = [&](int st) { return 1024 + st * C::A_BYTES + 1024 + (per_split + 1) * 1024; };
-  if (NORM) {
-    // as deep a ring as still lets a CTA of the plain kernel (the product before or after) share the SM:
-    // 228 KB, less that CTA's ring and the kilobyte the system keeps per CTA; never under four stages
-    const int room = 228 * 1024 - (C::smem_bytes(stages) + 1024) - 1024;
-    stages = C::MAX_STAGES;
-    while (stages > 4 && normed_bytes(stages) > room) --stages;
-    if (normed_bytes(stages) > 200 * 1024) return DLGO_ERR_SIZE;
-  }
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   q.stages = stages;
   q.staged = 0;
-  if (q.cluster > 1) {
-    // the partial tile of a slice (fp32 [BN][128]) is staged in the ring's memory
-    if (q.cluster > 8 || p.splits % q.cluster || !p.transposed || BN > 64) return DLGO_ERR_SIZE;
-    const int cpr = (BN + q.cluster - 1) / q.cluster;
-    const int staging = q.cluster * cpr * TILE_M * 4;
-    while (stages > 2 && C::smem_bytes(stages) + staging > 110 * 1024) --stages;
-    if (C::smem_bytes(stages) + staging > C::smem_bytes(C::MAX_STAGES)) return DLGO_ERR_SIZE;
-    q.stages = stages;
-    launch_kernel_cluster(tc_kernel_of<BN, NORM>(), dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages) + staging, stream,
-                          dim3(1, 1, q.cluster), ma, mb, q);
-    return launch_status();
-  }
-  if ((NORM != 0) != (q.norm_x != nullptr)) return DLGO_ERR_SIZE;
-  if (NORM && (BN != 16 || !p.transposed || q.Rb > 8 || q.K > (NORM == 2 ? 4096 : 2048))) return DLGO_ERR_SIZE;
-  launch_kernel(tc_kernel_of<BN, NORM>(), dim3(grid), dim3(TC_THREADS),
-                NORM ? normed_bytes(stages) : C::smem_bytes(stages), stream, ma, mb, q);
+  launch_kernel(gemm_tc_kernel<BN>, dim3(grid), dim3(TC_THREADS), C::smem_bytes(stages), stream, ma, mb, q);
   return launch_status();
 }
 
@@ -1180,23 +960,15 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 // tiles are then requested before the kernel waits for its predecessor), else 0.
 // pair_tile: 0, or 128 / 256 to compute 256 x pair_tile tiles with pairs of CTAs (cta_group::2; many
 // tokens only: not transposed, one K-slice; bn is then ignored).
-// cluster: 0 / 1, or 2..8 (transposed only, dividing splits): that many consecutive K-slices form a
-// thread-block cluster and are summed, in order, through distributed shared memory; no workspace, no
-// counters.  Every epilogue but 4 then needs cluster == splits; epilogue 4 writes splits / cluster
-// slices: out is [splits / cluster][Rb][ldo].
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
                              int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
-                             int* counters, int static_operand, int pair_tile, int cluster, cudaStream_t stream) {
+                             int* counters, int static_operand, int pair_tile, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
   if (epilogue < 0 || epilogue > 5) return DLGO_ERR_SIZE;
   if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
   if ((epilogue == TC_PARTIAL || epilogue == TC_RED_F32) && !transposed) return DLGO_ERR_SIZE;
-  if (cluster < 0 || cluster > 8) return DLGO_ERR_SIZE;
-  if (cluster > 1 && (!transposed || splits % cluster || (epilogue != TC_PARTIAL && cluster != splits) ||
-                      epilogue == TC_RED_F32))
-    return DLGO_ERR_SIZE;
-  if (splits > 1 && cluster <= 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32 &&
+  if (splits > 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32 &&
       (workspace == nullptr || counters == nullptr))
     return DLGO_ERR_SIZE;
   if (epilogue == TC_SWIGLU) {
@@ -1212,23 +984,6 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
-  p.cluster = cluster > 1 ? cluster : 1;
-  p.l2_ahead = 0;
-  p.norm_x = nullptr; p.norm_ld = 0; p.norm_w = nullptr; p.norm_eps = 0.f;
-  if (p.static_operand) {
-    // DLGO_TC_L2_AHEAD_MB: at most that many MB of weights per launch are pulled into L2 ahead of
-    // time.  Off by default: measured on a B200 it does not shorten a decode step (the CTAs of the
-    // next contraction enter an SM only a few microseconds before they may run, and an SM takes data
-    // out of L2 only about twice as fast as out of memory).
-    static const long long budget = [] {
-      const char* e = getenv("DLGO_TC_L2_AHEAD_MB");
-      return (e ? atoll(e) : 0LL) << 20;
-    }();
-    const long long box = (long long)(p.static_operand == 1 ? TILE_M : bn) * TILE_K * 2;
-    const long long ctas = (long long)((Ra + TILE_M - 1) / TILE_M) * ((Rb + bn - 1) / bn) * splits;
-    const long long cap = budget > 0 ? budget / (box * ctas) : 0;
-    p.l2_ahead = (int)(cap > 1024 ? 1024 : cap);
-  }
   if (!transposed && splits == 1 && pair_tile != 0) {
     // many tokens, CTA pairs: A's box is 128 rows, B's box is half the tile's width
     if (pair_tile != 128 && pair_tile != 256) return DLGO_ERR_SIZE;
@@ -1248,34 +1003,6 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
     case 256: return launch_tc<256>(ma, mb, p, stream);
     default: return DLGO_ERR_SIZE;
   }
-}
-
-// The few-token product out^T = W[Ra, K] . norm(X)[Rb, K]^T with B computed in the kernel: the RMSNorm of
-// the fp32 rows X (row stride ldx floats) with weight norm_w[K] and eps, rounded to bf16 as a norm kernel
-// would have left it.  Rb <= 8 and K <= 4096.  Epilogues 0, 1, 3 with one
-// K-slice; 4 and 5 with any number.
-DLGO_EXPORT int dlgo_gemm_tc_normed(const void* W, int Ra, int lda, const float* X, int Rb, int ldx,
-                                    const float* norm_w, float eps, int K, void* out, int ldo, int epilogue,
-                                    int splits, cudaStream_t stream) {
-  if (Ra <= 0 || Rb <= 0) return DLGO_OK;
-  if (K <= 0 || K % 8 || lda < K || ldx < K || splits < 1 || splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
-  if (Rb > 8 || K > 4096) return DLGO_ERR_SIZE;
-  if (epilogue != TC_STORE && epilogue != TC_STORE_F32 && epilogue != TC_SWIGLU && epilogue != TC_PARTIAL &&
-      epilogue != TC_RED_F32)
-    return DLGO_ERR_SIZE;
-  if (splits > 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32) return DLGO_ERR_SIZE;
-  if (epilogue == TC_SWIGLU && Ra % 32) return DLGO_ERR_SIZE;
-  if (((uintptr_t)X & 15) != 0 || ((uintptr_t)norm_w & 15) != 0 || (ldx & 3) != 0) return DLGO_ERR_ALIGN;
-  CUtensorMap ma;
-  int st = make_map(&ma, W, Ra, K, lda, TILE_M);
-  if (st != DLGO_OK) return st;
-  TcParams p;
-  p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = 1; p.epilogue = epilogue;
-  p.splits = splits; p.workspace = nullptr; p.counters = nullptr;
-  p.static_operand = 1; p.cluster = 1; p.l2_ahead = 0;
-  p.norm_x = X; p.norm_ld = ldx; p.norm_w = norm_w; p.norm_eps = eps;
-  // (no tile of B is loaded: its map is not used)
-  return K <= 2048 ? launch_tc<16, 1>(ma, ma, p, stream) : launch_tc<16, 2>(ma, ma, p, stream);
 }
 
 // 1 if a kernel of this library gave up a bounded wait since the last call (clears the flag).

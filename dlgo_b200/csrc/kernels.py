@@ -174,14 +174,11 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
                 token_seq: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
                 kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                 rotary_dim: int, interleaved: bool, write_cache: bool = True,
-                parts: Optional[torch.Tensor] = None, ahead_pages: int = 0, ahead_window: int = 0,
-                clear_parts: bool = False) -> None:
+                parts: Optional[torch.Tensor] = None, clear_parts: bool = False) -> None:
     """Rotate q (in place) and k, and store k and v at their positions' pages.
 
     ``parts`` ([S, T, ld] fp32): the projection's unsummed K-slices; they are added here and ``qkv``
-    only receives the rotated q.  With ``parts`` and ``ahead_pages`` > 0 the kernel also hints the most
-    recent pages of every sequence's keys and values (within ``ahead_window`` keys, if > 0) into L2
-    for the attention kernel that follows.  ``clear_parts``: the kernel leaves zeros where it read
+    only receives the rotated q.  ``clear_parts``: the kernel leaves zeros where it read
     ``parts`` (a sum that the projection adds into and that must be zero again for the next step)."""
     _need(qkv, None, "qkv")
     _need(cos, torch.float32, "cos")
@@ -197,8 +194,7 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
         _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages), _ptr(vpages),
         _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim), _i(page_size), _i(1 if interleaved else 0),
         _i(1 if write_cache else 0), _ptr(parts), _i(0 if parts is None else parts.shape[0]),
-        _ll(0 if parts is None else parts.stride(0)), _i(ahead_pages), _i(ahead_window),
-        _i(1 if clear_parts else 0), _stream())
+        _ll(0 if parts is None else parts.stride(0)), _i(1 if clear_parts else 0), _stream())
     _check(st, "rope_append")
 
 
@@ -380,27 +376,20 @@ def gemm_tc_workspace_floats(ra: int, rb: int, bn: int, splits: int) -> int:
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, epilogue: int, bn: int,
             splits: int = 1, workspace: Optional[torch.Tensor] = None,
-            counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0,
-            cluster: int = 0) -> torch.Tensor:
+            counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0) -> torch.Tensor:
     """D[Ra, Rb] = a[Ra, K] . b[Rb, K]^T on the tensor cores (bf16 in, fp32 accumulate).
 
     ``out`` receives D (``transposed``: D^T) through ``epilogue``; with ``splits`` > 1 the K range is
     shared by that many CTAs per tile, which needs ``workspace`` (fp32) and zeroed ``counters`` (int32).
     ``static_operand`` (1: a, 2: b) names the operand that holds weights no earlier kernel writes.
     ``pair_tile`` (128 or 256): many tokens, 256 x pair_tile tiles computed by pairs of CTAs (cta_group::2).
-    ``cluster`` (2..8, dividing ``splits``; transposed only): that many consecutive K-slices are one
-    thread-block cluster and meet through distributed shared memory instead of the workspace; partials
-    then come as ``splits // cluster`` slices, every other epilogue needs ``cluster == splits``.
-    ``TC_RED_F32`` (transposed only): every K-slice adds itself into the fp32 ``out`` with reductions at the
-    memory; no workspace, and the order of the adds (the sum's last bits) is not fixed.
+    ``TC_PARTIAL`` (transposed only): every K-slice leaves its fp32 tile in ``out`` [splits, Rb, Ra] for the
+    reader to add in order.  ``TC_RED_F32`` (transposed only): every K-slice adds itself into the fp32
+    ``out`` with reductions at the memory; no workspace, and the order of the adds (the sum's last bits) is
+    not fixed.
     """
-    cluster = cluster if cluster > 1 else 1
-    if epilogue == TC_RED_F32 and (not transposed or cluster > 1):
-        raise KernelError("gemm_tc: the atomic add is for transposed products without clusters")
-    if cluster > 1 and (not transposed or cluster > 8 or splits % cluster or
-                        (epilogue != TC_PARTIAL and cluster != splits)):
-        raise KernelError(f"gemm_tc: a cluster of {cluster} K-slices does not fit {splits} slices of this product")
-    slices_out = splits // cluster
+    if epilogue == TC_RED_F32 and not transposed:
+        raise KernelError("gemm_tc: the atomic add is for transposed products")
     for n, t in (("a", a), ("b", b)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"gemm_tc: {n} must be a 2-D bfloat16 GPU tensor with unit inner stride")
@@ -410,7 +399,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
         raise KernelError(f"gemm_tc: a has K={k}, b has K={k2}")
     if out.stride(-1) != 1:
         raise KernelError("gemm_tc: out must have unit inner stride")
-    if splits > 1 and cluster == 1 and epilogue not in (TC_PARTIAL, TC_RED_F32):
+    if splits > 1 and epilogue not in (TC_PARTIAL, TC_RED_F32):
         need = gemm_tc_workspace_floats(ra, rb, bn, splits)
         tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
         if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
@@ -418,8 +407,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
     if epilogue == TC_PARTIAL:
         # out is [slices, rb, ra]: the kernel's row stride is that of one slice's rows
         if not transposed or out.dim() != 3 or out.dtype != torch.float32 or \
-                tuple(out.shape) != (slices_out, rb, ra) or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
-            raise KernelError(f"gemm_tc: partials go to a float32 [{slices_out}, {rb}, {ra}] tensor of a transposed product")
+                tuple(out.shape) != (splits, rb, ra) or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
+            raise KernelError(f"gemm_tc: partials go to a float32 [{splits}, {rb}, {ra}] tensor of a transposed product")
         ldo = out.stride(1)
     else:
         want_shape = (rb, ra) if transposed else (ra, rb)
@@ -434,50 +423,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
     st = _lib("gemm_tc").dlgo_gemm_tc(_ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k),
                                       _ptr(out), _i(ldo), _i(1 if transposed else 0), _i(epilogue), _i(bn),
                                       _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand), _i(pair_tile),
-                                      _i(cluster), _stream())
+                                      _stream())
     _check(st, "gemm_tc")
-    return out
-
-
-def gemm_tc_normed_takes(tokens: int, k: int) -> bool:
-    """Whether the few-token product can compute its activations as an RMSNorm of fp32 rows itself."""
-    return tokens <= 8 and k <= 4096
-
-
-def gemm_tc_normed(weight: torch.Tensor, x: torch.Tensor, norm_weight: torch.Tensor, eps: float, out: torch.Tensor,
-                   epilogue: int, splits: int = 1) -> torch.Tensor:
-    """``out^T = weight[Ra, K] . rmsnorm(x)[Rb, K]^T`` for few tokens, the norm (fp32 rows ``x``, fp32
-    ``norm_weight``, rounded to bfloat16) computed inside the product's kernel.  ``out`` as for
-    :func:`gemm_tc` with ``transposed``; more than one K-slice only with partials or the atomic add."""
-    if not weight.is_cuda or weight.dtype != torch.bfloat16 or weight.dim() != 2 or weight.stride(1) != 1:
-        raise KernelError("gemm_tc_normed: the weight must be a 2-D bfloat16 GPU tensor with unit inner stride")
-    ra, k = weight.shape
-    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != k or x.stride(1) != 1:
-        raise KernelError(f"gemm_tc_normed: x must be float32 [tokens, {k}] with unit inner stride")
-    rb = x.shape[0]
-    if not gemm_tc_normed_takes(rb, k):
-        raise KernelError(f"gemm_tc_normed: {rb} tokens of {k} are more than the kernel keeps in registers")
-    if norm_weight.dtype != torch.float32 or norm_weight.numel() != k or not norm_weight.is_contiguous():
-        raise KernelError(f"gemm_tc_normed: the norm's weight must be float32 [{k}]")
-    if splits > 1 and epilogue not in (TC_PARTIAL, TC_RED_F32):
-        raise KernelError("gemm_tc_normed: K-slices only with partials or the atomic add")
-    if epilogue == TC_PARTIAL:
-        if out.dim() != 3 or out.dtype != torch.float32 or tuple(out.shape) != (splits, rb, ra) or \
-                out.stride(2) != 1 or out.stride(0) != rb * out.stride(1) or out.stride(1) < ra:
-            raise KernelError(f"gemm_tc_normed: partials go to a float32 [{splits}, {rb}, {ra}] tensor")
-        ldo = out.stride(1)
-    else:
-        want_shape = (rb, ra // 2) if epilogue == TC_SWIGLU else (rb, ra)
-        want_dtype = torch.bfloat16 if epilogue in (TC_STORE, TC_SWIGLU) else torch.float32
-        if epilogue not in (TC_STORE, TC_STORE_F32, TC_SWIGLU, TC_RED_F32):
-            raise KernelError(f"gemm_tc_normed: no epilogue {epilogue}")
-        if out.dim() != 2 or tuple(out.shape) != want_shape or out.dtype != want_dtype or out.stride(1) != 1:
-            raise KernelError(f"gemm_tc_normed: out must be {want_dtype} {list(want_shape)}")
-        ldo = out.stride(0)
-    st = _lib("gemm_tc").dlgo_gemm_tc_normed(_ptr(weight), _i(ra), _i(weight.stride(0)), _ptr(x), _i(rb),
-                                             _i(x.stride(0)), _ptr(norm_weight), ctypes.c_float(eps), _i(k),
-                                             _ptr(out), _i(ldo), _i(epilogue), _i(splits), _stream())
-    _check(st, "gemm_tc_normed")
     return out
 
 
@@ -521,14 +468,12 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
                          window: int = 0, n_splits: int = 1, keys_per_tile: int = 16,
                          scratch: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None,
                          cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
-                         write_cache: bool = True, clear_parts: bool = False,
-                         row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         write_cache: bool = True, clear_parts: bool = False) -> torch.Tensor:
     """Attention of one new token per sequence over its cached keys and values, bfloat16, on the
     tensor cores (mma.sync); 2..8 slices combine inside a thread-block cluster, more go through
     ``scratch`` (``attention_scratch_floats`` floats) and a second kernel.  With ``parts`` (the q|k|v
     projection as fp32 [slices, sequences, columns], unrotated) the kernel sums the slices, rotates q and k
-    and appends k and v itself; ``clear_parts`` (one slice, at most 8 page slices): the sum is left zero;
-    ``row_scale`` [sequences]: a factor on each token's sums."""
+    and appends k and v itself; ``clear_parts`` (one slice, at most 8 page slices): the sum is left zero."""
     for n, t in (("out", out), ("kpages", kpages), ("vpages", vpages)):
         _need(t, torch.bfloat16, n)
     for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
@@ -556,12 +501,8 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
         S, part_stride = parts.shape[0], parts.stride(0)
         if clear_parts and (S != 1 or n_splits > 8):
             raise KernelError("attention_decode_mma: only one summed slice read by at most 8 page slices can be cleared")
-        if row_scale is not None:
-            _need(row_scale, torch.float32, "row_scale")
-            if row_scale.numel() < B:
-                raise KernelError("attention_decode_mma: row_scale needs a factor per sequence")
-    if parts is None and (clear_parts or row_scale is not None):
-        raise KernelError("attention_decode_mma: clear_parts and row_scale go with parts")
+    if parts is None and clear_parts:
+        raise KernelError("attention_decode_mma: clear_parts goes with parts")
     page_size = kpages.shape[-2]
     if n_splits > 8:
         need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
@@ -572,7 +513,7 @@ def attention_decode_mma(q: Optional[torch.Tensor], ldq: int, B: int, kpages: to
         _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim),
         _i(page_size), _i(n_splits), _i(window), _f(scale), _i(keys_per_tile),
         _ptr(scratch if n_splits > 8 else None), _ptr(parts), _i(S), _ll(part_stride), _ptr(cos), _ptr(sin),
-        _i(1 if write_cache else 0), _i(1 if clear_parts else 0), _ptr(row_scale), _stream())
+        _i(1 if write_cache else 0), _i(1 if clear_parts else 0), _stream())
     _check(st, "attention_decode_mma", 2 if n_splits > 8 else 1)
     return out
 
@@ -637,53 +578,6 @@ def attention_prefill_tc(q: torch.Tensor, ldq: int, T: int, kpages: torch.Tensor
         _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _ptr(seq_slot), _ptr(token_pos), _ptr(out),
         _i(out.stride(0)), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(window), _f(scale), _stream())
     _check(st, "attention_prefill_tc")
-    return out
-
-
-def attention_decode_fuses_rope(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
-                                interleaved: bool, page_size: int) -> bool:
-    return bool(_lib("attention_decode").dlgo_attention_decode_fuses_rope(
-        _i(dtype_code(dtype)), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(rotary_dim),
-        _i(1 if interleaved else 0), _i(page_size)))
-
-
-def attention_decode_rope(qkv: Optional[torch.Tensor], parts: Optional[torch.Tensor], B: int, cos: torch.Tensor,
-                          sin: torch.Tensor, rotary_dim: int, interleaved: bool, write_cache: bool,
-                          kpages: torch.Tensor, vpages: torch.Tensor, page_table: torch.Tensor,
-                          seq_slot: torch.Tensor, token_pos: torch.Tensor, out: torch.Tensor, num_heads: int,
-                          num_kv_heads: int, head_dim: int, scale: float, window: int = 0, n_splits: int = 1,
-                          scratch: Optional[torch.Tensor] = None,
-                          counters: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode attention with the rotation of q and k and the append of k and v inside the kernel.
-
-    Give the projection's output either as ``qkv`` [B, ld] in the cache's type or as ``parts``
-    [S, B, ld] fp32 (its unsummed K-slices)."""
-    _need(out, kpages.dtype, "out")
-    _need(vpages, kpages.dtype, "vpages")
-    _need(cos, torch.float32, "cos")
-    _need(sin, torch.float32, "sin")
-    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_pos", token_pos)):
-        _need(t, torch.int32, n)
-    if (qkv is None) == (parts is None):
-        raise KernelError("attention_decode_rope: give qkv or parts, not both")
-    if qkv is not None:
-        _need(qkv, kpages.dtype, "qkv")
-        ld, S, pstride = qkv.stride(0), 0, 0
-    else:
-        if parts.dtype != torch.float32 or parts.dim() != 3 or parts.stride(2) != 1:
-            raise KernelError("attention_decode_rope: parts must be [S, B, ld] float32")
-        ld, S, pstride = parts.stride(1), parts.shape[0], parts.stride(0)
-    if n_splits > 8 or (n_splits > 1 and scratch is not None):
-        need = attention_scratch_floats(B, num_heads, head_dim, n_splits)
-        if scratch is None or scratch.numel() < need:
-            raise KernelError(f"attention_decode_rope: {n_splits} slices need {need} floats of scratch")
-    st = _lib("attention_decode").dlgo_attention_decode_rope(
-        _ptr(qkv), _ptr(parts), _i(S), _ll(pstride), _i(dtype_code(kpages.dtype)), _i(B), _i(ld), _ptr(cos), _ptr(sin),
-        _i(rotary_dim), _i(1 if interleaved else 0), _i(1 if write_cache else 0), _ptr(kpages), _ptr(vpages),
-        _ptr(page_table), _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(out), _i(out.stride(0)),
-        _ptr(scratch), _ptr(counters), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(kpages.shape[-2]),
-        _i(n_splits), _i(window), _f(scale), _stream())
-    _check(st, "attention_decode_rope", 2 if (n_splits > 1 and counters is None and scratch is not None) else 1)
     return out
 
 

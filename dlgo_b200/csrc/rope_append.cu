@@ -206,7 +206,7 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
                          const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
                          T* __restrict__ vpages, int Hq, int Hkv, int hd, int rot, int page_size,
                          int interleaved, int write_cache, const float* __restrict__ parts, int S,
-                         size_t part_stride, int ahead_pages, int ahead_window) {
+                         size_t part_stride) {
   pdl_launch_dependents();
   const int t = blockIdx.y;
   const int head = blockIdx.x * RP_WARPS + (threadIdx.x >> 5);
@@ -227,28 +227,6 @@ rope_append_parts_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ 
         dst = (is_k ? kpages : vpages) + (((size_t)page * Hkv + kvh) * page_size + (size_t)(pos % page_size)) * hd;
       else if (lane == 0)
         atomicExch(&g_rope_append_error, 1);
-    }
-  }
-  // The attention kernel that follows reads this sequence's cached keys and values; the warp of a
-  // key (value) head asks for that head's most recent `ahead_pages` pages to be brought into L2 now,
-  // while the projection still runs.  A hint only: no register or shared memory holds the data.
-  if (active && head >= Hq && write_cache && ahead_pages > 0) {
-    const int slot = seq_slot[token_seq[t]];
-    const bool is_k = head < Hq + Hkv;
-    const int kvh = is_k ? head - Hq : head - Hq - Hkv;
-    const int t_first = ahead_window > 0 ? max(0, pos - ahead_window + 1) : 0;
-    const int pg_last = pos / page_size;
-    const int pg_first = max(t_first / page_size, pg_last - ahead_pages + 1);
-    const int lines = (page_size * hd * (int)sizeof(T) + 127) / 128;
-    for (int pg0 = pg_first; pg0 <= pg_last; pg0 += 32) {
-      const int mine = pg0 + lane <= pg_last ? page_table[(size_t)slot * max_pages + pg0 + lane] : -1;
-      const int n = min(32, pg_last - pg0 + 1);
-      for (int j = 0; j < n; ++j) {
-        const int page = __shfl_sync(0xffffffffu, mine, j);
-        if (page < 0) continue;
-        const char* base = (const char*)((is_k ? kpages : vpages) + ((size_t)page * Hkv + kvh) * page_size * hd);
-        for (int ln = lane; ln < lines; ln += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (size_t)ln * 128));
-      }
     }
   }
   const bool rotates = active && head < Hq + Hkv;
@@ -316,8 +294,8 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
                                  const int* token_pos, const int* token_seq, const int* seq_slot,
                                  const int* page_table, int max_pages, void* kpages, void* vpages, int Hq, int Hkv,
                                  int hd, int rot, int page_size, int interleaved, int write_cache,
-                                 const float* parts, int S, long long part_stride, int ahead_pages, int ahead_window,
-                                 int clear_parts, cudaStream_t stream) {
+                                 const float* parts, int S, long long part_stride, int clear_parts,
+                                 cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
   if (hd <= 0 || hd % 2 || rot < 0 || rot > hd || rot % 2 || Hq <= 0 || Hkv <= 0 || page_size <= 0 ||
       ld < (Hq + 2 * Hkv) * hd)
@@ -345,7 +323,7 @@ DLGO_EXPORT int dlgo_rope_append(void* qkv, int dtype, int T, int ld, const floa
 #define DLGO_ROPE_PARTS(TT, SUM)                                                                                  \
   launch_kernel(rope_append_parts_kernel<TT, SUM>, grid, dim3(RP_WARPS * 32), 0, stream, (TT*)qkv, ld, cos_t, sin_t, \
                 token_pos, token_seq, seq_slot, page_table, max_pages, (TT*)kpages, (TT*)vpages, Hq, Hkv, hd, rot, \
-                page_size, interleaved, write_cache, parts, S, (size_t)part_stride, ahead_pages, ahead_window)
+                page_size, interleaved, write_cache, parts, S, (size_t)part_stride)
     if (dtype == DLGO_F32) {
       if (clear_parts) DLGO_ROPE_PARTS(float, true); else DLGO_ROPE_PARTS(float, false);
     } else if (dtype == DLGO_BF16) {

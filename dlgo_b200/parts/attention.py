@@ -33,14 +33,15 @@ _QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))
 _FUSE_ROPE = int(os.environ.get("DLGO_ATTN_FUSE_ROPE", 1))
 
 
+_DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 0))   # blocks wanted in flight for decode attention (0: four per SM)
+
+
 def _sm_count(device: torch.device) -> int:
     from .tensor_core import sm_count
     return sm_count(device)
 
 
 class GQAAttention(Mixer):
-    takes_deferred_norm = True   # its first contraction may compute the norm of the residual itself
-
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: Optional[int] = None, position_encoding: Optional[str] = "rope",
                  cache_group: str = "full"):
@@ -91,7 +92,7 @@ class GQAAttention(Mixer):
         """(page slices per sequence, scratch, counters) of the decode kernels: slices so that every SM has
         several blocks (whole waves: rounded down); 2..8 slices form a thread-block cluster and combine
         through distributed shared memory, more (one very long sequence alone) go through scratch memory."""
-        blocks = 4 * _sm_count(cache.keys.device)
+        blocks = _DECODE_BLOCKS or 4 * _sm_count(cache.keys.device)
         base_blocks = T * self.num_kv_heads * ((group + 3) // 4)
         n_splits = max(1, min(pages, blocks // base_blocks))
         scratch = counters = None
@@ -128,9 +129,10 @@ class GQAAttention(Mixer):
             # few tokens: the projection's K-slices add themselves, at the memory, into one fp32 sum that is zero
             # between steps; whoever rotates reads it once and leaves zeros behind
             qkv_sum = ctx.zeros(f"qkv_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(1, T, n_cols)
+            fuse = (mma and _FUSE_ROPE and n_splits <= 8 and
+                    K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter))
             self.wqkv(x, ADD_F32, qkv_sum[0])
-            if (mma and _FUSE_ROPE and n_splits <= 8 and
-                    K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter)):
+            if fuse:
                 # the decode kernel rotates, appends and clears itself: no launch for the rotation
                 K.attention_decode_mma(None, n_cols, T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                        ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
@@ -141,7 +143,7 @@ class GQAAttention(Mixer):
                 qkv = torch.empty((T, n_cols), dtype=x.dtype, device=x.device)
                 K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                               cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                              qkv_sum, 0, self.window or 0, True)
+                              qkv_sum, True)
         else:
             # ... or leaves its K-slices unsummed for the rotation to add in order; else the finished product
             qkv_parts = self.wqkv.partials(x, single_ok=False)
@@ -149,7 +151,7 @@ class GQAAttention(Mixer):
                    torch.empty((T, n_cols), dtype=x.dtype, device=x.device))
             K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                           cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
-                          qkv_parts, 0, self.window or 0, False)
+                          qkv_parts, False)
         if rotated:
             pass
         elif mma:

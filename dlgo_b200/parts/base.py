@@ -90,29 +90,6 @@ class Norm(Part):
         raise NotImplementedError
 
 
-class DeferredNorm:
-    """The norm of the residual stream, not computed yet.
-
-    A block hands this instead of a tensor to a mixer or feed-forward that declares
-    ``takes_deferred_norm = True``.  A contraction that can apply the norm while it loads its operand
-    (:class:`~dlgo_b200.parts.linear.Linear`, for few tokens) takes it as it is and the norm costs no
-    launch; anything else calls :meth:`tensor`, which runs the norm once and keeps the result.
-    ``kind`` names the formula (``"rmsnorm"``: ``weight`` fp32 and ``eps``), so that whoever fuses it knows
-    what to compute; a norm with another formula simply offers no ``deferred``.
-    """
-
-    def __init__(self, norm: "Norm", residual: torch.Tensor, kind: str, weight: torch.Tensor, eps: float,
-                 dtype: torch.dtype):
-        self.norm, self.residual, self.kind, self.weight, self.eps, self.dtype = norm, residual, kind, weight, eps, dtype
-        self.shape, self.device = residual.shape, residual.device
-        self._tensor: Optional[torch.Tensor] = None
-
-    def tensor(self) -> torch.Tensor:
-        if self._tensor is None:
-            self._tensor = self.norm.forward(self.residual)
-        return self._tensor
-
-
 class PositionEncoding(Part):
     pass
 

@@ -14,19 +14,15 @@ from .base import Block, PositionEncoding
 from .registry import BLOCKS
 
 
-def norm_of(norm: Any, residual: torch.Tensor, ctx: Any, reader: Any = None) -> Any:
+def norm_of(norm: Any, residual: torch.Tensor, ctx: Any) -> torch.Tensor:
     """The norm of the residual stream, adding first whatever the previous part left pending
-    (fused into the norm's pass where the norm offers that).  For a ``reader`` (the part that takes the
-    result) that declares ``takes_deferred_norm``, and with nothing pending, the norm is handed over
-    uncomputed where it can be (:class:`~dlgo_b200.parts.base.DeferredNorm`)."""
+    (fused into the norm's pass where the norm offers that)."""
     pending = ctx.take_pending() if hasattr(ctx, "take_pending") else None
     if pending is not None:
         if hasattr(norm, "forward_fused"):
             return norm.forward_fused(residual, pending)
         ctx.pending = pending
         ctx.settle(residual)
-    if getattr(reader, "takes_deferred_norm", False) and hasattr(norm, "deferred"):
-        return norm.deferred(residual)
     return norm.forward(residual)
 
 
@@ -44,9 +40,9 @@ class PreNormBlock(Block):
 
     def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
                 positions: Mapping[str, PositionEncoding]) -> None:
-        x = norm_of(self.mixer_norm, residual, ctx, self.mixer)
+        x = norm_of(self.mixer_norm, residual, ctx)
         self.mixer.forward(x, residual, ctx, cache, state, positions)
-        x = norm_of(self.ffn_norm, residual, ctx, self.ffn)
+        x = norm_of(self.ffn_norm, residual, ctx)
         self.ffn.forward(x, residual, ctx)
 
 

@@ -18,8 +18,6 @@ from .registry import FEED_FORWARDS
 
 
 class SwiGLU(FeedForward):
-    takes_deferred_norm = True   # its first contraction may compute the norm of the residual itself
-
     def __init__(self, hidden_size: int, intermediate_size: int):
         super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size)
         self.hidden_size = int(hidden_size)

@@ -13,7 +13,6 @@ from typing import Any, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import DeferredNorm
 
 STORE, STORE_F32, ADD_F32 = K.EPI_STORE, K.EPI_STORE_F32, K.EPI_ADD_F32
 
@@ -35,13 +34,7 @@ class Linear:
         if fused_swiglu and not self.fuses_swiglu:
             raise ValueError("this weight cannot take the fused SwiGLU epilogue")
 
-    def __call__(self, x: Any, epilogue: int = STORE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``x``: the activations, or a :class:`DeferredNorm` of the residual stream (computed inside the
-        contraction where its kernel can do that, else first)."""
-        if isinstance(x, DeferredNorm):
-            if self._tc is not None and self._tc.takes_norm(x):
-                return self._tc(x, epilogue, out)
-            x = x.tensor()
+    def __call__(self, x: torch.Tensor, epilogue: int = STORE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self._tc is not None:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
@@ -51,14 +44,12 @@ class Linear:
         into the target with reductions at the memory (the target may then be a plain zeroed sum)."""
         return self._tc is not None and not self.fuses_swiglu and self._tc.sums_slices_at_memory(tokens)
 
-    def partials(self, x: Any, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
+    def partials(self, x: torch.Tensor, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """The product as unsummed fp32 K-slices [slices, tokens, out] where the kernel offers that
         (few tokens on the tensor cores), else ``None``; also ``None`` for a single slice unless
         ``single_ok`` (a caller that wants the finished product in the activation type), and, with
         ``for_residual`` (the caller would leave the slices for the next norm to add to the residual
         stream), where the kernel would rather add its slices into the residual itself."""
         if self._tc is not None and not self.fuses_swiglu:
-            if isinstance(x, DeferredNorm) and not self._tc.takes_norm(x):
-                x = x.tensor()
             return self._tc.partials(x, single_ok, for_residual)
         return None

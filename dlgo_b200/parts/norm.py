@@ -7,7 +7,7 @@ from typing import Any, Callable, Dict, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import DeferredNorm, Norm, ParamSpec
+from .base import Norm, ParamSpec
 from .registry import NORMS
 
 
@@ -28,10 +28,6 @@ class RMSNorm(Norm):
 
     def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return K.rmsnorm(residual, self.weight, self.eps, self.out_dtype, rows)
-
-    def deferred(self, residual: torch.Tensor) -> DeferredNorm:
-        """The norm as a promise, for a contraction that computes it on its way in."""
-        return DeferredNorm(self, residual, "rmsnorm", self.weight, self.eps, self.out_dtype)
 
     def forward_fused(self, residual: torch.Tensor, parts: torch.Tensor,
                       rows: Optional[torch.Tensor] = None) -> torch.Tensor:

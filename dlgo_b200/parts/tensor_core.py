@@ -36,19 +36,13 @@ MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
 MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
-# K-slices summed on chip by a thread-block cluster (2..8; 1: off).  Off by default: measured on a
-# B200, clusters of these large CTAs start later than independent CTAs do (they cannot slip into an
-# SM one by one while the previous kernel drains), which costs more than the cheaper reduction saves.
-CLUSTER_MAX = int(os.environ.get("DLGO_TC_CLUSTER", 1))
-
 # Few tokens: a contraction whose result goes into the residual stream adds its K-slices there with
-# reductions at the memory (bit 0; up to RED_MAX_TOKENS tokens) instead of leaving them for the norm's
-# kernel to add.  Measured on a B200 (Llama 3.2 1B sizes, tokens a second): 8.99K -> 9.90K at batch 8,
-# 1.19K -> 1.32K at batch 1, 45.8K -> 49.0K at batch 64.
-# Bit 1: a contraction that follows a norm computes the norm itself on its way in (at most 8 tokens),
-# which spares the norm's launch.  Off: every CTA then reads all rows of the residual, 148 times 64 KB out
-# of L2 at once, and that takes longer (3.5 us) than the norm's own kernel (8.75K against 9.85K at batch 8).
-NORM_IN_GEMM = int(os.environ.get("DLGO_NORM_IN_GEMM", 1))   # bit 0: the atomic add, bit 1: the norm
+# reductions at the memory (up to RED_MAX_TOKENS tokens) instead of leaving them for the norm's kernel to
+# add.  Measured on a B200 (Llama 3.2 1B sizes, tokens a second): 8.99K -> 9.90K at batch 8, 1.19K -> 1.32K at
+# batch 1, 45.8K -> 49.0K at batch 64.  The order of such adds is not fixed, so the sums' last bits differ from
+# run to run; DLGO_ORDERED_SUMS=1 keeps the K-slices apart and lets the next norm add them in slice order
+# instead: slower, and bit for bit repeatable.
+ORDERED_SUMS = os.environ.get("DLGO_ORDERED_SUMS", "0") == "1"
 RED_MAX_TOKENS = int(os.environ.get("DLGO_TC_RED_MAX_TOKENS", 64))
 
 _workspaces: Dict[int, List[torch.Tensor]] = {}
@@ -96,36 +90,14 @@ def skinny_shape(tokens: int, n: int, k: int, device: Optional[torch.device] = N
     return bn, max(1, min(splits, kblocks, MAX_SPLITS))
 
 
-def clustered(splits: int, final: bool) -> tuple[int, int]:
-    """(splits, cluster) with the K-slices grouped into thread-block clusters that sum their partial
-    tiles on chip.  ``final``: the product needs ONE result (every epilogue but the partials), so all
-    slices must fit one cluster; partials may come as several clusters' slices."""
-    if CLUSTER_MAX <= 1 or splits <= 1:
-        return splits, 1
-    if splits <= CLUSTER_MAX:
-        return splits, splits
-    if final:
-        return CLUSTER_MAX, CLUSTER_MAX
-    groups = (splits + CLUSTER_MAX - 1) // CLUSTER_MAX
-    per = max(1, splits // groups)
-    return per * groups, per
-
-
 class TensorCorePlan:
     def __init__(self, weight: torch.Tensor, swiglu: bool = False):
         self.weight = weight
         self.n, self.k = weight.shape
         self.swiglu = swiglu
 
-    def takes_norm(self, x) -> bool:
-        """Whether this product computes the deferred norm ``x`` inside its kernel."""
-        return ((NORM_IN_GEMM & 2) != 0 and x.kind == "rmsnorm" and x.dtype == torch.bfloat16 and
-                x.residual.dtype == torch.float32 and x.residual.stride(1) == 1 and x.residual.stride(0) % 4 == 0 and
-                x.weight.dtype == torch.float32 and K.gemm_tc_normed_takes(x.shape[0], self.k))
-
     def __call__(self, x, epilogue: int, out: Optional[torch.Tensor]) -> torch.Tensor:
         t = x.shape[0]
-        normed = not isinstance(x, torch.Tensor)
         if self.swiglu:
             epi = K.TC_SWIGLU
             if out is None:
@@ -137,60 +109,42 @@ class TensorCorePlan:
                     raise K.KernelError("the add epilogue needs the tensor to add into")
                 out = torch.empty((t, self.n), dtype=torch.bfloat16 if epilogue == K.EPI_STORE else torch.float32,
                                   device=x.device)
-        if normed:
-            # one K-slice unless the epilogue can take several (the atomic add)
-            _, splits = skinny_shape(t, self.n, self.k, self.weight.device)
-            if epi == K.TC_ADD_F32:
-                epi = K.TC_RED_F32
-            elif epi != K.TC_RED_F32:
-                splits = 1
-            return K.gemm_tc_normed(self.weight, x.residual, x.weight, x.eps, out, epi, splits)
         if t <= SKINNY_MAX:
             bn, splits = skinny_shape(t, self.n, self.k, self.weight.device)
-            if (NORM_IN_GEMM & 1) and epi == K.TC_ADD_F32 and splits > 1 and t <= RED_MAX_TOKENS:
+            if not ORDERED_SUMS and epi == K.TC_ADD_F32 and splits > 1 and t <= RED_MAX_TOKENS:
                 return K.gemm_tc(self.weight, x, out, True, K.TC_RED_F32, bn, splits, static_operand=1)
-            splits, cluster = clustered(splits, True)
             ws = cnt = None
-            if splits > 1 and cluster == 1:
+            if splits > 1:
                 ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
                 cnt = _counter_buffer(x.device)
-            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1, cluster=cluster)
+            return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1)
         bn = 256 if self.n > 128 else 128
         if PREFILL_BN in (128, 256):
             bn = PREFILL_BN
         pair = PAIR_TILE if (t > 128 and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
-
     def sums_slices_at_memory(self, tokens: int) -> bool:
-        if not (NORM_IN_GEMM & 1) or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):
+        if ORDERED_SUMS or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):
             return False
         return skinny_shape(tokens, self.n, self.k, self.weight.device)[1] > 1
 
     def partials(self, x, single_ok: bool = True, for_residual: bool = False) -> Optional[torch.Tensor]:
         """For few tokens: the product's K-slices, unsummed, as fp32 [slices, tokens, out]; whoever
         reads the result next adds them in order (this spares the contraction a reduction pass through
-        memory; slices of one thread-block cluster are summed on chip and come as one).
-        ``None`` when the tokens are too many for that, or, unless ``single_ok``, when there would be
+        memory).  ``None`` when the tokens are too many for that, or, unless ``single_ok``, when there would be
         one slice only (the caller then asks for the finished product in the type it wants), or, with
         ``for_residual``, when the add epilogue would add the slices into the residual by itself."""
         t = x.shape[0]
         if t > SKINNY_MAX or self.swiglu:
             return None
-        if for_residual and (NORM_IN_GEMM & 1) and t <= RED_MAX_TOKENS:
+        if for_residual and not ORDERED_SUMS and t <= RED_MAX_TOKENS:
             return None                     # the caller's add epilogue adds the slices into the residual
         bn, splits = skinny_shape(t, self.n, self.k, self.weight.device)
-        if not isinstance(x, torch.Tensor):
-            # a deferred norm, computed by the kernel
-            if splits == 1 and not single_ok:
-                return None
-            out = torch.empty((splits, t, self.n), dtype=torch.float32, device=x.device)
-            return K.gemm_tc_normed(self.weight, x.residual, x.weight, x.eps, out, K.TC_PARTIAL, splits)
-        splits, cluster = clustered(splits, False)
-        if splits == cluster and not single_ok:
+        if splits == 1 and not single_ok:
             return None
-        out = torch.empty((splits // cluster, t, self.n), dtype=torch.float32, device=x.device)
-        K.gemm_tc(self.weight, x, out, True, K.TC_PARTIAL, bn, splits, static_operand=1, cluster=cluster)
+        out = torch.empty((splits, t, self.n), dtype=torch.float32, device=x.device)
+        K.gemm_tc(self.weight, x, out, True, K.TC_PARTIAL, bn, splits, static_operand=1)
         return out
 
 

@@ -287,20 +287,6 @@ def test_several_greedy_steps_in_one_native_call(model_dirs, dtype):
         eng.greedy_run([0], [5], 10)                              # a slot that is not held
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_decoding_with_the_norm_computed_inside_the_contraction(model_dirs, name, monkeypatch):
-    """The option that lets the contraction after a norm compute the norm itself (few tokens): the same
-    logits as the plain implementation, prompts and the last tokens one by one."""
-    from dlgo_b200.engine.engine import Engine
-    from dlgo_b200.parts import tensor_core
-    monkeypatch.setattr(tensor_core, "NORM_IN_GEMM", 3)
-    eng = Engine(model_dirs[name], dtype="bfloat16", max_tokens=1536, cuda_graphs=False)
-    eng.cache.poison()
-    reqs = requests_of(name)
-    steps = T.tail_one_by_one(reqs, 12)
-    check(name, model_dirs, "bfloat16", steps, T.run_in_process(eng, steps), reqs, "norm in the contraction")
-
-
 def test_sampled_steps_in_one_native_call_draw_what_single_steps_draw(model_dirs):
     """Sampled generation with nobody listening token by token runs many steps per native call (a captured
     step that ends with the filters and the draw; draw indices and the repetition penalty's window advance

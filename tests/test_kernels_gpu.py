@@ -682,120 +682,6 @@ def test_gemm_tc_k_slices_add_themselves_into_the_residual(N, T_, K_, splits):
     k.check_device_errors()
 
 
-def _normed_ref(x, nw, eps):
-    """RMSNorm of fp32 rows (ops/norm.go:10-32), rounded to bfloat16 as the norm kernel leaves it."""
-    xd = x.double()
-    return (xd * (1.0 / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps)) * nw.double()).float().to(torch.bfloat16)
-
-
-@pytest.mark.parametrize("N,T_,K_,splits,epi", [
-    (3072, 8, 2048, 6, "partial"), (256, 3, 2048, 1, "store"), (16384, 8, 2048, 1, "swiglu"), (200, 7, 520, 2, "red"),
-    (512, 5, 4096, 4, "red"), (640, 8, 1096, 3, "partial"), (130, 1, 72, 1, "f32"), (4096, 8, 3072, 4, "partial"),
-    (1024, 6, 4096, 1, "swiglu")])
-def test_gemm_tc_computes_the_norm_of_its_activations_itself(N, T_, K_, splits, epi):
-    """The few-token product with B = RMSNorm(fp32 rows) computed in the kernel, against the product of the
-    separately normed, bfloat16-rounded rows.  Rows differ in scale by orders of magnitude, and one row
-    has a single large element, so a wrong or shared sum of squares shows."""
-    k = K()
-    g = torch.Generator().manual_seed(N + T_ + K_)
-    w = (torch.randn(N, K_, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    x = torch.randn(T_, K_, generator=g) * (10.0 ** torch.arange(T_).remainder(5).sub(2).float()).view(T_, 1)
-    x[T_ // 2, K_ - 1] = 300.0
-    x = x.to(DEV)
-    nw = (1.0 + 0.3 * torch.randn(K_, generator=g)).to(DEV)
-    eps = 1e-5
-    xn = _normed_ref(x, nw, eps)
-    ref = _tc_ref(xn, w)                                            # [T, N] float64
-    if epi == "partial":
-        out = torch.full((splits, T_, N), float("nan"), device=DEV)
-        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_PARTIAL, splits)
-        got = out.double().sum(0)
-    elif epi == "red":
-        res = torch.randn(T_, N, generator=g).to(DEV)
-        out = res.clone()
-        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_RED_F32, splits)
-        got = out.double() - res.double()
-    elif epi == "swiglu":
-        out = torch.empty((T_, N // 2), dtype=torch.bfloat16, device=DEV)
-        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_SWIGLU)
-        r = ref.view(T_, N // 32, 2, 16)
-        want = (r[:, :, 0] / (1.0 + torch.exp(-r[:, :, 0])) * r[:, :, 1]).reshape(T_, N // 2)
-        torch.testing.assert_close(out.double(), want, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=1e-2)
-        k.check_device_errors()
-        return
-    elif epi == "store":
-        out = torch.empty((T_, N), dtype=torch.bfloat16, device=DEV)
-        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_STORE)
-        torch.testing.assert_close(out.double(), ref, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=1e-2)
-        k.check_device_errors()
-        return
-    else:
-        out = torch.full((T_, N), float("nan"), device=DEV)
-        k.gemm_tc_normed(w, x, nw, eps, out, k.TC_STORE_F32)
-        got = out.double()
-    # the normed rows may differ from the reference's by one bfloat16 rounding where the fp32 sum of squares
-    # differs in its last bit: a few 1e-3 relative on single elements, far less on the sums
-    torch.testing.assert_close(got, ref, atol=2e-3 * math.sqrt(K_) * 0.05, rtol=2e-3)
-    k.check_device_errors()
-
-
-def test_gemm_tc_normed_refuses_what_it_does_not_keep_in_registers():
-    k = K()
-    w = torch.zeros(128, 4096, dtype=torch.bfloat16, device=DEV)
-    nw = torch.ones(4096, device=DEV)
-    with pytest.raises(k.KernelError):
-        k.gemm_tc_normed(w, torch.zeros(9, 4096, device=DEV), nw, 1e-5, torch.empty(9, 128, device=DEV), k.TC_STORE_F32)
-    with pytest.raises(k.KernelError):   # K-slices need an epilogue that can take them
-        k.gemm_tc_normed(w, torch.zeros(4, 4096, device=DEV), nw, 1e-5, torch.empty(4, 128, device=DEV), k.TC_STORE_F32, 2)
-
-
-@pytest.mark.parametrize("N,T_,K_,splits,cluster,bn,epi", [
-    (256, 5, 512, 2, 2, 16, "store"), (384, 16, 2048, 8, 8, 16, "add"), (130, 33, 200, 4, 4, 64, "f32"),
-    (2048, 64, 8192, 8, 8, 64, "store"), (3072, 8, 2048, 8, 8, 16, "store"), (2048, 8, 8192, 18, 6, 16, "partial"),
-    (1000, 20, 1096, 6, 3, 32, "partial"), (512, 7, 640, 5, 5, 16, "partial"), (640, 9, 4096, 7, 7, 16, "swiglu")])
-def test_gemm_tc_k_slices_meet_in_a_cluster(N, T_, K_, splits, cluster, bn, epi):
-    """K-slices that form a thread-block cluster are summed through distributed shared memory: same
-    result as one slice up to the order of the fp32 sums, and the same bits on every run."""
-    g = torch.Generator().manual_seed(N + T_ + splits)
-    w = (torch.randn(N, K_, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    x = torch.randn(T_, K_, generator=g).to(torch.bfloat16).to(DEV)
-    ref = _tc_ref(x, w)                                            # [T, N] in float64
-    runs = []
-    for _ in range(2):
-        if epi == "partial":
-            out = torch.full((splits // cluster, T_, N), float("nan"), device=DEV)
-            K().gemm_tc(w, x, out, True, K().TC_PARTIAL, bn, splits, static_operand=1, cluster=cluster)
-            got = out.double().sum(0)
-        elif epi == "swiglu":
-            out = torch.empty((T_, N // 2), dtype=torch.bfloat16, device=DEV)
-            K().gemm_tc(w, x, out, True, K().TC_SWIGLU, bn, splits, static_operand=1, cluster=cluster)
-            got = out.double()
-        elif epi == "add":
-            out = torch.ones((T_, N), device=DEV)
-            K().gemm_tc(w, x, out, True, K().TC_ADD_F32, bn, splits, static_operand=1, cluster=cluster)
-            got = out.double() - 1.0
-        else:
-            dt = torch.bfloat16 if epi == "store" else torch.float32
-            out = torch.empty((T_, N), dtype=dt, device=DEV)
-            K().gemm_tc(w, x, out, True, K().TC_STORE if epi == "store" else K().TC_STORE_F32, bn, splits,
-                        static_operand=1, cluster=cluster)
-            got = out.double()
-        runs.append(out.clone())
-        if epi == "swiglu":
-            r = ref.view(T_, N // 32, 2, 16)
-            gate, up = r[:, :, 0], r[:, :, 1]
-            want = (gate / (1 + torch.exp(-gate)) * up).reshape(T_, N // 2)
-            torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
-        else:
-            tol = 2e-2 if epi == "store" else 2e-4
-            torch.testing.assert_close(got, ref, atol=tol * float(ref.abs().max()), rtol=0)
-    assert torch.equal(runs[0], runs[1])
-    K().check_device_errors()
-    with pytest.raises(Exception):                                 # a cluster must divide the slices
-        K().gemm_tc(w, x, torch.empty((T_, N), dtype=torch.bfloat16, device=DEV), True, K().TC_STORE, bn, splits,
-                    static_operand=1, cluster=splits + 1 if splits < 8 else 3)
-
-
 @pytest.mark.parametrize("T_", [3, 40, 200])
 def test_gemm_tc_swiglu_epilogue(T_):
     k = K()
@@ -919,7 +805,7 @@ def test_rope_append_from_a_sum_that_it_leaves_zero(write_cache):
     kp1, vp1 = _paged(3, hkv, hd, "bfloat16")
     q1 = torch.full((3, ld), float("nan"), device=DEV, dtype=torch.bfloat16)
     total = whole.clone().view(1, 3, ld)
-    k.rope_append(q1, cos, sin, pos, seq, slots, pt, kp1, vp1, hq, hkv, hd, 32, False, write_cache, total, 0, 0, True)
+    k.rope_append(q1, cos, sin, pos, seq, slots, pt, kp1, vp1, hq, hkv, hd, 32, False, write_cache, total, True)
     assert int((total != 0).sum()) == 0, "the sum was not left zero"
     # (the plain path rounds the projection to bfloat16 before it rotates, this one after: one rounding apart)
     torch.testing.assert_close(q1[:, :hq * hd].float(), q0[:, :hq * hd].float(), atol=4e-2, rtol=2e-2)
@@ -929,68 +815,7 @@ def test_rope_append_from_a_sum_that_it_leaves_zero(write_cache):
                                    atol=4e-2, rtol=2e-2)
     with pytest.raises(k.KernelError):      # two slices are not a sum
         k.rope_append(q1, cos, sin, pos, seq, slots, pt, kp1, vp1, hq, hkv, hd, 32, False, True,
-                      torch.zeros(2, 3, ld, device=DEV), 0, 0, True)
-
-
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hq,hkv,hd,rot,inter", [(8, 2, 64, 64, False), (3, 1, 32, 32, False), (4, 4, 128, 64, True),
-                                                 (4, 2, 16, 0, False)])
-@pytest.mark.parametrize("from_parts", [False, True])
-def test_decode_attention_with_the_rotation_and_append_inside(dtype, hq, hkv, hd, rot, inter, from_parts):
-    # the fused kernel against rope_append followed by the plain decode kernel, on the same inputs
-    from dlgo_b200.parts.rope import RotaryEmbedding
-    k = K()
-    if not k.attention_decode_fuses_rope(DT[dtype], hq, hkv, hd, rot, inter, 64):
-        pytest.skip("sizes the fused kernel does not take")
-    torch.manual_seed(hd + rot)
-    if rot:
-        cos, sin = (t.to(DEV) for t in RotaryEmbedding(hd, rot, 10000.0, 400, "interleaved" if inter else "split_half").tables())
-    else:
-        cos = sin = torch.zeros(1, 1, device=DEV)
-    lens = [300, 1, 64, 65]                                       # positions 299, 0, 63 (page end), 64 (page start)
-    B = len(lens)
-    pages_per = [(n + 63) // 64 for n in lens]
-    n_pages = sum(pages_per) + 1
-    perm = torch.randperm(n_pages).tolist()
-    pt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
-    for i, n in enumerate(pages_per):
-        for pg in range(n):
-            pt[i, pg] = perm.pop()
-    pt = pt.to(DEV)
-    ld = (hq + 2 * hkv) * hd
-    S = 3
-    parts = (torch.randn(S, B, ld, device=DEV) * 0.6)
-    whole = (parts[0] + parts[1] + parts[2])
-    if not from_parts:
-        whole = whole.to(DT[dtype]).float()
-    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
-    seq = torch.arange(B, dtype=torch.int32, device=DEV)
-    outs = []
-    caches = []
-    for fused in (False, True):
-        torch.manual_seed(1)
-        kp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(DT[dtype])
-        vp = torch.randn(n_pages, hkv, 64, hd, device=DEV).to(DT[dtype])
-        out = torch.full((B, hq * hd), float("nan"), device=DEV, dtype=DT[dtype])
-        for n_splits in (1, 4):
-            if not fused:
-                qkv = whole.to(DT[dtype]).clone()
-                k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, rot, inter, True,
-                              parts if from_parts else None)
-                k.attention_decode(qkv, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits)
-            else:
-                k.attention_decode_rope(None if from_parts else whole.to(DT[dtype]), parts if from_parts else None, B,
-                                        cos, sin, rot, inter, True, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5,
-                                        0, n_splits)
-            outs.append(out.float().clone())
-        caches.append((kp.float().clone(), vp.float().clone()))
-    t = dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)
-    torch.testing.assert_close(outs[2], outs[0], **t)
-    torch.testing.assert_close(outs[3], outs[1], **t)
-    # the same rows were appended (the two kernels may contract x0*c - x1*s differently: one ulp)
-    ct = dict(atol=1e-6, rtol=1e-6) if dtype == "float32" else dict(atol=1e-2, rtol=8e-3)
-    torch.testing.assert_close(caches[1][0], caches[0][0], **ct)
-    assert torch.equal(caches[1][1], caches[0][1])
+                      torch.zeros(2, 3, ld, device=DEV), True)
 
 
 @pytest.mark.parametrize("hq,hkv,hd,S", [(8, 2, 64, 3), (32, 8, 64, 6), (3, 1, 128, 8), (8, 1, 64, 11), (12, 4, 128, 1)])
@@ -1043,10 +868,10 @@ def test_tensor_core_decode_attention_with_the_rotation_and_append_inside(hq, hk
 
 @pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 64), (24, 8, 128), (8, 1, 64)])
 @pytest.mark.parametrize("n_splits", [1, 3, 8])
-def test_tensor_core_decode_attention_reads_scales_and_clears_the_projections_sum(hq, hkv, hd, n_splits):
+def test_tensor_core_decode_attention_reads_and_clears_the_projections_sum(hq, hkv, hd, n_splits):
     # the schedule of a decode step: the q|k|v projection's K-slices have added themselves into ONE fp32 sum;
-    # the attention kernel scales it per token, rotates, appends, attends, and leaves the sum zero.  Against
-    # rope_append (on the scaled sum) followed by the kernel fed with the finished q.
+    # the attention kernel rotates, appends, attends, and leaves the sum zero.  Against rope_append (on the
+    # sum) followed by the kernel fed with the finished q.
     from dlgo_b200.parts.rope import RotaryEmbedding
     k = K()
     torch.manual_seed(hd + n_splits)
@@ -1063,7 +888,6 @@ def test_tensor_core_decode_attention_reads_scales_and_clears_the_projections_su
     pt = pt.to(DEV)
     ld = (hq + 2 * hkv) * hd
     total = torch.randn(1, B, ld, device=DEV) * 0.6
-    factor = (torch.rand(B, device=DEV) + 0.5).contiguous()
     pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     seq = torch.arange(B, dtype=torch.int32, device=DEV)
     got = {}
@@ -1074,13 +898,12 @@ def test_tensor_core_decode_attention_reads_scales_and_clears_the_projections_su
         out = torch.full((B, hq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
         if not fused:
             qkv = torch.empty(B, ld, device=DEV, dtype=torch.bfloat16)
-            k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, hd, False, True,
-                          (total * factor[None, :, None]).contiguous())
+            k.rope_append(qkv, cos, sin, pos, seq, seq, pt, kp, vp, hq, hkv, hd, hd, False, True, total.clone())
             k.attention_decode_mma(qkv, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits, 32)
         else:
             work = total.clone()
             k.attention_decode_mma(None, ld, B, kp, vp, pt, seq, pos, out, hq, hkv, hd, hd ** -0.5, 0, n_splits, 32,
-                                   None, work, cos, sin, True, clear_parts=True, row_scale=factor)
+                                   None, work, cos, sin, True, clear_parts=True)
             assert float(work.abs().max()) == 0.0, "the sum must be zero again for the next step"
         got[fused] = (out.float().clone(), kp.float().clone(), vp.float().clone())
     torch.testing.assert_close(got[True][0], got[False][0], atol=2e-2, rtol=2e-2)
