@@ -113,7 +113,8 @@ class FusedRun:
 def plan_runs(model: Any, runtime: Any) -> Dict[int, FusedRun]:
     """{first run entry: FusedRun} for the model's runs of blocks the kernel takes (empty when switched off,
     in float32, or when no block qualifies)."""
-    if not ENABLED or runtime.dtype != torch.bfloat16:
+    from ..parts import tensor_core
+    if not ENABLED or runtime.dtype != torch.bfloat16 or tensor_core.ORDERED_SUMS:
         return {}
     runs: Dict[int, FusedRun] = {}
     i, order = 0, model.order

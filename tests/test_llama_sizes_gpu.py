@@ -231,6 +231,34 @@ def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dt
     kernels.check_device_errors()
 
 
+def test_ordered_sums_make_bfloat16_decoding_repeatable_bit_for_bit(batch8, monkeypatch):
+    # DLGO_ORDERED_SUMS=1: K-slices are kept apart and added in slice order by the next norm instead of adding
+    # themselves into the residual in whatever order they finish.  Two runs of the same batch then give the
+    # same bits (another batch size cuts K into other slices: close, not bit-equal).
+    from dlgo_b200.engine.engine import Engine
+    from dlgo_b200.parts import tensor_core
+    monkeypatch.setattr(tensor_core, "ORDERED_SUMS", True)
+    d, reqs, refs = batch8
+    eng = Engine(d, dtype="bfloat16", max_tokens=8 * 1024, max_seq_len=1024)
+    first = T.run_in_process(eng, batch_steps(reqs))
+    again = T.run_in_process(eng, batch_steps(reqs))
+    for s in range(N_DECODE + 1):
+        assert torch.equal(first[s], again[s]), f"step {s}: two runs differ"
+    for i, rid in enumerate(reqs):
+        scale = float(refs[rid].abs().max())
+        for s in range(N_DECODE + 1):
+            assert float((first[s][i] - refs[rid][s]).abs().max()) <= 3e-2 * scale, (rid, s)
+    # request r2 alone (batch 1: other K-slicing, other graph) decodes to the same bits as inside the batch of 8
+    rid, n = "r2", BATCH_LENS[2]
+    slot = eng.take_slot()
+    eng.step([slot], [reqs[rid][:n]])
+    for j in range(N_DECODE):
+        lg = eng.step([slot], [[reqs[rid][n + j]]]).float().cpu()
+        err = float((lg[0] - first[j + 1][2]).abs().max())
+        assert err <= 3e-2 * float(refs[rid].abs().max())      # (other slice counts: close, not bit-equal)
+    eng.free_slot(slot)
+
+
 def test_default_cache_sizing_and_a_very_long_capacity(batch8):
     # no max_tokens: the cache is sized from the context (131072 positions here), so a captured step's grids
     # cover 2048 pages a sequence and decode attention takes its many-slices path
