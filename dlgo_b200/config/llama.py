@@ -77,6 +77,10 @@ class LlamaConfig:
     eos_token_ids: Tuple[int, ...] = ()
     hidden_act: str = "silu"
     architecture: str = "LlamaForCausalLM"
+    # rotation pairs (2i, 2i+1) instead of (i, i + head_dim/2): for weights whose q/k rows were exported in the
+    # reference's own order (its llama default, models/llm/arch.go:18, ops/rope.go:26-31).  Checkpoints in the
+    # common safetensors layout are split-half: absent or false.
+    rope_interleaved: bool = False
 
     # ------------------------------------------------------------------ derived
     @property
@@ -198,6 +202,7 @@ class LlamaConfig:
             rope_scaling=scaling,
             max_position_embeddings=_opt(d, "max_position_embeddings", int, 2048),
             tie_word_embeddings=_opt(d, "tie_word_embeddings", bool, False),
+            rope_interleaved=_opt(d, "rope_interleaved", bool, False),
             bos_token_id=_opt(d, "bos_token_id", int, None),
             eos_token_ids=eos_ids,
             hidden_act=str(d.get("hidden_act", "silu")),
@@ -226,6 +231,8 @@ class LlamaConfig:
             "mlp_bias": False,
             "torch_dtype": "bfloat16",
         }
+        if self.rope_interleaved:
+            d["rope_interleaved"] = True
         if self.bos_token_id is not None:
             d["bos_token_id"] = self.bos_token_id
         if self.eos_token_ids:
@@ -242,7 +249,7 @@ class LlamaConfig:
             "rotary_dim": self.head_dim,
             "theta": self.rope_theta,
             "max_positions": self.max_position_embeddings,
-            "pairing": "split_half",
+            "pairing": "interleaved" if self.rope_interleaved else "split_half",
         }
         if self.rope_scaling is not None:
             rope_params["scaling"] = asdict(self.rope_scaling)

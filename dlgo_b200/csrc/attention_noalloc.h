@@ -19,9 +19,12 @@
 //     capture.
 //   * All calls share the one array and it keeps whatever the last call left in it.  Nothing in it
 //     has to start at zero: every (token, head, slice) entry that the combine kernel reads is
-//     written by the first kernel of the same call.  Two calls that overlap on the GPU (different
-//     streams, or the same stream from different threads without ordering) race on the array:
-//     order them.
+//     written by the first kernel of the same call, PROVIDED the tiles cover every token 0 .. T-1
+//     exactly once (as the engine's tile tables do).  The combine runs over all T tokens: a token
+//     that no tile covers would be combined from whatever an earlier, possibly foreign, call left
+//     in the array.  The tile table lives in device memory, so the entry point cannot check this.
+//     Two calls that overlap on the GPU (different streams, or the same stream from different
+//     threads without ordering) race on the array: order them.
 //   * It calls no cudaMalloc, cudaFree or any allocating routine, of CUDA or of PyTorch.
 //
 // Arguments are those of dlgo_attention without `scratch`; the result is the same.

@@ -60,6 +60,7 @@ class Engine:
                 source = WeightSource(model_dir, self.runtime.device)
             self.model.load_weights(source, self.runtime)
             source.release()
+        self._note_stand_ins()
         context = self.spec.max_positions
         if max_seq_len is None or max_seq_len <= 0 or max_seq_len > context:
             max_seq_len = context
@@ -84,6 +85,24 @@ class Engine:
         self.cuda_graphs = cuda_graphs
         self._graphs: Dict[int, "object"] = {}
         self.launches_last_step = 0
+
+    def _note_stand_ins(self) -> None:
+        """One line on stderr when a bfloat16 model's sizes land on the slower stand-in kernels (never a wrong
+        result, but a user should know why it is slow)."""
+        if self.runtime.dtype != torch.bfloat16:
+            return
+        import sys
+        notes = set()
+        for blk in self.model.blocks:
+            for part in blk.parts().values():
+                for v in vars(part).values():
+                    if hasattr(v, "_tc") and hasattr(v, "in_features") and v._tc is None:
+                        notes.add(f"contractions over {v.in_features} inputs (no multiple of 8) run on the fp32 pipes")
+                hd = getattr(part, "head_dim", None)
+                if hd is not None and hasattr(part, "num_kv_heads") and hd not in (64, 128):
+                    notes.add(f"attention with heads of {hd} runs on the general kernels (tensor-core kernels take 64 and 128)")
+        if notes:
+            print("[dlgo_b200] note: " + "; ".join(sorted(notes)), file=sys.stderr, flush=True)
 
     # -------------------------------------------------------------------- slots
     def take_slot(self) -> int:

@@ -82,16 +82,22 @@ def rope_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) -> Li
     return out
 
 
-def rope(vec: torch.Tensor, pos: int, freqs: List[float]) -> torch.Tensor:
+def rope(vec: torch.Tensor, pos: int, freqs: List[float], interleaved: bool = False) -> torch.Tensor:
     """Rotate one head vector at absolute position `pos`: angle = pos * theta_i in float64, cos/sin
     cast to the working precision (models/llm/workers.go:160-169); pairs (i, i + half) -> (x0 c - x1 s,
-    x0 s + x1 c) (ops/rope.go:21-25, models/llm/workers.go:196-204)."""
+    x0 s + x1 c) (ops/rope.go:21-25, models/llm/workers.go:196-204), or, `interleaved`, pairs (2i, 2i + 1)
+    (ops/rope.go:26-31, models/llm/workers.go:205-214)."""
     half = len(freqs)
     ang = torch.tensor([float(pos) * f for f in freqs], dtype=torch.float64)
     c = torch.cos(ang).to(torch.float32).to(vec.dtype)
     s = torch.sin(ang).to(torch.float32).to(vec.dtype)
-    x0, x1 = vec[:half], vec[half:2 * half]
     out = vec.clone()
+    if interleaved:
+        x0, x1 = vec[0:2 * half:2], vec[1:2 * half:2]
+        out[0:2 * half:2] = x0 * c - x1 * s
+        out[1:2 * half:2] = x0 * s + x1 * c
+        return out
+    x0, x1 = vec[:half], vec[half:2 * half]
     out[:half] = x0 * c - x1 * s
     out[half:2 * half] = x0 * s + x1 * c
     return out
@@ -147,11 +153,12 @@ def layer(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, f
     q = linear(xn, w[prefix + "self_attn.q_proj.weight"])
     k = linear(xn, w[prefix + "self_attn.k_proj.weight"])
     v = linear(xn, w[prefix + "self_attn.v_proj.weight"])
+    inter = bool(cfg.get("rope_interleaved", False))
     for p in range(x.shape[0]):
         for h in range(hq):
-            q[p, h * hd:(h + 1) * hd] = rope(q[p, h * hd:(h + 1) * hd], start_pos + p, freqs)
+            q[p, h * hd:(h + 1) * hd] = rope(q[p, h * hd:(h + 1) * hd], start_pos + p, freqs, inter)
         for h in range(hkv):
-            k[p, h * hd:(h + 1) * hd] = rope(k[p, h * hd:(h + 1) * hd], start_pos + p, freqs)
+            k[p, h * hd:(h + 1) * hd] = rope(k[p, h * hd:(h + 1) * hd], start_pos + p, freqs, inter)
     a = attention(q, k, v, hq, hkv, hd)
     r = x + linear(a, w[prefix + "self_attn.o_proj.weight"])
     rn = rmsnorm(r, w[prefix + "post_attention_layernorm.weight"], eps)

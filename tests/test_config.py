@@ -128,3 +128,13 @@ def test_command_line_writes_and_describes_a_model_folder(tmp_path):
     # generate refuses bad options before it looks for a GPU
     assert main(["generate", str(out), "--max-tokens", "0", "--prompt-ids", "1,2"]) == 2
     assert main(["generate", str(out)]) == 2
+
+
+def test_rope_pairing_comes_from_the_configuration():
+    from dlgo_b200.config import config_from_dict
+    from tiny_configs import TINY
+    base = dict(TINY["A"]["cfg"])
+    assert config_from_dict(base).architecture_spec().position_encodings["rope"].params["pairing"] == "split_half"
+    cfg = config_from_dict(dict(base, rope_interleaved=True))
+    assert cfg.architecture_spec().position_encodings["rope"].params["pairing"] == "interleaved"
+    assert cfg.to_dict()["rope_interleaved"] is True and "rope_interleaved" not in config_from_dict(base).to_dict()

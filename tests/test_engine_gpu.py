@@ -344,3 +344,26 @@ def test_the_command_line_generates_what_the_python_entry_point_does(model_dirs)
     out, err = _cli("generate", d, "--prompt-ids", ids[1], "--max-tokens", "4", "--greedy", "--bench", "--ctx", "64",
                     "--dtype", "float32", "--ignore-eos")
     assert len(out.split()) == 4 and "tok/s" in err and "prompt tokens: 3" in err
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_interleaved_rotation_pairs_from_the_configuration(tmp_path, dtype):
+    # config.json's rope_interleaved (the reference's own pairing for this architecture, ops/rope.go:26-31):
+    # the same weights give other logits than with split-half pairs, and the engine follows the plain
+    # implementation in both, prompts and single tokens
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.engine.engine import Engine
+    from dlgo_b200.weights import write_random_model
+    cfg = dict(TINY["B"]["cfg"], rope_interleaved=True)
+    d = write_random_model(config_from_dict(cfg), 1, str(tmp_path / "inter"), std=0.05)
+    reqs = {"i0": random_tokens(70, 384, 5), "i1": random_tokens(9, 384, 6)}
+    eng = Engine(d, dtype=dtype, max_tokens=512)
+    steps = T.tail_one_by_one(reqs, 8)
+    got = T.collect(steps, T.run_in_process(eng, steps), reqs)
+    pc, w = P.read_model(d)
+    assert pc["rope_interleaved"] is True
+    for rid, toks in reqs.items():
+        ref = P.forward(pc, w, toks)
+        assert_close(got[rid], ref, dtype, f"interleaved {rid}")
+        other = P.forward(dict(pc, rope_interleaved=False), w, toks)
+        assert float((ref - other).abs().max()) > 1e-3 * float(ref.abs().max()) or len(toks) < 2

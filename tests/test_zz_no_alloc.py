@@ -8,7 +8,9 @@ library (8 MiB per GPU, held until the process exits).  This test calls that sym
 pointers, as such a caller would, and checks the result against the ordinary entry point
 (`dlgo_attention`, which takes its scratch from the caller), twice in a row with different
 inputs: the array is shared by all calls and keeps the last call's contents, so the second call
-shows whether stale partial sums can leak into a result.  Needs a GPU.
+shows whether stale partial sums can leak into a result.  Both entry points run the same kernel,
+so each result is also compared with a plain float32 softmax over the keys of every head, which an
+error common to both could not pass.  Needs a GPU.
 """
 import ctypes
 import math
@@ -52,6 +54,24 @@ def _call_noalloc(lib, c, n_splits, out):
         ctypes.c_float(1.0 / math.sqrt(c["hd"])), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def _plain(c):
+    """softmax(q . k / sqrt(hd)) v over the keys 0 .. pos of every head, in float32 with tensor operations
+    (models/llm/forward.go:258-278); kv head = head // (heads per kv head)."""
+    B, hq, hkv, hd = c["B"], c["hq"], c["hkv"], c["hd"]
+    out = torch.zeros(B, hq * hd)
+    q, kp, vp, pt, pos = (c[k].float().cpu() if c[k].is_floating_point() else c[k].cpu() for k in ("q", "kp", "vp", "pt", "pos"))
+    for b in range(B):
+        n = int(pos[b]) + 1
+        pages = [int(pt[b, pg]) for pg in range((n + 63) // 64)]
+        for h in range(hq):
+            g = h // (hq // hkv)
+            keys = torch.cat([kp[p, g] for p in pages])[:n]
+            vals = torch.cat([vp[p, g] for p in pages])[:n]
+            s = (keys @ q[b, h * hd:(h + 1) * hd]) / math.sqrt(hd)
+            out[b, h * hd:(h + 1) * hd] = torch.softmax(s, dim=0) @ vals
+    return out
+
+
 def _call_ordinary(c, n_splits):
     from dlgo_b200.csrc import kernels as K
     out = torch.full((c["B"], c["hq"] * c["hd"]), float("nan"), dtype=c["q"].dtype, device=DEV)
@@ -82,6 +102,8 @@ def test_noalloc_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row(dtyp
         ref = _call_ordinary(c, n_splits)
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.float(), ref.float(), **tol)
+        plain_tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(out.float().cpu(), _plain(c), **plain_tol)
     # one slice needs no scratch at all and takes the same path
     c = _case(3, dtype, [100, 30])
     out = torch.full((2, c["hq"] * c["hd"]), float("nan"), dtype=dtype, device=DEV)
