@@ -263,6 +263,44 @@ def plain_cpu_baseline() -> dict:
     return out
 
 
+def phase_stamps(llm, batch):
+    """Phase timing of the persistent decode kernel (csrc/decode_layers.cu), which stamps the global timer at
+    its phase boundaries when built with -DDLGO_TIMING.  Run as
+        DLGO_FUSED_DECODE=1 DLGO_NVCC_FLAGS=-DDLGO_TIMING python bench.py --only phases --layers 4 --batch 8
+    Prints, for the launch's second layer, when each phase ended (us after the first CTA began the layer;
+    minimum, median and maximum over the CTAs)."""
+    import ctypes
+    import torch
+    from dlgo_b200.csrc import build, kernels
+    eng = llm.engine
+    if not eng.model.fused_runs or "DLGO_TIMING" not in os.environ.get("DLGO_NVCC_FLAGS", ""):
+        print("bench.py --only phases needs DLGO_FUSED_DECODE=1 and DLGO_NVCC_FLAGS=-DDLGO_TIMING in the environment")
+        return 2
+    prompts = prompts_for(batch)
+    slots = [eng.take_slot() for _ in prompts]
+    nxt = kernels.argmax(eng.step(slots, prompts)).cpu().tolist()
+    for _ in range(6):
+        eng.step(slots, [[t] for t in nxt])
+    torch.cuda.synchronize()
+    lib = build.load_library("decode_layers")
+    buf = (ctypes.c_ulonglong * (256 * 16))()
+    if lib.dlgo_decode_layers_times(buf) != 0:
+        return 1
+    grid = kernels.decode_layers_grid()
+    rows = [[buf[c * 16 + k] for k in range(15)] for c in range(grid)]
+    t0 = min(r[0] for r in rows)
+    names = ["layer begins", "P1 operand built", "P1 epilogue done", "barrier 1 passed", "P2 attention done",
+             "barrier 2 passed", "P3 operand built", "P3 epilogue done", "barrier 3 passed", "P4 operand built",
+             "P4 epilogue done", "barrier 4 passed", "P5 operand built", "P5 epilogue done", "barrier 5 passed"]
+    print(f"persistent decode kernel, batch {batch}, {grid} CTAs: us after the first CTA began the layer (min / median / max)")
+    for k, n in enumerate(names):
+        col = sorted((r[k] - t0) / 1e3 for r in rows)
+        print(f"  {n:18s} {col[0]:8.2f} {col[len(col) // 2]:8.2f} {col[-1]:8.2f}")
+    for s in slots:
+        eng.free_slot(s)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,7 +313,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length instead of uniform[128,1024]")
     ap.add_argument("--prompt-range", default="", help="LO,HI: prompt lengths uniform in [LO, HI] (default 128,1024)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the cache is sized for")
-    ap.add_argument("--only", choices=["decode", "prefill"], help="run one small workload (for profiling) and stop")
+    ap.add_argument("--only", choices=["decode", "prefill", "phases"],
+                    help="run one small workload (for profiling) and stop; phases: see phase_stamps()")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -311,6 +350,8 @@ def main() -> int:
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
     eng = llm.engine
+    if a.only == "phases":
+        return phase_stamps(llm, a.batch)
     if a.only == "decode":
         r = decode_run(llm, a.batch, a.steps, warmup)
         kv = sum(2 * n.num_kv_heads * n.head_dim for n in eng.model.cache_needs()[0] if n is not None) * 2

@@ -98,7 +98,6 @@ struct DlParams {
   unsigned int* sync;         // [0] barrier arrivals of this launch, [1] CTAs that left; zero between launches
   int stages;
   int operand_bytes;
-  int l2_ahead;               // weight tiles beyond the ring that the loader asks into L2 ahead of time
 };
 
 // ------------------------------------------------------------------------------------------- helpers
@@ -197,6 +196,33 @@ __device__ __forceinline__ void build_operand_f32(uint8_t* dst, const float* __r
   }
 }
 
+// The same for a K-slice of the rows (a few KB): a thread takes four columns of every row, all rows' loads in
+// flight at once.
+__device__ __forceinline__ void build_operand_slice(uint8_t* dst, const float* __restrict__ x, int ld,
+                                                    const float* __restrict__ w, int K, int T, int kb0, int kb1,
+                                                    int ctid) {
+  const int n4 = (kb1 - kb0) * (DL_TILE_K / 4);
+  const int k_base = kb0 * DL_TILE_K;
+  for (int j4 = ctid; j4 < n4; j4 += DL_CT) {
+    const int kk = 4 * j4, k = k_base + kk;
+    const bool in = k < K;        // K is a multiple of 8
+    float4 v[DL_BN];
+#pragma unroll
+    for (int t = 0; t < DL_BN; ++t)
+      v[t] = (in && t < T) ? __ldcg(reinterpret_cast<const float4*>(x + (size_t)t * ld + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 wv = in ? __ldg(reinterpret_cast<const float4*>(w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < DL_BN; ++t) {
+      if (t < T) {
+        __nv_bfloat162 hh[2] = {__floats2bfloat162_rn(v[t].x * wv.x, v[t].y * wv.y),
+                                __floats2bfloat162_rn(v[t].z * wv.z, v[t].w * wv.w)};
+        *reinterpret_cast<uint2*>(dst + operand_offset(kk >> 6, t, (kk & 63) >> 3) + ((kk & 7) << 1)) =
+            *reinterpret_cast<uint2*>(hh);
+      }
+    }
+  }
+}
+
 // Token operand from bf16 rows, K blocks [kb0, kb1): 16-byte chunks, four loads in flight a thread.
 __device__ __forceinline__ void build_operand_bf16(uint8_t* dst, const __nv_bfloat16* __restrict__ x, int ld, int K,
                                                    int T, int kb0, int kb1, int ctid) {
@@ -245,45 +271,6 @@ struct UnitIter {
     const int split = u / tiles;
     kb0 = split * per;
     kb1 = min(kblocks, kb0 + per);
-  }
-};
-
-// This CTA's weight tiles in the order the ring takes them: layers, products, units, K blocks.
-struct TileWalker {
-  const DlParams& p;
-  int cta, grid;
-  int li = 0, ph = 0, u = 0, kb = 0, kb1 = 0, tile = 0;
-  bool open = false;     // a unit is open (kb .. kb1 remain)
-  __device__ __forceinline__ TileWalker(const DlParams& p_, int cta_, int grid_) : p(p_), cta(cta_), grid(grid_), u(cta_) {}
-  __device__ __forceinline__ const DlGemm& gemm() const { return ph == 0 ? p.qkv : (ph == 1 ? p.o : (ph == 2 ? p.gu : p.down)); }
-  // false when no tile is left
-  __device__ __forceinline__ bool next(const CUtensorMap*& map, int& x, int& y) {
-    for (;;) {
-      if (li >= p.n_layers) return false;
-      if (!open) {
-        const UnitIter it(gemm());
-        if (u < it.count()) {
-          int kb0;
-          it.unit(u, tile, kb0, kb1);
-          kb = kb0;
-          open = true;
-        } else {
-          u = cta;
-          if (++ph == 4) { ph = 0; ++li; }
-          continue;
-        }
-      }
-      if (kb < kb1) {
-        const DlLayer& L = p.layers[li];
-        map = ph == 0 ? &L.w_qkv : (ph == 1 ? &L.w_o : (ph == 2 ? &L.w_gu : &L.w_down));
-        x = kb * DL_TILE_K;
-        y = tile * DL_TILE_M;
-        ++kb;
-        return true;
-      }
-      open = false;
-      u += grid;
-    }
   }
 };
 
@@ -535,29 +522,25 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
   if (warp == 0) {
     // ------------------------------------------------------------------ weights: one stream for all phases
     if (elect_one()) {
-      // one walker feeds the ring; a second one runs `l2_ahead` tiles in front of it and asks for those tiles
-      // to be brought into L2, so that memory keeps streaming while a phase that reads little (attention, the
-      // barriers) holds the ring up, and the ring later refills from L2
-      TileWalker load(p, cta, grid), ahead(p, cta, grid);
-      uint32_t sc = 0, pf = 0;     // tiles loaded / prefetched so far
-      bool more_ahead = true;
-      const CUtensorMap* map;
-      int x, y;
-      while (load.next(map, x, y)) {
-        while (more_ahead && pf < sc + (uint32_t)STAGES + (uint32_t)p.l2_ahead) {
-          const CUtensorMap* m2;
-          int x2, y2;
-          more_ahead = ahead.next(m2, x2, y2);
-          if (more_ahead) {
-            if (pf >= sc + (uint32_t)STAGES) tma_prefetch_l2_2d(m2, x2, y2);   // (tiles the ring takes at once need no hint)
-            ++pf;
+      uint32_t sc = 0;     // stages filled so far
+      bool ok = true;
+      for (int li = 0; ok && li < p.n_layers; ++li) {
+        const DlLayer& L = p.layers[li];
+        for (int ph = 0; ok && ph < 4; ++ph) {
+          const DlGemm& g = ph == 0 ? p.qkv : (ph == 1 ? p.o : (ph == 2 ? p.gu : p.down));
+          const CUtensorMap* map = ph == 0 ? &L.w_qkv : (ph == 1 ? &L.w_o : (ph == 2 ? &L.w_gu : &L.w_down));
+          const UnitIter it(g);
+          for (int u = cta; ok && u < it.count(); u += grid) {
+            int tile, kb0, kb1;
+            it.unit(u, tile, kb0, kb1);
+            for (int kb = kb0; kb < kb1; ++kb, ++sc) {
+              const uint32_t s = sc % (uint32_t)STAGES, phs = (sc / (uint32_t)STAGES) & 1u;
+              if (!mbar_wait(&sh.empty[s], phs ^ 1u, abort_flag)) { ok = false; break; }
+              mbar_expect_tx(&sh.full[s], DL_A_BYTES);
+              tma_load_2d(sh.ring + (size_t)s * DL_A_BYTES, map, &sh.full[s], kb * DL_TILE_K, tile * DL_TILE_M);
+            }
           }
         }
-        const uint32_t s = sc % (uint32_t)STAGES, phs = (sc / (uint32_t)STAGES) & 1u;
-        if (!mbar_wait(&sh.empty[s], phs ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&sh.full[s], DL_A_BYTES);
-        tma_load_2d(sh.ring + (size_t)s * DL_A_BYTES, map, &sh.full[s], x, y);
-        ++sc;
       }
     }
   } else if (warp == 1) {
@@ -663,12 +646,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
       DL_STAMP(0);
       // ---- P1: q|k|v sums
       my_range(p.qkv, kb0, kb1);
-      if (p.T <= 8)
-        build_operand_f32<false, 8>(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid, 0.f, sh.red,
-                                    sh.scales);
-      else
-        build_operand_f32<false, 16>(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid, 0.f,
-                                     sh.red, sh.scales);
+      build_operand_slice(sh.operand, p.residual, p.ld_res, L.norm1_w, p.d, p.T, kb0, kb1, ctid);
       operand_ready();
       DL_STAMP(1);
       if (cta < p.T) {        // this CTA computes the norm's scale of token `cta`
@@ -950,8 +928,6 @@ DLGO_EXPORT int dlgo_decode_layers(const void* layers, int n_layers, int T, int 
   p.sync = sync;
   p.stages = layout(p.qkv, p.o, p.gu, p.down, hd, &p.operand_bytes);
   if (p.stages <= 0) return DLGO_ERR_SIZE;
-  static const int l2_ahead = [] { const char* e = getenv("DLGO_DL_L2_AHEAD"); return e ? atoi(e) : 0; }();
-  p.l2_ahead = l2_ahead < 0 ? 0 : l2_ahead;
   const int smem = p.stages * DL_A_BYTES + p.operand_bytes + 1024 /* control */ + 1024 /* alignment */;
   auto kernel = hd == 64 ? decode_layers_kernel<64> : decode_layers_kernel<128>;
   static bool configured[2] = {false, false};
