@@ -31,6 +31,7 @@ _QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))
 # ... which the tensor-core decode kernel reads itself: it rotates q and k, appends k and v and clears the sum, so
 # the rotation needs no launch of its own.  Measured on a B200 (Llama 3.2 1B sizes, batch 8): see DESIGN.md.
 _FUSE_ROPE = int(os.environ.get("DLGO_ATTN_FUSE_ROPE", 1))
+_FUSE_ROPE_MAX_HEAD = 64
 
 
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 0))   # blocks wanted in flight for decode attention (0: four per SM)
@@ -129,7 +130,9 @@ class GQAAttention(Mixer):
             # few tokens: the projection's K-slices add themselves, at the memory, into one fp32 sum that is zero
             # between steps; whoever rotates reads it once and leaves zeros behind
             qkv_sum = ctx.zeros(f"qkv_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(1, T, n_cols)
-            fuse = (mma and _FUSE_ROPE and n_splits <= 8 and
+            # (heads of 64 only: at 128 the kernel is at its register limit and the fused form measured 2 to 3 %
+            # slower in a whole step at the layer sizes of Llama 3.2 3B and 3.1 8B, batch 8)
+            fuse = (mma and _FUSE_ROPE and n_splits <= 8 and self.head_dim <= _FUSE_ROPE_MAX_HEAD and
                     K.attention_decode_mma_fuses_rope(self.num_heads, self.num_kv_heads, self.head_dim, rot, inter))
             self.wqkv(x, ADD_F32, qkv_sum[0])
             if fuse:
