@@ -29,7 +29,8 @@ _MMA_KEYS = int(os.environ.get("DLGO_ATTN_MMA_KEYS", 32))    # keys per warp ite
 # few tokens: the projection's K-slices meet in one fp32 sum (reductions at the memory) that is zero between steps
 _QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))
 # ... which the tensor-core decode kernel reads itself: it rotates q and k, appends k and v and clears the sum, so
-# the rotation needs no launch of its own.  Measured on a B200 (Llama 3.2 1B sizes, batch 8): see DESIGN.md.
+# the rotation needs no launch of its own.  Measured on a B200 (Llama 3.2 1B sizes): 0.789 -> 0.761 ms a step at
+# batch 8, 1.31 -> 1.28 ms at batch 64.
 _FUSE_ROPE = int(os.environ.get("DLGO_ATTN_FUSE_ROPE", 1))
 _FUSE_ROPE_MAX_HEAD = 64
 

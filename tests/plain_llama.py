@@ -8,10 +8,18 @@ elementary torch tensor arithmetic only.
 
 The reference's model code is Go and there is no Go toolchain on the build
 machine, so it cannot be imported or compiled for a comparison: this
-implementation rests on the formulas as read from the source.  The one piece
-of the reference that does compile here, the C kernels of quant/simd_dot.c
-(softmax, SwiGLU, dot product, axpy), anchors the matching functions below
-through tests/golden/primitives.json (made by tests/golden/make_primitives.py).  Differences that
+implementation rests on the formulas as read from the source.  What pins it:
+  * the C kernels of quant/simd_dot.c do compile here and anchor softmax,
+    swiglu, the dot product and the axpy of the weighted sum through
+    tests/golden/primitives.json (made by tests/golden/make_primitives.py);
+  * the cases of the reference's own unit tests (ops/norm_test.go,
+    ops/rope_test.go, ops/ops_test.go, ops/activation_test.go,
+    ops/sampling_test.go), read as text, anchor rmsnorm, rope, softmax, argmax,
+    linear, swiglu and the sampling filters (tests/test_reference_vectors.py);
+  * inputs for which the formulas give the answer in closed form anchor the
+    causal bound, the kv head a query head reads, the score scale, a layer's
+    order, the tied head and the three bands of the llama3 scaling (same file).
+Differences that
 follow from the weight layout, not from the formulas: checkpoints in the
 safetensors layout pair rotary dims (i, i + hd/2) (the reference's ``neox``
 branch, ops/rope.go:21-25), and the llama3 frequency scaling is not in the
