@@ -40,6 +40,8 @@ def _add_generation_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--stream", action="store_true", help="print tokens as they are produced")
     p.add_argument("--bench", action="store_true", help="print prompt tokens, output tokens, prefill ms, tok/s")
+    p.add_argument("--profile", action="store_true",
+                   help="time every kernel (CUDA events, no CUDA graphs) and print the totals; also DLGO_PROFILE=1")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--max-batch", type=int, default=64)
@@ -58,22 +60,32 @@ def _cmd_generate(a: argparse.Namespace) -> int:
     if a.ctx < 0 or a.max_tokens <= 0 or a.temp < 0:
         print("error: --ctx must be >= 0, --max-tokens > 0 and --temp >= 0", file=sys.stderr)
         return 2
-    llm = load_llm(a.model, a.ctx, dtype=a.dtype, device=a.device, max_batch=a.max_batch)
+    import os
+    profile = a.profile or os.environ.get("DLGO_PROFILE", "") not in ("", "0")
+    llm = load_llm(a.model, a.ctx, dtype=a.dtype, device=a.device, max_batch=a.max_batch, cuda_graphs=not profile)
     print(f"Model: {llm.model_info()}", file=sys.stderr)
+    if profile:
+        from .csrc import kernels
+        kernels.profile_start()
     opts = dict(max_tokens=a.max_tokens, temperature=a.temp, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p,
                 repetition_penalty=a.repetition_penalty, seed=a.seed, greedy=a.greedy,
                 stop_token_ids=_parse_ids(a.stop_token_ids), ignore_eos=a.ignore_eos)
     if a.stream:
         llm.generate_stream(prompts, lambda r, t: print(f"{r}\t{t}", flush=True), **opts)
-        return 0
-    if a.bench:
+    elif a.bench:
         res = llm.benchmark(prompts, **opts)
         for out in res.tokens:
             print(" ".join(str(t) for t in out))
         print(f"{res} | prompt tokens: {res.prompt_tokens}", file=sys.stderr)
-        return 0
-    for out in llm.generate(prompts, **opts):
-        print(" ".join(str(t) for t in out))
+    else:
+        for out in llm.generate(prompts, **opts):
+            print(" ".join(str(t) for t in out))
+    if profile:
+        rows = kernels.profile_stop()
+        whole = sum(ms for _, _, ms in rows) or 1.0
+        print(f"{'kernel entry point':28s} {'launches':>9s} {'ms':>10s} {'share':>7s}", file=sys.stderr)
+        for name, n, ms in rows:
+            print(f"{name:28s} {n:9d} {ms:10.3f} {100 * ms / whole:6.1f}%", file=sys.stderr)
     return 0
 
 

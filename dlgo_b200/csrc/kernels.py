@@ -33,11 +33,42 @@ def dtype_code(dt: torch.dtype) -> int:
 
 LAUNCHES = 0  # kernels of this package launched (or captured into a graph) so far
 
+# Per-kernel timing a user can switch on (the reference's DLGO_PROFILE, examples/benchmark/main.go:24-28): while
+# on, a CUDA event follows every launch of this package; the time between two consecutive events is the time of
+# the later launch (kernels of one stream run in order).  Meant for runs without CUDA graphs.
+_profile_events: Optional[list] = None
+
+
+def profile_start() -> None:
+    """Begin timing every launch of this package on the current stream."""
+    global _profile_events
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    _profile_events = [("", first)]
+
+
+def profile_stop() -> List[tuple]:
+    """End the timing; returns [(entry point, launches, total ms)] sorted by time, most first."""
+    global _profile_events
+    events, _profile_events = _profile_events or [], None
+    if len(events) < 2:
+        return []
+    torch.cuda.synchronize()
+    total: dict = {}
+    for (_, before), (name, after) in zip(events, events[1:]):
+        n, ms = total.get(name, (0, 0.0))
+        total[name] = (n + 1, ms + before.elapsed_time(after))
+    return sorted(((k, n, ms) for k, (n, ms) in total.items()), key=lambda r: -r[2])
+
 
 def _check(status: int, what: str, launches: int = 1) -> None:
     global LAUNCHES
     if status == 0:
         LAUNCHES += launches
+        if _profile_events is not None and launches > 0 and not torch.cuda.is_current_stream_capturing():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            _profile_events.append((what, ev))
         return
     if status < 0:
         raise KernelError(f"{what}: refused ({_STATUS.get(status, status)})")

@@ -13,6 +13,7 @@ there is no padding that could change a result.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -83,7 +84,8 @@ class Engine:
         self.max_seq_len = self.cache.max_seq_len
         self.vocab_size = self.spec.vocab_size
         self.cuda_graphs = cuda_graphs
-        self._graphs: Dict[int, "object"] = {}
+        self._graphs: "OrderedDict[int, object]" = OrderedDict()
+        self._graph_pool = None
         self.launches_last_step = 0
 
     def _note_stand_ins(self) -> None:
@@ -103,6 +105,12 @@ class Engine:
                     notes.add(f"attention with heads of {hd} runs on the general kernels (tensor-core kernels take 64 and 128)")
         if notes:
             print("[dlgo_b200] note: " + "; ".join(sorted(notes)), file=sys.stderr, flush=True)
+
+    def graph_pool(self):
+        """The memory pool that all captured steps of this engine share."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
 
     # -------------------------------------------------------------------- slots
     def take_slot(self) -> int:

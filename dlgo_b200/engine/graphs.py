@@ -17,6 +17,12 @@ from ..csrc import kernels
 from .runtime import StepContext
 
 
+# Captured steps kept per engine, one per batch size (a batch that drains one sequence at a time asks for every
+# size once); each holds its fp32 logits [batch, vocab], so their number is bounded and the least recently used
+# goes first.  Intermediates of all captures share one memory pool: they never run at the same time.
+MAX_GRAPHS = 24
+
+
 class NotOnHost:
     """Stands where a captured step has no host-side value (slots, start positions): a replay serves
     whatever sequences the step brings, so a part must read ``ctx.seq_slot`` and ``ctx.token_pos`` on
@@ -90,7 +96,7 @@ class DecodeGraph:
         if saved is not None:
             eng.cache.state.restore(slots, saved)
         before = kernels.LAUNCHES
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, pool=eng.graph_pool()):
             self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
         self.kernels_per_replay = kernels.LAUNCHES - before
         self._exec = self.graph.raw_cuda_graph_exec()
@@ -100,7 +106,7 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = kernels.LAUNCHES
         self.greedy_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.greedy_graph):
+        with torch.cuda.graph(self.greedy_graph, pool=eng.graph_pool()):
             self.meta.copy_(self.host, non_blocking=True)      # the step's inputs out of the pinned buffer
             logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
             kernels.argmax(logits, self.ids_dev)
@@ -128,7 +134,7 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = kernels.LAUNCHES
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, pool=eng.graph_pool()):
             self.meta.copy_(self.host, non_blocking=True)
             d.copy_(self.draw_host[:d.numel()], non_blocking=True)
             logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
@@ -202,7 +208,11 @@ def graph_for(engine: Any, slots: List[int], token_ids: List[int], starts: List[
     """The captured step of this batch size, made when first asked for."""
     b = len(slots)
     g = engine._graphs.get(b)
+    if g is not None:
+        engine._graphs.move_to_end(b)
     if g is None:
+        while len(engine._graphs) >= MAX_GRAPHS:
+            engine._graphs.popitem(last=False)      # the batch size that was used longest ago
         g = DecodeGraph(engine, b)
         # the warm-up before the capture runs the step for real, on whatever the buffers hold: give it
         # this step's inputs so that it writes where this step writes anyway

@@ -344,6 +344,11 @@ def test_the_command_line_generates_what_the_python_entry_point_does(model_dirs)
     out, err = _cli("generate", d, "--prompt-ids", ids[1], "--max-tokens", "4", "--greedy", "--bench", "--ctx", "64",
                     "--dtype", "float32", "--ignore-eos")
     assert len(out.split()) == 4 and "tok/s" in err and "prompt tokens: 3" in err
+    # per-kernel timing a user can switch on (the reference's DLGO_PROFILE): same tokens, a table on stderr
+    out2, err = _cli("generate", d, "--prompt-ids", ids[1], "--max-tokens", "4", "--greedy", "--profile", "--dtype",
+                     "float32", "--ignore-eos")
+    assert out2.split() == out.split()
+    assert "kernel entry point" in err and "gemm_simt" in err and "rmsnorm" in err
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
