@@ -170,33 +170,38 @@ def decode_run(llm, batch, steps, warmup, sample_clocks=False):
                 clocks=clocks, mean_context=sum(lens) / len(lens) - steps / 2)
 
 
-def prefill_run(llm, n_tokens, reps=5):
+def prefill_run(llm, n_tokens, reps=5, lens=None):
+    """Median time (ms) of one prompt step: one prompt of `n_tokens`, or, with `lens`, a packed batch of
+    prompts of those lengths (what generate() runs first)."""
     import torch
     eng = llm.engine
     g = torch.Generator().manual_seed(11)
     times = []
+    lens = list(lens) if lens else [n_tokens]
     for r in range(reps + 2):
-        toks = torch.randint(0, MODEL["vocab_size"], (n_tokens,), generator=g).tolist()
-        s = eng.take_slot()
+        toks = [torch.randint(0, MODEL["vocab_size"], (n,), generator=g).tolist() for n in lens]
+        slots = [eng.take_slot() for _ in lens]
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        eng.step([s], [toks])
+        eng.step(slots, toks)
         end.record()
         torch.cuda.synchronize()
-        eng.free_slot(s)
+        for s in slots:
+            eng.free_slot(s)
         if r >= 2:
             times.append(start.elapsed_time(end))
     return statistics.median(times)
 
 
-def prefill_flops(n_tokens):
+def prefill_flops(n_tokens, lens=None):
     m = MODEL
     d, f, hq, hkv, hd, L = (m["hidden_size"], m["intermediate_size"], m["num_attention_heads"],
                             m["num_key_value_heads"], m["head_dim"], m["num_hidden_layers"])
+    lens = list(lens) if lens else [n_tokens]
     per_token = 2 * d * (hq * hd + 2 * hkv * hd) + 2 * hq * hd * d + 2 * d * 2 * f + 2 * f * d
-    gemm = n_tokens * per_token * L + 2 * d * m["vocab_size"]      # the head runs for the last row only
-    attn = L * hq * hd * 2 * 2 * (n_tokens * (n_tokens + 1) // 2)  # causal QK^T and PV
+    gemm = sum(lens) * per_token * L + len(lens) * 2 * d * m["vocab_size"]   # the head runs for each prompt's last row
+    attn = sum(L * hq * hd * 2 * 2 * (n * (n + 1) // 2) for n in lens)       # causal QK^T and PV
     return gemm + attn
 
 
@@ -313,6 +318,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length instead of uniform[128,1024]")
     ap.add_argument("--prompt-range", default="", help="LO,HI: prompt lengths uniform in [LO, HI] (default 128,1024)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the cache is sized for")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
+    ap.add_argument("--prefill-batch", type=int, default=0,
+                    help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
     ap.add_argument("--only", choices=["decode", "prefill", "phases"],
                     help="run one small workload (for profiling) and stop; phases: see phase_stamps()")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
@@ -362,8 +370,13 @@ def main() -> int:
                           "hbm_frac": round(gbs / pk["hbm_gbs"], 4), "peaks": pk["source"]}))
         return 0
     if a.only == "prefill":
-        ms = prefill_run(llm, PREFILL_TOKENS, reps=max(1, a.steps))
-        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(ms, 3)}))
+        lens = [len(p) for p in prompts_for(a.prefill_batch)] if a.prefill_batch > 0 else [a.prefill_tokens]
+        ms = prefill_run(llm, a.prefill_tokens, reps=max(1, a.steps), lens=lens)
+        fl = prefill_flops(a.prefill_tokens, lens)
+        print(json.dumps({"only": "prefill", "shape": a.shape, "layers": a.layers, "prompts": len(lens),
+                          "tokens": sum(lens), "ms": round(ms, 3), "tok_s": round(sum(lens) / (ms / 1e3), 1),
+                          "tflops": round(fl / (ms / 1e3) / 1e12, 1),
+                          "frac_of_burst": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "peaks": pk["source"]}))
         return 0
     main_run = decode_run(llm, a.batch, a.steps, warmup, sample_clocks=True)
     points = {}

@@ -713,6 +713,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int tiles_a = (p.Ra + 2 * TILE_M - 1) / (2 * TILE_M), tiles_b = (p.Rb + BN - 1) / BN;
   const int n_tiles = tiles_a * tiles_b;
   const int nkb = (p.K + TILE_K - 1) / TILE_K;
+  // K-slices (add-reduce epilogue only: every slice adds its tile into the target by TMA): unit u is tile
+  // u % n_tiles, K blocks [(u / n_tiles) * kper, ...)
+  const int ksplits = p.splits > 1 ? p.splits : 1;
+  const int kper = (nkb + ksplits - 1) / ksplits;
+  const int n_units = n_tiles * ksplits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -742,11 +747,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (elect_one()) {
       pdl_wait();
       int it = 0;
-      for (int t = pair; t < n_tiles; t += n_pairs) {
+      for (int u = pair; u < n_units; u += n_pairs) {
+        const int t = u % n_tiles;
         const int tile_a = t % tiles_a, tile_b = t / tiles_a;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int kb0 = (u / n_tiles) * kper, kb1 = min(nkb, kb0 + kper);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
-          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { t = n_tiles; break; }
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { u = n_units; break; }
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           // the leader's barrier counts the bytes of both CTAs' loads
           const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
@@ -760,13 +767,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (rank == 0 && elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(2 * TILE_M, BN);
       int it = 0, local = 0;
-      for (int t = pair; t < n_tiles; t += n_pairs, ++local) {
+      for (int u = pair; u < n_units; u += n_pairs, ++local) {
         const int buf = local & 1;
         if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
         bool ok = true;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int kb0 = (u / n_tiles) * kper, kb1 = min(nkb, kb0 + kper);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
@@ -775,7 +783,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < TILE_K / UMMA_K; ++k)
-            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb0) || (k != 0));
           umma_commit_pair(&empty[s]);     // both CTAs may refill the stage
         }
         umma_commit_pair(&acc_full[buf]);  // both CTAs' epilogues may read the accumulator
@@ -789,7 +797,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     pdl_wait();
     constexpr int NV = 32;
     int local = 0, chunk = 0;
-    for (int t = pair; t < n_tiles; t += n_pairs, ++local) {
+    for (int u = pair; u < n_units; u += n_pairs, ++local) {
+      const int t = u % n_tiles;
       const int tile_a = t % tiles_a, tile_b = t / tiles_a;
       const int buf = local & 1;
       const int row0 = tile_a * 2 * TILE_M + (int)rank * TILE_M;
@@ -979,11 +988,24 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
   }
   const int tiles = ((p.Ra + 2 * TILE_M - 1) / (2 * TILE_M)) * ((p.Rb + BN - 1) / BN);
   int pairs = sms / 2;
-  if (tiles < pairs) pairs = tiles;
   TcParams q = p;
   q.stages = STAGES;
   CUtensorMap mo = ma;
   q.staged = (getenv("DLGO_TC_DIRECT_EPILOGUE") == nullptr && make_out_map(&mo, q) == DLGO_OK) ? 1 : 0;
+  // Fewer tiles than CTA pairs (prompts of a few hundred tokens against a long K): a product whose epilogue
+  // adds into its target by TMA reduction is cut into K-slices, so that every pair works; each slice adds its
+  // own tile.  Slices of at least 8 K blocks.
+  q.splits = 1;
+  if (q.staged && p.epilogue == TC_ADD_F32 && tiles < pairs) {
+    const int kblocks = (p.K + TILE_K - 1) / TILE_K;
+    int ks = pairs / tiles;
+    if (ks > kblocks / 8) ks = kblocks / 8;
+    if (ks > 1) {
+      const int per = (kblocks + ks - 1) / ks;
+      q.splits = (kblocks + per - 1) / per;      // no empty slices
+    }
+  }
+  if (tiles * q.splits < pairs) pairs = tiles * q.splits;
   launch_kernel_cluster(gemm_tc_pair_kernel<BN>, dim3(2 * pairs), dim3(TC_THREADS), SMEM, stream, dim3(2, 1, 1), ma, mb,
                         mo, q);
   return launch_status();
