@@ -221,7 +221,7 @@ def plain_cpu_baseline() -> dict:
     import torch
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import plain_llama as P
-    from tiny_configs import TINY, random_tokens, write_tiny
+    from tiny_configs import random_tokens, write_tiny
     out = {"impl": "plain-cpu", "threads": torch.get_num_threads()}
     for name, lens, n_new in (("A", (5, 17, 32), 16), ("B", (1, 9, 70, 130), 24)):
         with tempfile.TemporaryDirectory() as tmp:

@@ -13,7 +13,7 @@ No size stands in code: every number a part is built with comes from here.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass, asdict
 from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 from .registry import ConfigError, register_architecture

@@ -14,7 +14,7 @@ there is no padding that could change a result.
 from __future__ import annotations
 
 from collections import OrderedDict
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 
@@ -24,7 +24,7 @@ from ..config.registry import load_config
 from ..weights.loader import DictSource, WeightSource
 from .graphs import decode_with_graph, greedy_with_graph, sampled_with_graph
 from .model import CausalLM
-from .runtime import Runtime, StepContext, build_context
+from .runtime import Runtime, build_context
 
 
 class StepError(ValueError):

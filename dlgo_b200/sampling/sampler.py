@@ -15,8 +15,8 @@ not depend on which other requests share its batch.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, replace
-from typing import List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Optional, Sequence
 
 import torch
 

@@ -15,7 +15,7 @@ import mmap
 import os
 import struct
 from dataclasses import dataclass
-from typing import Dict, Iterable, Iterator, List, Mapping, Tuple
+from typing import Dict, Iterable, List, Mapping, Tuple
 
 import torch
 
