@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "hoststep": ["hoststep.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "decode_layers": ["decode_layers.cu"],
+    "prompt_layers": ["prompt_layers.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 

@@ -748,3 +748,70 @@ def decode_layers(desc: torch.Tensor, n_layers: int, residual: torch.Tensor, hid
         _ptr(tickets), _ptr(page_table), _i(page_table.shape[1]), _ptr(seq_slot), _ptr(token_pos), _ptr(cos), _ptr(sin),
         _i(page_size), _i(n_splits), _i(0), _ptr(sync), _i(1 if first else 0), _stream())
     _check(st, "decode_layers")
+
+
+# ------------------------------------------------------------------ the layer loop of a prompt step, native
+class PromptEntryPoints(ctypes.Structure):
+    _fields_ = [(n, _p) for n in ("rmsnorm", "gemm_tc", "rope_append", "attention")]
+
+
+class PromptShape(ctypes.Structure):
+    _fields_ = [(n, _i) for n in ("hidden", "heads", "kv_heads", "head_dim", "ffn", "rotary_dim", "interleaved",
+                                  "window", "page_size")] + [("scale", _f)]
+
+
+class PromptLayer(ctypes.Structure):
+    _fields_ = [("w_qkv", _p), ("w_o", _p), ("w_gate_up", _p), ("w_down", _p), ("norm1_w", _p), ("norm2_w", _p),
+                ("eps1", _f), ("eps2", _f), ("kpages", _p), ("vpages", _p), ("n_pages", _i), ("write_cache", _i)]
+
+
+class PromptStep(ctypes.Structure):
+    _fields_ = [("tokens", _i), ("residual", _p), ("x", _p), ("qkv", _p), ("attn_out", _p), ("h", _p), ("cos_t", _p),
+                ("sin_t", _p), ("token_pos", _p), ("token_seq", _p), ("seq_slot", _p), ("page_table", _p),
+                ("max_pages", _i), ("tiles", _p), ("n_tiles", _i), ("bn", _i * 4), ("pair", _i * 4)]
+
+
+PROMPT_CALLS = ("mixer norm", "q/k/v projection", "rotation and cache append", "attention", "output projection",
+                "feed-forward norm", "gate/up projection", "down projection")
+
+
+def prompt_entry_points() -> PromptEntryPoints:
+    """Addresses of the entry points that the native layer loop calls (their libraries are loaded, and
+    compiled first if need be)."""
+    def address(lib: str, fn: str) -> int:
+        return ctypes.cast(getattr(_lib(lib), fn), ctypes.c_void_p).value
+    return PromptEntryPoints(address("elementwise", "dlgo_rmsnorm"), address("gemm_tc", "dlgo_gemm_tc"),
+                             address("rope_append", "dlgo_rope_append"),
+                             address("attention_prefill_tc", "dlgo_attention_prefill_tc"))
+
+
+def prompt_layers_describe(layers: Sequence[dict]) -> tuple:
+    """The host-side descriptor array of a run of layers: (ctypes array, the tensors it points at, which the
+    caller keeps alive with it).  Each entry gives ``w_qkv, w_o, w_gate_up, w_down`` (bfloat16, contiguous),
+    ``norm1_w, norm2_w`` (float32), ``kpages, vpages`` (bfloat16) and ``eps1, eps2, write_cache``."""
+    arr = (PromptLayer * len(layers))()
+    keep = []
+    for i, L in enumerate(layers):
+        for n in ("w_qkv", "w_o", "w_gate_up", "w_down", "kpages", "vpages"):
+            _need(L[n], torch.bfloat16, n)
+        for n in ("norm1_w", "norm2_w"):
+            _need(L[n], torch.float32, n)
+        a = arr[i]
+        for n in ("w_qkv", "w_o", "w_gate_up", "w_down", "norm1_w", "norm2_w", "kpages", "vpages"):
+            setattr(a, n, L[n].data_ptr())
+            keep.append(L[n])
+        a.eps1, a.eps2 = L["eps1"], L["eps2"]
+        a.n_pages, a.write_cache = L["kpages"].shape[0], 1 if L["write_cache"] else 0
+    return arr, keep
+
+
+def prompt_layers(entry: PromptEntryPoints, shape: PromptShape, layers: ctypes.Array, step: PromptStep) -> None:
+    """Run ``len(layers)`` pre-norm layers of a prompt step: eight launches a layer, issued from one native loop
+    (csrc/prompt_layers.cu).  The caller has checked types and sizes of what ``step`` points at."""
+    failed = _i(-1)
+    n = len(layers)
+    st = _lib("prompt_layers").dlgo_prompt_layers(ctypes.byref(entry), ctypes.byref(shape), layers, _i(n),
+                                                  ctypes.byref(step), ctypes.byref(failed), _stream())
+    if st != 0 and failed.value >= 0:
+        _check(st, f"prompt_layers (layer {failed.value // 8} of the run, {PROMPT_CALLS[failed.value % 8]})")
+    _check(st, "prompt_layers", 8 * n)

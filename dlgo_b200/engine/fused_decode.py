@@ -21,6 +21,7 @@ separate kernels' prologues run under their predecessors' tails.
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -62,7 +63,7 @@ class FusedRun:
     def __init__(self, first: int, entries: List[int], sig: tuple):
         self.first, self.entries, self.sig = first, entries, sig
         self.n = len(entries)
-        self._desc: Dict[int, torch.Tensor] = {}      # per cache (its pages are part of the descriptors)
+        self._desc: Dict[int, tuple] = {}      # per cache (its pages are part of the descriptors)
 
     def takes(self, ctx: Any, cache: Any) -> bool:
         d, hq, hkv, hd, f = self.sig[:5]
@@ -72,6 +73,8 @@ class FusedRun:
 
     def _descriptors(self, model: Any, cache: Any, device: torch.device) -> torch.Tensor:
         hit = self._desc.get(id(cache))
+        if hit is not None and hit[0]() is not cache:
+            hit = None                          # another cache at a recycled address
         if hit is None:
             d, hq, hkv, hd, f = self.sig[:5]
             layers = []
@@ -83,8 +86,8 @@ class FusedRun:
                     w_down=blk.ffn.w_down.weight, norm1_w=blk.mixer_norm.weight, norm2_w=blk.ffn_norm.weight,
                     eps1=blk.mixer_norm.eps, eps2=blk.ffn_norm.eps, kpages=view.keys, vpages=view.values,
                     write_cache=view.writes))
-            hit = self._desc[id(cache)] = K.decode_layers_describe(layers, d, hq, hkv, hd, f, device)
-        return hit
+            hit = self._desc[id(cache)] = (weakref.ref(cache), K.decode_layers_describe(layers, d, hq, hkv, hd, f, device))
+        return hit[1]
 
     def run(self, model: Any, residual: torch.Tensor, ctx: Any, cache: Any) -> None:
         d, hq, hkv, hd, f, scale, pe_name, _ = self.sig

@@ -43,6 +43,7 @@ class CausalLM:
                     raise ValueError(f"run entry {i} cannot read the cache of entry {e.cache_of}: their shapes differ")
         self.runtime: Any = None
         self.fused_runs: Dict[int, Any] = {}
+        self.prompt_runs: Dict[int, Any] = {}
 
     # ------------------------------------------------------------ declarations
     def _named_parts(self) -> List[Tuple[str, Part]]:
@@ -100,8 +101,9 @@ class CausalLM:
         for pe in self.positions.values():
             pe.prepare(runtime)
         runtime.forget_copies()
-        from .fused_decode import plan_runs
-        self.fused_runs = plan_runs(self, runtime)
+        from . import fused_decode, prompt_run
+        self.fused_runs = fused_decode.plan_runs(self, runtime)
+        self.prompt_runs = prompt_run.plan_runs(self, runtime)
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: Any, cache: Any, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -109,9 +111,10 @@ class CausalLM:
         residual = self.embedding.forward(ctx.token_ids)
         i = 0
         while i < len(self.order):
-            run = self.fused_runs.get(i) if ctx.decode else None
+            run = (self.fused_runs if ctx.decode else self.prompt_runs).get(i)
             if run is not None and run.takes(ctx, cache):
-                # a run of like blocks on a decode step: one persistent kernel instead of eight a layer
+                # a run of like blocks: one persistent kernel on a decode step (where that is switched on), one
+                # native loop over the layers' launches on a prompt step
                 ctx.settle(residual)
                 run.run(self, residual, ctx, cache)
                 i += run.n

@@ -118,11 +118,16 @@ class TensorCorePlan:
                 ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
                 cnt = _counter_buffer(x.device)
             return K.gemm_tc(self.weight, x, out, True, epi, bn, splits, ws, cnt, static_operand=1)
+        bn, pair = self.many_token_shape(t)
+        return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
+
+    def many_token_shape(self, tokens: int) -> tuple[int, int]:
+        """(tile width, CTA-pair tile or 0) for more than SKINNY_MAX tokens: the activations are the M operand."""
         bn = 256 if self.n > 128 else 128
         if PREFILL_BN in (128, 256):
             bn = PREFILL_BN
-        pair = PAIR_TILE if (t > 128 and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
-        return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
+        pair = PAIR_TILE if (tokens > 128 and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
+        return bn, pair
 
     def sums_slices_at_memory(self, tokens: int) -> bool:
         if ORDERED_SUMS or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):

@@ -125,6 +125,57 @@ def test_llama_1b_sizes_against_the_plain_implementation(big, dtype):
         run(eng2, reqs, refs, dtype, "no graphs")
 
 
+def test_prompt_steps_run_through_the_native_layer_loop_and_match_the_parts(big, monkeypatch):
+    """A bfloat16 prompt step of more than 64 tokens hands its run of like layers to one native call, which
+    launches what the parts launch one by one, with the same arguments: with the epilogue that adds a tile into
+    the residual in one piece (no K-slices, whose order is not fixed) the logits are the same bit for bit.  A
+    prompt on top of a cache that is not empty goes the same way."""
+    from dlgo_b200.csrc import kernels
+    from dlgo_b200.engine import prompt_run
+    from dlgo_b200.engine.engine import Engine
+    d, reqs, refs = big
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in (300, 77, 129)]
+    more = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in (90, 70, 101)]
+    calls = []
+    real = kernels.prompt_layers
+    monkeypatch.setattr(kernels, "prompt_layers", lambda e, sh, layers, step: (calls.append((len(layers), step.tokens)),
+                                                                                 real(e, sh, layers, step))[1])
+
+    def logits(eng):
+        slots = [eng.take_slot() for _ in prompts]
+        a = eng.step(slots, prompts, [[len(p) - 1, 0, len(p) // 2] for p in prompts]).float().cpu()
+        b = eng.step(slots, more, [[len(p) - 1] for p in more]).float().cpu()
+        for s in slots:
+            eng.free_slot(s)
+        return torch.cat([a, b])
+
+    eng = Engine(d, dtype="bfloat16", max_tokens=2048, max_seq_len=512)
+    runs = eng.model.prompt_runs
+    assert len(runs) == 1 and runs[0].n == CFG["num_hidden_layers"]
+    for direct in ("1", None):
+        if direct:
+            monkeypatch.setenv("DLGO_TC_DIRECT_EPILOGUE", direct)     # read at every call
+        else:
+            monkeypatch.delenv("DLGO_TC_DIRECT_EPILOGUE")
+        del calls[:]
+        monkeypatch.setattr(eng.model, "prompt_runs", runs)
+        got = logits(eng)
+        assert calls == [(CFG["num_hidden_layers"], 506), (CFG["num_hidden_layers"], 261)]
+        monkeypatch.setattr(eng.model, "prompt_runs", {})
+        want = logits(eng)
+        assert len(calls) == 2
+        if direct:
+            assert torch.equal(got, want)
+        else:
+            # K-slices add themselves into the residual in no fixed order: bfloat16 rounding apart
+            assert float((got - want).abs().max()) <= 3e-2 * float(want.abs().max())
+    kernels.check_device_errors()
+    # float32 has no native loop: the parts run
+    eng32 = Engine(d, dtype="float32", max_tokens=512, max_seq_len=256)
+    assert eng32.model.prompt_runs == {} and prompt_run.ENABLED
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_llama_8b_layer_sizes_against_the_plain_implementation(big8, dtype):
     from dlgo_b200.engine.engine import Engine
