@@ -84,7 +84,7 @@ class Engine:
         self.max_seq_len = self.cache.max_seq_len
         self.vocab_size = self.spec.vocab_size
         self.cuda_graphs = cuda_graphs
-        self._graphs: "OrderedDict[int, object]" = OrderedDict()
+        self._graphs: "OrderedDict[tuple, object]" = OrderedDict()    # (batch size, reach) -> captured step
         self._graph_pool = None
         self.launches_last_step = 0
 

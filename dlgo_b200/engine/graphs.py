@@ -2,14 +2,15 @@
 
 A decode step is a hundred-odd small launches; at one token per sequence the
 GPU work of each is a few microseconds, so the launches themselves bound the
-step.  One graph per batch size replays the whole step from persistent input
-buffers (token ids, positions, slots).  Nothing inside the graph may depend on
-the sequences' lengths through the host: grids are sized from the cache's
-capacity and every kernel reads lengths and pages from device memory.
+step.  One graph per batch size and reach replays the whole step from persistent
+input buffers (token ids, positions, slots).  Nothing inside the graph may depend
+on the sequences' lengths through the host: grids are sized for the graph's reach
+(the longest sequence it is asked to serve: 4,096 positions, 16,384, ... up to the
+cache's capacity) and every kernel reads lengths and pages from device memory.
 """
 from __future__ import annotations
 
-from typing import Any, List, Sequence
+from typing import Any, List, Optional, Sequence
 
 import torch
 
@@ -17,10 +18,22 @@ from ..csrc import kernels
 from .runtime import StepContext
 
 
-# Captured steps kept per engine, one per batch size (a batch that drains one sequence at a time asks for every
-# size once); each holds its fp32 logits [batch, vocab], so their number is bounded and the least recently used
+# Captured steps kept per engine, one per batch size and reach (a batch that drains one sequence at a time asks
+# for every size once); each holds its fp32 logits [batch, vocab], so their number is bounded and the least recently used
 # goes first.  Intermediates of all captures share one memory pool: they never run at the same time.
 MAX_GRAPHS = 24
+FIRST_REACH = 4096
+
+
+def reach_bucket(reach: int, max_seq_len: int) -> int:
+    """The reach a captured step is sized for when its longest sequence ends at ``reach`` positions: 4,096,
+    16,384, 65,536, ... but no more than the cache holds per sequence.  A context limit of 131,072 would
+    otherwise size every step for 2,048 pages a sequence, and a sequence of a few hundred tokens would be
+    cut into dozens of mostly empty slices that meet again through scratch memory and a second kernel."""
+    b = FIRST_REACH
+    while b < reach and b < max_seq_len:
+        b *= 4
+    return min(b, max_seq_len)
 
 
 class NotOnHost:
@@ -39,10 +52,11 @@ class NotOnHost:
 
 
 class DecodeGraph:
-    def __init__(self, engine: Any, batch: int):
+    def __init__(self, engine: Any, batch: int, reach: int):
         rt = engine.runtime
         dev = rt.device
         self.batch = batch
+        self.reach = reach
         self.meta = torch.zeros((3, batch), dtype=torch.int32, device=dev)   # ids, positions, slots
         self.host = torch.zeros((3, batch), dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()     # a view: the step's inputs are written here without tensor construction
@@ -52,8 +66,8 @@ class DecodeGraph:
             runtime=rt, n_tokens=batch, n_seqs=batch, token_ids=self.meta[0], token_pos=self.meta[1],
             token_seq=self.token_seq, seq_slot=self.meta[2], seq_slots_host=NotOnHost("a sequence's slot"),
             seq_start_host=NotOnHost("a sequence's start position"),
-            seq_ntok_host=[1] * batch, decode=True, max_len=engine.max_seq_len, captured=True,
-            capacity=engine.max_seq_len, want_identity=True)
+            seq_ntok_host=[1] * batch, decode=True, max_len=reach, captured=True,
+            capacity=reach, want_identity=True)
         # one token per sequence: the tile table is the same for every replay (built before capture: a
         # capture may not copy from pageable host memory)
         self.ctx._tiles[(1, False)] = (torch.stack([self.token_seq, self.token_seq, torch.ones_like(self.token_seq)],
@@ -161,7 +175,7 @@ def greedy_with_graph(engine: Any, slots: List[int], token_ids: List[int], start
     """Up to ``n_steps`` greedy decode steps through the graph of this batch size in one native call;
     the ids chosen, a list per step (fewer than ``n_steps`` if a sequence chose a stop id)."""
     b = len(slots)
-    g = graph_for(engine, slots, token_ids, starts)
+    g = graph_for(engine, slots, token_ids, starts, max(starts) + n_steps)
     if g.greedy_exec is None:
         g.capture_greedy()
     g._native.wait()
@@ -181,7 +195,7 @@ def sampled_with_graph(engine: Any, slots: List[int], token_ids: List[int], star
     ``recents[i]`` are its latest tokens, oldest first, for the repetition penalty."""
     from ..sampling.sampler import RECENT_WINDOW
     b, w = len(slots), RECENT_WINDOW
-    g = graph_for(engine, slots, token_ids, starts)
+    g = graph_for(engine, slots, token_ids, starts, max(starts) + n_steps)
     graph_exec, n_kernels = g.capture_sampled(cfg)
     g._native.wait()
     h = g.host_np
@@ -204,16 +218,19 @@ def sampled_with_graph(engine: Any, slots: List[int], token_ids: List[int], star
                                      g._dev_index, n_kernels)
 
 
-def graph_for(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> DecodeGraph:
-    """The captured step of this batch size, made when first asked for."""
+def graph_for(engine: Any, slots: List[int], token_ids: List[int], starts: List[int],
+              reach: Optional[int] = None) -> DecodeGraph:
+    """The captured step of this batch size whose grids cover sequences of up to ``reach`` positions (default:
+    the longest sequence after one step), made when first asked for."""
     b = len(slots)
-    g = engine._graphs.get(b)
+    key = (b, reach_bucket(max(starts) + 1 if reach is None else reach, engine.max_seq_len))
+    g = engine._graphs.get(key)
     if g is not None:
-        engine._graphs.move_to_end(b)
+        engine._graphs.move_to_end(key)
     if g is None:
         while len(engine._graphs) >= MAX_GRAPHS:
-            engine._graphs.popitem(last=False)      # the batch size that was used longest ago
-        g = DecodeGraph(engine, b)
+            engine._graphs.popitem(last=False)      # the one that was used longest ago
+        g = DecodeGraph(engine, b, key[1])
         # the warm-up before the capture runs the step for real, on whatever the buffers hold: give it
         # this step's inputs so that it writes where this step writes anyway
         g.host_np[0, :] = token_ids
@@ -221,14 +238,16 @@ def graph_for(engine: Any, slots: List[int], token_ids: List[int], starts: List[
         g.host_np[2, :] = slots
         g.meta.copy_(g.host)
         g.capture()
-        engine._graphs[b] = g
+        engine._graphs[key] = g
     return g
 
 
-def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int]) -> torch.Tensor:
-    """Logits [batch, vocab] of one decode step, through the graph of this batch size.
+def decode_with_graph(engine: Any, slots: List[int], token_ids: List[int], starts: List[int],
+                      reach: Optional[int] = None) -> torch.Tensor:
+    """Logits [batch, vocab] of one decode step, through the graph of this batch size (and ``reach``, see
+    :func:`graph_for`).
 
     The returned tensor is the graph's output buffer: it is overwritten by the next
     decode step of the same batch size.
     """
-    return graph_for(engine, slots, token_ids, starts).run(slots, token_ids, starts)
+    return graph_for(engine, slots, token_ids, starts, reach).run(slots, token_ids, starts)

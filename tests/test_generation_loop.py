@@ -241,3 +241,13 @@ def test_several_greedy_steps_in_one_backend_call_change_no_decision():
     be = MultiStepBackend(max_seq_len=8, script=script)
     res = GenerationLoop(be).run([[1, 2, 3]], GenerateConfig(max_tokens=50, sampler=GREEDY, seed=0))
     assert len(res.tokens[0]) == 5 and be.multi_calls[0]["n"] == 4
+
+
+def test_captured_steps_are_sized_for_a_reach_not_for_the_whole_context():
+    from dlgo_b200.engine.graphs import reach_bucket
+    assert reach_bucket(1, 131072) == 4096 and reach_bucket(4096, 131072) == 4096
+    assert reach_bucket(4097, 131072) == 16384 and reach_bucket(70000, 131072) == 131072
+    assert reach_bucket(131072, 131072) == 131072
+    # a cache that holds less than the first reach: one size, the cache's
+    assert reach_bucket(10, 1024) == 1024 and reach_bucket(1024, 1024) == 1024
+    assert reach_bucket(5000, 6000) == 6000

@@ -265,11 +265,11 @@ def test_a_batch_of_eight_unequal_sequences_decodes_through_the_graph(batch8, dt
     eng = Engine(d, dtype=dtype, max_tokens=8 * 1024, max_seq_len=1024)      # grids sized for 16 pages a sequence
     eng.cache.poison()
     outs = T.run_in_process(eng, batch_steps(reqs))
-    assert 8 in eng._graphs, "the decode steps should have replayed the graph of batch 8"
+    assert (8, 1024) in eng._graphs, "the decode steps should have replayed the graph of batch 8"
     assert bool(eng.model.fused_runs) == fused
     if fused:
         # both layers as one persistent kernel: embedding, that kernel, final norm, head
-        assert eng._graphs[8].kernels_per_replay <= 6, eng._graphs[8].kernels_per_replay
+        assert eng._graphs[(8, 1024)].kernels_per_replay <= 6, eng._graphs[(8, 1024)].kernels_per_replay
     tol = 1e-4 if dtype == "float32" else 3e-2
     for i, rid in enumerate(reqs):
         ref = refs[rid]
@@ -311,8 +311,11 @@ def test_ordered_sums_make_bfloat16_decoding_repeatable_bit_for_bit(batch8, monk
 
 
 def test_default_cache_sizing_and_a_very_long_capacity(batch8):
-    # no max_tokens: the cache is sized from the context (131072 positions here), so a captured step's grids
-    # cover 2048 pages a sequence and decode attention takes its many-slices path
+    # no max_tokens: the cache is sized from the context (131072 positions here).  Captured steps are sized for
+    # the reach they are asked for: these short sequences replay the graph for 4,096 positions; the same step
+    # through the graph for the whole context (2048 pages a sequence: decode attention takes its many-slices
+    # path through scratch memory) gives the same logits
+    from dlgo_b200.engine import graphs
     from dlgo_b200.engine.engine import Engine
     d, reqs, refs = batch8
     eng = Engine(d, dtype="bfloat16")
@@ -323,12 +326,19 @@ def test_default_cache_sizing_and_a_very_long_capacity(batch8):
     lg = [eng.step(slots, [reqs[r][:n] for r, n in zip(ids, lens)]).float().cpu()]
     for j in range(3):
         lg.append(eng.step(slots, [[reqs[r][n + j]] for r, n in zip(ids, lens)]).float().cpu().clone())
+    assert list(eng._graphs) == [(3, 4096)]
+    # the last of these steps once more, through the graph that reaches the whole context (it writes the same
+    # keys and values to the same places)
+    far = graphs.decode_with_graph(eng, slots, [reqs[r][n + 2] for r, n in zip(ids, lens)], [n + 2 for n in lens],
+                                   reach=eng.max_seq_len).float().cpu()
+    assert list(eng._graphs) == [(3, 4096), (3, 131072)]
     for s in slots:
         eng.free_slot(s)
     for i, rid in enumerate(ids):
         scale = float(refs[rid].abs().max())
         for s in range(4):
             assert float((lg[s][i] - refs[rid][s]).abs().max()) <= 3e-2 * scale, (rid, s)
+        assert float((far[i] - refs[rid][3]).abs().max()) <= 3e-2 * scale, rid
     # this engine's cache took half of the device's free memory: hand it back now, so that later tests do not
     # find the allocator releasing cached blocks in the middle of a graph capture
     del eng
