@@ -213,6 +213,20 @@ def e2e_run(llm, batch, steps):
     return batch * steps / (res.generate_ms / 1e3)
 
 
+def sampled_run(llm, batch, steps) -> dict:
+    """Decode tokens a second through the public entry point (host ids in and out, the prompts' step not
+    counted) for greedy choice, the reference's default sampler (temperature 0.7, top-k 40, top-p 0.9,
+    repetition penalty 1.1: ops/sampling.go:19-27), and temperature alone."""
+    prompts = prompts_for(batch)
+    out = {"only": "sampled", "batch": batch, "steps": steps}
+    for name, opts in (("greedy", dict(greedy=True)), ("default_sampler", dict(seed=1)),
+                       ("temperature_only", dict(seed=1, temperature=0.7, top_k=0, top_p=1.0, repetition_penalty=1.0))):
+        llm.generate(prompts, max_tokens=4, ignore_eos=True, **opts)          # warm-up (graphs, pages)
+        res = llm.generate_detailed(prompts, max_tokens=steps + 1, ignore_eos=True, **opts)
+        out[name] = round(batch * steps / (res.generate_ms / 1e3), 1)
+    return out
+
+
 def plain_cpu_baseline() -> dict:
     """The plain implementation (tests/plain_llama.py: whole sequences, no cache, float32, CPU) timed as the
     reference times itself: prefill = the prompt's forward pass, generation = the tokens after the first,
@@ -321,7 +335,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--prefill-batch", type=int, default=0,
                     help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
-    ap.add_argument("--only", choices=["decode", "prefill", "phases"],
+    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled"],
                     help="run one small workload (for profiling) and stop; phases: see phase_stamps()")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
@@ -368,6 +382,9 @@ def main() -> int:
                           "mean_context": round(r["mean_context"], 1), "ms_per_step": round(r["ms_per_step"], 4),
                           "tok_s": round(r["tok_s"], 1), "launches": r["launches"], "hbm_gbs": round(gbs, 1),
                           "hbm_frac": round(gbs / pk["hbm_gbs"], 4), "peaks": pk["source"]}))
+        return 0
+    if a.only == "sampled":
+        print(json.dumps(sampled_run(llm, a.batch, a.steps)))
         return 0
     if a.only == "prefill":
         lens = [len(p) for p in prompts_for(a.prefill_batch)] if a.prefill_batch > 0 else [a.prefill_tokens]

@@ -377,10 +377,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tenso
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     if seed_dev is not None and (seed_dev.dtype != torch.int32 or seed_dev.numel() < 2 or not seed_dev.is_cuda):
         raise KernelError("sample: seed_dev must be two int32 on the GPU")
-    st = _lib("sampling").dlgo_sample(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(temperature),
-                                      _ptr(request), _ptr(draw), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
-                                      _ptr(seed_dev), _ptr(out), _stream())
-    _check(st, "sample")
+    lib = _lib("sampling")
+    chunks = int(lib.dlgo_sample_chunks(_i(V)))       # > 0: a large vocabulary, drawn from in two kernels
+    part = torch.empty((R * chunks * 2,), dtype=torch.float32, device=logits.device) if chunks > 0 else None
+    st = lib.dlgo_sample(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(temperature), _ptr(request),
+                         _ptr(draw), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(seed_dev), _ptr(out), _ptr(part),
+                         _stream())
+    _check(st, "sample", 2 if chunks > 0 else 1)
     return out
 
 
@@ -634,6 +637,48 @@ def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: f
                                       _stream())
     _check(st, "filter")
     return work
+
+
+def filter_draw_chunks(V: int, top_k: int) -> int:
+    """Chunks of the vocabulary :func:`filter_draw` works in, or 0 where it does not take the sizes (top-k off or
+    above 256, a very large vocabulary): the caller then uses :func:`filter_logits` and :func:`sample`."""
+    return int(_lib("sampling").dlgo_filter_draw_chunks(_i(V), _i(top_k)))
+
+
+def filter_draw(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, penalty: float,
+                recent: Optional[torch.Tensor], request: torch.Tensor, draw: torch.Tensor, seed: int,
+                out: Optional[torch.Tensor] = None, seed_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`filter_logits` followed by :func:`sample` for a small top-k, without a pass of one block over the
+    whole row: blocks over chunks of the vocabulary list what top-k can keep, one block per row filters and
+    draws from that list (csrc/sampling.cu)."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 [rows, vocab] on the GPU with unit stride along the vocabulary")
+    R, V = logits.shape
+    lib = _lib("sampling")
+    C = int(lib.dlgo_filter_draw_chunks(_i(V), _i(top_k)))
+    if C == 0:
+        raise KernelError(f"filter_draw does not take top_k={top_k} with a vocabulary of {V}")
+    cap = int(lib.dlgo_filter_draw_cap(_i(top_k)))
+    _need(request, torch.int32, "request")
+    _need(draw, torch.int32, "draw")
+    n_recent = 0
+    if recent is not None:
+        _need(recent, torch.int32, "recent")
+        n_recent = recent.shape[1]
+    if seed_dev is not None and (seed_dev.dtype != torch.int32 or seed_dev.numel() < 2 or not seed_dev.is_cuda):
+        raise KernelError("filter_draw: seed_dev must be two int32 on the GPU")
+    dev = logits.device
+    cand_v = torch.empty((R * C * cap,), dtype=torch.float32, device=dev)
+    cand_i = torch.empty((R * C * cap + R * C,), dtype=torch.int32, device=dev)      # indices, then counts
+    work = torch.empty((R, V), dtype=torch.float32, device=dev)      # (rows with more ties than the lists hold)
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=dev)
+    st = lib.dlgo_filter_draw(_ptr(logits), _i(R), _i(logits.stride(0)), _i(V), _ptr(work), _f(temperature), _i(top_k),
+                              _f(top_p), _f(min_p), _f(penalty), _ptr(recent), _i(n_recent), _ptr(cand_v),
+                              _ptr(cand_i), _p(cand_i.data_ptr() + 4 * R * C * cap), _ptr(request), _ptr(draw),
+                              ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(seed_dev), _ptr(out), _stream())
+    _check(st, "filter_draw", 2)
+    return out
 
 
 # ------------------------------------------------------------------ host side of a decode step

@@ -193,6 +193,19 @@ class GenerationLoop:
                                                   cfg.sampler, seed, [s.request for s in live],
                                                   [len(s.out) for s in live], [s.recent for s in live])
                         if chunk is not None:
+                            head = chunk[:-1]
+                            if len(head) > 1 and all(stops.isdisjoint(row) for row in head):
+                                # Only the run's last step can end a sequence (by a stop token, or by count:
+                                # n was chosen so).  The steps before it just append, a sequence at a time
+                                # instead of a token at a time.
+                                for s, col in zip(live, zip(*head)):
+                                    s.length += len(col)
+                                    s.out.extend(col)
+                                    s.recent = (s.recent + list(col))[-RECENT_WINDOW:]
+                                    s.last = int(col[-1])
+                                steps += len(head)
+                                feed = [[s.last] for s in live]
+                                chunk = chunk[-1:]
                             for sampled in chunk:
                                 steps += 1
                                 account(sampled)

@@ -72,6 +72,10 @@ def draw_on_device(logits: torch.Tensor, cfg: SamplerConfig, requests: torch.Ten
         if top_k > K.FILTER_MAX_K:
             raise ValueError(f"top_k up to {K.FILTER_MAX_K} (or 0 for none), got {cfg.top_k}")
         rec = recent if cfg.repetition_penalty > 1.0 else None
+        if K.filter_draw_chunks(logits.shape[1], top_k) > 0:
+            # a small top-k: only what it can keep is looked at
+            return K.filter_draw(logits, cfg.temperature, top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty, rec,
+                                 requests, draws, seed, out, seed_dev)
         work = K.filter_logits(logits, cfg.temperature, top_k, cfg.top_p, cfg.min_p, cfg.repetition_penalty, rec)
         return K.sample(work, temperature, requests, draws, seed, out, seed_dev)
     return K.sample(logits, temperature, requests, draws, seed, out, seed_dev)

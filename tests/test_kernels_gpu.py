@@ -464,7 +464,7 @@ def test_uniform_matches_the_plain_philox():
         assert got == want
 
 
-@pytest.mark.parametrize("V", [7, 384, 5000, 128256])
+@pytest.mark.parametrize("V", [7, 384, 5000, 16384, 20000, 128256])
 def test_sample_is_the_inverse_cdf_of_the_softmax(V):
     torch.manual_seed(V)
     R = 64
@@ -533,6 +533,78 @@ def test_filter_kernel_against_the_plain_filters(V, k, p, mp, pen, temp):
         both = kept_w & kept_g
         assert both.any()
         torch.testing.assert_close(got[r][both], want[both], atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("V,k,p,mp,pen,temp", [(50, 5, 0.9, 0.0, 1.1, 0.7), (1000, 40, 0.9, 0.0, 1.1, 0.7),
+                                               (777, 1, 1.0, 0.0, 2.0, 0.5), (5000, 200, 0.95, 0.01, 1.5, 1.0),
+                                               (128256, 40, 0.9, 0.02, 1.1, 0.7), (4099, 64, 1.0, 0.1, 1.0, 2.0),
+                                               (128256, 128, 0.5, 0.0, 1.0, 1.3), (20000, 3, 1.0, 0.0, 1.0, 1.0)])
+def test_filters_and_draw_from_the_top_k_candidates(V, k, p, mp, pen, temp):
+    """The fused path for a small top-k (candidates per chunk of the vocabulary, then one block per row)
+    against the plain filters and the plain inverse CDF, and against the two separate kernels."""
+    kk = K()
+    assert kk.filter_draw_chunks(V, k) == (V + 8191) // 8192
+    g = torch.Generator().manual_seed(V + k)
+    R = 6
+    lg = torch.randn(R, V, generator=g) * 3.0
+    lg[1, : min(V, 20)] = 7.5                                   # a block of ties at the top of row 1
+    lg[2, V // 2] = -float("inf")
+    recent = [torch.randint(0, V, (n,), generator=g).tolist() for n in (64, 10, 0, 33, 64, 1)]
+    recent[0][5] = recent[0][4]                                 # a repeated token counts once
+    rec = torch.tensor([(r + [-1] * 64)[:64] for r in recent], dtype=torch.int32, device=DEV)
+    pad = torch.full((R, V + 3), 99.0)                          # a row stride that is not the width
+    pad[:, :V] = lg
+    dev_lg = pad.to(DEV)[:, :V]
+    reqs = torch.tensor([0, 3, 1, 70000, 5, 2], dtype=torch.int32, device=DEV)
+    kept, cdf = [], []
+    for r in range(R):
+        want = P.filter_logits(lg[r], recent[r], pen, temp, k, p, mp)
+        kept.append(torch.isfinite(want))
+        cdf.append(torch.cumsum(torch.softmax(want.double(), dim=0), dim=0))
+    same = total = 0
+    for d in range(12):
+        draws = torch.full((R,), d, dtype=torch.int32, device=DEV)
+        got = kk.filter_draw(dev_lg, temp, k, p, mp, pen, rec, reqs, draws, 9).cpu().tolist()
+        assert got == kk.filter_draw(dev_lg, temp, k, p, mp, pen, rec, reqs, draws, 9).cpu().tolist()
+        work = kk.filter_logits(dev_lg, temp, k, p, mp, pen, rec)
+        old = kk.sample(work, torch.ones(R, device=DEV), reqs, draws, 9).cpu().tolist()
+        for r in range(R):
+            t, u = got[r], P.philox_uniform(9, d, int(reqs[r]))
+            total += 1
+            same += t == old[r]
+            if not kept[r][t]:
+                # only a value that ties with the last kept one, or a prefix that meets p within rounding
+                w = work[r].cpu()
+                assert torch.isfinite(w[t]) and abs(float(w[t] - w[torch.isfinite(w)].min())) < 1e-5, (r, d, t)
+                continue
+            lo = float(cdf[r][t - 1]) if t > 0 else 0.0
+            assert lo - 2e-5 <= u <= float(cdf[r][t]) + 2e-5, f"row {r} draw {d}: u={u} outside [{lo}, {float(cdf[r][t])}]"
+    assert same >= total - 2, (same, total)                     # (sums in another order: a draw on an edge may differ)
+
+
+def test_filters_and_draw_fall_back_when_ties_overflow_the_candidate_lists():
+    # every logit equal: top-k keeps the whole vocabulary (ties at the cutoff stay), far more than the lists
+    # hold; such a row goes through the whole-row filters and draw, the other rows do not notice
+    kk = K()
+    V, R = 128256, 3
+    lg = torch.randn(R, V, device=DEV) * 2.0
+    lg[1] = 0.25
+    reqs = torch.arange(R, dtype=torch.int32, device=DEV)
+    seen = set()
+    for d in range(6):
+        draws = torch.full((R,), d, dtype=torch.int32, device=DEV)
+        got = kk.filter_draw(lg, 0.7, 40, 0.9, 0.0, 1.0, None, reqs, draws, 3).cpu().tolist()
+        work = kk.filter_logits(lg, 0.7, 40, 0.9, 0.0, 1.0, None)
+        old = kk.sample(work, torch.ones(R, device=DEV), reqs, draws, 3).cpu().tolist()
+        assert got[1] == old[1]
+        u = P.philox_uniform(3, d, 1)
+        assert abs(got[1] - u * V) <= 2                          # uniform over the vocabulary, in index order
+        seen.add(got[1])
+        assert got[0] == old[0] and got[2] == old[2]
+    assert len(seen) == 6
+    assert kk.filter_draw_chunks(V, 0) == 0 and kk.filter_draw_chunks(V, 257) == 0 and kk.filter_draw_chunks(300, 300) == 0
+    with pytest.raises(kk.KernelError):
+        kk.filter_draw(lg, 0.7, 0, 0.9, 0.0, 1.0, None, reqs, reqs, 3)
 
 
 def test_filtered_sampling_stays_inside_the_kept_set():
