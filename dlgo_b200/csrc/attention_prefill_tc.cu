@@ -450,9 +450,8 @@ int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     // With heads of 64 three CTAs fit an SM (3 x 64 KB of shared memory, 3 x 128 columns of tensor
     // memory), with heads of 128 two: one's softmax runs beside the others' MMAs and maxima.  That
     // needs the largest carve-out.
-    if (getenv("DLGO_PF_NO_CARVEOUT") == nullptr)
-      cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                           (int)cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   launch_kernel(attention_prefill_tc_kernel<HD>, dim3(p.Hq, n_tiles), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);

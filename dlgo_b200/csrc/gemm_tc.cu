@@ -963,8 +963,6 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcP
   // one CTA per SM with as deep a ring as shared memory allows beside the epilogue's staging buffers
   int ctas_per_sm = 1;
   q.stages = C::MAX_STAGES;
-  const char* e = getenv("DLGO_TC_PERSISTENT_STAGES");
-  if (e != nullptr && atoi(e) >= 2 && atoi(e) <= C::MAX_STAGES) q.stages = atoi(e);
   const int slots = sms * ctas_per_sm;
   CUtensorMap mo = ma;   // a valid map even when unused
   q.staged = (getenv("DLGO_TC_DIRECT_EPILOGUE") == nullptr && make_out_map(&mo, q) == DLGO_OK) ? 1 : 0;
@@ -1062,7 +1060,7 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
     if (st != DLGO_OK) return st;
     return pair_tile == 256 ? launch_tc_pair<256>(ma, mb, p, stream) : launch_tc_pair<128>(ma, mb, p, stream);
   }
-  if (!transposed && splits == 1 && (bn == 128 || bn == 256) && getenv("DLGO_GEMM_NONPERSISTENT") == nullptr) {
+  if (!transposed && splits == 1 && (bn == 128 || bn == 256)) {
     // many tokens: persistent CTAs with two accumulators in tensor memory
     return bn == 256 ? launch_tc_persistent<256>(ma, mb, p, stream) : launch_tc_persistent<128>(ma, mb, p, stream);
   }

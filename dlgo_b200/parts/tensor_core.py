@@ -35,7 +35,6 @@ TARGET_CTAS_FEW = int(os.environ.get("DLGO_TC_TARGET_CTAS_FEW", 0))  # 0: one an
 MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PAIR_MIN_TOKENS = int(os.environ.get("DLGO_TC_PAIR_MIN_TOKENS", 64))   # CTA pairs for more tokens than this
-PREFILL_BN = int(os.environ.get("DLGO_TC_PREFILL_BN", 0))   # experiment switch: tile width for many tokens
 MIN_KBLOCKS_PER_SPLIT = int(os.environ.get("DLGO_TC_MIN_KBLOCKS", 4))
 # Few tokens: a contraction whose result goes into the residual stream adds its K-slices there with
 # reductions at the memory (up to RED_MAX_TOKENS tokens) instead of leaving them for the norm's kernel to
@@ -125,8 +124,6 @@ class TensorCorePlan:
     def many_token_shape(self, tokens: int) -> tuple[int, int]:
         """(tile width, CTA-pair tile or 0) for more than SKINNY_MAX tokens: the activations are the M operand."""
         bn = 256 if self.n > 128 else 128
-        if PREFILL_BN in (128, 256):
-            bn = PREFILL_BN
         pair = PAIR_TILE if (tokens > PAIR_MIN_TOKENS and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
         return bn, pair
 
