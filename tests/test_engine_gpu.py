@@ -115,8 +115,9 @@ def test_requests_fed_in_pieces_of_several_tokens(model_dirs, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_decoding_behind_a_prompt_of_more_than_64_pages(tmp_path_factory, dtype):
-    # 4,300 prompt tokens (68 pages), then four tokens one by one: decode attention then cuts a
-    # sequence into more slices than a cluster holds and combines them through scratch memory
+    # 4,090 prompt tokens, then fourteen tokens one by one across position 4,096 (the end of page 64): the
+    # captured step sized for 4,096 positions hands over to the one sized for the whole cache, whose decode
+    # attention cuts a sequence into more slices than a cluster holds and combines them through scratch memory
     from dlgo_b200.config import config_from_dict
     from dlgo_b200.engine.engine import Engine
     from dlgo_b200.weights import write_random_model
@@ -127,17 +128,33 @@ def test_decoding_behind_a_prompt_of_more_than_64_pages(tmp_path_factory, dtype)
     if d is None:
         d = _long_dir["d"] = str(tmp_path_factory.mktemp("long_context"))
         write_random_model(config_from_dict(cfg), 12, d)
-    toks = random_tokens(4304, 300, 21)
+    n_prompt, n_more = 4090, 14
+    toks = random_tokens(n_prompt + n_more, 300, 21)
     eng = Engine(d, dtype=dtype, max_tokens=4608, max_seq_len=8192)
     eng.cache.poison()
-    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:4300], "want": [0, 2047, 4299]}], "end": []}]
-    for j in range(4300, 4304):
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:n_prompt], "want": [0, 2047, n_prompt - 1]}], "end": []}]
+    for j in range(n_prompt, n_prompt + n_more):
         steps.append({"step": len(steps), "entries": [{"id": "x", "tokens": [toks[j]], "want": [0]}],
-                      "end": ["x"] if j == 4303 else []})
+                      "end": ["x"] if j == n_prompt + n_more - 1 else []})
     outs = T.run_in_process(eng, steps)
+    assert list(eng._graphs) == [(1, 4096), (1, eng.max_seq_len)] and eng.max_seq_len == 4608
     ref = plain_logits(d, toks)
-    got = torch.cat([outs[i] for i in range(5)])
-    assert_close(got, ref[[0, 2047, 4299, 4300, 4301, 4302, 4303]], dtype, f"long context ({dtype})")
+    got = torch.cat([outs[i] for i in range(1 + n_more)])
+    assert_close(got, ref[[0, 2047, n_prompt - 1] + list(range(n_prompt, n_prompt + n_more))], dtype,
+                 f"long context ({dtype})")
+    # the same tokens chosen greedily in one native run across the boundary as step by step
+    slot = eng.take_slot()
+    first = int(eng.step([slot], [toks[:n_prompt]]).argmax())
+    run = eng.greedy_run([slot], [first], 12)
+    eng.free_slot(slot)
+    slot = eng.take_slot()
+    tok = int(eng.step([slot], [toks[:n_prompt]]).argmax())
+    single = []
+    for _ in range(12):
+        tok = int(eng.step([slot], [[tok]]).argmax())
+        single.append(tok)
+    eng.free_slot(slot)
+    assert run is not None and [r[0] for r in run] == single
 
 
 _long_dir = {}
