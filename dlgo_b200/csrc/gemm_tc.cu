@@ -36,7 +36,7 @@ namespace dlgo {
 
 using namespace sm100;
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4, TC_RED_F32 = 5 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4, TC_RED_F32 = 5, TC_ROPE_QKV = 6 };
 
 constexpr int TILE_M = 128;
 constexpr int TILE_K = 64;  // 128 bytes of bf16: one swizzle row
@@ -45,7 +45,24 @@ constexpr int TC_THREADS = 192;
 
 __device__ int g_gemm_tc_error = 0;  // set when a bounded wait ran out
 
+// What the q | k | v projection's epilogue needs to finish the job of the rotation kernel (models/llm/
+// forward.go:246-257): rotate every q and k head at its token's position (pairs (i, i + hd/2), the whole
+// head) and put k and v where the cache keeps them.  Pages of 64 positions, heads of 64 or 128.
+struct TcRope {
+  const float* cos_t;       // [positions][hd / 2]
+  const float* sin_t;
+  const int* token_pos;     // [tokens]
+  const int* token_seq;     // [tokens] index of the token's sequence in the batch
+  const int* seq_slot;      // [sequences]
+  const int* page_table;    // [slots][max_pages]
+  int max_pages;
+  __nv_bfloat16* kpages;    // [pages][Hkv][64][hd]
+  __nv_bfloat16* vpages;
+  int Hq, Hkv, hd, write_cache;
+};
+
 struct TcParams {
+  TcRope rope;        // TC_ROPE_QKV only
   int Ra, Rb, K;      // rows of A, rows of B, contraction length
   void* out;
   int ldo;
@@ -476,12 +493,160 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Called by the 128 epilogue threads together; `chunk` counts staging buffers used so far.
 constexpr int STAGING_BYTES = 2 * 16384;
 
+// 32 accumulator columns of a row as bfloat16 into four 16-byte pieces of a swizzled 128-byte staging row
+__device__ __forceinline__ void stage_bf16_32(uint8_t* row, int r, int first_piece, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 b2[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) b2[q] = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+    *reinterpret_cast<uint4*>(row + (((first_piece + j) ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(b2);
+  }
+}
+// ... and straight to memory (16-byte aligned)
+__device__ __forceinline__ void store_bf16_32(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 b2[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) b2[q] = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+    *reinterpret_cast<uint4*>(dst + 8 * j) = *reinterpret_cast<uint4*>(b2);
+  }
+}
+
+// The epilogue of the q | k | v projection of a prompt step: a head at a time (64 or 128 accumulator columns of
+// the thread's token), q and k heads rotated in fp32 and rounded once; q goes to the output through the staging
+// buffers and TMA stores as TC_STORE does, k and v go straight to the token's row of its cache page.
+// What a thread of the rotating epilogue knows about its token before the accumulator is ready: where its k and
+// v rows go and, for heads of 64, the token's 32 cosines and 32 sines (they stay in registers for all heads of
+// the tile: beside a ring of 200 KB the SM's L1 holds 28 KB, so re-read per head they would come from L2 every
+// time).  Fetched while the tile's MMAs still run.
+struct RopeRow {
+  const float* cs;
+  const float* sn;
+  __nv_bfloat16* krow;
+  __nv_bfloat16* vrow;
+  float4 c4[8], s4[8];
+  bool table_held;
+};
+
+__device__ __forceinline__ void rope_prepare(const TcParams& p, int row0, int r, RopeRow& rr) {
+  const TcRope& R = p.rope;
+  const int hd = R.hd, half = hd >> 1;
+  const int t = row0 + r;
+  const bool live = t < p.Ra;
+  const int pos = live ? R.token_pos[t] : 0;
+  rr.cs = R.cos_t + (size_t)pos * half;
+  rr.sn = R.sin_t + (size_t)pos * half;
+  rr.krow = rr.vrow = nullptr;
+  rr.table_held = half == 32;
+  if (rr.table_held) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      rr.c4[i] = __ldg(reinterpret_cast<const float4*>(rr.cs) + i);
+      rr.s4[i] = __ldg(reinterpret_cast<const float4*>(rr.sn) + i);
+    }
+  }
+  if (live && R.write_cache) {
+    const int slot = R.seq_slot[R.token_seq[t]];
+    const int page = R.page_table[(size_t)slot * R.max_pages + (pos >> 6)];
+    if (page >= 0) {
+      const size_t base = ((size_t)page * R.Hkv * 64 + (size_t)(pos & 63)) * hd;
+      rr.krow = R.kpages + base;
+      rr.vrow = R.vpages + base;
+    } else {
+      atomicExch(&g_gemm_tc_error, 1);        // a page that was never reserved: nothing is written
+    }
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void rope_qkv_epilogue(const TcParams& p, const CUtensorMap* map_out, uint8_t* staging,
+                                                  uint32_t lane_addr, int row0, int col0, int r, bool issuer,
+                                                  int& chunk, RopeRow& rr) {
+  const TcRope& R = p.rope;
+  const int hd = R.hd, half = hd >> 1;
+  const float* cs = rr.cs;
+  const float* sn = rr.sn;
+  __nv_bfloat16* krow = rr.krow;
+  __nv_bfloat16* vrow = rr.vrow;
+  float4 (&c4)[8] = rr.c4;
+  float4 (&s4)[8] = rr.s4;
+  const bool table_held = rr.table_held;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += hd) {
+    const int head = (col0 + c0) / hd;                       // the same for the whole CTA
+    if (head >= R.Hq + 2 * R.Hkv) break;                     // (columns beyond the projection's rows)
+    const bool is_q = head < R.Hq, is_k = !is_q && head < R.Hq + R.Hkv;
+    const int bufs = hd >> 6;                                // staging buffers a q head takes: 64 columns each
+    if (is_q) {
+      if (issuer) { if (bufs == 2) tma_store_wait_read<0>(); else tma_store_wait_read<1>(); }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const int kvh = is_k ? head - R.Hq : head - R.Hq - R.Hkv;
+    __nv_bfloat16* dst = is_q ? nullptr : ((is_k ? krow : vrow) == nullptr ? nullptr
+                                           : (is_k ? krow : vrow) + (size_t)kvh * 64 * hd);
+#pragma unroll 1
+    for (int g = 0; g < half; g += 32) {
+      // dimensions [g, g + 32) and their partners [g + half, g + half + 32); the 16 loads of the token's
+      // cosines and sines are all on their way before anything waits for one (one round trip, not eight)
+      if (!table_held && (is_q || is_k)) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          c4[i] = __ldg(reinterpret_cast<const float4*>(cs + g) + i);
+          s4[i] = __ldg(reinterpret_cast<const float4*>(sn + g) + i);
+        }
+      }
+      float a[32], b[32];
+      tmem_ld_32x32(lane_addr + c0 + g, a);
+      tmem_ld_32x32(lane_addr + c0 + half + g, b);
+      tmem_ld_wait();
+      if (is_q || is_k) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float cc[4] = {c4[i].x, c4[i].y, c4[i].z, c4[i].w}, ss[4] = {s4[i].x, s4[i].y, s4[i].z, s4[i].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x0 = a[4 * i + e], x1 = b[4 * i + e];
+            a[4 * i + e] = x0 * cc[e] - x1 * ss[e];
+            b[4 * i + e] = x0 * ss[e] + x1 * cc[e];
+          }
+        }
+      }
+      if (is_q) {
+        // column c of the head lies in staging buffer c / 64, 16-byte piece (c % 64) / 8
+        uint8_t* b0 = staging + ((chunk + (g >> 6)) & 1) * 16384 + r * 128;
+        uint8_t* b1 = staging + ((chunk + ((half + g) >> 6)) & 1) * 16384 + r * 128;
+        stage_bf16_32(b0, r, (g & 63) >> 3, a);
+        stage_bf16_32(b1, r, ((half + g) & 63) >> 3, b);
+      } else if (dst != nullptr) {
+        store_bf16_32(dst + g, a);
+        store_bf16_32(dst + half + g, b);
+      }
+    }
+    if (is_q) {
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (issuer) {
+        for (int j = 0; j < bufs; ++j)
+          tma_store_2d(map_out, staging + ((chunk + j) & 1) * 16384, col0 + c0 + 64 * j, row0);
+        tma_store_commit();
+      }
+      chunk += bufs;
+    }
+  }
+}
+
 template <int BN>
 __device__ __forceinline__ void staged_epilogue(const TcParams& p, const CUtensorMap* map_out, uint8_t* staging,
                                                 uint32_t acc_addr, int row0, int col0, int quarter, int lane,
-                                                bool issuer, int& chunk) {
+                                                bool issuer, int& chunk, RopeRow* rope_row = nullptr) {
   const int r = quarter * 32 + lane;
   const uint32_t lane_addr = acc_addr + ((uint32_t)(quarter * 32) << 16);
+  if (p.epilogue == TC_ROPE_QKV) {
+    rope_qkv_epilogue<BN>(p, map_out, staging, lane_addr, row0, col0, r, issuer, chunk, *rope_row);
+    return;
+  }
   // accumulator columns that make one 128-byte output row chunk
   const int step = p.epilogue == TC_STORE ? 64 : (p.epilogue == TC_SWIGLU ? 128 : 32);
 #pragma unroll 1
@@ -645,11 +810,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       const int tile_a = t % tiles_a, tile_b = t / tiles_a;
       const int buf = local & 1;
       const int row = tile_a * TILE_M + quarter * 32 + lane;
+      RopeRow rope_row;
+      if (p.epilogue == TC_ROPE_QKV) rope_prepare(p, tile_a * TILE_M, quarter * 32 + lane, rope_row);
       if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;
       tc_fence_after_sync();
       if (staged) {
         staged_epilogue<BN>(p, &map_out, staging, tmem_base + buf * C::TMEM_COLS, tile_a * TILE_M, tile_b * BN, quarter,
-                            lane, issuer, chunk);
+                            lane, issuer, chunk, &rope_row);
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += NV) {
@@ -803,11 +970,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int buf = local & 1;
       const int row0 = tile_a * 2 * TILE_M + (int)rank * TILE_M;
       const int row = row0 + quarter * 32 + lane;
+      RopeRow rope_row;               // (fetched while the tile's MMAs still run)
+      if (p.epilogue == TC_ROPE_QKV) rope_prepare(p, row0, quarter * 32 + lane, rope_row);
       if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag)) break;
       tc_fence_after_sync();
       if (staged) {
         staged_epilogue<BN>(p, &map_out, staging, tmem_base + buf * ACC_COLS, row0, tile_b * BN, quarter, lane, issuer,
-                            chunk);
+                            chunk, &rope_row);
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += NV) {
@@ -879,7 +1048,7 @@ int make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_
 int make_out_map(CUtensorMap* m, const TcParams& p) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return DLGO_ERR_DRIVER;
-  const bool bf16 = p.epilogue == TC_STORE || p.epilogue == TC_SWIGLU;
+  const bool bf16 = p.epilogue == TC_STORE || p.epilogue == TC_SWIGLU || p.epilogue == TC_ROPE_QKV;
   const int esize = bf16 ? 2 : 4;
   const long long cols = p.epilogue == TC_SWIGLU ? p.Rb / 2 : p.Rb;
   if (((uintptr_t)p.out & 15) != 0 || ((long long)p.ldo * esize) % 16 != 0) return DLGO_ERR_ALIGN;
@@ -1049,7 +1218,7 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   if (st != DLGO_OK) return st;
   st = make_map(&mb, B, Rb, K, ldb, bn);
   if (st != DLGO_OK) return st;
-  TcParams p;
+  TcParams p = {};
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
@@ -1072,6 +1241,62 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
     case 256: return launch_tc<256>(ma, mb, p, stream);
     default: return DLGO_ERR_SIZE;
   }
+}
+
+// The q | k | v projection of a prompt step with the rotation and the cache append in its epilogue:
+// qkv[T, Rb] (bf16, row stride ldo) receives the rotated q heads (its k and v columns are left alone), the
+// rotated k heads and the v heads go to their tokens' rows of the pages [pages][Hkv][64][hd].  x[T, K] and
+// w[Rb, K] bf16 with Rb = (Hq + 2 Hkv) * hd; hd 64 or 128, whole-head rotation in the split-half pairing,
+// cos / sin tables [positions][hd / 2]; pages of 64 positions.  Tiles of 256 columns: pair_tile 256 (CTA
+// pairs) or 0 (single CTAs).  DLGO_ERR_ALIGN where the output cannot go through TMA stores.
+struct DlgoRopeArgs {
+  const float* cos_t;
+  const float* sin_t;
+  const int* token_pos;
+  const int* token_seq;
+  const int* seq_slot;
+  const int* page_table;
+  int max_pages;
+  void* kpages;
+  void* vpages;
+  int Hq, Hkv, hd, write_cache;
+};
+
+DLGO_EXPORT int dlgo_gemm_tc_rope_takes(int Rb, int K, int Hq, int Hkv, int hd, int page_size) {
+  return (hd == 64 || hd == 128) && page_size == 64 && Hq > 0 && Hkv > 0 && Rb == (Hq + 2 * Hkv) * hd && Rb >= 256 &&
+         K > 0 && K % 8 == 0;
+}
+
+DLGO_EXPORT int dlgo_gemm_tc_rope(const void* x, int T, int ldx, const void* w, int Rb, int ldw, int K, void* qkv,
+                                  int ldo, int pair_tile, const DlgoRopeArgs* rope, cudaStream_t stream) {
+  if (T <= 0) return DLGO_OK;
+  if (rope == nullptr || !dlgo_gemm_tc_rope_takes(Rb, K, rope->Hq, rope->Hkv, rope->hd, 64) || ldx < K || ldw < K ||
+      (pair_tile != 0 && pair_tile != 256))
+    return DLGO_ERR_SIZE;
+  if (rope->cos_t == nullptr || rope->sin_t == nullptr || rope->token_pos == nullptr ||
+      (rope->write_cache && (rope->token_seq == nullptr || rope->seq_slot == nullptr || rope->page_table == nullptr ||
+                             rope->kpages == nullptr || rope->vpages == nullptr)))
+    return DLGO_ERR_SIZE;
+  if (((uintptr_t)rope->cos_t & 15) || ((uintptr_t)rope->sin_t & 15) || ((uintptr_t)rope->kpages & 15) ||
+      ((uintptr_t)rope->vpages & 15))
+    return DLGO_ERR_ALIGN;
+  CUtensorMap ma, mb;
+  int st = make_map(&ma, x, T, K, ldx, TILE_M);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mb, w, Rb, K, ldw, pair_tile ? pair_tile / 2 : 256);
+  if (st != DLGO_OK) return st;
+  TcParams p = {};
+  p.Ra = T; p.Rb = Rb; p.K = K; p.out = qkv; p.ldo = ldo; p.transposed = 0; p.epilogue = TC_ROPE_QKV;
+  p.splits = 1; p.workspace = nullptr; p.counters = nullptr; p.static_operand = 2;
+  p.rope.cos_t = rope->cos_t; p.rope.sin_t = rope->sin_t; p.rope.token_pos = rope->token_pos;
+  p.rope.token_seq = rope->token_seq; p.rope.seq_slot = rope->seq_slot; p.rope.page_table = rope->page_table;
+  p.rope.max_pages = rope->max_pages;
+  p.rope.kpages = (__nv_bfloat16*)rope->kpages; p.rope.vpages = (__nv_bfloat16*)rope->vpages;
+  p.rope.Hq = rope->Hq; p.rope.Hkv = rope->Hkv; p.rope.hd = rope->hd; p.rope.write_cache = rope->write_cache;
+  // this epilogue exists in the staged form only
+  CUtensorMap probe;
+  if (getenv("DLGO_TC_DIRECT_EPILOGUE") != nullptr || make_out_map(&probe, p) != DLGO_OK) return DLGO_ERR_ALIGN;
+  return pair_tile ? launch_tc_pair<256>(ma, mb, p, stream) : launch_tc_persistent<256>(ma, mb, p, stream);
 }
 
 // 1 if a kernel of this library gave up a bounded wait since the last call (clears the flag).

@@ -462,6 +462,58 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
     return out
 
 
+class RopeArgs(ctypes.Structure):
+    """What the q|k|v projection's epilogue needs to rotate q and k and to append k and v (DlgoRopeArgs)."""
+    _fields_ = [("cos_t", _p), ("sin_t", _p), ("token_pos", _p), ("token_seq", _p), ("seq_slot", _p),
+                ("page_table", _p), ("max_pages", _i), ("kpages", _p), ("vpages", _p), ("Hq", _i), ("Hkv", _i),
+                ("hd", _i), ("write_cache", _i)]
+
+
+def rope_args(cos: torch.Tensor, sin: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+              seq_slot: torch.Tensor, page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor,
+              num_heads: int, num_kv_heads: int, head_dim: int, write_cache: bool) -> RopeArgs:
+    """Checked :class:`RopeArgs`; the caller keeps the tensors alive while a launch may read them."""
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    _need(kpages, torch.bfloat16, "kpages")
+    _need(vpages, torch.bfloat16, "vpages")
+    if cos.dim() != 2 or cos.shape[1] * 2 != head_dim or sin.shape != cos.shape:
+        raise KernelError("rope_args: whole-head rotation tables [positions, head_dim / 2] only")
+    if kpages.shape[-2] != 64 or kpages.shape[-1] != head_dim or kpages.shape[-3] != num_kv_heads:
+        raise KernelError("rope_args: pages must be [pages, kv heads, 64, head_dim]")
+    return RopeArgs(cos.data_ptr(), sin.data_ptr(), token_pos.data_ptr(), token_seq.data_ptr(), seq_slot.data_ptr(),
+                    page_table.data_ptr(), page_table.shape[1], kpages.data_ptr(), vpages.data_ptr(), num_heads,
+                    num_kv_heads, head_dim, 1 if write_cache else 0)
+
+
+def gemm_tc_rope_takes(out_features: int, in_features: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                       page_size: int) -> bool:
+    """Whether :func:`gemm_tc_rope` takes a q|k|v weight [out, in] with these heads and pages."""
+    import os
+    return os.environ.get("DLGO_TC_DIRECT_EPILOGUE") is None and bool(_lib("gemm_tc").dlgo_gemm_tc_rope_takes(
+        _i(out_features), _i(in_features), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size)))
+
+
+def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, pair_tile: int, rope: RopeArgs) -> torch.Tensor:
+    """The q|k|v projection of a prompt step (``x`` [T, K] . ``w`` [(Hq + 2 Hkv) hd, K]^T on the tensor cores)
+    whose epilogue rotates q and k in fp32 (whole head, split-half pairing), rounds once, writes the q heads to
+    ``qkv`` [T, out] and appends k and v to the tokens' rows of their pages; the k and v columns of ``qkv`` are
+    not written.  ``pair_tile``: 256 (CTA pairs) or 0."""
+    for n, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_tc_rope: {n} must be a 2-D bfloat16 GPU tensor with unit inner stride")
+    T, k = x.shape
+    n_out, k2 = w.shape
+    if k != k2 or qkv.dtype != torch.bfloat16 or tuple(qkv.shape) != (T, n_out) or qkv.stride(1) != 1:
+        raise KernelError("gemm_tc_rope: x [T, K], w [out, K] and a bfloat16 qkv [T, out] with unit inner stride")
+    st = _lib("gemm_tc").dlgo_gemm_tc_rope(_ptr(x), _i(T), _i(x.stride(0)), _ptr(w), _i(n_out), _i(w.stride(0)), _i(k),
+                                           _ptr(qkv), _i(qkv.stride(0)), _i(pair_tile), ctypes.byref(rope), _stream())
+    _check(st, "gemm_tc_rope")
+    return qkv
+
+
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait on the device since the last check (synchronises)."""
     for lib, fn in (("gemm_tc", "dlgo_gemm_tc_error"), ("attention_prefill_tc", "dlgo_attention_tc_error")):
@@ -797,7 +849,7 @@ def decode_layers(desc: torch.Tensor, n_layers: int, residual: torch.Tensor, hid
 
 # ------------------------------------------------------------------ the layer loop of a prompt step, native
 class PromptEntryPoints(ctypes.Structure):
-    _fields_ = [(n, _p) for n in ("rmsnorm", "gemm_tc", "rope_append", "attention")]
+    _fields_ = [(n, _p) for n in ("rmsnorm", "gemm_tc", "rope_append", "attention", "gemm_tc_rope")]
 
 
 class PromptShape(ctypes.Structure):
@@ -813,10 +865,10 @@ class PromptLayer(ctypes.Structure):
 class PromptStep(ctypes.Structure):
     _fields_ = [("tokens", _i), ("residual", _p), ("x", _p), ("qkv", _p), ("attn_out", _p), ("h", _p), ("cos_t", _p),
                 ("sin_t", _p), ("token_pos", _p), ("token_seq", _p), ("seq_slot", _p), ("page_table", _p),
-                ("max_pages", _i), ("tiles", _p), ("n_tiles", _i), ("bn", _i * 4), ("pair", _i * 4)]
+                ("max_pages", _i), ("tiles", _p), ("n_tiles", _i), ("bn", _i * 4), ("pair", _i * 4), ("fuse_rope", _i)]
 
 
-PROMPT_CALLS = ("mixer norm", "q/k/v projection", "rotation and cache append", "attention", "output projection",
+PROMPT_CALLS = ("mixer norm", "q/k/v projection", "rotation and cache append (0 launches where the projection does it)", "attention", "output projection",
                 "feed-forward norm", "gate/up projection", "down projection")
 
 
@@ -827,7 +879,8 @@ def prompt_entry_points() -> PromptEntryPoints:
         return ctypes.cast(getattr(_lib(lib), fn), ctypes.c_void_p).value
     return PromptEntryPoints(address("elementwise", "dlgo_rmsnorm"), address("gemm_tc", "dlgo_gemm_tc"),
                              address("rope_append", "dlgo_rope_append"),
-                             address("attention_prefill_tc", "dlgo_attention_prefill_tc"))
+                             address("attention_prefill_tc", "dlgo_attention_prefill_tc"),
+                             address("gemm_tc", "dlgo_gemm_tc_rope"))
 
 
 def prompt_layers_describe(layers: Sequence[dict]) -> tuple:
@@ -851,7 +904,8 @@ def prompt_layers_describe(layers: Sequence[dict]) -> tuple:
 
 
 def prompt_layers(entry: PromptEntryPoints, shape: PromptShape, layers: ctypes.Array, step: PromptStep) -> None:
-    """Run ``len(layers)`` pre-norm layers of a prompt step: eight launches a layer, issued from one native loop
+    """Run ``len(layers)`` pre-norm layers of a prompt step: eight launches a layer (seven where the q/k/v
+    projection rotates and appends in its epilogue: ``step.fuse_rope``), issued from one native loop
     (csrc/prompt_layers.cu).  The caller has checked types and sizes of what ``step`` points at."""
     failed = _i(-1)
     n = len(layers)
@@ -859,4 +913,4 @@ def prompt_layers(entry: PromptEntryPoints, shape: PromptShape, layers: ctypes.A
                                                   ctypes.byref(step), ctypes.byref(failed), _stream())
     if st != 0 and failed.value >= 0:
         _check(st, f"prompt_layers (layer {failed.value // 8} of the run, {PROMPT_CALLS[failed.value % 8]})")
-    _check(st, "prompt_layers", 8 * n)
+    _check(st, "prompt_layers", (7 if step.fuse_rope else 8) * n)

@@ -31,12 +31,29 @@ typedef int (*AttentionFn)(const void* q, int T, int ldq, const void* kpages, co
                            const int* token_pos, void* out, int ldo, int Hq, int Hkv, int hd, int window, float scale,
                            cudaStream_t stream);
 
+// as in gemm_tc.cu
+struct DlgoRopeArgs {
+  const float* cos_t;
+  const float* sin_t;
+  const int* token_pos;
+  const int* token_seq;
+  const int* seq_slot;
+  const int* page_table;
+  int max_pages;
+  void* kpages;
+  void* vpages;
+  int Hq, Hkv, hd, write_cache;
+};
+typedef int (*GemmTcRopeFn)(const void* x, int T, int ldx, const void* w, int Rb, int ldw, int K, void* qkv, int ldo,
+                            int pair_tile, const DlgoRopeArgs* rope, cudaStream_t stream);
+
 // Entry points of the kernel libraries.
 struct DlgoPromptEntryPoints {
   RmsNormFn rmsnorm;
   GemmTcFn gemm_tc;
   RopeAppendFn rope_append;
   AttentionFn attention;
+  GemmTcRopeFn gemm_tc_rope;
 };
 
 // What the layers of a run share.
@@ -81,6 +98,7 @@ struct DlgoPromptStep {
   int n_tiles;
   int bn[4];              // tile width of qkv, o, gate_up, down
   int pair[4];            // their CTA-pair tile (0: none)
+  int fuse_rope;          // the q/k/v projection's epilogue rotates and appends: no launch for that
 };
 
 }  // extern "C"
@@ -95,7 +113,8 @@ DLGO_EXPORT int dlgo_prompt_layers(const DlgoPromptEntryPoints* fn, const DlgoPr
                                    const DlgoPromptLayer* layers, int n_layers, const DlgoPromptStep* p,
                                    int* failed_call, cudaStream_t stream) {
   if (fn == nullptr || s == nullptr || layers == nullptr || p == nullptr) return DLGO_ERR_SIZE;
-  if (fn->rmsnorm == nullptr || fn->gemm_tc == nullptr || fn->rope_append == nullptr || fn->attention == nullptr)
+  if (fn->rmsnorm == nullptr || fn->gemm_tc == nullptr || fn->rope_append == nullptr || fn->attention == nullptr ||
+      fn->gemm_tc_rope == nullptr)
     return DLGO_ERR_DRIVER;
   const int T = p->tokens, d = s->hidden;
   const int q_dim = s->heads * s->head_dim, n_cols = (s->heads + 2 * s->kv_heads) * s->head_dim;
@@ -114,11 +133,19 @@ DLGO_EXPORT int dlgo_prompt_layers(const DlgoPromptEntryPoints* fn, const DlgoPr
     const DlgoPromptLayer& L = layers[l];
     call = 8 * l;
     DLGO_STEP(fn->rmsnorm(p->residual, L.norm1_w, p->x, DLGO_BF16, nullptr, T, d, L.eps1, stream));
-    DLGO_STEP(fn->gemm_tc(p->x, T, d, L.w_qkv, n_cols, d, d, p->qkv, n_cols, 0, TC_STORE, p->bn[0], 1, nullptr, nullptr,
-                          2, p->pair[0], stream));
-    DLGO_STEP(fn->rope_append(p->qkv, DLGO_BF16, T, n_cols, p->cos_t, p->sin_t, p->token_pos, p->token_seq, p->seq_slot,
-                              p->page_table, p->max_pages, L.kpages, L.vpages, s->heads, s->kv_heads, s->head_dim,
-                              s->rotary_dim, s->page_size, s->interleaved, L.write_cache, nullptr, 0, 0, 0, stream));
+    if (p->fuse_rope) {
+      const DlgoRopeArgs rope = {p->cos_t, p->sin_t, p->token_pos, p->token_seq, p->seq_slot, p->page_table,
+                                 p->max_pages, L.kpages, L.vpages, s->heads, s->kv_heads, s->head_dim, L.write_cache};
+      DLGO_STEP(fn->gemm_tc_rope(p->x, T, d, L.w_qkv, n_cols, d, d, p->qkv, n_cols, p->pair[0], &rope, stream));
+      ++call;
+    } else {
+      DLGO_STEP(fn->gemm_tc(p->x, T, d, L.w_qkv, n_cols, d, d, p->qkv, n_cols, 0, TC_STORE, p->bn[0], 1, nullptr,
+                            nullptr, 2, p->pair[0], stream));
+      DLGO_STEP(fn->rope_append(p->qkv, DLGO_BF16, T, n_cols, p->cos_t, p->sin_t, p->token_pos, p->token_seq,
+                                p->seq_slot, p->page_table, p->max_pages, L.kpages, L.vpages, s->heads, s->kv_heads,
+                                s->head_dim, s->rotary_dim, s->page_size, s->interleaved, L.write_cache, nullptr, 0, 0,
+                                0, stream));
+    }
     DLGO_STEP(fn->attention(p->qkv, T, n_cols, L.kpages, L.vpages, L.n_pages, p->page_table, p->max_pages, p->tiles,
                             p->n_tiles, p->seq_slot, p->token_pos, p->attn_out, q_dim, s->heads, s->kv_heads,
                             s->head_dim, s->window, s->scale, stream));
@@ -135,4 +162,4 @@ DLGO_EXPORT int dlgo_prompt_layers(const DlgoPromptEntryPoints* fn, const DlgoPr
 }
 
 // Launches per layer, for the caller's count.
-DLGO_EXPORT int dlgo_prompt_layers_launches() { return 8; }
+DLGO_EXPORT int dlgo_prompt_layers_launches(int fuse_rope) { return fuse_rope ? 7 : 8; }

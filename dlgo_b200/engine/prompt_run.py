@@ -120,6 +120,7 @@ class PromptRun:
         step.tiles, step.n_tiles = tiles.data_ptr(), n_tiles
         for j, lin in enumerate((blk.mixer.wqkv, blk.mixer.wo, blk.ffn.w_gate_up, blk.ffn.w_down)):
             step.bn[j], step.pair[j] = lin._tc.many_token_shape(T)
+        step.fuse_rope = 1 if (pe_name is not None and blk.mixer.fuses_prompt_rope(ctx, view, model.positions)) else 0
         shape = K.PromptShape(d, hq, hkv, hd, f, rot, 1 if inter else 0, window, view.page_size, scale)
         K.prompt_layers(self._entry, shape, layers, step)
 

@@ -33,6 +33,8 @@ _QKV_SUM = int(os.environ.get("DLGO_ATTN_QKV_SUM", 1))
 # batch 8, 1.31 -> 1.28 ms at batch 64.
 _FUSE_ROPE = int(os.environ.get("DLGO_ATTN_FUSE_ROPE", 1))
 _FUSE_ROPE_MAX_HEAD = 64
+# prompts: the q|k|v projection's epilogue rotates and appends (0: the rotation kernel runs behind it)
+_PROMPT_ROPE = int(os.environ.get("DLGO_PROMPT_ROPE", 1))
 
 
 _DECODE_BLOCKS = int(os.environ.get("DLGO_ATTN_BLOCKS", 0))   # blocks wanted in flight for decode attention (0: four per SM)
@@ -105,6 +107,17 @@ class GQAAttention(Mixer):
             counters = ctx.zeros("attention_counters", T * self.num_kv_heads * ((group + 3) // 4))
         return n_splits, scratch, counters
 
+    def fuses_prompt_rope(self, ctx: Any, cache: Any, positions: Mapping[str, PositionEncoding]) -> bool:
+        """Whether this step's q|k|v projection rotates and appends in its own epilogue: a prompt step in
+        bfloat16 of more tokens than the few-token kernel takes, whole-head rotation in the split-half pairing,
+        heads and pages the tensor-core kernel takes."""
+        if ctx.decode or self.position_encoding is None or not _PROMPT_ROPE:
+            return False
+        pe = positions[self.position_encoding]
+        return (pe.rotary_dim == self.head_dim and not pe.interleaved and cache.keys.dtype == torch.bfloat16 and
+                self.wqkv.rope_qkv_takes(ctx.n_tokens, self.num_heads, self.num_kv_heads, self.head_dim,
+                                         cache.page_size))
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
         T = ctx.n_tokens
@@ -148,6 +161,12 @@ class GQAAttention(Mixer):
                 K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                               cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
                               qkv_sum, True)
+        elif self.fuses_prompt_rope(ctx, cache, positions):
+            # prompts: the projection's epilogue rotates q and k and appends k and v (no launch for that, and
+            # one rounding to bfloat16 instead of two)
+            rope = K.rope_args(cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                               cache.values, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
+            qkv = self.wqkv.rope_qkv(x, rope)
         else:
             # ... or leaves its K-slices unsummed for the rotation to add in order; else the finished product
             qkv_parts = self.wqkv.partials(x, single_ok=False)

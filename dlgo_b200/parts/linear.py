@@ -39,6 +39,18 @@ class Linear:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
 
+    def rope_qkv_takes(self, tokens: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+        """Whether, for this many tokens, this weight can run as the q|k|v projection whose epilogue rotates q and
+        k (whole head, split-half pairs) and appends k and v to the cache (tensor-core kernel, many tokens)."""
+        if self._tc is None or self.fuses_swiglu:
+            return False
+        from . import tensor_core
+        return (tokens > tensor_core.SKINNY_MAX and self._tc.many_token_shape(tokens)[0] == 256 and
+                K.gemm_tc_rope_takes(self.out_features, self.in_features, num_heads, num_kv_heads, head_dim, page_size))
+
+    def rope_qkv(self, x: torch.Tensor, rope: Any, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self._tc.rope_qkv(x, out, rope)
+
     def sums_slices_at_memory(self, tokens: int) -> bool:
         """Whether, for this many tokens, the add epilogue runs as several K-slices that add themselves
         into the target with reductions at the memory (the target may then be a plain zeroed sum)."""

@@ -127,6 +127,15 @@ class TensorCorePlan:
         pair = PAIR_TILE if (tokens > PAIR_MIN_TOKENS and self.n >= 256) else 0      # CTA pairs share 256 x 256 tiles
         return bn, pair
 
+    def rope_qkv(self, x, out: Optional[torch.Tensor], rope: "K.RopeArgs") -> torch.Tensor:
+        """This weight as the q|k|v projection of a prompt step, its epilogue rotating q and k and appending k
+        and v (``rope``: :func:`kernels.rope_args`); more than SKINNY_MAX tokens."""
+        t = x.shape[0]
+        if out is None:
+            out = torch.empty((t, self.n), dtype=torch.bfloat16, device=x.device)
+        bn, pair = self.many_token_shape(t)
+        return K.gemm_tc_rope(x, self.weight, out, pair, rope)
+
     def sums_slices_at_memory(self, tokens: int) -> bool:
         if ORDERED_SUMS or tokens > min(RED_MAX_TOKENS, SKINNY_MAX):
             return False

@@ -890,6 +890,62 @@ def test_rope_append_from_a_sum_that_it_leaves_zero(write_cache):
                       torch.zeros(2, 3, ld, device=DEV), True)
 
 
+@pytest.mark.parametrize("hq,hkv,hd,d", [(8, 2, 64, 256), (32, 8, 64, 2048), (3, 1, 128, 384), (24, 8, 128, 512),
+                                         (2, 1, 64, 200)])
+@pytest.mark.parametrize("pair", [256, 0])
+@pytest.mark.parametrize("write_cache", [True, False])
+def test_qkv_projection_that_rotates_and_appends_in_its_epilogue(hq, hkv, hd, d, pair, write_cache):
+    """Prompt tokens of three sequences (positions across page edges, pages in a scrambled order) through the
+    q|k|v projection whose epilogue rotates q and k and appends k and v, against the product in float32 followed
+    by the plain rotation; rows of pages that no token of the step owns stay untouched."""
+    from dlgo_b200.parts.rope import RotaryEmbedding
+    k = K()
+    n_cols = (hq + 2 * hkv) * hd
+    assert k.gemm_tc_rope_takes(n_cols, d, hq, hkv, hd, 64) and not k.gemm_tc_rope_takes(n_cols, d, hq, hkv, 96, 64)
+    assert not k.gemm_tc_rope_takes(n_cols, d, hq, hkv, hd, 32) and not k.gemm_tc_rope_takes(n_cols + hd, d, hq, hkv, hd, 64)
+    torch.manual_seed(hq + hd + d)
+    cos, sin = (t.to(DEV) for t in RotaryEmbedding(hd, hd, 10000.0, 600, "split_half").tables())
+    seqs = [(0, 70), (120, 141), (63, 2)]                          # (positions already held, new tokens)
+    T_ = sum(n for _, n in seqs)
+    pages_per = [(s + n + 63) // 64 for s, n in seqs]
+    n_pages = sum(pages_per) + 2
+    perm = torch.randperm(n_pages).tolist()
+    pt = torch.full((len(seqs) + 1, max(pages_per)), -1, dtype=torch.int32)
+    slots = [2, 0, 3]
+    for i, n in enumerate(pages_per):
+        for pg in range(n):
+            pt[slots[i], pg] = perm.pop()
+    pos = torch.tensor([s + j for s, n in seqs for j in range(n)], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([i for i, (s, n) in enumerate(seqs) for _ in range(n)], dtype=torch.int32, device=DEV)
+    x = (torch.randn(T_, d, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n_cols, d, device=DEV) * d ** -0.5).to(torch.bfloat16)
+    kp = torch.full((n_pages, hkv, 64, hd), 55.0, device=DEV, dtype=torch.bfloat16)
+    vp = torch.full((n_pages, hkv, 64, hd), 55.0, device=DEV, dtype=torch.bfloat16)
+    qkv = torch.full((T_, n_cols), 33.0, device=DEV, dtype=torch.bfloat16)
+    rope = k.rope_args(cos, sin, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), pt.to(DEV), kp, vp,
+                       hq, hkv, hd, write_cache)
+    k.gemm_tc_rope(x, w, qkv, pair, rope)
+    k.check_device_errors()
+    ref = (x.float().cpu() @ w.float().cpu().t()).view(T_, hq + 2 * hkv, hd)
+    freqs = P.rope_frequencies(hd, 10000.0, None)
+    rot = torch.stack([torch.stack([P.rope(ref[t, h], int(pos[t]), freqs) for h in range(hq + hkv)]) for t in range(T_)])
+    got = qkv.float().cpu().view(T_, hq + 2 * hkv, hd)
+    torch.testing.assert_close(got[:, :hq], rot[:, :hq], atol=2e-2, rtol=2e-2)
+    assert float((got[:, hq:] - 33.0).abs().max()) == 0.0         # the k and v columns are not written
+    written = torch.zeros(n_pages, 64, dtype=torch.bool)
+    kc, vc = kp.float().cpu(), vp.float().cpu()
+    for t in range(T_):
+        i, p_ = int(seq[t]), int(pos[t])
+        page = int(pt[slots[i], p_ // 64])
+        written[page, p_ % 64] = True
+        if write_cache:
+            torch.testing.assert_close(kc[page, :, p_ % 64], rot[t, hq:], atol=2e-2, rtol=2e-2)
+            torch.testing.assert_close(vc[page, :, p_ % 64], ref[t, hq + hkv:], atol=1e-2, rtol=1e-2)   # (rounded to bfloat16)
+    untouched = ~written if write_cache else torch.ones_like(written)
+    assert float((kc.transpose(1, 2)[untouched] - 55.0).abs().max()) == 0.0
+    assert float((vc.transpose(1, 2)[untouched] - 55.0).abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("hq,hkv,hd,S", [(8, 2, 64, 3), (32, 8, 64, 6), (3, 1, 128, 8), (8, 1, 64, 11), (12, 4, 128, 1)])
 @pytest.mark.parametrize("keys", [16, 32])
 def test_tensor_core_decode_attention_with_the_rotation_and_append_inside(hq, hkv, hd, S, keys):
