@@ -32,6 +32,11 @@ TARGET_CTAS = int(os.environ.get("DLGO_TC_TARGET_CTAS", 0))          # 0: the de
 # SM.  Measured (tokens a second, 148 / 222 / 296): 9.90K / 10.10K / 10.05K at batch 8, 1.32K / 1.40K /
 # 1.38K at batch 1; at batch 64, with tiles four times as wide, 49.0K / 42.9K / 39.7K.
 TARGET_CTAS_FEW = int(os.environ.get("DLGO_TC_TARGET_CTAS_FEW", 0))  # 0: one and a half times the SM count
+# ... and two per SM for a weight of 25 MB and more, whose K-slices are then still long (down at every size, q/k/v
+# and o_proj at the larger ones).  Measured (ms a step at batch 8, three against four CTAs per two SMs for those
+# weights): 0.760 -> 0.747 at Llama 3.2 1B sizes (0.698 -> 0.686 at batch 1), 1.827 -> 1.789 at 3B, 1.709 ->
+# 1.645 at 8B; for every weight (threshold 0) 3B loses what it gained.  The SwiGLU product keeps one CTA per tile.
+BIG_WEIGHT_BYTES = int(os.environ.get("DLGO_TC_BIG_WEIGHT_MB", 25)) << 20
 MAX_SPLITS = int(os.environ.get("DLGO_TC_MAX_SPLITS", 32))    # upper bound on K-slices per tile
 PAIR_TILE = int(os.environ.get("DLGO_TC_PAIR_TILE", 256))    # 0 switches the CTA-pair kernel off
 PAIR_MIN_TOKENS = int(os.environ.get("DLGO_TC_PAIR_MIN_TOKENS", 64))   # CTA pairs for more tokens than this
@@ -77,13 +82,17 @@ def sm_count(device: Optional[torch.device] = None) -> int:
     return n
 
 
-def skinny_shape(tokens: int, n: int, k: int, device: Optional[torch.device] = None) -> tuple[int, int]:
-    """(bn, splits) for ``tokens`` <= SKINNY_MAX against a weight [n, k]."""
+def skinny_shape(tokens: int, n: int, k: int, device: Optional[torch.device] = None,
+                 fused_epilogue: bool = False) -> tuple[int, int]:
+    """(bn, splits) for ``tokens`` <= SKINNY_MAX against a weight [n, k]; ``fused_epilogue``: the product's
+    epilogue is not a plain sum (SwiGLU), so K-slices would have to meet in a workspace first."""
     bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
     tiles = (n + K.TC_TILE_M - 1) // K.TC_TILE_M
     kblocks = (k + K.TC_TILE_K - 1) // K.TC_TILE_K
     if tokens <= 16:
-        target = TARGET_CTAS_FEW or (3 * sm_count(device)) // 2
+        big = n * k * 2 >= BIG_WEIGHT_BYTES and not fused_epilogue
+        few = 2 * sm_count(device) if big else (3 * sm_count(device)) // 2
+        target = TARGET_CTAS_FEW or few
     else:
         target = TARGET_CTAS or sm_count(device)
     splits = max(1, min(kblocks // MIN_KBLOCKS_PER_SPLIT, target // tiles)) if tiles < target else 1
@@ -110,7 +119,7 @@ class TensorCorePlan:
                 out = torch.empty((t, self.n), dtype=torch.bfloat16 if epilogue == K.EPI_STORE else torch.float32,
                                   device=x.device)
         if t <= SKINNY_MAX:
-            bn, splits = skinny_shape(t, self.n, self.k, self.weight.device)
+            bn, splits = skinny_shape(t, self.n, self.k, self.weight.device, self.swiglu)
             if not ORDERED_SUMS and epi == K.TC_ADD_F32 and splits > 1 and t <= RED_MAX_TOKENS:
                 return K.gemm_tc(self.weight, x, out, True, K.TC_RED_F32, bn, splits, static_operand=1)
             ws = cnt = None
