@@ -1175,6 +1175,21 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams&
       const int per = (kblocks + ks - 1) / ks;
       q.splits = (kblocks + per - 1) / per;      // no empty slices
     }
+  } else if (q.staged && p.epilogue == TC_ADD_F32) {
+    // A few more tiles than pairs (96 tiles are two rounds of 74 pairs, the second a third full): K-slices
+    // where they shorten the rounds by more than their extra epilogues cost (a tenth of a tile's time each).
+    static const int max_ks = [] { const char* e = getenv("DLGO_TC_PAIR_KSPLIT_MAX"); return e ? atoi(e) : 4; }();
+    const int kblocks = (p.K + TILE_K - 1) / TILE_K;
+    float best = (float)((tiles + pairs - 1) / pairs);
+    int best_ks = 1;
+    for (int ks = 2; ks <= max_ks && ks <= kblocks / 8; ++ks) {
+      const float cost = (float)((tiles * ks + pairs - 1) / pairs) / ks * (1.0f + 0.1f * (ks - 1) * 32.0f / kblocks);
+      if (cost < 0.9f * best) { best = cost; best_ks = ks; }
+    }
+    if (best_ks > 1) {
+      const int per = (kblocks + best_ks - 1) / best_ks;
+      q.splits = (kblocks + per - 1) / per;
+    }
   }
   if (tiles * q.splits < pairs) pairs = tiles * q.splits;
   launch_kernel_cluster(gemm_tc_pair_kernel<BN>, dim3(2 * pairs), dim3(TC_THREADS), SMEM, stream, dim3(2, 1, 1), ma, mb,
